@@ -1,0 +1,171 @@
+/*
+ * streamk_b200 — C ABI of the B200 (sm_100a) Stream-K GEMM library.
+ *
+ * Every function is extern "C", takes plain pointers and sizes, returns an int
+ * status (0 = SK_OK), never throws, never synchronises the device and — except
+ * where a comment says otherwise — never allocates.  All device pointers must
+ * belong to the device that is current on the calling thread.  `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).
+ *
+ * The reference (LeiWang1999/Stream-k.tvm) has no FFI: each script builds a TVM
+ * prim_func and calls `tl_mod(A, B, C)` with caller-owned, pre-zeroed CUDA
+ * tensors.  Each entry point below names the reference call it stands in for.
+ */
+#ifndef STREAMK_B200_H_
+#define STREAMK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+  SK_OK = 0,
+  SK_ERR_ARCH = 1,          /* device is not compute capability 10.x           */
+  SK_ERR_ALIGN = 2,         /* pointer / leading dimension alignment           */
+  SK_ERR_SHAPE = 3,         /* non-positive or unsupported extent              */
+  SK_ERR_WORKSPACE = 4,     /* workspace missing or too small                  */
+  SK_ERR_LAUNCH = 5,        /* CUDA runtime / driver error (see sk_last_cuda_error) */
+  SK_ERR_FIXUP_TIMEOUT = 6, /* device: a tile owner gave up waiting on a peer  */
+  SK_ERR_PIPE_TIMEOUT = 7,  /* device: an mbarrier wait ran out                */
+  SK_ERR_ARG = 8,           /* bad enum value / null pointer                   */
+  SK_ERR_LIMIT = 9          /* size beyond a stated maximum                    */
+};
+
+/* ---- enums ------------------------------------------------------------- */
+enum { SK_LAYOUT_NN = 0,      /* B is [K,N] row-major  (streamk_fp32.py:74, streamk_fp16_nn.py)   */
+       SK_LAYOUT_NT = 1,      /* B is [N,K] row-major  (streamk_fp16.py:128, streamk_fp16_nt.py)  */
+       SK_LAYOUT_LADDER = 2   /* B pre-laid-out by sk_prepack_ladder (streamk_fp16_ladder.py:153) */ };
+
+enum { SK_SCHED_STREAMK = 0,        /* every tile is Stream-K'd                                   */
+       SK_SCHED_HYBRID = 1,         /* reference order: SK tiles first, then DP waves
+                                       (streamk_fp16.py:98-113, 353-371)                          */
+       SK_SCHED_HYBRID_DP_FIRST = 2,/* same tile split, DP waves first, SK remainder last         */
+       SK_SCHED_DP = 3              /* plain data-parallel: one whole tile per CTA per wave       */ };
+
+enum { SK_FIXUP_ATOMIC = 0,        /* fp32 red.global.add into a self-cleaning workspace
+                                      (replaces T.atomic_addx2, streamk_fp16.py:248-255)          */
+       SK_FIXUP_BLOCK_REDUCE = 1   /* flag-synchronised, fixed-order, bitwise reproducible        */ };
+
+/* ---- problem description ------------------------------------------------ */
+typedef struct sk_problem {
+  int32_t M, N, K;
+  int32_t lda, ldb, ldc;      /* leading dimensions in elements (row-major)   */
+  int32_t layout;             /* SK_LAYOUT_*                                  */
+  int32_t schedule;           /* SK_SCHED_*                                   */
+  int32_t fixup;              /* SK_FIXUP_*                                   */
+  int32_t tile_n;             /* 0 = choose; fp16/w4a16: 128 or 256           */
+  int32_t num_sms;            /* 0 = all SMs of the device; else grid size    */
+  int32_t group_m;            /* 0 = choose; tile rasterisation group height  */
+  int32_t fixup_timeout_us;   /* 0 = default (2 s); bound of every device wait */
+  int32_t test_drop_flag_cta; /* -1 = off. Test only: this CTA never publishes
+                                 its block-reduce flag, so its tile owner runs
+                                 into the bounded wait and reports a timeout. */
+} sk_problem;
+
+/* Host scheduler result: the integers of streamk_fp16.py:83-113 plus the
+ * derived per-CTA split, exposed so callers and tests can inspect them.     */
+typedef struct sk_schedule_info {
+  int32_t tile_m, tile_n, tile_k;
+  int32_t tiles_m, tiles_n, total_tiles, iters_per_tile;
+  int32_t sk_tiles, dp_tiles;
+  int32_t grid;                /* persistent CTAs launched                    */
+  int32_t sk_iters_per_cta;    /* "streamk_full_tiles"  (floor)               */
+  int32_t sk_iters_rem;        /* "streamk_partial_tiles" (CTAs with one more)*/
+  int32_t dp_waves;            /* ceil(dp_tiles / grid)                       */
+  int32_t dp_first;
+  int32_t group_m;
+} sk_schedule_info;
+
+typedef struct sk_device_info {
+  int32_t cc_major, cc_minor;
+  int32_t num_sms;
+  int32_t max_smem_optin;
+  int64_t l2_bytes;
+  int64_t total_mem;
+} sk_device_info;
+
+typedef struct sk_status {
+  uint32_t code;     /* SK_OK, SK_ERR_FIXUP_TIMEOUT or SK_ERR_PIPE_TIMEOUT     */
+  uint32_t cta;      /* CTA that reported                                      */
+  uint32_t detail0;  /* fixup: tile id      pipe: barrier id                   */
+  uint32_t detail1;  /* fixup: awaited CTA  pipe: role                         */
+} sk_status;
+
+/* ---- library / device --------------------------------------------------- */
+const char* sk_version(void);
+const char* sk_status_string(int status);
+/* cudaError_t of the most recent SK_ERR_LAUNCH on this thread. */
+int sk_last_cuda_error(void);
+int sk_query(int device, sk_device_info* out);
+
+/* ---- scheduler (host only, no GPU needed) ------------------------------- */
+/* kernel_kind: 0 = fp32 SIMT tiles (64x64x16), 1 = fp16 / w4a16 UMMA tiles
+ * (128 x tile_n x 64).  Mirrors streamk_fp16.py:83-113 for SK_SCHED_HYBRID.  */
+int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* out);
+/* Iteration interval [begin,end) of CTA `cta` (streamk_fp16.py:176-181). */
+int sk_cta_interval(const sk_schedule_info* s, int cta, int64_t* begin, int64_t* end);
+/* Tile id -> (tile row, tile column) under the grouped rasterisation. */
+int sk_tile_coords(const sk_schedule_info* s, int tile, int* tile_m, int* tile_n);
+
+/* ---- workspace ----------------------------------------------------------- */
+/* One workspace serves every kernel of this library on one device; it holds
+ * the status word, per-CTA counters and flags, the zero-kept fp32 accumulation
+ * slots of the atomic fixup and the partial slots of the block-reduce fixup.
+ * Size depends only on the SM count.  The caller allocates it (cudaMalloc or a
+ * torch tensor), calls sk_workspace_init once, and must not share it between
+ * launches that can overlap on the GPU.  Kernels leave it clean; after a
+ * reported device error call sk_workspace_init again.                        */
+size_t sk_workspace_bytes(int num_sms);
+int sk_workspace_init(void* ws, size_t bytes, void* stream);
+/* Asynchronously copies the 16-byte status word into host_out (pinned memory
+ * recommended); valid after the stream is synchronised.                      */
+int sk_poll_status(const void* ws, sk_status* host_out, void* stream);
+
+/* ---- GEMM entry points --------------------------------------------------- */
+/* C[M,N] = A[M,K] . B, fp32 in / fp32 accumulate / fp32 out, CUDA-core FFMA
+ * (no TF32).  Replaces tl_mod(A, B, C) of streamk_fp32.py:57-202 (layout NN)
+ * and accepts NT as well.  C need not be zeroed.                             */
+int sk_gemm_f32(const sk_problem* p, const float* A, const float* B, float* C,
+                void* ws, size_t ws_bytes, void* stream);
+
+/* C[M,N] = A[M,K] . op(B), fp16 in / fp32 accumulate in TMEM / fp16 out on
+ * tcgen05 tensor cores.  Replaces tl_mod(A, B, C) of streamk_fp16.py:116-387
+ * (NT), streamk_fp16_nn.py (NN), streamk_fp16_block_reduce.py and
+ * streamk_fp16_ladder*.py (LADDER: B from sk_prepack_ladder).  A, B 16-byte
+ * aligned, lda/ldb multiples of 8.  C need not be zeroed.                    */
+int sk_gemm_f16(const sk_problem* p, const void* A, const void* B, void* C,
+                void* ws, size_t ws_bytes, void* stream);
+
+/* Bytes of the pre-laid-out image of an fp16 weight B[N,K]. */
+size_t sk_ladder_bytes(int N, int K);
+/* One-time re-layout of B[N,K] (row-major fp16, ldb elements) into the image
+ * the LADDER mainloop streams with 1-D bulk copies.  Replaces
+ * bitblas.ops.LadderPermutate on CPU (streamk_fp16_ladder.py:468-477).        */
+int sk_prepack_ladder(const void* B, int N, int K, int ldb, void* out, size_t out_bytes,
+                      void* stream);
+
+/* W4A16: C[M,N] = A[M,K] . W^T with W = (q - z) * s, q uint4, per-group z
+ * (uint4 stored as uint8) and fp16 s, group size 128 along K.
+ * Bytes of the packed image produced by sk_prepack_q4.                        */
+size_t sk_q4_bytes(int N, int K);
+/* qweight: int32 [N, K/8], nibble j of word w of row n is k = 8w + j (byte
+ * identical to the reference's int8 [N,K/2] low-nibble-first storage,
+ * streamk_fp16_ladder_block_reduce_q4.py:545-554).  scales fp16 [N, K/128] or
+ * NULL (=1), zeros uint8 [N, K/128] or NULL (=0).  Replaces LadderPermutate +
+ * LOP3Permutate on CPU (…q4.py:568-595).  K must be a multiple of 128.        */
+int sk_prepack_q4(const void* qweight, const void* scales, const void* zeros, int N, int K,
+                  void* out, size_t out_bytes, void* stream);
+/* W[N,K] fp16 = dequantised image (bit-exact (q - z) * s with fp16 rounding). */
+int sk_dequant_q4(const void* packed, int N, int K, void* W, int ldw, void* stream);
+/* Replaces tl_mod(A, QLB, C) of streamk_fp16_ladder_block_reduce_q4.py:143-599. */
+int sk_gemm_w4a16(const sk_problem* p, const void* A, const void* packed, void* C,
+                  void* ws, size_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STREAMK_B200_H_ */

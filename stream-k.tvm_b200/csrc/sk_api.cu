@@ -1,0 +1,197 @@
+// Library-level C ABI: version, device query, host scheduler, workspace.
+#include <string.h>
+
+#include "sk_common.cuh"
+
+static thread_local int g_last_cuda_error = 0;
+
+int sk_set_cuda_error(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return SK_ERR_LAUNCH;
+}
+
+extern "C" const char* sk_version(void) { return "streamk_b200 0.1 (sm_100a)"; }
+
+extern "C" int sk_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" const char* sk_status_string(int status) {
+  switch (status) {
+    case SK_OK: return "ok";
+    case SK_ERR_ARCH: return "device is not an sm_100 GPU";
+    case SK_ERR_ALIGN: return "pointer or leading dimension is not aligned as required";
+    case SK_ERR_SHAPE: return "unsupported problem shape";
+    case SK_ERR_WORKSPACE: return "workspace missing or too small";
+    case SK_ERR_LAUNCH: return "CUDA error (see sk_last_cuda_error)";
+    case SK_ERR_FIXUP_TIMEOUT: return "device: tile owner timed out waiting for a peer partial";
+    case SK_ERR_PIPE_TIMEOUT: return "device: pipeline barrier wait timed out";
+    case SK_ERR_ARG: return "invalid argument";
+    case SK_ERR_LIMIT: return "size beyond the supported maximum";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int sk_query(int device, sk_device_info* out) {
+  if (!out) return SK_ERR_ARG;
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  out->cc_major = prop.major;
+  out->cc_minor = prop.minor;
+  out->num_sms = prop.multiProcessorCount;
+  out->max_smem_optin = static_cast<int32_t>(prop.sharedMemPerBlockOptin);
+  out->l2_bytes = prop.l2CacheSize;
+  out->total_mem = static_cast<int64_t>(prop.totalGlobalMem);
+  return prop.major == 10 ? SK_OK : SK_ERR_ARCH;
+}
+
+// SM count of the current device (cached per device) and the grid bound asked for.
+int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out) {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  if (dev < 0 || dev >= 64) return SK_ERR_ARG;
+  if (cached[dev] == 0) {
+    int sms = 0, major = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    if (major != 10) return SK_ERR_ARCH;
+    cached[dev] = sms;
+  }
+  int sms = cached[dev];
+  *device_sms_out = sms;
+  if (p->num_sms > 0) {
+    if (p->num_sms > sms) return SK_ERR_LIMIT;  // co-residency of all CTAs is required
+    sms = p->num_sms;
+  }
+  *num_sms_out = sms;
+  return SK_OK;
+}
+
+int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
+                  SkSched* s) {
+  if (!p || num_sms <= 0) return SK_ERR_ARG;
+  if (p->M <= 0 || p->N <= 0 || p->K <= 0) return SK_ERR_SHAPE;
+  int tm, tn, tk;
+  if (kernel_kind == 0) {
+    tm = 64; tn = 64; tk = 16;
+  } else {
+    tm = 128; tk = 64;
+    tn = p->tile_n;
+    if (tn == 0) {
+      // Wide tiles halve shared-memory traffic per flop; use them once there is
+      // enough work to fill every SM twice over, else favour granularity.
+      const long long t256 = static_cast<long long>((p->M + 127) / 128) * ((p->N + 255) / 256);
+      tn = (t256 >= 2LL * num_sms) ? 256 : 128;
+    }
+    if (tn != 128 && tn != 256) return SK_ERR_ARG;
+  }
+  const long long tiles_m = (p->M + tm - 1) / tm;
+  const long long tiles_n = (p->N + tn - 1) / tn;
+  const long long total = tiles_m * tiles_n;
+  const long long I = (p->K + tk - 1) / tk;
+  if (total > (1LL << 30)) return SK_ERR_LIMIT;
+  const int P = num_sms;
+  long long T;
+  switch (p->schedule) {
+    case SK_SCHED_STREAMK: T = total; break;
+    case SK_SCHED_HYBRID:
+    case SK_SCHED_HYBRID_DP_FIRST:
+      // "Two-tile SK + DP": streamk_fp16.py:98-104
+      T = total % P;
+      if (total - T > P) T += P;
+      break;
+    case SK_SCHED_DP: T = 0; break;
+    default: return SK_ERR_ARG;
+  }
+  const long long S = T * I;
+  if (S >= (1LL << 31)) return SK_ERR_LIMIT;
+  const long long dp = total - T;
+  long long grid;
+  if (dp > 0) grid = dp < P && T == 0 ? dp : P;
+  else grid = S < P ? S : P;
+  if (grid < 1) grid = 1;
+  int gm = p->group_m;
+  if (gm <= 0) gm = tiles_m > 1 ? (tiles_m < 16 ? static_cast<int>(tiles_m) : 16) : 1;
+  if (gm > tiles_m) gm = static_cast<int>(tiles_m);
+
+  SkSched sc;
+  sc.tiles_m = static_cast<int>(tiles_m);
+  sc.tiles_n = static_cast<int>(tiles_n);
+  sc.total_tiles = static_cast<int>(total);
+  sc.iters_per_tile = static_cast<int>(I);
+  sc.sk_tiles = static_cast<int>(T);
+  sc.grid = static_cast<int>(grid);
+  sc.sk_f = static_cast<int>(S / grid);
+  sc.sk_r = static_cast<int>(S % grid);
+  sc.dp_first = p->schedule == SK_SCHED_HYBRID_DP_FIRST ? 1 : 0;
+  sc.group_m = gm;
+  if (s) *s = sc;
+  if (info) {
+    info->tile_m = tm; info->tile_n = tn; info->tile_k = tk;
+    info->tiles_m = sc.tiles_m; info->tiles_n = sc.tiles_n;
+    info->total_tiles = sc.total_tiles; info->iters_per_tile = sc.iters_per_tile;
+    info->sk_tiles = sc.sk_tiles; info->dp_tiles = static_cast<int>(dp);
+    info->grid = sc.grid;
+    info->sk_iters_per_cta = sc.sk_f; info->sk_iters_rem = sc.sk_r;
+    info->dp_waves = static_cast<int>((dp + grid - 1) / grid);
+    info->dp_first = sc.dp_first;
+    info->group_m = gm;
+  }
+  return SK_OK;
+}
+
+extern "C" int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms,
+                           sk_schedule_info* out) {
+  if (!out) return SK_ERR_ARG;
+  if (kernel_kind != 0 && kernel_kind != 1) return SK_ERR_ARG;
+  return sk_make_sched(p, kernel_kind, num_sms, out, nullptr);
+}
+
+static SkSched sched_from_info(const sk_schedule_info* i) {
+  SkSched s;
+  s.tiles_m = i->tiles_m; s.tiles_n = i->tiles_n; s.total_tiles = i->total_tiles;
+  s.iters_per_tile = i->iters_per_tile; s.sk_tiles = i->sk_tiles; s.grid = i->grid;
+  s.sk_f = i->sk_iters_per_cta; s.sk_r = i->sk_iters_rem; s.dp_first = i->dp_first;
+  s.group_m = i->group_m;
+  return s;
+}
+
+extern "C" int sk_cta_interval(const sk_schedule_info* info, int cta, int64_t* begin,
+                               int64_t* end) {
+  if (!info || !begin || !end || cta < 0 || cta >= info->grid) return SK_ERR_ARG;
+  const SkSched s = sched_from_info(info);
+  *begin = sk_cta_begin(s, cta);
+  *end = sk_cta_begin(s, cta + 1);
+  return SK_OK;
+}
+
+extern "C" int sk_tile_coords(const sk_schedule_info* info, int tile, int* tile_m, int* tile_n) {
+  if (!info || !tile_m || !tile_n || tile < 0 || tile >= info->total_tiles) return SK_ERR_ARG;
+  const SkSched s = sched_from_info(info);
+  sk_tile_mn(s, tile, *tile_m, *tile_n);
+  return SK_OK;
+}
+
+extern "C" size_t sk_workspace_bytes(int num_sms) {
+  if (num_sms <= 0) return 0;
+  return sk_ws_total_bytes(num_sms);
+}
+
+extern "C" int sk_workspace_init(void* ws, size_t bytes, void* stream) {
+  if (!ws) return SK_ERR_WORKSPACE;
+  if (bytes < SK_WS_HEADER) return SK_ERR_WORKSPACE;
+  cudaError_t e = cudaMemsetAsync(ws, 0, bytes, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
+}
+
+extern "C" int sk_poll_status(const void* ws, sk_status* host_out, void* stream) {
+  if (!ws || !host_out) return SK_ERR_ARG;
+  cudaError_t e = cudaMemcpyAsync(host_out, ws, sizeof(sk_status), cudaMemcpyDeviceToHost,
+                                  static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
+}

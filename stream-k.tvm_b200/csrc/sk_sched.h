@@ -1,0 +1,108 @@
+// Stream-K work decomposition shared by host and device code.
+//
+// Follows the host arithmetic of the reference (streamk_fp16.py:83-113) and the
+// per-CTA interval walk of its kernels (streamk_fp16.py:176-193, 274-277), with
+// the defects removed: no data-parallel pass is run when there are no
+// data-parallel tiles, and a ragged last data-parallel wave is allowed.
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define SK_HD __host__ __device__ __forceinline__
+#else
+#define SK_HD inline
+#endif
+
+struct SkSched {
+  int tiles_m, tiles_n, total_tiles, iters_per_tile;
+  int sk_tiles;   // tiles [0, sk_tiles) are Stream-K'd
+  int grid;       // persistent CTAs
+  int sk_f;       // iterations per CTA (floor)      "streamk_full_tiles"
+  int sk_r;       // CTAs that get one more          "streamk_partial_tiles"
+  int dp_first;   // 1: data-parallel waves before the Stream-K part
+  int group_m;    // rasterisation group height in tiles (1 = row-major)
+};
+
+struct SkSeg {
+  int tile;
+  int k0, k1;     // iteration range inside the tile, [k0, k1) of iters_per_tile
+};
+
+struct SkCursor {
+  int stage;      // 0 first phase, 1 second phase, 2 done
+  int it, it_end; // Stream-K iteration cursor
+  int dp_w;       // next data-parallel wave
+};
+
+// First iteration of CTA p: p*f + min(p, r)   (streamk_fp16.py:176-181)
+SK_HD int sk_cta_begin(const SkSched& s, int p) {
+  return p * s.sk_f + (p < s.sk_r ? p : s.sk_r);
+}
+
+// Inverse of sk_cta_begin: which CTA executes Stream-K iteration i.
+SK_HD int sk_cta_of(const SkSched& s, int i) {
+  const int big = s.sk_r * (s.sk_f + 1);
+  if (i < big) return i / (s.sk_f + 1);
+  return s.sk_r + (i - big) / s.sk_f;   // sk_f > 0 here, else i < big always
+}
+
+// Tile id -> tile coordinates.  group_m == 1 is the reference's row-major order
+// (streamk_fp16.py:192-193); group_m > 1 walks column-major inside bands of
+// group_m tile rows so that a wave of CTAs shares A and B panels in L2.
+SK_HD void sk_tile_mn(const SkSched& s, int tile, int& tm, int& tn) {
+  if (s.group_m <= 1) {
+    tm = tile / s.tiles_n;
+    tn = tile - tm * s.tiles_n;
+    return;
+  }
+  const int width = s.group_m * s.tiles_n;
+  const int g = tile / width;
+  const int first_m = g * s.group_m;
+  const int rem = s.tiles_m - first_m;
+  const int gsize = rem < s.group_m ? rem : s.group_m;
+  const int in_g = tile - g * width;
+  tn = in_g / gsize;
+  tm = first_m + (in_g - tn * gsize);
+}
+
+SK_HD void sk_cursor_init(const SkSched& s, int pid, SkCursor& c) {
+  c.stage = 0;
+  c.it = sk_cta_begin(s, pid);
+  c.it_end = sk_cta_begin(s, pid + 1);
+  c.dp_w = 0;
+}
+
+// Next work segment of CTA pid, or false when it has none left.
+SK_HD bool sk_next(const SkSched& s, int pid, SkCursor& c, SkSeg& seg) {
+  while (c.stage < 2) {
+    const bool sk_phase = (c.stage == 0) != (s.dp_first != 0);
+    if (sk_phase) {
+      if (c.it < c.it_end) {
+        const int I = s.iters_per_tile;
+        const int tile = c.it / I;
+        const int k0 = c.it - tile * I;
+        int k1 = k0 + (c.it_end - c.it);
+        if (k1 > I) k1 = I;
+        seg.tile = tile; seg.k0 = k0; seg.k1 = k1;
+        c.it += k1 - k0;
+        return true;
+      }
+    } else {
+      const int tile = s.sk_tiles + pid + c.dp_w * s.grid;
+      if (tile < s.total_tiles) {
+        seg.tile = tile; seg.k0 = 0; seg.k1 = s.iters_per_tile;
+        c.dp_w++;
+        return true;
+      }
+    }
+    c.stage++;
+  }
+  return false;
+}
+
+// CTAs that contribute to Stream-K tile `tile`: [first, last].
+SK_HD void sk_tile_ctas(const SkSched& s, int tile, int& first, int& last) {
+  const int I = s.iters_per_tile;
+  first = sk_cta_of(s, tile * I);
+  last = sk_cta_of(s, tile * I + I - 1);
+}

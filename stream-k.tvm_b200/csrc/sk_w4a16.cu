@@ -1,0 +1,456 @@
+// W4A16 Stream-K GEMM on sm_100a: C[M,N] = A[M,K] . W^T, W = (q - z) * s with
+// uint4 q, per-group (128 along K) uint4 zero-point z and fp16 scale s.
+//
+// Stands in for the TL kernel of streamk_fp16_ladder_block_reduce_q4.py:143-522
+// (int8-packed weight tile in shared memory, decode_i4u_to_f16 in registers, then
+// mma.sync) and for its CPU weight preparation (LadderPermutate + LOP3Permutate,
+// …q4.py:568-595).  The reference applies no scale or zero-point; with s = 1,
+// z = 0 this kernel computes the same C = A . unpack_u4(qB)^T.
+//
+// Packed image (sk_prepack_q4):
+//   nibble blocks  [n_block][k_block] of 128 rows x 64 K = 4096 B, stored as
+//                  [half h][row r][16 B]; the 16 B hold K = h*32 .. h*32+31 of row r
+//                  as four words, each word's eight nibbles in the order
+//                  e0 e2 e4 e6 e1 e3 e5 e7 so that (w >> 4i) & 0x000F000F yields
+//                  the fp16 pair (e(2i), e(2i+1)) in one lop3;
+//   group blocks   [n_block][group] = 128 fp16 scales + 128 uint8 zero-points (384 B).
+//
+// CTA roles (320 threads): warp 0 producer (TMA A tile + bulk copies of the packed
+// blocks), warp 1 MMA issuer, warps 2..5 epilogue, warps 6..9 dequantise the
+// packed block into the 128-byte-swizzled fp16 stage the UMMA descriptor reads.
+#include "sk_common.cuh"
+#include "sk_epilogue.cuh"
+
+namespace {
+
+using namespace skptx;
+
+constexpr int BM = SK_BM;
+constexpr int BN = 128;
+constexpr int BK = 64;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16384
+constexpr int Q_BLOCK_BYTES = BN * BK / 2;   // 4096
+constexpr int SZ_BLOCK_BYTES = BN * 2 + BN;  // 384
+constexpr int B_STAGE_BYTES = BN * BK * 2;   // 16384
+constexpr int LS = 8;                        // load stages (A tile + packed block)
+constexpr int BS = 3;                        // dequantised B stages
+constexpr int NUM_THREADS = 320;
+constexpr int DQ_THREADS = 128;
+constexpr int DQ_BAR_ID = 2;
+constexpr int TMEM_COLS = 2 * BN;
+constexpr int OFF_Q = LS * A_STAGE_BYTES;
+constexpr int OFF_SZ = OFF_Q + LS * Q_BLOCK_BYTES;
+constexpr int OFF_B = OFF_SZ + LS * SZ_BLOCK_BYTES;   // 166,912 = 163 * 1024
+constexpr int PIPE_BYTES = OFF_B + BS * B_STAGE_BYTES;
+constexpr int SMEM_BYTES = PIPE_BYTES + 1024 + 256;
+static_assert(OFF_B % 1024 == 0, "dequantised stages must start on a swizzle atom");
+
+struct Ctrl {
+  uint64_t load_full[LS];
+  uint64_t load_empty[LS];
+  uint64_t b_full[BS];
+  uint64_t b_empty[BS];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+  uint32_t bcast;
+};
+static_assert(sizeof(Ctrl) <= 256, "Ctrl must fit its reserved space");
+
+// Eight uint4 values of one packed word -> eight fp16 (q - z) * s, in K order.
+// zmagic = half2(1024 + z), s2 = half2(s, s).  The subtraction is exact and the
+// product is rounded once, exactly like ((q.half() - z.half()) * s) on the CPU.
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 zmagic, __half2 s2) {
+  constexpr uint32_t MASK = 0x000F000Fu;
+  constexpr uint32_t MAGIC = 0x64006400u;  // fp16 1024.0 in both halves
+  uint32_t t[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t sh = w >> (4 * i);
+    // (sh & MASK) | MAGIC in one lop3 (truth table 0xEA = (a & b) | c)
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t[i]) : "r"(sh), "r"(MASK), "r"(MAGIC));
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 x = *reinterpret_cast<const __half2*>(&t[i]);
+    const __half2 y = __hmul2(__hsub2(x, zmagic), s2);
+    o[i] = *reinterpret_cast<const uint32_t*>(&y);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __restrict__ qblocks,
+                     const uint8_t* __restrict__ szblocks, __half* __restrict__ C, const SkParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t sA = base;
+  const uint32_t sQ = base + OFF_Q;
+  const uint32_t sSZ = base + OFF_SZ;
+  const uint32_t sB = base + OFF_B;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + PIPE_BYTES);
+  volatile uint32_t* abort_flag = &ctrl->abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int pid = blockIdx.x;
+  const SkSched& s = p.sched;
+  const int kblocks = s.iters_per_tile;  // K / 64
+  const int groups = kblocks >> 1;       // K / 128
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < LS; ++i) {
+      mbar_init(smem_u32(&ctrl->load_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->load_empty[i]), 2);  // dequant warps + MMA commit
+    }
+    for (int i = 0; i < BS; ++i) {
+      mbar_init(smem_u32(&ctrl->b_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->b_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[i]), 4);
+    }
+    ctrl->abort = 0u;
+    ctrl->bcast = 0u;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tensormap(&tmA);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      SkCursor cur;
+      sk_cursor_init(s, pid, cur);
+      SkSeg seg;
+      int ls = 0;
+      uint32_t lph = 0;
+      bool ok = true;
+      while (ok && sk_next(s, pid, cur, seg)) {
+        int tm, tn;
+        sk_tile_mn(s, seg.tile, tm, tn);
+        const int m0 = tm * BM;
+        for (int k = seg.k0; k < seg.k1; ++k) {
+          const uint32_t full = smem_u32(&ctrl->load_full[ls]);
+          if (!sk_wait_bar(smem_u32(&ctrl->load_empty[ls]), lph ^ 1u, abort_flag, p, ls, 0)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(full, A_STAGE_BYTES + Q_BLOCK_BYTES + SZ_BLOCK_BYTES);
+          tma_load_2d(sA + ls * A_STAGE_BYTES, &tmA, full, k * BK, m0);
+          bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
+                       qblocks + (static_cast<size_t>(tn) * kblocks + k) * Q_BLOCK_BYTES,
+                       Q_BLOCK_BYTES, full);
+          bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
+                       szblocks + (static_cast<size_t>(tn) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
+                       SZ_BLOCK_BYTES, full);
+          if (++ls == LS) { ls = 0; lph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC = umma_idesc_f16(BM, BN, 0);
+      SkCursor cur;
+      sk_cursor_init(s, pid, cur);
+      SkSeg seg;
+      int ls = 0, bs = 0;
+      uint32_t lph = 0, bph = 0, nseg = 0;
+      bool ok = true;
+      while (ok && sk_next(s, pid, cur, seg)) {
+        const uint32_t buf = nseg & 1u;
+        const uint32_t acc_ph = (nseg >> 1) & 1u;
+        if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 32 + buf, 1))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int k = seg.k0; k < seg.k1; ++k) {
+          if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 8 + ls, 1) ||
+              !sk_wait_bar(smem_u32(&ctrl->b_full[bs]), bph, abort_flag, p, 16 + bs, 1)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = sA + ls * A_STAGE_BYTES;
+          const uint32_t b_addr = sB + bs * B_STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = umma_desc_sw128(a_addr + kk * 32, 16, 1024);
+            const uint64_t db = umma_desc_sw128(b_addr + kk * 32, 16, 1024);
+            umma_f16_ss(d_tmem, da, db, IDESC, (k > seg.k0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&ctrl->load_empty[ls]));
+          umma_commit(smem_u32(&ctrl->b_empty[bs]));
+          if (++ls == LS) { ls = 0; lph ^= 1u; }
+          if (++bs == BS) { bs = 0; bph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+        ++nseg;
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------- epilogue
+    sk_epilogue_loop<BN>(p, C, pid, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                         smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag);
+  } else {
+    // ------------------------------------------------------------- dequantise
+    const int r = (warp - 6) * 32 + lane;  // weight row inside the tile
+    SkCursor cur;
+    sk_cursor_init(s, pid, cur);
+    SkSeg seg;
+    int ls = 0, bs = 0;
+    uint32_t lph = 0, bph = 0;
+    bool dead = false;
+    while (sk_next(s, pid, cur, seg)) {
+      for (int k = seg.k0; k < seg.k1; ++k) {
+        if (!dead) {
+          if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 40 + ls, 3) ||
+              !sk_wait_bar(smem_u32(&ctrl->b_empty[bs]), bph ^ 1u, abort_flag, p, 48 + bs, 3))
+            dead = true;
+        }
+        if (!dead) {
+          const uint8_t* q = smem + OFF_Q + ls * Q_BLOCK_BYTES;
+          const uint8_t* sz = smem + OFF_SZ + ls * SZ_BLOCK_BYTES;
+          const uint4 w0 = *reinterpret_cast<const uint4*>(q + r * 16);
+          const uint4 w1 = *reinterpret_cast<const uint4*>(q + 2048 + r * 16);
+          const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
+          const uint32_t z = sz[256 + r];
+          const __half2 s2 = __half2half2(sc);
+          const uint32_t zm = 0x64006400u | z | (z << 16);
+          const __half2 zmagic = *reinterpret_cast<const __half2*>(&zm);
+          uint8_t* brow = smem + OFF_B + bs * B_STAGE_BYTES + r * 128;
+          const int sw = r & 7;
+          const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(brow + ((c ^ sw) << 4)) = dequant_word(words[c], zmagic, s2);
+          fence_proxy_async_smem();  // generic-proxy stores -> visible to the UMMA reads
+        }
+        named_bar_sync(DQ_BAR_ID, DQ_THREADS);
+        if (r == 0) {
+          mbar_arrive(smem_u32(&ctrl->b_full[bs]));
+          mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
+        }
+        if (++ls == LS) { ls = 0; lph ^= 1u; }
+        if (++bs == BS) { bs = 0; bph ^= 1u; }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ULL) __nanosleep(1000);
+    }
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- prepack / dequant
+// One thread per output word.  Source nibble e of an 8-element group sits at bits 4e.
+__global__ void prepack_q4_kernel(const uint32_t* __restrict__ qw, const __half* __restrict__ scales,
+                                  const uint8_t* __restrict__ zeros, int N, int K,
+                                  uint32_t* __restrict__ qout, uint8_t* __restrict__ szout,
+                                  int nblocks, int kblocks) {
+  const int kwords = K / 8;
+  const int groups = K / 128;
+  const size_t total_words = static_cast<size_t>(nblocks) * kblocks * 1024;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total_words;
+       i += stride) {
+    const size_t blk = i >> 10;
+    const int in_blk = static_cast<int>(i & 1023);
+    const int h = in_blk >> 9;
+    const int r = (in_blk >> 2) & 127;
+    const int j = in_blk & 3;
+    const int nb = static_cast<int>(blk / kblocks);
+    const int kb = static_cast<int>(blk - static_cast<size_t>(nb) * kblocks);
+    const int n = nb * 128 + r;
+    uint32_t out = 0u;
+    if (n < N) {
+      const uint32_t w = qw[static_cast<size_t>(n) * kwords + kb * 8 + h * 4 + j];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        out |= ((w >> (8 * t)) & 0xFu) << (4 * t);            // even elements 0,2,4,6
+        out |= ((w >> (8 * t + 4)) & 0xFu) << (4 * (t + 4));  // odd elements 1,3,5,7
+      }
+    }
+    qout[i] = out;
+  }
+  const size_t total_sz = static_cast<size_t>(nblocks) * groups * 128;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total_sz;
+       i += stride) {
+    const size_t gblk = i >> 7;
+    const int r = static_cast<int>(i & 127);
+    const int nb = static_cast<int>(gblk / groups);
+    const int g = static_cast<int>(gblk - static_cast<size_t>(nb) * groups);
+    const int n = nb * 128 + r;
+    __half sc = __float2half(0.f);
+    uint8_t z = 0;
+    if (n < N) {
+      sc = scales ? scales[static_cast<size_t>(n) * groups + g] : __float2half(1.f);
+      z = zeros ? static_cast<uint8_t>(zeros[static_cast<size_t>(n) * groups + g] & 0xF) : 0;
+    }
+    uint8_t* dst = szout + gblk * SZ_BLOCK_BYTES;
+    *reinterpret_cast<__half*>(dst + r * 2) = sc;
+    dst[256 + r] = z;
+  }
+}
+
+// One thread per packed word -> eight halves of W[n, k..k+7].
+__global__ void dequant_q4_kernel(const uint32_t* __restrict__ qblocks,
+                                  const uint8_t* __restrict__ szblocks, int N, int K,
+                                  __half* __restrict__ W, int ldw, int kblocks) {
+  const int groups = K / 128;
+  const size_t nb_used = (static_cast<size_t>(N) + 127) / 128;
+  const size_t total_words = nb_used * kblocks * 1024;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total_words;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t blk = i >> 10;
+    const int in_blk = static_cast<int>(i & 1023);
+    const int h = in_blk >> 9;
+    const int r = (in_blk >> 2) & 127;
+    const int j = in_blk & 3;
+    const int nb = static_cast<int>(blk / kblocks);
+    const int kb = static_cast<int>(blk - static_cast<size_t>(nb) * kblocks);
+    const int n = nb * 128 + r;
+    if (n >= N) continue;
+    const uint8_t* sz = szblocks + (static_cast<size_t>(nb) * groups + (kb >> 1)) * SZ_BLOCK_BYTES;
+    const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
+    const uint32_t z = sz[256 + r];
+    const uint32_t zm = 0x64006400u | z | (z << 16);
+    const uint4 o = dequant_word(qblocks[i], *reinterpret_cast<const __half2*>(&zm), __half2half2(sc));
+    __half* dst = W + static_cast<size_t>(n) * ldw + kb * 64 + h * 32 + j * 8;
+    if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      *reinterpret_cast<uint4*>(dst) = o;
+    } else {
+      const __half* hv = reinterpret_cast<const __half*>(&o);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst[e] = hv[e];
+    }
+  }
+}
+
+inline int q4_nblocks(int N) { return (N + 255) / 256 * 2; }
+
+}  // namespace
+
+int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                     uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
+
+extern "C" size_t sk_q4_bytes(int N, int K) {
+  if (N <= 0 || K <= 0 || (K % 128) != 0) return 0;
+  const size_t nb = q4_nblocks(N);
+  return nb * (K / 64) * Q_BLOCK_BYTES + nb * (K / 128) * SZ_BLOCK_BYTES;
+}
+
+extern "C" int sk_prepack_q4(const void* qweight, const void* scales, const void* zeros, int N,
+                             int K, void* out, size_t out_bytes, void* stream) {
+  if (!qweight || !out) return SK_ERR_ARG;
+  if (N <= 0 || K <= 0 || (K % 128) != 0) return SK_ERR_SHAPE;
+  if (out_bytes < sk_q4_bytes(N, K)) return SK_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(out) & 15u) || (reinterpret_cast<uintptr_t>(qweight) & 3u))
+    return SK_ERR_ALIGN;
+  const int nb = q4_nblocks(N), kb = K / 64;
+  uint8_t* o = static_cast<uint8_t*>(out);
+  uint8_t* sz = o + static_cast<size_t>(nb) * kb * Q_BLOCK_BYTES;
+  const size_t total = static_cast<size_t>(nb) * kb * 1024;
+  const int grid = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  prepack_q4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(qweight), static_cast<const __half*>(scales),
+      static_cast<const uint8_t*>(zeros), N, K, reinterpret_cast<uint32_t*>(o), sz, nb, kb);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
+}
+
+extern "C" int sk_dequant_q4(const void* packed, int N, int K, void* W, int ldw, void* stream) {
+  if (!packed || !W) return SK_ERR_ARG;
+  if (N <= 0 || K <= 0 || (K % 128) != 0 || ldw < K) return SK_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(packed) & 15u) return SK_ERR_ALIGN;
+  const int nb = q4_nblocks(N), kb = K / 64;
+  const uint8_t* o = static_cast<const uint8_t*>(packed);
+  const uint8_t* sz = o + static_cast<size_t>(nb) * kb * Q_BLOCK_BYTES;
+  const size_t total = (static_cast<size_t>(N) + 127) / 128 * kb * 1024;
+  const int grid = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  dequant_q4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(o), sz, N, K, static_cast<__half*>(W), ldw, kb);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
+}
+
+extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* packed, void* C,
+                             void* ws, size_t ws_bytes, void* stream) {
+  if (!prob || !A || !packed || !C) return SK_ERR_ARG;
+  if (prob->fixup != SK_FIXUP_ATOMIC && prob->fixup != SK_FIXUP_BLOCK_REDUCE) return SK_ERR_ARG;
+  if (prob->tile_n != 0 && prob->tile_n != BN) return SK_ERR_ARG;
+  int num_sms = 0, dev_sms = 0;
+  int st = sk_resolve_grid(prob, &num_sms, &dev_sms);
+  if (st != SK_OK) return st;
+  const int M = prob->M, N = prob->N, K = prob->K;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0) return SK_ERR_SHAPE;
+  if (prob->lda < K || prob->ldc < N) return SK_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(packed) & 15u))
+    return SK_ERR_ALIGN;
+  if ((prob->lda & 7) != 0 || (reinterpret_cast<uintptr_t>(C) & 1u) != 0) return SK_ERR_ALIGN;
+  if (!ws || ws_bytes < sk_ws_total_bytes(dev_sms)) return SK_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return SK_ERR_ALIGN;
+
+  sk_problem q = *prob;
+  q.tile_n = BN;
+  SkParams p;
+  memset(&p, 0, sizeof(p));
+  st = sk_make_sched(&q, 1, num_sms, nullptr, &p.sched);
+  if (st != SK_OK) return st;
+  p.M = M; p.N = N; p.K = K;
+  p.lda = prob->lda; p.ldb = 0; p.ldc = prob->ldc;
+  p.fixup = prob->fixup;
+  p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
+  p.drop_flag_cta = prob->test_drop_flag_cta;
+  p.timeout_ns = (prob->fixup_timeout_us > 0 ? static_cast<unsigned long long>(prob->fixup_timeout_us)
+                                             : 2000000ULL) * 1000ULL;
+  p.ws = sk_ws_carve(ws, dev_sms);
+
+  CUtensorMap tmA;
+  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, BM);
+  if (st != SK_OK) return st;
+  const int nb = q4_nblocks(N), kb = K / 64;
+  const uint8_t* qb = static_cast<const uint8_t*>(packed);
+  const uint8_t* sz = qb + static_cast<size_t>(nb) * kb * Q_BLOCK_BYTES;
+
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(sk_gemm_w4a16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    attr_set[dev & 63] = true;
+  }
+  sk_gemm_w4a16_kernel<<<p.sched.grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+      tmA, qb, sz, static_cast<__half*>(C), p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
+}

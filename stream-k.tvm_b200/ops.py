@@ -1,0 +1,389 @@
+"""Python operator surface: the reference's entry points, backed by the C ABI.
+
+The reference (LeiWang1999/Stream-k.tvm) has no importable API; each script
+builds `tl_matmul_streamk(...)` and calls `tl_mod(A, B, C)` on CUDA tensors
+(streamk_fp32.py:57-202, streamk_fp16.py:116-387, streamk_fp16_ladder.py,
+streamk_fp16_ladder_block_reduce_q4.py).  The functions here keep those names
+and argument meanings (A [M,K]; B [K,N] for NN, [N,K] for NT; C [M,N]) but
+return a fresh C instead of accumulating into a pre-zeroed one.
+
+Everything runs on the GPU through libstreamk_b200.so; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib as L
+
+__all__ = [
+    "streamk_fp32", "streamk_fp16_nn", "streamk_fp16_nt", "streamk_fp16_atomic",
+    "streamk_fp16_block_reduce", "ladder_prepack", "streamk_fp16_ladder",
+    "streamk_fp16_ladder_block_reduce", "q4_prepack", "dequant_w4",
+    "streamk_fp16_ladder_block_reduce_q4", "schedule_info", "check_status",
+    "reset_workspace", "device_info", "LadderWeight", "PackedQ4", "StreamKError",
+]
+
+StreamKError = L.StreamKError
+GROUP_SIZE = 128
+
+
+# --------------------------------------------------------------------------- state
+class _Workspace:
+    __slots__ = ("buf", "nbytes", "status_host")
+
+    def __init__(self, device: torch.device, stream_ptr: int):
+        lib = L.load()
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.nbytes = int(lib.sk_workspace_bytes(sms))
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        L.check(lib.sk_workspace_init(self.buf.data_ptr(), self.nbytes, stream_ptr),
+                "sk_workspace_init")
+
+
+_workspaces: dict[tuple[int, int], _Workspace] = {}
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _workspace(device: torch.device) -> _Workspace:
+    """One workspace per (device, stream): launches that may overlap never share one."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           _stream_ptr(device))
+    ws = _workspaces.get(key)
+    if ws is None:
+        with torch.cuda.device(device):
+            ws = _Workspace(device, key[1])
+        _workspaces[key] = ws
+    return ws
+
+
+def reset_workspace(device=None) -> None:
+    """Re-zero the workspace of the current stream (needed after a device-reported error)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspace(device)
+    with torch.cuda.device(device):
+        L.check(L.load().sk_workspace_init(ws.buf.data_ptr(), ws.nbytes, _stream_ptr(device)),
+                "sk_workspace_init")
+
+
+def check_status(device=None) -> None:
+    """Synchronise the current stream and raise if a kernel reported a timeout."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspace(device)
+    lib = L.load()
+    with torch.cuda.device(device):
+        st = C.cast(ws.status_host.data_ptr(), C.POINTER(L.SkStatus))
+        L.check(lib.sk_poll_status(ws.buf.data_ptr(), st, _stream_ptr(device)), "sk_poll_status")
+        torch.cuda.current_stream(device).synchronize()
+    code, cta, d0, d1 = (int(x) & 0xFFFFFFFF for x in ws.status_host.tolist())
+    if code != L.SK_OK:
+        reset_workspace(device)
+        raise StreamKError(code, "device status", f"[cta {cta}, detail {d0}, {d1}]")
+
+
+def device_info(device: int = 0) -> dict:
+    info = L.SkDeviceInfo()
+    st = L.load().sk_query(device, C.byref(info))
+    d = {n: getattr(info, n) for n, _ in info._fields_}
+    d["status"] = st
+    return d
+
+
+# --------------------------------------------------------------------------- helpers
+def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, tile_n, num_sms, group_m,
+             timeout_us, drop_flag_cta) -> L.SkProblem:
+    if schedule not in L.SCHEDULES:
+        raise ValueError(f"schedule must be one of {sorted(L.SCHEDULES)}, got {schedule!r}")
+    if fixup not in L.FIXUPS:
+        raise ValueError(f"fixup must be one of {sorted(L.FIXUPS)}, got {fixup!r}")
+    return L.SkProblem(M=M, N=N, K=K, lda=lda, ldb=ldb, ldc=ldc, layout=L.LAYOUTS[layout],
+                       schedule=L.SCHEDULES[schedule], fixup=L.FIXUPS[fixup],
+                       tile_n=int(tile_n or 0), num_sms=int(num_sms or 0),
+                       group_m=int(group_m or 0), fixup_timeout_us=int(timeout_us or 0),
+                       test_drop_flag_cta=int(drop_flag_cta))
+
+
+def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "hybrid",
+                  tile_n: int | None = None, num_sms: int = 148, group_m: int | None = None) -> dict:
+    """Host scheduler integers (streamk_fp16.py:83-113) for a problem; needs no GPU."""
+    prob = _problem(M, N, K, K, K, N, "nt", schedule, "atomic", tile_n, 0, group_m, 0, -1)
+    info = L.SkScheduleInfo()
+    L.check(L.load().sk_schedule(C.byref(prob), 0 if kind == "f32" else 1, num_sms, C.byref(info)),
+            "sk_schedule")
+    return info.as_dict()
+
+
+def _check_matrix(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+
+
+def _rowmajor(t: torch.Tensor) -> torch.Tensor:
+    # The reference asserts contiguity (triton_impl.py:199-201); row-major views
+    # with a padded leading dimension are accepted here as well.
+    if t.stride(1) == 1 and t.stride(0) >= t.shape[1]:
+        return t
+    return t.contiguous()
+
+
+def _out(out, M, N, dtype, device):
+    if out is None:
+        return torch.empty((M, N), dtype=dtype, device=device)
+    if out.shape != (M, N) or out.dtype != dtype or out.device != device or out.stride(1) != 1:
+        raise ValueError("out must be a row-major [M,N] tensor of the result dtype on A's device")
+    return out
+
+
+def _pad_k8(t: torch.Tensor, k_dim: int) -> torch.Tensor:
+    """TMA needs 16-byte row pitches: pad the K extent of an fp16 operand to a multiple of 8."""
+    k = t.shape[k_dim]
+    pad = (-k) % 8
+    if pad == 0:
+        return t
+    spec = (0, pad) if k_dim == 1 else (0, 0, 0, pad)
+    return torch.nn.functional.pad(t, spec)
+
+
+def _aligned16(t: torch.Tensor) -> torch.Tensor:
+    if t.data_ptr() % 16 == 0 and t.stride(0) % 8 == 0:
+        return t
+    n = torch.empty((t.shape[0], (t.shape[1] + 7) // 8 * 8), dtype=t.dtype, device=t.device)
+    n[:, : t.shape[1]].copy_(t)
+    return n[:, : t.shape[1]]
+
+
+# --------------------------------------------------------------------------- fp32
+def streamk_fp32(A: torch.Tensor, B: torch.Tensor, *, fixup: str = "atomic",
+                 schedule: str = "hybrid", trans_b: bool = False, num_sms: int | None = None,
+                 group_m: int | None = None, out: torch.Tensor | None = None,
+                 timeout_us: int | None = None, _drop_flag_cta: int = -1) -> torch.Tensor:
+    """C = A @ B in fp32 (FFMA, no TF32).  A [M,K]; B [K,N] (or [N,K] with trans_b).
+
+    Mirrors `tl_matmul_streamk(..., "float32", "float32", "float32", ...)` of
+    streamk_fp32.py:57-202.  `schedule="hybrid"` is the reference's split.
+    """
+    _check_matrix("A", A, torch.float32)
+    _check_matrix("B", B, torch.float32)
+    A = _rowmajor(A)
+    B = _rowmajor(B)
+    M, K = A.shape
+    if trans_b:
+        N, Kb = B.shape
+    else:
+        Kb, N = B.shape
+    if K != Kb:
+        raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} B {tuple(B.shape)}")
+    Cout = _out(out, M, N, torch.float32, A.device)
+    prob = _problem(M, N, K, A.stride(0), B.stride(0), Cout.stride(0), "nt" if trans_b else "nn",
+                    schedule, fixup, 0, num_sms, group_m, timeout_us, _drop_flag_cta)
+    with torch.cuda.device(A.device):
+        ws = _workspace(A.device)
+        L.check(L.load().sk_gemm_f32(C.byref(prob), A.data_ptr(), B.data_ptr(), Cout.data_ptr(),
+                                     ws.buf.data_ptr(), ws.nbytes, _stream_ptr(A.device)),
+                "sk_gemm_f32")
+    return Cout
+
+
+# --------------------------------------------------------------------------- fp16
+def _gemm_f16(A, B, layout, *, fixup, schedule, tile_n, num_sms, group_m, out, timeout_us,
+              _drop_flag_cta, N=None):
+    _check_matrix("A", A, torch.float16)
+    M, K = A.shape
+    if layout == "ladder":
+        if not isinstance(B, LadderWeight):
+            raise TypeError("B must come from ladder_prepack()")
+        if B.K != K:
+            raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} weight K={B.K}")
+        N = B.N
+        Bt, ldb = B.data, 0
+        A = _aligned16(_rowmajor(_pad_k8(A, 1)))
+    else:
+        _check_matrix("B", B, torch.float16)
+        if layout == "nt":
+            N, Kb = B.shape
+        else:
+            Kb, N = B.shape
+        if K != Kb:
+            raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} B {tuple(B.shape)}")
+        A = _aligned16(_rowmajor(_pad_k8(A, 1)))
+        if layout == "nt":
+            Bt = _aligned16(_rowmajor(_pad_k8(B, 1)))
+        else:
+            # NN: rows of B are K; the N pitch must be a multiple of 8 halves
+            Bt = _aligned16(_rowmajor(_pad_k8(B, 0)))
+        ldb = Bt.stride(0)
+    Cout = _out(out, M, N, torch.float16, A.device)
+    prob = _problem(M, N, A.shape[1], A.stride(0), ldb, Cout.stride(0), layout, schedule, fixup,
+                    tile_n, num_sms, group_m, timeout_us, _drop_flag_cta)
+    with torch.cuda.device(A.device):
+        ws = _workspace(A.device)
+        L.check(L.load().sk_gemm_f16(C.byref(prob), A.data_ptr(), Bt.data_ptr(), Cout.data_ptr(),
+                                     ws.buf.data_ptr(), ws.nbytes, _stream_ptr(A.device)),
+                "sk_gemm_f16")
+    return Cout
+
+
+def streamk_fp16_nt(A, B, *, fixup="atomic", schedule="hybrid", tile_n=None, num_sms=None,
+                    group_m=None, out=None, timeout_us=None, _drop_flag_cta=-1):
+    """C = A @ B.T, fp16 in, fp32 accumulate, fp16 out.  A [M,K], B [N,K].
+
+    Mirrors `tl_matmul_streamk(M, N, K, streamk_tiles, "float16", "float16", ...)` +
+    `tl_mod(A, B, C)` of streamk_fp16.py:116-387 and streamk_fp16_nt.py:57-192.
+    """
+    return _gemm_f16(A, B, "nt", fixup=fixup, schedule=schedule, tile_n=tile_n, num_sms=num_sms,
+                     group_m=group_m, out=out, timeout_us=timeout_us, _drop_flag_cta=_drop_flag_cta)
+
+
+def streamk_fp16_nn(A, B, *, fixup="atomic", schedule="hybrid", tile_n=None, num_sms=None,
+                    group_m=None, out=None, timeout_us=None, _drop_flag_cta=-1):
+    """C = A @ B, fp16.  A [M,K], B [K,N]  (streamk_fp16_nn.py:57-177)."""
+    return _gemm_f16(A, B, "nn", fixup=fixup, schedule=schedule, tile_n=tile_n, num_sms=num_sms,
+                     group_m=group_m, out=out, timeout_us=timeout_us, _drop_flag_cta=_drop_flag_cta)
+
+
+def streamk_fp16_atomic(A, B, **kw):
+    """NT GEMM with the order-nondeterministic fp32 red.global.add fixup
+    (the role of T.atomic_addx2 in streamk_fp16.py:248-255)."""
+    return streamk_fp16_nt(A, B, fixup="atomic", **kw)
+
+
+def streamk_fp16_block_reduce(A, B, **kw):
+    """NT GEMM with the deterministic flag-synchronised fixup.  Keeps the entry name of
+    streamk_fp16_block_reduce.py; the intra-CTA split-K it performs there is subsumed by
+    TMEM accumulation, the name now denotes the bitwise-reproducible cross-CTA reduction."""
+    return streamk_fp16_nt(A, B, fixup="block_reduce", **kw)
+
+
+@dataclass
+class LadderWeight:
+    """Weight pre-laid-out by ladder_prepack (opaque image + logical shape)."""
+    data: torch.Tensor
+    N: int
+    K: int
+
+
+def ladder_prepack(B: torch.Tensor) -> LadderWeight:
+    """Re-lay B [N,K] fp16 into the streaming image of the ladder mainloop.
+
+    Replaces `bitblas.ops.LadderPermutate(...)(B.cpu())` (streamk_fp16_ladder.py:468-477);
+    runs on the GPU."""
+    _check_matrix("B", B, torch.float16)
+    B = _rowmajor(B)
+    N, K = B.shape
+    lib = L.load()
+    nbytes = int(lib.sk_ladder_bytes(N, K))
+    out = torch.empty(nbytes, dtype=torch.uint8, device=B.device)
+    with torch.cuda.device(B.device):
+        L.check(lib.sk_prepack_ladder(B.data_ptr(), N, K, B.stride(0), out.data_ptr(), nbytes,
+                                      _stream_ptr(B.device)), "sk_prepack_ladder")
+    return LadderWeight(out, N, K)
+
+
+def streamk_fp16_ladder(A, LB: LadderWeight, *, fixup="atomic", schedule="hybrid", tile_n=None,
+                        num_sms=None, group_m=None, out=None, timeout_us=None, _drop_flag_cta=-1):
+    """C = A @ W.T with W pre-laid-out (streamk_fp16_ladder.py:137-486)."""
+    return _gemm_f16(A, LB, "ladder", fixup=fixup, schedule=schedule, tile_n=tile_n,
+                     num_sms=num_sms, group_m=group_m, out=out, timeout_us=timeout_us,
+                     _drop_flag_cta=_drop_flag_cta)
+
+
+def streamk_fp16_ladder_block_reduce(A, LB: LadderWeight, **kw):
+    """Ladder path with the deterministic fixup (streamk_fp16_ladder_block_reduce.py)."""
+    return streamk_fp16_ladder(A, LB, fixup="block_reduce", **kw)
+
+
+# --------------------------------------------------------------------------- W4A16
+@dataclass
+class PackedQ4:
+    """uint4 weight + group scales/zeros packed by q4_prepack (opaque image + shape)."""
+    data: torch.Tensor
+    N: int
+    K: int
+
+
+def q4_prepack(qweight: torch.Tensor, scales: torch.Tensor | None = None,
+               zeros: torch.Tensor | None = None, group_size: int = GROUP_SIZE) -> PackedQ4:
+    """Pack uint4 weights for the W4A16 mainloop.
+
+    qweight: int32 [N, K/8] (nibble j of word w = element 8w+j) or int8/uint8 [N, K/2]
+    (low nibble = even k, the reference's storage, …_q4.py:28-30,545-554).
+    scales: fp16 [N, K/128] or None (=1).  zeros: uint8 [N, K/128] in 0..15 or None (=0).
+    With scales=None, zeros=None the GEMM reproduces the reference's `A @ unpack(qB).T`.
+    Replaces LadderPermutate + LOP3Permutate on the CPU (…_q4.py:568-595).
+    """
+    if group_size != GROUP_SIZE:
+        raise ValueError("group_size must be 128")
+    if not qweight.is_cuda:
+        raise ValueError("qweight must be a CUDA tensor (this library has no CPU path)")
+    if qweight.dtype in (torch.int8, torch.uint8):
+        N, Kh = qweight.shape
+        K = Kh * 2
+    elif qweight.dtype == torch.int32:
+        N, Kw = qweight.shape
+        K = Kw * 8
+    else:
+        raise TypeError("qweight must be int32 [N,K/8] or int8/uint8 [N,K/2]")
+    if K % GROUP_SIZE:
+        raise ValueError("K must be a multiple of 128")
+    qweight = qweight.contiguous()
+    G = K // GROUP_SIZE
+    sp = zp = None
+    if scales is not None:
+        if scales.shape != (N, G) or scales.dtype != torch.float16:
+            raise ValueError(f"scales must be fp16 [{N},{G}]")
+        scales = scales.contiguous(); sp = scales.data_ptr()
+    if zeros is not None:
+        if zeros.shape != (N, G) or zeros.dtype != torch.uint8:
+            raise ValueError(f"zeros must be uint8 [{N},{G}]")
+        zeros = zeros.contiguous(); zp = zeros.data_ptr()
+    lib = L.load()
+    nbytes = int(lib.sk_q4_bytes(N, K))
+    out = torch.empty(nbytes, dtype=torch.uint8, device=qweight.device)
+    with torch.cuda.device(qweight.device):
+        L.check(lib.sk_prepack_q4(qweight.data_ptr(), sp, zp, N, K, out.data_ptr(), nbytes,
+                                  _stream_ptr(qweight.device)), "sk_prepack_q4")
+    return PackedQ4(out, N, K)
+
+
+def dequant_w4(QLB: PackedQ4) -> torch.Tensor:
+    """W [N,K] fp16 = (q - z) * s, bit-exact with the fp16 expression evaluated on the CPU."""
+    W = torch.empty((QLB.N, QLB.K), dtype=torch.float16, device=QLB.data.device)
+    with torch.cuda.device(W.device):
+        L.check(L.load().sk_dequant_q4(QLB.data.data_ptr(), QLB.N, QLB.K, W.data_ptr(),
+                                       W.stride(0), _stream_ptr(W.device)), "sk_dequant_q4")
+    return W
+
+
+def streamk_fp16_ladder_block_reduce_q4(A, QLB: PackedQ4, *, fixup="block_reduce",
+                                        schedule="hybrid", tile_n=None, num_sms=None,
+                                        group_m=None, out=None, timeout_us=None,
+                                        _drop_flag_cta=-1):
+    """W4A16: C = A @ ((q - z) * s).T, fp16 activations, uint4 weights.
+
+    Mirrors `tl_mod(A, QLB, C)` of streamk_fp16_ladder_block_reduce_q4.py:143-599."""
+    _check_matrix("A", A, torch.float16)
+    if not isinstance(QLB, PackedQ4):
+        raise TypeError("QLB must come from q4_prepack()")
+    M, K = A.shape
+    if K != QLB.K:
+        raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} weight K={QLB.K}")
+    A = _aligned16(_rowmajor(A))
+    Cout = _out(out, M, QLB.N, torch.float16, A.device)
+    prob = _problem(M, QLB.N, K, A.stride(0), 0, Cout.stride(0), "nt", schedule, fixup, tile_n,
+                    num_sms, group_m, timeout_us, _drop_flag_cta)
+    with torch.cuda.device(A.device):
+        ws = _workspace(A.device)
+        L.check(L.load().sk_gemm_w4a16(C.byref(prob), A.data_ptr(), QLB.data.data_ptr(),
+                                       Cout.data_ptr(), ws.buf.data_ptr(), ws.nbytes,
+                                       _stream_ptr(A.device)), "sk_gemm_w4a16")
+    return Cout
