@@ -93,9 +93,13 @@ def load(path: str | None = None):
     global _lib
     if _lib is not None:
         return _lib
-    path = path or os.environ.get("STREAMK_B200_LIB") or _build.lib_path()
-    if os.environ.get("STREAMK_B200_BUILD") == "1" or not os.path.exists(path):
-        path = _build.build()
+    explicit = path or os.environ.get("STREAMK_B200_LIB")
+    if explicit:
+        path = explicit   # a named library that is absent is an error (CDLL raises OSError)
+    else:
+        path = _build.lib_path()
+        if os.environ.get("STREAMK_B200_BUILD") == "1" or not os.path.exists(path):
+            path = _build.build()   # compiles the CUDA sources; raises if nvcc fails
     lib = C.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if the symbol is missing: fail loudly

@@ -1,0 +1,104 @@
+"""The library's host scheduler (C, sk_schedule) against the CPU oracle."""
+import ctypes as C
+import random
+
+import pytest
+
+import oracle
+
+
+def _sched(lib, M, N, K, kind, schedule, P, tile_n=0, group_m=0):
+    from streamk_b200 import _lib as L
+    prob = L.SkProblem(M=M, N=N, K=K, lda=K, ldb=K, ldc=N, layout=1, schedule=L.SCHEDULES[schedule],
+                       fixup=0, tile_n=tile_n, num_sms=0, group_m=group_m, fixup_timeout_us=0,
+                       test_drop_flag_cta=-1)
+    info = L.SkScheduleInfo()
+    st = lib.sk_schedule(C.byref(prob), kind, P, C.byref(info))
+    assert st == 0, st
+    return info.as_dict(), info
+
+
+def test_hybrid_equals_reference_formula(lib):
+    rnd = random.Random(0)
+    for _ in range(300):
+        M, N, K = rnd.randint(1, 9000), rnd.randint(1, 30000), rnd.randint(1, 12000)
+        P = rnd.choice([1, 2, 3, 5, 108, 132, 148])
+        tn = rnd.choice([128, 256])
+        d, _ = _sched(lib, M, N, K, 1, "hybrid", P, tile_n=tn)
+        r = oracle.reference_schedule(M, N, K, 128, tn, 64, P)
+        assert d["total_tiles"] == r["total_tiles"]
+        assert d["iters_per_tile"] == r["iters_per_tile"]
+        assert d["sk_tiles"] == r["streamk_tiles"]
+        assert d["dp_tiles"] == r["blocking_tiles"]
+        if d["grid"] == P:   # the library shrinks the grid when there is less work than CTAs
+            assert d["sk_iters_per_cta"] == r["streamk_full_tiles"]
+            assert d["sk_iters_rem"] == r["streamk_partial_tiles"]
+        else:
+            assert r["streamk_iters"] < P and d["grid"] == max(r["streamk_iters"], 1)
+
+
+def test_worked_values_for_148_sms(lib):
+    # shape -> (tiles, iters/tile, SK tiles, DP tiles, f, r) for 128x128x64 tiles on 148 SMs
+    table = {
+        (384, 384, 8192, 128): (9, 128, 9, 0, 7, 116),
+        (128, 4096, 4096, 128): (32, 64, 32, 0, 13, 124),
+        (128, 11008, 4096, 128): (86, 64, 86, 0, 37, 28),
+        (128, 4096, 11008, 128): (32, 172, 32, 0, 37, 28),
+        (128, 12288, 4096, 128): (96, 64, 96, 0, 41, 76),
+        (256, 11008, 4096, 128): (172, 64, 24, 148, 10, 56),
+        (256, 12288, 4096, 128): (192, 64, 44, 148, 19, 4),
+        (8192, 28672, 8192, 256): (7168, 128, 212, 6956, 183, 52),
+        (8192, 3584, 8192, 256): (896, 128, 156, 740, 134, 136),
+    }
+    for (M, N, K, tn), want in table.items():
+        d, _ = _sched(lib, M, N, K, 1, "hybrid", 148, tile_n=tn)
+        got = (d["total_tiles"], d["iters_per_tile"], d["sk_tiles"], d["dp_tiles"],
+               d["sk_iters_per_cta"], d["sk_iters_rem"])
+        assert got == want, (M, N, K, got, want)
+
+
+@pytest.mark.parametrize("schedule", ["streamk", "hybrid", "hybrid_dp_first", "dp"])
+def test_every_iteration_covered_exactly_once(lib, schedule):
+    rnd = random.Random(hash(schedule) & 0xFFFF)
+    for _ in range(60):
+        kind = rnd.choice([0, 1])
+        M, N, K = rnd.randint(1, 900), rnd.randint(1, 2500), rnd.randint(1, 1500)
+        P = rnd.choice([1, 2, 3, 5, 7, 108, 132, 148])
+        d, info = _sched(lib, M, N, K, kind, schedule, P, tile_n=rnd.choice([0, 128, 256]) if kind else 0)
+        assert 1 <= d["grid"] <= P
+        cov = oracle.coverage(d)
+        assert len(cov) == d["total_tiles"] * d["iters_per_tile"], (M, N, K, P, d)
+        assert set(cov.values()) == {1}
+        # interval endpoints agree with the reference formula p*f + min(p, r)
+        b, e = C.c_int64(), C.c_int64()
+        for p in (0, d["grid"] // 2, d["grid"] - 1):
+            assert lib.sk_cta_interval(C.byref(info), p, C.byref(b), C.byref(e)) == 0
+            f, r = d["sk_iters_per_cta"], d["sk_iters_rem"]
+            assert b.value == p * f + min(p, r) and e.value == (p + 1) * f + min(p + 1, r)
+
+
+def test_tile_rasterisation_is_a_bijection(lib):
+    rnd = random.Random(7)
+    for _ in range(40):
+        M, N = rnd.randint(1, 3000), rnd.randint(1, 3000)
+        gm = rnd.choice([0, 1, 2, 3, 8, 16])
+        d, info = _sched(lib, M, N, 512, 1, "hybrid", 148, tile_n=128, group_m=gm)
+        seen = set()
+        tm, tn = C.c_int(), C.c_int()
+        for t in range(d["total_tiles"]):
+            assert lib.sk_tile_coords(C.byref(info), t, C.byref(tm), C.byref(tn)) == 0
+            assert (tm.value, tn.value) == oracle.tile_coords(t, d["tiles_m"], d["tiles_n"], d["group_m"])
+            assert 0 <= tm.value < d["tiles_m"] and 0 <= tn.value < d["tiles_n"]
+            seen.add((tm.value, tn.value))
+        assert len(seen) == d["total_tiles"]
+
+
+def test_bad_arguments(lib):
+    from streamk_b200 import _lib as L
+    info = L.SkScheduleInfo()
+    prob = L.SkProblem(M=0, N=4, K=4, schedule=1)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_SHAPE
+    prob = L.SkProblem(M=4, N=4, K=4, schedule=9)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_ARG
+    prob = L.SkProblem(M=4, N=4, K=4, schedule=1, tile_n=64)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_ARG
