@@ -1,0 +1,444 @@
+#!/usr/bin/env python
+"""Benchmark of the Stream-K GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--sweep FILE]
+
+Headline workload (every N): configuration 5, the large fp16 NT GEMM
+M=8192 N=28672 K=8192 (A ~ N(0,1), B ~ N(0,0.02), seeded, synthetic).  With N GPUs the
+weight rows (output columns) are sharded N-ways, each GPU runs its own Stream-K launch on
+its slab and no collective is on the data path (strong scaling: the total work is fixed).
+A step is one GEMM over the whole problem.  Rank 0 prints ONE JSON line.
+
+--sweep FILE additionally times configurations 2, 3 and 4 (24 fp16 shapes x schedules, 9
+W4A16 shapes) L2-cold on one GPU and writes the table to FILE as JSON.
+
+--impl reference times the reference's CPU expression for the path
+(`torch.matmul(A.float(), B.float().T)` on the host cores) on a bounded row slice.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M5, N5, K5 = 8192, 28672, 8192
+BASE_SLAB = N5 // 8            # B is generated in eight 3584-row slabs, whatever N is
+CPU_SAMPLE_ROWS = 256
+NOMINAL_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smmax, power, reasons = [], [], [], set()
+        for line in out.strip().split("\n"):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smmax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smmax), "samples": len(sm),
+                "power_w_max": max(power), "reasons": sorted(reasons)}
+
+
+def cpu_gemm_sample(A_rows, B, reps: int) -> tuple[float, int]:
+    """Seconds per `torch.matmul(A.float(), B.float().T)` on the host, threads used."""
+    import torch
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    Af, Bf = A_rows.float(), B.float()
+    torch.matmul(Af, Bf.t())  # warm the thread pool
+    t0 = time.perf_counter()
+    torch.matmul(Af, Bf.t())
+    one = time.perf_counter() - t0
+    reps = max(reps, min(200, int(10.0 / max(one, 1e-3))))   # about 10 s of CPU work
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        torch.matmul(Af, Bf.t())
+    return (time.perf_counter() - t0) / reps, torch.get_num_threads()
+
+
+def make_operands(rank: int, world: int, device):
+    """A (full) and this rank's slab of B, identical global values for every world size."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(5000)
+    A = torch.randn(M5, K5, generator=g, device=device, dtype=torch.float32).half()
+    per = 8 // world
+    slabs = []
+    for s in range(rank * per, (rank + 1) * per):
+        g.manual_seed(5001 + s)
+        slabs.append((0.02 * torch.randn(BASE_SLAB, K5, generator=g, device=device,
+                                         dtype=torch.float32)).half())
+    return A, torch.cat(slabs, 0)
+
+
+def reference_arm(args, rank: int) -> None:
+    if rank != 0:
+        return
+    import torch
+    g = torch.Generator().manual_seed(5000)
+    A = torch.randn(CPU_SAMPLE_ROWS, K5, generator=g).half()
+    B = (0.02 * torch.randn(N5, K5, generator=g)).half()
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    Af, Bf = A.float(), B.float()
+    for _ in range(max(args.warmup, 1)):
+        torch.matmul(Af, Bf.t())
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        torch.matmul(Af, Bf.t())
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * CPU_SAMPLE_ROWS * N5 * K5 / dt / 1e12
+    sample = (f"{CPU_SAMPLE_ROWS}-row slice of A (1/{M5 // CPU_SAMPLE_ROWS} of the problem) against the "
+              f"full B; torch.matmul(A.float(), B.float().T) on host cores")
+    print(json.dumps({
+        "impl": "reference", "metric": "Stream-K fp16 GEMM TFLOP/s", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": f"cfg5 fp16 NT GEMM M={M5} N={N5} K={K5}", "sampled": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------- sweep
+def time_rotating(launch, n_copies: int, est_us: float, batches: int = 25):
+    """p50/p10/p90 per-launch microseconds; launch(i) uses operand copy i (L2-cold rotation)."""
+    import torch
+    n = max(n_copies, int(math.ceil(1000.0 / max(est_us, 1.0))))
+    for i in range(max(3, n_copies)):
+        launch(i % n_copies)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(batches):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            launch(i % n_copies)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / n)
+    times.sort()
+    return times[len(times) // 2], times[len(times) // 10], times[(len(times) * 9) // 10]
+
+
+def run_sweep(path: str, peaks: dict) -> None:
+    import torch
+    import oracle
+    import streamk_b200 as sk
+    dev = torch.device("cuda", torch.cuda.current_device())
+    l2 = torch.cuda.get_device_properties(dev).L2_cache_size
+    rows = []
+
+    def roof(flops, nbytes):
+        t_nom = max(flops / (NOMINAL_TFLOPS * 1e12), nbytes / (NOMINAL_HBM_GBS * 1e9))
+        t_meas = max(flops / (peaks["bf16_tflops"] * 1e12), nbytes / (peaks["hbm_gbs"] * 1e9))
+        bound = "tensor" if flops / (peaks["bf16_tflops"] * 1e12) > nbytes / (peaks["hbm_gbs"] * 1e9) else "hbm"
+        return t_nom * 1e6, t_meas * 1e6, bound
+
+    def record(cfg, name, M, N, K, variant, us, flops, nbytes, extra=None):
+        t_nom, t_meas, bound = roof(flops, nbytes)
+        r = {"cfg": cfg, "entry": name, "M": M, "N": N, "K": K, "variant": variant,
+             "p50_us": round(us[0], 3), "p10_us": round(us[1], 3), "p90_us": round(us[2], 3),
+             "tflops": round(flops / us[0] / 1e6, 2), "gbs": round(nbytes / us[0] / 1e3, 1),
+             "bound": bound, "frac_of_nominal_roof": round(t_nom / us[0], 4),
+             "frac_of_measured_roof": round(t_meas / us[0], 4)}
+        if extra:
+            r.update(extra)
+        rows.append(r)
+        print(json.dumps(r), file=sys.stderr, flush=True)
+
+    def fp16_case(cfg, case):
+        c = oracle.make_case(cfg, case)
+        M, N, K = c["M"], c["N"], c["K"]
+        A = c["A"].to(dev)
+        wbytes = 2 * N * K
+        copies = min(int(math.ceil(2 * l2 / wbytes)) + 1, 40)
+        Bs = [c["B"].to(dev).clone() for _ in range(copies)]
+        out = torch.empty(M, N, dtype=torch.float16, device=dev)
+        flops, nbytes = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+        est = max(nbytes / 6.5e3, flops / 1.5e9) / 1e3 + 3
+        ref = oracle.gemm_ref(c["A"], c["B"], "nt")
+        variants = [("streamk", "atomic"), ("streamk", "block_reduce"), ("hybrid", "atomic"), ("dp", "atomic")]
+        for schedule, fixup in variants:
+            for tile_n in (128, 256):
+                if tile_n == 256 and N * M < 256 * 4096:
+                    continue
+                fn = lambda i: sk.streamk_fp16_nt(A, Bs[i], schedule=schedule, fixup=fixup, out=out, tile_n=tile_n)
+                fn(0)
+                sk.check_status()
+                err = oracle.rel_err(out, ref)
+                us = time_rotating(fn, copies, est)
+                record(cfg, "streamk_fp16_nt", M, N, K, f"{schedule}/{fixup}/bn{tile_n}", us, flops, nbytes,
+                       {"rel_err": float(f"{err:.3e}")})
+        fn = lambda i: torch.matmul(A, Bs[i].t(), out=out)
+        us = time_rotating(fn, copies, est)
+        record(cfg, "cublas torch.matmul", M, N, K, "data-parallel library GEMM", us, flops, nbytes)
+
+    def q4_case(case):
+        c = oracle.make_case(4, case)
+        M, N, K = c["M"], c["N"], c["K"]
+        A = c["A"].to(dev)
+        wbytes = N * K // 2
+        copies = min(int(math.ceil(2 * l2 / wbytes)) + 1, 64)
+        P0 = sk.q4_prepack(c["qweight"].to(dev), c["scales"].to(dev), c["zeros"].to(dev))
+        Ps = [P0] + [sk.PackedQ4(P0.data.clone(), N, K) for _ in range(copies - 1)]
+        out = torch.empty(M, N, dtype=torch.float16, device=dev)
+        flops = 2.0 * M * N * K
+        nbytes = 2.0 * M * K + N * K / 2 + 3.0 * N * K / 128 + 2.0 * M * N
+        est = max(nbytes / 6.5e3, flops / 1.5e9) / 1e3 + 3
+        ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
+        for schedule, fixup in (("streamk", "block_reduce"), ("hybrid", "block_reduce"), ("streamk", "atomic")):
+            fn = lambda i: sk.streamk_fp16_ladder_block_reduce_q4(A, Ps[i], schedule=schedule, fixup=fixup, out=out)
+            fn(0)
+            sk.check_status()
+            err = oracle.rel_err(out, ref)
+            us = time_rotating(fn, copies, est)
+            record(4, "streamk_fp16_ladder_block_reduce_q4", M, N, K, f"{schedule}/{fixup}", us, flops, nbytes,
+                   {"rel_err": float(f"{err:.3e}")})
+        W = sk.dequant_w4(P0)
+        Ws = [W.clone() for _ in range(min(copies, int(math.ceil(2 * l2 / (2 * N * K))) + 1))]
+        fn = lambda i: torch.matmul(A, Ws[i % len(Ws)].t(), out=out)
+        us = time_rotating(fn, len(Ws), est)
+        record(4, "cublas on dequantised fp16 W", M, N, K, "library GEMM, 4x the weight bytes", us, flops, nbytes)
+
+    fp16_case(2, 0)
+    for case in range(len(oracle.CONFIGS[3]["shapes"])):
+        fp16_case(3, case)
+    for case in range(len(oracle.CONFIGS[4]["shapes"])):
+        q4_case(case)
+    json.dump({"peaks": peaks, "protocol": "L2-cold: weights rotate through ceil(2*L2/bytes)+1 copies; "
+               "CUDA events around batches of >= 1 ms; p50 over 25 batches", "rows": rows},
+              open(path, "w"), indent=1)
+
+
+# ------------------------------------------------------------------------- main arm
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sweep", default=None, help="also time configs 2-4 and write the table here")
+    ap.add_argument("--schedule", default=os.environ.get("SK_BENCH_SCHEDULE", "hybrid"))
+    ap.add_argument("--fixup", default=os.environ.get("SK_BENCH_FIXUP", "block_reduce"))
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import streamk_b200 as sk
+
+    if world not in (1, 2, 4, 8):
+        raise SystemExit("the column sharding of configuration 5 supports 1, 2, 4 or 8 GPUs")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    n_slab = N5 // world
+    A, B = make_operands(rank, world, dev)
+    C = torch.empty(M5, n_slab, dtype=torch.float16, device=dev)
+    step = lambda: sk.streamk_fp16_nt(A, B, out=C, schedule=args.schedule, fixup=args.fixup)
+    info = sk.schedule_info(M5, n_slab, K5, schedule=args.schedule,
+                            num_sms=torch.cuda.get_device_properties(dev).multi_processor_count)
+
+    # ---- device-resident timing -------------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    sk.check_status()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    my_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = max_over_ranks(my_ms)
+    sk.check_status()
+    flops_total = 2.0 * M5 * N5 * K5
+    value = flops_total * args.steps / (total_ms * 1e-3) / 1e12
+
+    # spot check of the timed output against an fp32 product of the same operands
+    rows = torch.arange(0, M5, M5 // 16, device=dev)[:16]
+    ref = A[rows].float() @ B.float().t()
+    check = float((C[rows].float() - ref).abs().max() / ref.abs().max())
+
+    # ---- end to end: host buffers in, host result out ---------------------------
+    e2e_steps = max(1, min(args.steps, 5))
+    A_h = torch.empty(A.shape, dtype=A.dtype).pin_memory(); A_h.copy_(A)
+    B_h = torch.empty(B.shape, dtype=B.dtype).pin_memory(); B_h.copy_(B)
+    C_h = torch.empty(C.shape, dtype=C.dtype).pin_memory()
+
+    def e2e_step():
+        A.copy_(A_h, non_blocking=True)
+        B.copy_(B_h, non_blocking=True)
+        step()
+        C_h.copy_(C, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    e2e_value = flops_total * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    h2d = (A_h.numel() + B_h.numel()) * 2 * world
+    d2h = C_h.numel() * 2 * world
+
+    # ---- optional collective, timed on its own (not part of `value`) -------------
+    gather_ms = None
+    if world > 1:
+        parts = torch.empty(world, M5, n_slab, dtype=torch.float16, device=dev)
+        for _ in range(2):
+            dist.all_gather_into_tensor(parts, C)
+        barrier()
+        e0.record()
+        for _ in range(5):
+            step()
+            dist.all_gather_into_tensor(parts, C)
+        e1.record()
+        barrier()
+        gather_ms = max_over_ranks(e0.elapsed_time(e1)) / 5
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant (only) kernel ---------------------------------
+    launch_ms = my_ms / args.steps
+    achieved = 2.0 * M5 * n_slab * K5 / (launch_ms * 1e-3) / 1e12
+    timed_s = total_ms * 1e-3
+    peak_key = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if os.path.exists(tpath):
+        t = json.load(open(tpath)).get("sk_gemm_f16_kernel_cfg5")
+        if t:
+            traffic = t["dram_bytes_per_launch_full_problem"] / world
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_key], "unit": "TFLOP/s",
+                "frac": achieved / peaks[peak_key], "traffic": traffic,
+                "peak_source": f"{peaks['source']} {peak_key}",
+                "frac_of_nominal_2250": achieved / NOMINAL_TFLOPS,
+                "kernel": "sk_gemm_f16_kernel<256, NT>"}
+
+    cpu_baseline = None
+    if world == 1:
+        rows_s = A[:CPU_SAMPLE_ROWS].cpu()
+        sec, threads = cpu_gemm_sample(rows_s, B.cpu(), reps=3)
+        cpu_baseline = {"value": 2.0 * CPU_SAMPLE_ROWS * N5 * K5 / sec / 1e12, "unit": "TFLOP/s",
+                        "cores": threads, "kind": "port",
+                        "sample": f"{CPU_SAMPLE_ROWS}-row slice of A against the full B, "
+                                  f"torch.matmul(A.float(), B.float().T), {sec:.3f} s per product, "
+                                  f"repeated for about 10 s"}
+
+    out = {
+        "metric": "Stream-K fp16 GEMM TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": f"cfg5 fp16 NT GEMM M={M5} N={N5} K={K5}, N sharded {world}-way",
+                   "schedule": args.schedule, "fixup": args.fixup, "tile": [128, info["tile_n"], 64],
+                   "sk_tiles": info["sk_tiles"], "dp_tiles": info["dp_tiles"],
+                   "l2": "operands (>= 0.25 GB per GPU) exceed the 126 MB L2; no flush needed"},
+        "per_gpu_tflops": value / world,
+        "roofline": roofline, "cpu_baseline": cpu_baseline,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": args.steps, "clocks": clocks, "check_rel_err": check,
+    }
+    if gather_ms is not None:
+        out["gemm_plus_allgather_ms"] = gather_ms
+    if args.sweep and world == 1:
+        run_sweep(args.sweep, peaks)
+        out["sweep_file"] = args.sweep
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

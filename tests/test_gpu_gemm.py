@@ -1,0 +1,198 @@
+"""GPU parity: every entry point, through the C ABI, against the CPU oracle.
+
+Tolerances: fp16 / W4A16  max|C - C_ref| <= 1e-2 * max|C_ref|  (the benchmark's bar; the
+reference itself uses rtol = atol = 1e-2, streamk_fp16.py:399); fp32  1e-4 relative.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import streamk_b200 as sk
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL16 = 1e-2
+TOL32 = 1e-4
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+SCHEDULES = ("streamk", "hybrid", "hybrid_dp_first", "dp")
+FIXUPS = ("atomic", "block_reduce")
+
+
+def _rand16(M, N, K, seed, layout="nt"):
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randn(M, K, generator=g).half()
+    B = (torch.randn((N, K) if layout == "nt" else (K, N), generator=g) / K ** 0.5).half()
+    return A, B
+
+
+def _check(C, ref, tol):
+    sk.check_status()
+    err = oracle.rel_err(C, ref)
+    assert err <= tol, err
+
+
+# ----------------------------------------------------------------------------- golden
+def test_golden_vectors():
+    z = np.load(os.path.join(GOLD, "gemm_golden.npz"))
+    A, B = torch.from_numpy(z["nt_A"]), torch.from_numpy(z["nt_B"])
+    for fixup in FIXUPS:
+        _check(sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), fixup=fixup, schedule="streamk"),
+               torch.from_numpy(z["nt_C"]), TOL16)
+    A, B = torch.from_numpy(z["nn_A"]), torch.from_numpy(z["nn_B"])
+    _check(sk.streamk_fp16_nn(A.to(DEV), B.to(DEV)), torch.from_numpy(z["nn_C"]), TOL16)
+    A, B = torch.from_numpy(z["nn32_A"]), torch.from_numpy(z["nn32_B"])
+    for fixup in FIXUPS:
+        _check(sk.streamk_fp32(A.to(DEV), B.to(DEV), fixup=fixup, schedule="streamk"),
+               torch.from_numpy(z["nn32_C"]), TOL32)
+
+
+# ----------------------------------------------------------------------------- fp32
+@pytest.mark.parametrize("fixup", FIXUPS)
+def test_fp32_config1(fixup):
+    c = oracle.make_case(1)
+    ref = oracle.gemm_ref(c["A"], c["B"], "nn")
+    for schedule in SCHEDULES:
+        _check(sk.streamk_fp32(c["A"].to(DEV), c["B"].to(DEV), fixup=fixup, schedule=schedule),
+               ref, TOL32)
+
+
+@pytest.mark.parametrize("shape", [(32, 64, 32), (64, 64, 64), (1, 1, 1), (100, 90, 70), (257, 130, 513)])
+def test_fp32_shapes_and_grids(shape):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M * 7 + N)
+    A = torch.rand(M, K, generator=g) * 2 - 1
+    B = torch.rand(K, N, generator=g) * 2 - 1
+    ref = oracle.gemm_ref(A, B, "nn")
+    for fixup in FIXUPS:
+        for sms in (None, 1, 2, 3, 5):
+            _check(sk.streamk_fp32(A.to(DEV), B.to(DEV), fixup=fixup, schedule="streamk", num_sms=sms),
+                   ref, TOL32)
+    # NT form of the same product
+    _check(sk.streamk_fp32(A.to(DEV), B.t().contiguous().to(DEV), trans_b=True), ref, TOL32)
+
+
+# ----------------------------------------------------------------------------- fp16
+@pytest.mark.parametrize("fixup", FIXUPS)
+def test_fp16_config2_deep_k_nine_tiles(fixup):
+    c = oracle.make_case(2)
+    ref = oracle.gemm_ref(c["A"], c["B"], "nt")
+    A, B = c["A"].to(DEV), c["B"].to(DEV)
+    for schedule in SCHEDULES:
+        _check(sk.streamk_fp16_nt(A, B, fixup=fixup, schedule=schedule, tile_n=128), ref, TOL16)
+    info = sk.schedule_info(384, 384, 8192, tile_n=128)
+    assert info["total_tiles"] == 9 and info["sk_tiles"] == 9
+
+
+@pytest.mark.parametrize("shape", [
+    (128, 128, 64), (128, 128, 1024), (256, 1024, 512), (512, 512, 512),   # reference smoke shapes
+    (1, 128, 128), (7, 200, 136), (33, 520, 1000), (255, 300, 72), (300, 520, 1032)])
+def test_fp16_nt_ragged_shapes_schedules_fixups(shape):
+    M, N, K = shape
+    A, B = _rand16(M, N, K, seed=M + N + K)
+    ref = oracle.gemm_ref(A, B, "nt")
+    A, B = A.to(DEV), B.to(DEV)
+    for fixup in FIXUPS:
+        for schedule in SCHEDULES:
+            for tile_n in (128, 256):
+                _check(sk.streamk_fp16_nt(A, B, fixup=fixup, schedule=schedule, tile_n=tile_n), ref, TOL16)
+
+
+@pytest.mark.parametrize("sms", [1, 2, 3, 5, 37, 148])
+def test_fp16_grid_sizes(sms):
+    A, B = _rand16(300, 700, 1032, seed=sms)
+    ref = oracle.gemm_ref(A, B, "nt")
+    for fixup in FIXUPS:
+        _check(sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), fixup=fixup, schedule="streamk", num_sms=sms),
+               ref, TOL16)
+
+
+def test_fp16_odd_k_is_padded():
+    A, B = _rand16(20, 40, 77, seed=3)
+    _check(sk.streamk_fp16_nt(A.to(DEV), B.to(DEV)), oracle.gemm_ref(A, B, "nt"), TOL16)
+    A, B = _rand16(20, 44, 77, seed=4, layout="nn")
+    _check(sk.streamk_fp16_nn(A.to(DEV), B.to(DEV)), oracle.gemm_ref(A, B, "nn"), TOL16)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 384, 512), (100, 200, 136), (16, 1024, 1024)])
+def test_fp16_nn(shape):
+    M, N, K = shape
+    A, B = _rand16(M, N, K, seed=11, layout="nn")
+    ref = oracle.gemm_ref(A, B, "nn")
+    for tile_n in (128, 256):
+        for fixup in FIXUPS:
+            _check(sk.streamk_fp16_nn(A.to(DEV), B.to(DEV), fixup=fixup, schedule="streamk", tile_n=tile_n),
+                   ref, TOL16)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (128, 256, 512), (100, 200, 136), (16, 4096, 4096)])
+def test_fp16_ladder(shape):
+    M, N, K = shape
+    A, B = _rand16(M, N, K, seed=12)
+    ref = oracle.gemm_ref(A, B, "nt")
+    LB = sk.ladder_prepack(B.to(DEV))
+    for tile_n in (128, 256):
+        _check(sk.streamk_fp16_ladder(A.to(DEV), LB, schedule="streamk", tile_n=tile_n), ref, TOL16)
+        _check(sk.streamk_fp16_ladder_block_reduce(A.to(DEV), LB, tile_n=tile_n), ref, TOL16)
+
+
+def test_fp16_config3_sample_of_the_sweep():
+    # the full 24-shape sweep is the benchmark's job; parity on its extremes here
+    for case in (0, 7, 22):
+        c = oracle.make_case(3, case)
+        ref = oracle.gemm_ref(c["A"], c["B"], "nt")
+        A, B = c["A"].to(DEV), c["B"].to(DEV)
+        for schedule in ("streamk", "hybrid", "dp"):
+            _check(sk.streamk_fp16_nt(A, B, schedule=schedule, fixup="block_reduce"), ref, TOL16)
+
+
+def test_out_argument_and_views():
+    A, B = _rand16(64, 256, 256, seed=5)
+    big = torch.zeros(64, 512, dtype=torch.float16, device=DEV)
+    out = big[:, :256]
+    r = sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), out=out)
+    assert r.data_ptr() == out.data_ptr()
+    _check(out, oracle.gemm_ref(A, B, "nt"), TOL16)
+    assert float(big[:, 256:].abs().max()) == 0.0
+
+
+# ----------------------------------------------------------------------------- W4A16
+@pytest.mark.parametrize("shape", [(1, 128, 128), (4, 300, 256), (16, 4096, 4096)])
+def test_dequant_is_bit_exact(shape):
+    c = oracle.make_case(4, shape=shape)
+    P = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
+    W = sk.dequant_w4(P).cpu()
+    Wref = oracle.dequant_ref(c["q"], c["scales"], c["zeros"])
+    assert torch.equal(W.view(torch.int16), Wref.view(torch.int16))
+    # reference semantics: no scale, no zero-point; int8 low-nibble-first storage accepted
+    q8 = c["qweight"].view(torch.int8).reshape(c["N"], c["K"] // 2)
+    assert torch.equal(sk.dequant_w4(sk.q4_prepack(q8.to(DEV))).cpu(), c["q"].half())
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 128), (16, 512, 512), (33, 300, 256), (1, 4096, 4096),
+                                   (128, 4096, 4096)])
+def test_w4a16_gemm(shape):
+    c = oracle.make_case(4, shape=shape)
+    ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
+    P = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
+    A = c["A"].to(DEV)
+    for schedule, fixup in (("dp", "atomic"), ("streamk", "block_reduce"), ("hybrid", "atomic"),
+                            ("hybrid_dp_first", "block_reduce")):
+        _check(sk.streamk_fp16_ladder_block_reduce_q4(A, P, schedule=schedule, fixup=fixup), ref, TOL16)
+
+
+def test_w4a16_reference_semantics_no_scale_no_zero():
+    c = oracle.make_case(4, shape=(32, 1024, 1024))         # the reference's q4 check shape
+    ref = oracle.w4a16_ref(c["A"], c["q"])                   # A @ unpack(qB).T
+    P = sk.q4_prepack(c["qweight"].to(DEV))
+    _check(sk.streamk_fp16_ladder_block_reduce_q4(c["A"].to(DEV), P), ref, TOL16)
+
+
+def test_w4a16_config4_extremes():
+    for case in (0, 8):
+        c = oracle.make_case(4, case)
+        ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
+        P = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
+        _check(sk.streamk_fp16_ladder_block_reduce_q4(c["A"].to(DEV), P), ref, TOL16)
