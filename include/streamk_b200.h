@@ -102,6 +102,12 @@ const char* sk_status_string(int status);
 int sk_last_cuda_error(void);
 int sk_query(int device, sk_device_info* out);
 
+/* Debugging aid, no counterpart in the reference: while `buf` (device memory, 64 bytes per
+ * SM) is set, tensor-core launches record eight %globaltimer stamps per CTA: entry, set-up
+ * done, first TMA issued, first stage consumed, last MMA issued, first accumulator ready,
+ * epilogue done, exit.  NULL switches it off.                                             */
+int sk_debug_set_trace(void* buf);
+
 /* ---- scheduler (host only, no GPU needed) ------------------------------- */
 /* kernel_kind: 0 = fp32 SIMT tiles (64x64x16), 1 = fp16 / w4a16 UMMA tiles
  * (128 x tile_n x 64).  Mirrors streamk_fp16.py:83-113 for SK_SCHED_HYBRID.  */

@@ -54,6 +54,7 @@ SIGNATURES = {
     "sk_status_string": (C.c_char_p, [C.c_int]),
     "sk_last_cuda_error": (C.c_int, []),
     "sk_query": (C.c_int, [C.c_int, C.POINTER(SkDeviceInfo)]),
+    "sk_debug_set_trace": (C.c_int, [_P]),
     "sk_schedule": (C.c_int, [C.POINTER(SkProblem), C.c_int, C.c_int, C.POINTER(SkScheduleInfo)]),
     "sk_cta_interval": (C.c_int, [C.POINTER(SkScheduleInfo), C.c_int, C.POINTER(C.c_int64),
                                   C.POINTER(C.c_int64)]),

@@ -10,6 +10,17 @@ int sk_set_cuda_error(cudaError_t e) {
   return SK_ERR_LAUNCH;
 }
 
+static unsigned long long* g_trace = nullptr;
+unsigned long long* sk_trace_buffer() { return g_trace; }
+
+// Debugging aid (not part of the reference surface): later launches of the tensor-core
+// kernels record eight %globaltimer stamps per CTA into `buf` (device memory, 64 bytes per
+// SM); pass NULL to switch it off.
+extern "C" int sk_debug_set_trace(void* buf) {
+  g_trace = static_cast<unsigned long long*>(buf);
+  return SK_OK;
+}
+
 extern "C" const char* sk_version(void) { return "streamk_b200 0.1 (sm_100a)"; }
 
 extern "C" int sk_last_cuda_error(void) { return g_last_cuda_error; }

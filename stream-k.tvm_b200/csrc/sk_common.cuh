@@ -52,10 +52,17 @@ struct SkParams {
   SkSched sched;
   int fixup;               // SK_FIXUP_*
   int c_vec_ok;            // C rows can take 16-byte stores
+  int a_tx_bytes;          // bytes one TMA load of the A stage tile delivers
   int drop_flag_cta;       // test hook, -1 = off
   unsigned long long timeout_ns;
   SkWorkspace ws;
+  unsigned long long* trace;  // debugging: 8 timestamps per CTA, or null
 };
+
+// Debugging aid: record %globaltimer at a numbered point of this CTA's life.
+__device__ __forceinline__ void sk_trace(const SkParams& p, int slot) {
+  if (p.trace) p.trace[blockIdx.x * 8 + slot] = skptx::globaltimer_ns();
+}
 
 // First reporter wins; later errors keep the first record.
 __device__ __forceinline__ void sk_report(uint32_t* status, uint32_t code, uint32_t d0, uint32_t d1) {
@@ -84,3 +91,4 @@ __device__ __forceinline__ bool sk_wait_flag(const uint32_t* flag, unsigned long
 int sk_set_cuda_error(cudaError_t e);
 int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out);
 int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info, SkSched* s);
+unsigned long long* sk_trace_buffer();

@@ -132,6 +132,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
       if (!__all_sync(0xffffffffu, got)) dead = true;
     }
     tc_fence_after();
+    if (nseg == 1 && etid == 0) sk_trace(p, 5);
     const uint32_t t_addr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
 
     float* acc_slot = p.ws.acc_slots + static_cast<size_t>(first) * SLOT_FLOATS;
@@ -216,4 +217,5 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
         for (int peer = first + 1; peer <= last; ++peer) p.ws.flags[peer] = 0u;
     }
   }
+  if (etid == 0) sk_trace(p, 6);
 }

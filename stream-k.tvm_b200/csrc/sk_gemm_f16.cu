@@ -75,6 +75,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int pid = blockIdx.x;
   const SkSched& s = p.sched;
+  if (threadIdx.x == 0) sk_trace(p, 0);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -100,10 +101,12 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+  if (threadIdx.x == 0) sk_trace(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
     if (lane == 0) {
+      bool traced = false;
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
@@ -120,7 +123,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
+          mbar_arrive_expect_tx(full, p.a_tx_bytes + B_STAGE_BYTES);
           tma_load_2d(sA + stage * A_STAGE_BYTES, &tmA, full, k * BK, m0);
           const uint32_t dstB = sB + stage * B_STAGE_BYTES;
           if (BMODE == BMODE_NT) {
@@ -139,6 +142,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
           }
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
+          if (!traced) { sk_trace(p, 2); traced = true; }
         }
       }
     }
@@ -165,6 +169,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             break;
           }
           tc_fence_after();
+          if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
           const uint32_t a_addr = sA + stage * A_STAGE_BYTES;
           const uint32_t b_addr = sB + stage * B_STAGE_BYTES;
 #pragma unroll
@@ -185,6 +190,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         umma_commit(smem_u32(&ctrl->tmem_full[buf]));
         ++nseg;
       }
+      sk_trace(p, 4);
     }
   } else {
     // ------------------------------------------------------------- epilogue
@@ -205,6 +211,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     tc_fence_after();
     __syncwarp();
     tmem_dealloc(tmem_base, cfg::TMEM_COLS);
+    if (lane == 0) sk_trace(p, 7);
   }
 }
 
@@ -306,11 +313,16 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   p.timeout_ns = (prob->fixup_timeout_us > 0 ? static_cast<unsigned long long>(prob->fixup_timeout_us)
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);  // layout fixed per device, whatever the grid
+  p.trace = sk_trace_buffer();
 
   const int BN = info.tile_n;
   CUtensorMap tmA, tmB;
   memset(&tmB, 0, sizeof(tmB));
-  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, BM);
+  // A short problem loads only the rows it has (rounded up to 8): the UMMA still reads 128
+  // rows of the stage, the rest is stale shared memory feeding accumulator rows nobody reads.
+  const int a_rows = M >= BM ? BM : ((M + 7) & ~7);
+  p.a_tx_bytes = a_rows * BK * 2;
+  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, a_rows);
   if (st != SK_OK) return st;
   if (layout == SK_LAYOUT_NT) {
     st = sk_make_tmap_f16(&tmB, B, N, K, prob->ldb, BK, BN);

@@ -149,7 +149,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, A_STAGE_BYTES + Q_BLOCK_BYTES + SZ_BLOCK_BYTES);
+          mbar_arrive_expect_tx(full, p.a_tx_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES);
           tma_load_2d(sA + ls * A_STAGE_BYTES, &tmA, full, k * BK, m0);
           bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
                        qblocks + (static_cast<size_t>(tn) * kblocks + k) * Q_BLOCK_BYTES,
@@ -433,7 +433,9 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   p.ws = sk_ws_carve(ws, dev_sms);
 
   CUtensorMap tmA;
-  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, BM);
+  const int a_rows = M >= BM ? BM : ((M + 7) & ~7);
+  p.a_tx_bytes = a_rows * BK * 2;
+  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, a_rows);
   if (st != SK_OK) return st;
   const int nb = q4_nblocks(N), kb = K / 64;
   const uint8_t* qb = static_cast<const uint8_t*>(packed);
