@@ -57,7 +57,11 @@ typedef struct sk_problem {
   int32_t layout;             /* SK_LAYOUT_*                                  */
   int32_t schedule;           /* SK_SCHED_*                                   */
   int32_t fixup;              /* SK_FIXUP_*                                   */
-  int32_t tile_n;             /* 0 = choose; fp16/w4a16: 128 or 256           */
+  int32_t tile_m;             /* 0 = choose; 128 = M feeds the UMMA M dimension;
+                                 16..256 (multiple of 16) = operands swapped: the
+                                 weights feed the UMMA M dimension and the tile
+                                 spans tile_m rows of C (for short M)          */
+  int32_t tile_n;             /* 0 = choose; 128 or 256 (128 when swapped)     */
   int32_t num_sms;            /* 0 = all SMs of the device; else grid size    */
   int32_t group_m;            /* 0 = choose; tile rasterisation group height  */
   int32_t fixup_timeout_us;   /* 0 = default (2 s); bound of every device wait */
@@ -78,6 +82,7 @@ typedef struct sk_schedule_info {
   int32_t dp_waves;            /* ceil(dp_tiles / grid)                       */
   int32_t dp_first;
   int32_t group_m;
+  int32_t swap_ab;             /* 1: weights feed the UMMA M dimension          */
 } sk_schedule_info;
 
 typedef struct sk_device_info {
@@ -102,15 +107,16 @@ const char* sk_status_string(int status);
 int sk_last_cuda_error(void);
 int sk_query(int device, sk_device_info* out);
 
-/* Debugging aid, no counterpart in the reference: while `buf` (device memory, 64 bytes per
- * SM) is set, tensor-core launches record eight %globaltimer stamps per CTA: entry, set-up
- * done, first TMA issued, first stage consumed, last MMA issued, first accumulator ready,
- * epilogue done, exit.  NULL switches it off.                                             */
+/* Debugging aid, no counterpart in the reference: while `buf` (device memory, 128 bytes per
+ * SM) is set, tensor-core launches record %globaltimer stamps per CTA (16 slots of 8 bytes):
+ * 0 entry, 1 set-up done, 2 first TMA issued, 3 first stage consumed, 4 last MMA issued,
+ * 5 first accumulator ready, 6 epilogue done, 7 exit, 8 fixup flags seen, 9 / 10 first /
+ * second split tile reduced, 11 flags re-armed.  NULL switches it off.                    */
 int sk_debug_set_trace(void* buf);
 
 /* ---- scheduler (host only, no GPU needed) ------------------------------- */
-/* kernel_kind: 0 = fp32 SIMT tiles (64x64x16), 1 = fp16 / w4a16 UMMA tiles
- * (128 x tile_n x 64).  Mirrors streamk_fp16.py:83-113 for SK_SCHED_HYBRID.  */
+/* kernel_kind: 0 = fp32 SIMT tiles (64x64x16), 1 = fp16 UMMA tiles, 2 = W4A16 UMMA
+ * tiles (tile_m x tile_n x 64).  Mirrors streamk_fp16.py:83-113 for SK_SCHED_HYBRID. */
 int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* out);
 /* Iteration interval [begin,end) of CTA `cta` (streamk_fp16.py:176-181). */
 int sk_cta_interval(const sk_schedule_info* s, int cta, int64_t* begin, int64_t* end);

@@ -22,7 +22,7 @@ FIXUPS = {"atomic": 0, "block_reduce": 1}
 
 class SkProblem(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
-        "M", "N", "K", "lda", "ldb", "ldc", "layout", "schedule", "fixup", "tile_n", "num_sms",
+        "M", "N", "K", "lda", "ldb", "ldc", "layout", "schedule", "fixup", "tile_m", "tile_n", "num_sms",
         "group_m", "fixup_timeout_us", "test_drop_flag_cta")]
 
 
@@ -30,7 +30,7 @@ class SkScheduleInfo(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "tile_m", "tile_n", "tile_k", "tiles_m", "tiles_n", "total_tiles", "iters_per_tile",
         "sk_tiles", "dp_tiles", "grid", "sk_iters_per_cta", "sk_iters_rem", "dp_waves",
-        "dp_first", "group_m")]
+        "dp_first", "group_m", "swap_ab")]
 
     def as_dict(self) -> dict:
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -14,8 +14,8 @@ static unsigned long long* g_trace = nullptr;
 unsigned long long* sk_trace_buffer() { return g_trace; }
 
 // Debugging aid (not part of the reference surface): later launches of the tensor-core
-// kernels record eight %globaltimer stamps per CTA into `buf` (device memory, 64 bytes per
-// SM); pass NULL to switch it off.
+// kernels record up to sixteen %globaltimer stamps per CTA into `buf` (device memory, 128
+// bytes per SM); pass NULL to switch it off.
 extern "C" int sk_debug_set_trace(void* buf) {
   g_trace = static_cast<unsigned long long*>(buf);
   return SK_OK;
@@ -81,27 +81,58 @@ int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out) 
   return SK_OK;
 }
 
-int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
-                  SkSched* s) {
-  if (!p || num_sms <= 0) return SK_ERR_ARG;
-  if (p->M <= 0 || p->N <= 0 || p->K <= 0) return SK_ERR_SHAPE;
-  int tm, tn, tk;
+// Chooses the tile shape and whether the operands are swapped.
+//   kernel_kind 0 (fp32 SIMT): 64 x 64 x 16 tiles, never swapped.
+//   kernel_kind 1/2 (fp16 / W4A16 UMMA): the UMMA M dimension is always 128.  Normally it
+//   runs along M and the tile is 128 x tile_n (128 or 256).  For short M the weights take
+//   the UMMA M dimension instead (128 along N) and the tile spans tile_m = M rounded up to
+//   16 along M: no tensor-core work, shared memory or epilogue lanes are spent on padding.
+static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* plan) {
   if (kernel_kind == 0) {
-    tm = 64; tn = 64; tk = 16;
-  } else {
-    tm = 128; tk = 64;
-    tn = p->tile_n;
-    if (tn == 0) {
+    plan->swap = 0; plan->bn = 64; plan->rows = p->M; plan->cols = p->N;
+    return SK_OK;
+  }
+  int tm = p->tile_m, tn = p->tile_n;
+  if (tm < 0 || tn < 0) return SK_ERR_ARG;
+  bool swap;
+  if (tm == 0 && tn == 0) swap = p->M <= 64;
+  else if (tm != 0 && tm != 128) swap = true;
+  else if (tm == 128 && tn == 0 && p->M <= 64) swap = false;
+  else swap = false;
+  if (swap) {
+    if (tn != 0 && tn != 128) return SK_ERR_ARG;
+    if (tm == 0) tm = (p->M + 15) & ~15;
+    if (tm < 16 || tm > 256 || (tm & 15) != 0) return SK_ERR_ARG;
+    plan->swap = 1; plan->bn = tm; plan->rows = p->N; plan->cols = p->M;
+    return SK_OK;
+  }
+  if (tn == 0) {
+    if (kernel_kind == 2) {
+      tn = 128;
+    } else {
       // Wide tiles halve shared-memory traffic per flop; use them once there is
       // enough work to fill every SM twice over, else favour granularity.
       const long long t256 = static_cast<long long>((p->M + 127) / 128) * ((p->N + 255) / 256);
       tn = (t256 >= 2LL * num_sms) ? 256 : 128;
     }
-    if (tn != 128 && tn != 256) return SK_ERR_ARG;
   }
-  const long long tiles_m = (p->M + tm - 1) / tm;
-  const long long tiles_n = (p->N + tn - 1) / tn;
-  const long long total = tiles_m * tiles_n;
+  if (tn != 128 && !(tn == 256 && kernel_kind == 1)) return SK_ERR_ARG;
+  plan->swap = 0; plan->bn = tn; plan->rows = p->M; plan->cols = p->N;
+  return SK_OK;
+}
+
+int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
+                  SkSched* s, SkPlan* plan_out) {
+  if (!p || num_sms <= 0) return SK_ERR_ARG;
+  if (p->M <= 0 || p->N <= 0 || p->K <= 0) return SK_ERR_SHAPE;
+  SkPlan plan;
+  int st = make_plan(p, kernel_kind, num_sms, &plan);
+  if (st != SK_OK) return st;
+  const int tr = kernel_kind == 0 ? 64 : 128;   // tile extent along kernel-space rows
+  const int tk = kernel_kind == 0 ? 16 : 64;
+  const long long tiles_r = (plan.rows + tr - 1) / tr;
+  const long long tiles_c = (plan.cols + plan.bn - 1) / plan.bn;
+  const long long total = tiles_r * tiles_c;
   const long long I = (p->K + tk - 1) / tk;
   if (total > (1LL << 30)) return SK_ERR_LIMIT;
   const int P = num_sms;
@@ -125,12 +156,12 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   else grid = S < P ? S : P;
   if (grid < 1) grid = 1;
   int gm = p->group_m;
-  if (gm <= 0) gm = tiles_m > 1 ? (tiles_m < 16 ? static_cast<int>(tiles_m) : 16) : 1;
-  if (gm > tiles_m) gm = static_cast<int>(tiles_m);
+  if (gm <= 0) gm = (tiles_r > 1 && tiles_c > 1) ? (tiles_r < 16 ? static_cast<int>(tiles_r) : 16) : 1;
+  if (gm > tiles_r) gm = static_cast<int>(tiles_r);
 
   SkSched sc;
-  sc.tiles_m = static_cast<int>(tiles_m);
-  sc.tiles_n = static_cast<int>(tiles_n);
+  sc.tiles_m = static_cast<int>(tiles_r);
+  sc.tiles_n = static_cast<int>(tiles_c);
   sc.total_tiles = static_cast<int>(total);
   sc.iters_per_tile = static_cast<int>(I);
   sc.sk_tiles = static_cast<int>(T);
@@ -140,9 +171,14 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   sc.dp_first = p->schedule == SK_SCHED_HYBRID_DP_FIRST ? 1 : 0;
   sc.group_m = gm;
   if (s) *s = sc;
+  if (plan_out) *plan_out = plan;
   if (info) {
-    info->tile_m = tm; info->tile_n = tn; info->tile_k = tk;
-    info->tiles_m = sc.tiles_m; info->tiles_n = sc.tiles_n;
+    info->swap_ab = plan.swap;
+    info->tile_m = plan.swap ? plan.bn : tr;
+    info->tile_n = plan.swap ? tr : plan.bn;
+    info->tile_k = tk;
+    info->tiles_m = plan.swap ? sc.tiles_n : sc.tiles_m;
+    info->tiles_n = plan.swap ? sc.tiles_m : sc.tiles_n;
     info->total_tiles = sc.total_tiles; info->iters_per_tile = sc.iters_per_tile;
     info->sk_tiles = sc.sk_tiles; info->dp_tiles = static_cast<int>(dp);
     info->grid = sc.grid;
@@ -157,13 +193,16 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
 extern "C" int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms,
                            sk_schedule_info* out) {
   if (!out) return SK_ERR_ARG;
-  if (kernel_kind != 0 && kernel_kind != 1) return SK_ERR_ARG;
-  return sk_make_sched(p, kernel_kind, num_sms, out, nullptr);
+  if (kernel_kind < 0 || kernel_kind > 2) return SK_ERR_ARG;
+  return sk_make_sched(p, kernel_kind, num_sms, out, nullptr, nullptr);
 }
 
+// Kernel-space schedule (rows = the 128-wide UMMA M side) from the logical description.
 static SkSched sched_from_info(const sk_schedule_info* i) {
   SkSched s;
-  s.tiles_m = i->tiles_m; s.tiles_n = i->tiles_n; s.total_tiles = i->total_tiles;
+  s.tiles_m = i->swap_ab ? i->tiles_n : i->tiles_m;
+  s.tiles_n = i->swap_ab ? i->tiles_m : i->tiles_n;
+  s.total_tiles = i->total_tiles;
   s.iters_per_tile = i->iters_per_tile; s.sk_tiles = i->sk_tiles; s.grid = i->grid;
   s.sk_f = i->sk_iters_per_cta; s.sk_r = i->sk_iters_rem; s.dp_first = i->dp_first;
   s.group_m = i->group_m;
@@ -182,7 +221,10 @@ extern "C" int sk_cta_interval(const sk_schedule_info* info, int cta, int64_t* b
 extern "C" int sk_tile_coords(const sk_schedule_info* info, int tile, int* tile_m, int* tile_n) {
   if (!info || !tile_m || !tile_n || tile < 0 || tile >= info->total_tiles) return SK_ERR_ARG;
   const SkSched s = sched_from_info(info);
-  sk_tile_mn(s, tile, *tile_m, *tile_n);
+  int r, c;
+  sk_tile_mn(s, tile, r, c);
+  *tile_m = info->swap_ab ? c : r;
+  *tile_n = info->swap_ab ? r : c;
   return SK_OK;
 }
 

@@ -8,60 +8,90 @@
 #include "sk_ptx.cuh"
 #include "sk_sched.h"
 
-// ---- workspace layout (fixed for a given SM count) -------------------------
-//   [0, 256)                      status word (sk_status) + padding
-//   [256, +4*P)                   counters   (atomic fixup; kept zero)
-//   [.., +4*P)                    flags      (block-reduce fixup; kept zero)
-//   [align 1024, +P*SLOT)         fp32 accumulation slots (atomic; kept zero)
-//   [.., +P*SLOT)                 fp32 partial slots (block-reduce; any content)
-// One slot belongs to one CTA: a CTA owns at most one split tile (the last
-// segment of its interval) and writes at most one head partial (the first).
+// ---- workspace layout (fixed for a given SM count P) -------------------------
+//   [0, 256)                 status word (sk_status) + padding
+//   counters   [P] u32       atomic fixup: arrivals per split tile        (kept zero)
+//   done       [P] u32       block-reduce: contributors finished reducing (kept zero)
+//   flag_head  [P] u32       block-reduce: CTA's head partial is published (kept zero)
+//   flag_tail  [P] u32       block-reduce: CTA's tail partial is published (kept zero)
+//   acc_slots  [P]   x SLOT  fp32 accumulation slots of the atomic fixup  (kept zero)
+//   part_slots [2P]  x SLOT  fp32 partials of the block-reduce fixup      (any content)
+// A split tile is identified by its first contributor (the CTA that computes the
+// tile's K iteration 0): a CTA starts at most one tile it does not finish (its last
+// segment, the "tail") and finishes at most one tile it did not start (its first
+// segment, the "head").  part_slots[2p] is CTA p's head partial, [2p+1] its tail.
 constexpr size_t SK_WS_HEADER = 256;
 constexpr size_t SK_SLOT_BYTES = 128 * 256 * sizeof(float);  // largest tile, fp32
+constexpr size_t SK_SLOT_FLOATS = SK_SLOT_BYTES / sizeof(float);
 
 struct SkWorkspace {
-  uint32_t* status;    // 4 words
-  uint32_t* counters;  // P
-  uint32_t* flags;     // P
-  float* acc_slots;    // P * SLOT (zero between launches)
-  float* part_slots;   // P * SLOT
+  uint32_t* status;     // 4 words
+  uint32_t* counters;   // P
+  uint32_t* done;       // P
+  uint32_t* flag_head;  // P
+  uint32_t* flag_tail;  // P
+  float* acc_slots;     // P * SLOT (zero between launches)
+  float* part_slots;    // 2P * SLOT
 };
 
 inline size_t sk_ws_acc_offset(int P) {
-  size_t off = SK_WS_HEADER + 2 * sizeof(uint32_t) * static_cast<size_t>(P);
+  size_t off = SK_WS_HEADER + 4 * sizeof(uint32_t) * static_cast<size_t>(P);
   return (off + 1023) & ~static_cast<size_t>(1023);
 }
 inline size_t sk_ws_total_bytes(int P) {
-  return sk_ws_acc_offset(P) + 2 * static_cast<size_t>(P) * SK_SLOT_BYTES;
+  return sk_ws_acc_offset(P) + 3 * static_cast<size_t>(P) * SK_SLOT_BYTES;
 }
 inline SkWorkspace sk_ws_carve(void* ws, int P) {
   char* b = static_cast<char*>(ws);
   SkWorkspace w;
   w.status = reinterpret_cast<uint32_t*>(b);
   w.counters = reinterpret_cast<uint32_t*>(b + SK_WS_HEADER);
-  w.flags = w.counters + P;
+  w.done = w.counters + P;
+  w.flag_head = w.done + P;
+  w.flag_tail = w.flag_head + P;
   w.acc_slots = reinterpret_cast<float*>(b + sk_ws_acc_offset(P));
   w.part_slots = reinterpret_cast<float*>(b + sk_ws_acc_offset(P) + static_cast<size_t>(P) * SK_SLOT_BYTES);
   return w;
 }
 
+// How an operand's stage tile gets into shared memory.
+enum { SK_LOAD_TMA_K = 0,    // tensor map over a K-major matrix, one box per stage
+       SK_LOAD_TMA_MN = 1,   // tensor map over an MN-major matrix, one 64-wide box per chunk
+       SK_LOAD_IMAGE = 2,    // pre-laid-out 16 KB blocks, 1-D bulk copies
+       SK_LOAD_NONE = 3 };   // produced on chip (dequantised weights)
+
 // ---- kernel parameter block ------------------------------------------------
+// The tensor-core kernels work in "kernel space": `rows` runs along the operand that
+// feeds the UMMA M dimension (128 per tile), `cols` along the operand that feeds the
+// UMMA N dimension (bn per tile).  Normally rows = M, cols = N.  With the operands
+// swapped (short M) rows = N, cols = M and the result is stored transposed.
 struct SkParams {
-  int M, N, K;
+  int M, N, K;             // logical problem (fp32 kernel uses these)
   int lda, ldb, ldc;
+  int rows, cols;          // kernel-space extents
+  int transposed;          // 1: element (row, col) of the tile goes to C[col][row]
+  int bn;                  // UMMA N = tile extent along cols (multiple of 16, <= 256)
+  int acc_stride;          // TMEM columns between the two accumulators
+  int tmem_cols;           // TMEM columns allocated (power of two >= 32)
+  int stages;              // shared-memory pipeline depth
+  int col_stage_bytes;     // bn * 128
+  int row_tx_bytes, col_tx_bytes;   // bytes the loads of one stage deliver per operand
+  int row_loader, col_loader;       // SK_LOAD_*
+  uint32_t idesc;          // UMMA instruction descriptor
   SkSched sched;
   int fixup;               // SK_FIXUP_*
   int c_vec_ok;            // C rows can take 16-byte stores
-  int a_tx_bytes;          // bytes one TMA load of the A stage tile delivers
   int drop_flag_cta;       // test hook, -1 = off
   unsigned long long timeout_ns;
   SkWorkspace ws;
-  unsigned long long* trace;  // debugging: 8 timestamps per CTA, or null
+  const void* row_img;     // SK_LOAD_IMAGE sources
+  const void* col_img;
+  unsigned long long* trace;  // debugging: 16 timestamps per CTA, or null
 };
 
 // Debugging aid: record %globaltimer at a numbered point of this CTA's life.
 __device__ __forceinline__ void sk_trace(const SkParams& p, int slot) {
-  if (p.trace) p.trace[blockIdx.x * 8 + slot] = skptx::globaltimer_ns();
+  if (p.trace) p.trace[blockIdx.x * 16 + slot] = skptx::globaltimer_ns();
 }
 
 // First reporter wins; later errors keep the first record.
@@ -88,7 +118,14 @@ __device__ __forceinline__ bool sk_wait_flag(const uint32_t* flag, unsigned long
 }
 
 // Host-side helpers implemented in sk_api.cu.
+struct SkPlan {
+  int swap;          // operands swapped (weights feed the UMMA M dimension)
+  int bn;            // tile extent along kernel-space cols
+  int rows, cols;    // kernel-space extents
+};
 int sk_set_cuda_error(cudaError_t e);
 int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out);
-int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info, SkSched* s);
+// kernel_kind 0: fp32 SIMT (64x64x16 tiles); 1: fp16 UMMA; 2: W4A16 UMMA.
+int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
+                  SkSched* s, SkPlan* plan);
 unsigned long long* sk_trace_buffer();

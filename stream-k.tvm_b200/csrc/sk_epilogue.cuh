@@ -3,16 +3,23 @@
 //
 // Two fixups, both on fp32 partial sums (the reference adds fp16 halves straight
 // into a pre-zeroed C with T.atomic_addx2, streamk_fp16.py:248-255):
+//
 //   atomic        every contributor red.global.add's its partial into the tile's
 //                 zero-kept slot; the last one to arrive (a counter tells) folds the
-//                 slot into C and zeroes it again.
-//   block_reduce  contributors other than the tile owner publish their partial and
-//                 a flag; the owner (the CTA that computed the tile's first K
-//                 iteration, which it reaches last) waits with a time limit, adds the
-//                 partials in ascending CTA order and stores C.  The order is fixed,
-//                 so the result is bitwise reproducible.
-// Slot layout (private): float4 index = (column / 4) * 128 + row, so a warp's 32
-// rows write 512 contiguous bytes per instruction.
+//                 slot into C and zeroes it again.  Order of additions is not fixed.
+//
+//   block_reduce  every contributor stores its partial and raises a flag, without ever
+//                 waiting.  After a CTA has finished all of its segments it returns to
+//                 the (at most two) split tiles it took part in, waits with a time limit
+//                 for the tile's other contributors, and reduces ITS SLICE of the tile:
+//                 contributor j of n sums elements [j*L/n, (j+1)*L/n) over all partials
+//                 in ascending CTA order and stores them to C.  The order is fixed, so
+//                 the result is bitwise reproducible, and the reduction of a tile that is
+//                 split n ways is spread over n SMs instead of serialised on its owner.
+//                 Nothing waits while it still owes work to anyone, so there is no cycle.
+//
+// Slot layout (private): float4 index = (column / 4) * 128 + row, so a warp's 32 rows
+// write 512 contiguous bytes per instruction.
 #pragma once
 #include "sk_common.cuh"
 
@@ -23,7 +30,7 @@ constexpr int SK_EPI_BAR_ID = 1;
 // Bounded mbarrier wait.  On time-out the waiter raises the CTA-wide abort flag
 // and records the barrier; every other wait in the CTA then returns false too.
 __device__ __forceinline__ bool sk_wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                         const SkParams& p, uint32_t bar_id, uint32_t role) {
+                                            const SkParams& p, uint32_t bar_id, uint32_t role) {
   if (skptx::mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = skptx::globaltimer_ns();
   unsigned spins = 0;
@@ -40,11 +47,18 @@ __device__ __forceinline__ bool sk_wait_bar(uint32_t bar, uint32_t parity, volat
   }
 }
 
-// 32 fp32 values of one row -> fp16 -> C[row, col0 .. col0+31]
-__device__ __forceinline__ void sk_store_c_row(__half* __restrict__ C, const SkParams& p, int grow,
-                                            int gcol0, const float (&v)[32]) {
+// nv (<= 32) fp32 values of tile row `grow`, columns gcol0.. -> fp16 C
+__device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkParams& p, int grow,
+                                               int gcol0, int nv, const float (&v)[32]) {
+  if (p.transposed) {
+    __half* dst = C + static_cast<size_t>(gcol0) * p.ldc + grow;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < nv) dst[static_cast<size_t>(j) * p.ldc] = __float2half_rn(v[j]);
+    return;
+  }
   __half* dst = C + static_cast<size_t>(grow) * p.ldc + gcol0;
-  if (p.c_vec_ok && gcol0 + 32 <= p.N) {
+  if (p.c_vec_ok && nv == 32) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
@@ -61,24 +75,174 @@ __device__ __forceinline__ void sk_store_c_row(__half* __restrict__ C, const SkP
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (gcol0 + j < p.N) dst[j] = __float2half_rn(v[j]);
+      if (j < nv) dst[j] = __float2half_rn(v[j]);
   }
 }
 
-// Runs on the four epilogue warps (any four consecutive warps; `warp & 3` picks the
-// TMEM lane quadrant a warp may read).  tmem_full_bar / tmem_empty_bar are the
-// shared-memory addresses of two consecutive mbarriers each (one per accumulator).
-template <int BN>
+// One float4 of the slot layout (row, columns gcol..gcol+3) -> fp16 C
+__device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
+                                          const float4& x) {
+  const float v[4] = {x.x, x.y, x.z, x.w};
+  if (p.transposed) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (gcol + e < p.cols) C[static_cast<size_t>(gcol + e) * p.ldc + grow] = __float2half_rn(v[e]);
+  } else {
+    __half* dst = C + static_cast<size_t>(grow) * p.ldc + gcol;
+    if (p.c_vec_ok && gcol + 4 <= p.cols) {
+      __half2 h0 = __floats2half2_rn(v[0], v[1]);
+      __half2 h1 = __floats2half2_rn(v[2], v[3]);
+      uint2 u;
+      u.x = *reinterpret_cast<uint32_t*>(&h0);
+      u.y = *reinterpret_cast<uint32_t*>(&h1);
+      *reinterpret_cast<uint2*>(dst) = u;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (gcol + e < p.cols) dst[e] = __float2half_rn(v[e]);
+    }
+  }
+}
+
+struct SkPending {
+  int tile;    // -1 = none
+  int first, last;
+};
+
+// Sum one slice of a split tile over all of its partials, in ascending CTA order, and
+// store it.  The loop is bound by L2 latency, not by arithmetic, so a thread keeps U items
+// x V contributors = 16 loads in flight: a deep split (many contributors, few items per
+// thread) fetches all contributors of an item at once, a shallow one many items at once.
+template <int U, int V>
+__device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __restrict__ C,
+                                                   int first, int last, int r0, int c0,
+                                                   int rows_valid, int begin, int end, int tid,
+                                                   int nthreads) {
+  for (int base = begin + tid; base < end; base += U * nthreads) {
+    float4 acc[U];
+    bool on[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int idx = base + u * nthreads;
+      on[u] = idx < end && (idx & (SK_BM - 1)) < rows_valid;
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int cta = first; cta <= last; cta += V) {
+      float4 x[V][U];
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        const int c = cta + v;
+        if (c <= last) {
+          // partial of contributor c: the first one's tail slot, everybody else's head slot
+          const float4* src = reinterpret_cast<const float4*>(
+              p.ws.part_slots + static_cast<size_t>(2 * c + (c == first ? 1 : 0)) * SK_SLOT_FLOATS);
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (on[u]) x[v][u] = __ldcg(src + base + u * nthreads);
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        if (cta + v <= last) {
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (on[u]) {
+              acc[u].x += x[v][u].x; acc[u].y += x[v][u].y;
+              acc[u].z += x[v][u].z; acc[u].w += x[v][u].w;
+            }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int idx = base + u * nthreads;
+      if (on[u]) sk_store4(C, p, r0 + (idx & (SK_BM - 1)), c0 + (idx >> 7) * 4, acc[u]);
+    }
+  }
+}
+
+__device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __restrict__ C,
+                                                const SkPending& pd, int pid, int tid, int nthreads) {
+  const SkSched& s = p.sched;
+  const int first = pd.first, last = pd.last;
+  const int n = last - first + 1;
+  int tr, tc;
+  sk_tile_mn(s, pd.tile, tr, tc);
+  const int r0 = tr * SK_BM, c0 = tc * p.bn;
+  int valid_cols = p.cols - c0;
+  if (valid_cols > p.bn) valid_cols = p.bn;
+  int rows_valid = p.rows - r0;
+  if (rows_valid > SK_BM) rows_valid = SK_BM;
+  const int L = ((valid_cols + 3) >> 2) * SK_BM;  // float4 items of the tile
+  const int j = pid - first;
+  const int begin = static_cast<int>(static_cast<long long>(j) * L / n);
+  const int end = static_cast<int>(static_cast<long long>(j + 1) * L / n);
+  // The summation order (0 + p_first + p_first+1 + ...) is the same in every variant.
+  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else             sk_reduce_items_uv<1, 16>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
+}
+
+// Deferred block-reduce of the (at most two) split tiles this CTA took part in (see the
+// header comment).  Called by EVERY thread of the CTA after all roles have finished;
+// pend[0] is the tile the CTA started, pend[1] the tile it continued; ok[] is scratch.
+__device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __restrict__ C, int pid,
+                                                  const SkPending* pend, volatile uint32_t* ok) {
+  using namespace skptx;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  if (pend[0].tile < 0 && pend[1].tile < 0) return;   // uniform over the CTA
+  if (tid < 2) ok[tid] = 1u;
+  __syncthreads();
+  // 1. wait (bounded) for every contributor of both tiles; one flag per thread
+  const int n0 = pend[0].tile >= 0 ? pend[0].last - pend[0].first + 1 : 0;
+  const int n1 = pend[1].tile >= 0 ? pend[1].last - pend[1].first + 1 : 0;
+  for (int i = tid; i < n0 + n1; i += nthreads) {
+    const int t = i < n0 ? 0 : 1;
+    const int k = i < n0 ? i : i - n0;
+    const int first = pend[t].first;
+    const uint32_t* flag = (k == 0) ? (p.ws.flag_tail + first) : (p.ws.flag_head + first + k);
+    if (!sk_wait_flag(flag, p.timeout_ns)) {
+      sk_report(p.ws.status, SK_ERR_FIXUP_TIMEOUT, pend[t].tile, first + k);
+      ok[t] = 0u;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) sk_trace(p, 8);
+  // 2. reduce this CTA's slice of each tile
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (pend[t].tile >= 0 && ok[t] != 0u) sk_reduce_items(p, C, pend[t], pid, tid, nthreads);
+    if (tid == 0) sk_trace(p, 9 + t);
+  }
+  // 3. everybody has read what it needs; the last contributor to get here re-arms the flags
+  __syncthreads();
+  if (tid < 2 && pend[tid].tile >= 0) {
+    const int first = pend[tid].first, last = pend[tid].last;
+    const uint32_t old = atom_add_acqrel_u32(p.ws.done + first, 1u);
+    if (old == static_cast<uint32_t>(last - first) && ok[tid] != 0u) {
+      p.ws.flag_tail[first] = 0u;
+      for (int peer = first + 1; peer <= last; ++peer) p.ws.flag_head[peer] = 0u;
+      p.ws.done[first] = 0u;
+    }
+  }
+  if (tid == 0) sk_trace(p, 11);
+}
+
+// Runs on the four epilogue warps (warps 2..5; `warp & 3` picks the TMEM lane quadrant a
+// warp may read).  Leaves the split tiles still to be reduced in pend_out[0..1].  tmem_full_bar /
+// tmem_empty_bar are the shared-memory addresses of two consecutive mbarriers each
+// (one per accumulator).
 __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __restrict__ C, int pid,
                                                  int warp, int lane, uint32_t tmem_base,
                                                  uint32_t tmem_full_bar, uint32_t tmem_empty_bar,
                                                  volatile uint32_t* bcast,
-                                                 volatile uint32_t* abort_flag) {
+                                                 volatile uint32_t* abort_flag,
+                                                 SkPending* pend_out) {
   using namespace skptx;
   constexpr int BM = SK_BM;
   constexpr int EPI_THREADS = SK_EPI_THREADS;
   constexpr int EPI_BAR_ID = SK_EPI_BAR_ID;
-  constexpr size_t SLOT_FLOATS = SK_SLOT_BYTES / sizeof(float);
   const SkSched& s = p.sched;
   const int q = warp & 3;            // TMEM lane quadrant this warp may read
   const int row = q * 32 + lane;     // row inside the tile
@@ -88,41 +252,24 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
   SkSeg seg;
   uint32_t nseg = 0;
   bool dead = false;
+  SkPending head{-1, 0, 0}, tail{-1, 0, 0};
   while (sk_next(s, pid, cur, seg)) {
     const uint32_t buf = nseg & 1u;
     const uint32_t acc_ph = (nseg >> 1) & 1u;
     ++nseg;
-    int tm, tn;
-    sk_tile_mn(s, seg.tile, tm, tn);
-    const int m0 = tm * BM, n0 = tn * BN;
-    const int grow = m0 + row;
-    const bool row_ok = grow < p.M;
-    const bool warp_ok = (m0 + q * 32) < p.M;  // warp-uniform
-    int nchunks = (p.N - n0 + 31) / 32;
-    if (nchunks > BN / 32) nchunks = BN / 32;
+    int tr, tc;
+    sk_tile_mn(s, seg.tile, tr, tc);
+    const int r0 = tr * BM, c0 = tc * p.bn;
+    const int grow = r0 + row;
+    const bool row_ok = grow < p.rows;
+    const bool warp_ok = (r0 + q * 32) < p.rows;  // warp-uniform
+    int valid_cols = p.cols - c0;
+    if (valid_cols > p.bn) valid_cols = p.bn;
+    const int nchunks = (valid_cols + 31) >> 5;
     const bool whole = (seg.k0 == 0 && seg.k1 == s.iters_per_tile);
     int first = 0, last = 0;
     if (!whole) sk_tile_ctas(s, seg.tile, first, last);
-    const bool owner = !whole && p.fixup == SK_FIXUP_BLOCK_REDUCE && seg.k0 == 0;
-
-    // The owner waits for its peers' partials before it touches TMEM so that the
-    // registers it loads can be finished column chunk by column chunk.
-    bool peers_ok = true;
-    if (owner) {
-      if (etid == 0) {
-        uint32_t ok = 1u;
-        for (int peer = first + 1; peer <= last; ++peer) {
-          if (!sk_wait_flag(p.ws.flags + peer, p.timeout_ns)) {
-            sk_report(p.ws.status, SK_ERR_FIXUP_TIMEOUT, seg.tile, peer);
-            ok = 0u;
-            break;
-          }
-        }
-        *bcast = ok;
-      }
-      named_bar_sync(EPI_BAR_ID, EPI_THREADS);
-      peers_ok = *bcast != 0u;
-    }
+    const bool is_tail = !whole && seg.k0 == 0;   // this CTA starts the tile (its "owner")
 
     // A wait that ran out must not leave the warps disagreeing: every epilogue
     // thread keeps walking the segment list (and meeting the named barriers) but
@@ -133,10 +280,10 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     }
     tc_fence_after();
     if (nseg == 1 && etid == 0) sk_trace(p, 5);
-    const uint32_t t_addr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t t_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(q * 32) << 16);
 
-    float* acc_slot = p.ws.acc_slots + static_cast<size_t>(first) * SLOT_FLOATS;
-    float* my_part = p.ws.part_slots + static_cast<size_t>(pid) * SLOT_FLOATS;
+    float* acc_slot = p.ws.acc_slots + static_cast<size_t>(first) * SK_SLOT_FLOATS;
+    float* my_part = p.ws.part_slots + static_cast<size_t>(2 * pid + (is_tail ? 1 : 0)) * SK_SLOT_FLOATS;
 
     if (warp_ok && !dead) {
       for (int c = 0; c < nchunks; ++c) {
@@ -147,29 +294,22 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         if (!row_ok) continue;
+        int nv = valid_cols - c * 32;
+        if (nv > 32) nv = 32;
         if (whole) {
-          sk_store_c_row(C, p, grow, n0 + c * 32, v);
+          sk_store_chunk(C, p, grow, c0 + c * 32, nv, v);
         } else if (p.fixup == SK_FIXUP_ATOMIC) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            red_add_v4(acc_slot + (static_cast<size_t>(c * 8 + j) * BM + row) * 4, v[4 * j],
-                       v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-        } else if (!owner) {
+            if (4 * j < nv)
+              red_add_v4(acc_slot + (static_cast<size_t>(c * 8 + j) * BM + row) * 4, v[4 * j],
+                         v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            __stcg(reinterpret_cast<float4*>(my_part + (static_cast<size_t>(c * 8 + j) * BM + row) * 4),
-                   make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-        } else if (peers_ok) {
-          for (int peer = first + 1; peer <= last; ++peer) {
-            const float* part = p.ws.part_slots + static_cast<size_t>(peer) * SLOT_FLOATS;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 x = __ldcg(reinterpret_cast<const float4*>(
-                  part + (static_cast<size_t>(c * 8 + j) * BM + row) * 4));
-              v[4 * j] += x.x; v[4 * j + 1] += x.y; v[4 * j + 2] += x.z; v[4 * j + 3] += x.w;
-            }
-          }
-          sk_store_c_row(C, p, grow, n0 + c * 32, v);
+            if (4 * j < nv)
+              __stcg(reinterpret_cast<float4*>(my_part + (static_cast<size_t>(c * 8 + j) * BM + row) * 4),
+                     make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
         }
       }
     }
@@ -188,34 +328,47 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
       }
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);
       if (*bcast != 0u) {
-        // last contributor: fold the slot into C and leave the slot zeroed
+        // last contributor: fold the slot into C and leave the slot zeroed; all 128
+        // threads share the work whatever the number of valid rows
         __threadfence();
-        if (row_ok) {
-          for (int c = 0; c < nchunks; ++c) {
-            float v[32];
+        int rows_valid = p.rows - r0;
+        if (rows_valid > BM) rows_valid = BM;
+        const int L = ((valid_cols + 3) >> 2) * BM;
+        float4* slot4 = reinterpret_cast<float4*>(acc_slot);
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+        constexpr int UF = 12;   // loads in flight per thread: this pass is L2-latency bound
+        for (int idx = etid; idx < L; idx += UF * EPI_THREADS) {
+          float4 x[UF];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4* q4 = reinterpret_cast<float4*>(
-                  acc_slot + (static_cast<size_t>(c * 8 + j) * BM + row) * 4);
-              const float4 x = __ldcg(q4);
-              __stcg(q4, make_float4(0.f, 0.f, 0.f, 0.f));
-              v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+          for (int u = 0; u < UF; ++u) {
+            const int i = idx + u * EPI_THREADS;
+            if (i < L && (i & (BM - 1)) < rows_valid) x[u] = __ldcg(slot4 + i);
+          }
+#pragma unroll
+          for (int u = 0; u < UF; ++u) {
+            const int i = idx + u * EPI_THREADS;
+            if (i < L && (i & (BM - 1)) < rows_valid) {
+              __stcg(slot4 + i, zero);
+              sk_store4(C, p, r0 + (i & (BM - 1)), c0 + (i >> 7) * 4, x[u]);
             }
-            sk_store_c_row(C, p, grow, n0 + c * 32, v);
           }
         }
         if (etid == 0) p.ws.counters[first] = 0u;
       }
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);  // bcast is reused by the next segment
-    } else if (!owner) {
+    } else {
+      // publish the partial; never wait here
       __threadfence();
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);
-      if (etid == 0 && pid != p.drop_flag_cta) st_release_u32(p.ws.flags + pid, 1u);
-    } else {
-      named_bar_sync(EPI_BAR_ID, EPI_THREADS);  // every thread has read the partials
-      if (etid == 0 && peers_ok)
-        for (int peer = first + 1; peer <= last; ++peer) p.ws.flags[peer] = 0u;
+      if (etid == 0 && pid != p.drop_flag_cta)
+        st_release_u32(is_tail ? (p.ws.flag_tail + pid) : (p.ws.flag_head + pid), 1u);
+      SkPending& pd = is_tail ? tail : head;
+      pd.tile = seg.tile; pd.first = first; pd.last = last;
     }
   }
-  if (etid == 0) sk_trace(p, 6);
+  if (etid == 0) {
+    sk_trace(p, 6);
+    pend_out[0] = tail;   // reduced by the whole CTA once every role is done
+    pend_out[1] = head;
+  }
 }

@@ -27,48 +27,55 @@ using namespace skptx;
 
 constexpr int BM = SK_BM;
 constexpr int BK = 64;
-constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int ROW_STAGE_BYTES = BM * BK * 2;   // 16 KB: 128 rows x 128 B
 constexpr int NUM_THREADS = 192;
-
-enum { BMODE_NT = 0, BMODE_NN = 1, BMODE_LADDER = 2 };
-
-template <int BN>
-struct Cfg {
-  static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int STAGES = (BN == 128) ? 6 : 4;
-  static constexpr int TMEM_COLS = 2 * BN;  // two fp32 accumulators of BN columns
-  static constexpr int PIPE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
-  static constexpr int SMEM_BYTES = PIPE_BYTES + 1024 /*alignment slack*/ + 256 /*Ctrl*/;
-};
+constexpr int MAX_STAGES = 12;
+constexpr int CTRL_BYTES = 512;
+constexpr int SMEM_LIMIT = 232448;             // 227 KB opt-in maximum per CTA
 
 struct Ctrl {
-  uint64_t full[8];
-  uint64_t empty[8];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t bcast;
+  uint32_t ok[2];
+  SkPending pend[2];
 };
-static_assert(sizeof(Ctrl) <= 256, "Ctrl must fit its reserved space");
+static_assert(sizeof(Ctrl) <= CTRL_BYTES, "Ctrl must fit its reserved space");
 
-template <int BN, int BMODE>
+// Issue the loads of one operand's stage tile.  `first_row` is the tile's first row along
+// the operand's MN extent, k the K iteration.
+__device__ __forceinline__ void load_operand(int loader, uint32_t dst, const CUtensorMap* tm,
+                                             const void* img, uint32_t bar, int first_row, int k,
+                                             int tile_rows, int kblocks) {
+  if (loader == SK_LOAD_TMA_K) {
+    tma_load_2d(dst, tm, bar, k * BK, first_row);
+  } else if (loader == SK_LOAD_TMA_MN) {
+    for (int j = 0; j < tile_rows / 64; ++j) tma_load_2d(dst + j * 8192, tm, bar, first_row + j * 64, k * BK);
+  } else {
+    // pre-laid-out image: blocks of 128 rows x 64 halves, [row_block][k_block]
+    const __half* src = static_cast<const __half*>(img);
+    for (int j = 0; j < tile_rows / 128; ++j) {
+      const size_t blk = static_cast<size_t>(first_row / 128 + j) * kblocks + k;
+      bulk_load_1d(dst + j * 16384, src + blk * (128 * 64), 16384, bar);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const __half* __restrict__ Bimg, __half* __restrict__ C, const SkParams p) {
-  using cfg = Cfg<BN>;
-  constexpr int STAGES = cfg::STAGES;
-  constexpr int B_STAGE_BYTES = cfg::B_STAGE_BYTES;
-  constexpr uint32_t IDESC = umma_idesc_f16(BM, BN, BMODE == BMODE_NN ? 1 : 0);
-  constexpr size_t SLOT_FLOATS = SK_SLOT_BYTES / sizeof(float);
-
+sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_constant__ CUtensorMap tmCol,
+                   __half* __restrict__ C, const SkParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw_addr);
-  const uint32_t sA = base;
-  const uint32_t sB = base + STAGES * A_STAGE_BYTES;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + cfg::PIPE_BYTES);
+  const int STAGES = p.stages;
+  const uint32_t sRow = base;
+  const uint32_t sCol = base + STAGES * ROW_STAGE_BYTES;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * (ROW_STAGE_BYTES + p.col_stage_bytes));
   volatile uint32_t* abort_flag = &ctrl->abort;
 
   const int warp = threadIdx.x >> 5;
@@ -88,13 +95,15 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
     ctrl->abort = 0u;
     ctrl->bcast = 0u;
+    ctrl->pend[0].tile = -1;
+    ctrl->pend[1].tile = -1;
     fence_mbar_init();
     fence_proxy_async_smem();
-    prefetch_tensormap(&tmA);
-    if (BMODE != BMODE_LADDER) prefetch_tensormap(&tmB);
+    if (p.row_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmRow);
+    if (p.col_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmCol);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), cfg::TMEM_COLS);
+    tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -113,34 +122,22 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       int stage = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const uint32_t tx = p.row_tx_bytes + p.col_tx_bytes;
       while (ok && sk_next(s, pid, cur, seg)) {
-        int tm, tn;
-        sk_tile_mn(s, seg.tile, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        int tr, tc;
+        sk_tile_mn(s, seg.tile, tr, tc);
+        const int r0 = tr * BM, c0 = tc * p.bn;
         for (int k = seg.k0; k < seg.k1; ++k) {
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           if (!sk_wait_bar(smem_u32(&ctrl->empty[stage]), ph ^ 1u, abort_flag, p, stage, 0)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, p.a_tx_bytes + B_STAGE_BYTES);
-          tma_load_2d(sA + stage * A_STAGE_BYTES, &tmA, full, k * BK, m0);
-          const uint32_t dstB = sB + stage * B_STAGE_BYTES;
-          if (BMODE == BMODE_NT) {
-            tma_load_2d(dstB, &tmB, full, k * BK, n0);
-          } else if (BMODE == BMODE_NN) {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(dstB + j * 8192, &tmB, full, n0 + j * 64, k * BK);
-          } else {
-            // pre-laid-out image: blocks of 128 rows x 64 halves, [n_block][k_block]
-            const int kblocks = s.iters_per_tile;
-#pragma unroll
-            for (int j = 0; j < BN / 128; ++j) {
-              const size_t blk = static_cast<size_t>(n0 / 128 + j) * kblocks + k;
-              bulk_load_1d(dstB + j * 16384, Bimg + blk * (128 * 64), 16384, full);
-            }
-          }
+          mbar_arrive_expect_tx(full, tx);
+          load_operand(p.row_loader, sRow + stage * ROW_STAGE_BYTES, &tmRow, p.row_img, full, r0, k,
+                       BM, s.iters_per_tile);
+          load_operand(p.col_loader, sCol + stage * p.col_stage_bytes, &tmCol, p.col_img, full, c0, k,
+                       p.bn, s.iters_per_tile);
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
           if (!traced) { sk_trace(p, 2); traced = true; }
         }
@@ -156,32 +153,34 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       uint32_t ph = 0;
       uint32_t nseg = 0;
       bool ok = true;
+      // K-major operand: 8-row groups 1024 B apart, 16 halves of K = 32 B.
+      // MN-major operand: 64-wide chunks 8192 B apart, 8-row K groups 1024 B apart,
+      // 16 rows of K = 2048 B.
+      const bool row_mn = p.row_loader == SK_LOAD_TMA_MN;
+      const bool col_mn = p.col_loader == SK_LOAD_TMA_MN;
+      const uint32_t row_kstep = row_mn ? 2048u : 32u, row_lbo = row_mn ? 8192u : 16u;
+      const uint32_t col_kstep = col_mn ? 2048u : 32u, col_lbo = col_mn ? 8192u : 16u;
       while (ok && sk_next(s, pid, cur, seg)) {
         const uint32_t buf = nseg & 1u;
         const uint32_t acc_ph = (nseg >> 1) & 1u;
         if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
         for (int k = seg.k0; k < seg.k1; ++k) {
-          if (!sk_wait_bar(smem_u32(&ctrl->full[stage]), ph, abort_flag, p, 8 + stage, 1)) {
+          if (!sk_wait_bar(smem_u32(&ctrl->full[stage]), ph, abort_flag, p, 32 + stage, 1)) {
             ok = false;
             break;
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          const uint32_t a_addr = sA + stage * A_STAGE_BYTES;
-          const uint32_t b_addr = sB + stage * B_STAGE_BYTES;
+          const uint32_t a_addr = sRow + stage * ROW_STAGE_BYTES;
+          const uint32_t b_addr = sCol + stage * p.col_stage_bytes;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            // K-major operand: 8-row groups 1024 B apart, 16 halves of K = 32 B.
-            const uint64_t da = umma_desc_sw128(a_addr + kk * 32, 16, 1024);
-            // MN-major B (NN layout): 64-column chunks 8192 B apart, 8-row K groups
-            // 1024 B apart, 16 rows of K = 2048 B.
-            const uint64_t db = (BMODE == BMODE_NN)
-                                    ? umma_desc_sw128(b_addr + kk * 2048, 8192, 1024)
-                                    : umma_desc_sw128(b_addr + kk * 32, 16, 1024);
-            umma_f16_ss(d_tmem, da, db, IDESC, (k > seg.k0 || kk > 0) ? 1u : 0u);
+            const uint64_t da = umma_desc_sw128(a_addr + kk * row_kstep, row_lbo, 1024);
+            const uint64_t db = umma_desc_sw128(b_addr + kk * col_kstep, col_lbo, 1024);
+            umma_f16_ss(d_tmem, da, db, p.idesc, (k > seg.k0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&ctrl->empty[stage]));  // frees the stage when the MMAs retire
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
@@ -194,13 +193,16 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------- epilogue
-    sk_epilogue_loop<BN>(p, C, pid, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                         smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag);
+    sk_epilogue_loop(p, C, pid, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                     smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   }
 
   // ------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
+  // the split tiles it took part in.
+  sk_reduce_pending(p, C, pid, ctrl->pend, ctrl->ok);
   if (warp == 1) {
     if (*abort_flag) {
       // A wait ran out: give copies and MMAs still in flight time to land before
@@ -210,7 +212,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
     tc_fence_after();
     __syncwarp();
-    tmem_dealloc(tmem_base, cfg::TMEM_COLS);
+    tmem_dealloc(tmem_base, p.tmem_cols);
     if (lane == 0) sk_trace(p, 7);
   }
 }
@@ -255,28 +257,19 @@ int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
   return SK_OK;
 }
 
-namespace {
-
-template <int BN, int BMODE>
-int launch_f16(const CUtensorMap& tmA, const CUtensorMap& tmB, const __half* Bimg, __half* C,
-               const SkParams& p, cudaStream_t cs) {
-  using cfg = Cfg<BN>;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(sk_gemm_f16_kernel<BN, BMODE>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return sk_set_cuda_error(e);
-    attr_set[dev & 63] = true;
-  }
-  sk_gemm_f16_kernel<BN, BMODE><<<p.sched.grid, NUM_THREADS, cfg::SMEM_BYTES, cs>>>(tmA, tmB, Bimg, C, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return sk_set_cuda_error(e);
-  return SK_OK;
+// Fields of SkParams that depend only on the tile width: TMEM layout and pipeline depth.
+void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_stages,
+                         int reserved_bytes) {
+  p->bn = bn;
+  p->acc_stride = (bn + 31) & ~31;
+  int cols = 32;
+  while (cols < 2 * p->acc_stride) cols <<= 1;
+  p->tmem_cols = cols;
+  p->col_stage_bytes = bn * 128;
+  int stages = (SMEM_LIMIT - 1024 - CTRL_BYTES - reserved_bytes) / (stage_fixed_bytes + p->col_stage_bytes);
+  if (stages > max_stages) stages = max_stages;
+  p->stages = stages;
 }
-
-}  // namespace
 
 extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B, void* C, void* ws,
                            size_t ws_bytes, void* stream) {
@@ -288,8 +281,8 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   if (st != SK_OK) return st;
   SkParams p;
   memset(&p, 0, sizeof(p));
-  sk_schedule_info info;
-  st = sk_make_sched(prob, 1, num_sms, &info, &p.sched);
+  SkPlan plan;
+  st = sk_make_sched(prob, 1, num_sms, nullptr, &p.sched, &plan);
   if (st != SK_OK) return st;
   const int layout = prob->layout;
   const int M = prob->M, N = prob->N, K = prob->K;
@@ -307,6 +300,8 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
 
   p.M = M; p.N = N; p.K = K;
   p.lda = prob->lda; p.ldb = prob->ldb; p.ldc = prob->ldc;
+  p.rows = plan.rows; p.cols = plan.cols;
+  p.transposed = plan.swap;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
   p.drop_flag_cta = prob->test_drop_flag_cta;
@@ -314,33 +309,55 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);  // layout fixed per device, whatever the grid
   p.trace = sk_trace_buffer();
+  sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, 0);
+  if (p.stages < 2) return SK_ERR_SHAPE;
 
-  const int BN = info.tile_n;
-  CUtensorMap tmA, tmB;
-  memset(&tmB, 0, sizeof(tmB));
-  // A short problem loads only the rows it has (rounded up to 8): the UMMA still reads 128
-  // rows of the stage, the rest is stale shared memory feeding accumulator rows nobody reads.
-  const int a_rows = M >= BM ? BM : ((M + 7) & ~7);
-  p.a_tx_bytes = a_rows * BK * 2;
-  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, a_rows);
-  if (st != SK_OK) return st;
-  if (layout == SK_LAYOUT_NT) {
-    st = sk_make_tmap_f16(&tmB, B, N, K, prob->ldb, BK, BN);
-  } else if (layout == SK_LAYOUT_NN) {
-    st = sk_make_tmap_f16(&tmB, B, K, N, prob->ldb, 64, BK);
-  }
-  if (st != SK_OK) return st;
-
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  const __half* Bh = static_cast<const __half*>(B);
-  __half* Ch = static_cast<__half*>(C);
-  if (BN == 128) {
-    if (layout == SK_LAYOUT_NT) return launch_f16<128, BMODE_NT>(tmA, tmB, Bh, Ch, p, cs);
-    if (layout == SK_LAYOUT_NN) return launch_f16<128, BMODE_NN>(tmA, tmB, Bh, Ch, p, cs);
-    return launch_f16<128, BMODE_LADDER>(tmA, tmB, Bh, Ch, p, cs);
+  // Which matrix feeds which side of the UMMA.  Activations A are always K-major; the
+  // weight operand is K-major (NT), MN-major (NN) or a pre-laid-out image (LADDER).
+  const int w_loader = layout == SK_LAYOUT_NT ? SK_LOAD_TMA_K
+                     : layout == SK_LAYOUT_NN ? SK_LOAD_TMA_MN : SK_LOAD_IMAGE;
+  CUtensorMap tmRow, tmCol;
+  memset(&tmRow, 0, sizeof(tmRow));
+  memset(&tmCol, 0, sizeof(tmCol));
+  auto weight_map = [&](CUtensorMap* tm, int tile_rows) -> int {
+    if (layout == SK_LAYOUT_NT) return sk_make_tmap_f16(tm, B, N, K, prob->ldb, BK, tile_rows);
+    if (layout == SK_LAYOUT_NN) return sk_make_tmap_f16(tm, B, K, N, prob->ldb, 64, BK);
+    return SK_OK;
+  };
+  if (!plan.swap) {
+    p.row_loader = SK_LOAD_TMA_K;
+    p.col_loader = w_loader;
+    st = sk_make_tmap_f16(&tmRow, A, M, K, prob->lda, BK, BM);
+    if (st == SK_OK) st = weight_map(&tmCol, plan.bn);
+    p.col_img = B;
+    if (w_loader != SK_LOAD_TMA_K && (plan.bn % 128) != 0) return SK_ERR_ARG;
   } else {
-    if (layout == SK_LAYOUT_NT) return launch_f16<256, BMODE_NT>(tmA, tmB, Bh, Ch, p, cs);
-    if (layout == SK_LAYOUT_NN) return launch_f16<256, BMODE_NN>(tmA, tmB, Bh, Ch, p, cs);
-    return launch_f16<256, BMODE_LADDER>(tmA, tmB, Bh, Ch, p, cs);
+    p.row_loader = w_loader;
+    p.col_loader = SK_LOAD_TMA_K;
+    st = weight_map(&tmRow, BM);
+    if (st == SK_OK) st = sk_make_tmap_f16(&tmCol, A, M, K, prob->lda, BK, plan.bn);
+    p.row_img = B;
   }
+  if (st != SK_OK) return st;
+  p.row_tx_bytes = ROW_STAGE_BYTES;
+  p.col_tx_bytes = p.col_stage_bytes;
+  p.idesc = umma_idesc_f16(BM, plan.bn, 0) |
+            (p.row_loader == SK_LOAD_TMA_MN ? (1u << 15) : 0u) |
+            (p.col_loader == SK_LOAD_TMA_MN ? (1u << 16) : 0u);
+
+  const int smem_bytes = p.stages * (ROW_STAGE_BYTES + p.col_stage_bytes) + 1024 + CTRL_BYTES;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(sk_gemm_f16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    attr_set[dev & 63] = true;
+  }
+  sk_gemm_f16_kernel<<<p.sched.grid, NUM_THREADS, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
+      tmRow, tmCol, static_cast<__half*>(C), p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
 }

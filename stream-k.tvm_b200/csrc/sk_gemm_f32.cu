@@ -4,13 +4,14 @@
 // CTA walks its share of tiles x K-iterations, partial tiles fixed up across
 // CTAs).  Differences by design: the scheduler integers are kernel parameters
 // (no recompilation per shape), C does not have to be pre-zeroed, partial sums
-// meet in an fp32 workspace, and a deterministic fixup is available.
+// meet in an fp32 workspace, and a deterministic fixup is available: the CTA that
+// starts a split tile waits (with a time limit) for the partials of the CTAs that
+// continue it and adds them in ascending CTA order.
 #include "sk_common.cuh"
 
 namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, THREADS = 256;
-constexpr int SLOT_FLOATS = BM * BN;
 
 template <bool B_IS_NT>
 __global__ void __launch_bounds__(THREADS)
@@ -133,23 +134,23 @@ sk_gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
       }
       __syncthreads();  // s_last is reused by the next segment
     } else {
-      const size_t slot_f = SK_SLOT_BYTES / sizeof(float);
+      const size_t slot_f = SK_SLOT_FLOATS;
       if (seg.k0 != 0) {
         // peer: publish the partial, never wait
-        float* slot = p.ws.part_slots + static_cast<size_t>(pid) * slot_f;
+        float* slot = p.ws.part_slots + static_cast<size_t>(2 * pid) * slot_f;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           __stcg(reinterpret_cast<float4*>(slot + (ty * 4 + i) * BN + tx * 4),
                  make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]));
         __threadfence();
         __syncthreads();
-        if (tid == 0 && pid != p.drop_flag_cta) skptx::st_release_u32(p.ws.flags + pid, 1u);
+        if (tid == 0 && pid != p.drop_flag_cta) skptx::st_release_u32(p.ws.flag_head + pid, 1u);
       } else {
         // owner: add the peers' partials in ascending CTA order
         if (tid == 0) {
           int ok = 1;
           for (int peer = first + 1; peer <= last; ++peer) {
-            if (!sk_wait_flag(p.ws.flags + peer, p.timeout_ns)) {
+            if (!sk_wait_flag(p.ws.flag_head + peer, p.timeout_ns)) {
               sk_report(p.ws.status, SK_ERR_FIXUP_TIMEOUT, seg.tile, peer);
               ok = 0;
               break;
@@ -160,7 +161,7 @@ sk_gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
         __syncthreads();
         if (s_last) {
           for (int peer = first + 1; peer <= last; ++peer) {
-            const float* slot = p.ws.part_slots + static_cast<size_t>(peer) * slot_f;
+            const float* slot = p.ws.part_slots + static_cast<size_t>(2 * peer) * slot_f;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const float4 v =
@@ -172,7 +173,7 @@ sk_gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
         }
         __syncthreads();
         if (tid == 0 && s_last)
-          for (int peer = first + 1; peer <= last; ++peer) p.ws.flags[peer] = 0u;
+          for (int peer = first + 1; peer <= last; ++peer) p.ws.flag_head[peer] = 0u;
       }
     }
   }
@@ -190,7 +191,7 @@ extern "C" int sk_gemm_f32(const sk_problem* prob, const float* A, const float* 
   if (st != SK_OK) return st;
   SkParams p;
   memset(&p, 0, sizeof(p));
-  st = sk_make_sched(prob, 0, num_sms, nullptr, &p.sched);
+  st = sk_make_sched(prob, 0, num_sms, nullptr, &p.sched, nullptr);
   if (st != SK_OK) return st;
   const bool nt = prob->layout == SK_LAYOUT_NT;
   if (prob->lda < prob->K || prob->ldc < prob->N || prob->ldb < (nt ? prob->K : prob->N))

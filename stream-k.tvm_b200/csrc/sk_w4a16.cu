@@ -15,9 +15,11 @@
 //                  the fp16 pair (e(2i), e(2i+1)) in one lop3;
 //   group blocks   [n_block][group] = 128 fp16 scales + 128 uint8 zero-points (384 B).
 //
-// CTA roles (320 threads): warp 0 producer (TMA A tile + bulk copies of the packed
-// blocks), warp 1 MMA issuer, warps 2..5 epilogue, warps 6..9 dequantise the
-// packed block into the 128-byte-swizzled fp16 stage the UMMA descriptor reads.
+// CTA roles (448 threads): warp 0 producer (TMA activation tile + bulk copies of the
+// packed blocks), warp 1 MMA issuer, warps 2..5 epilogue, warps 6..13 dequantise the
+// packed block into the 128-byte-swizzled fp16 stage the UMMA descriptor reads.  For short
+// M the operands are swapped: the dequantised weights feed the UMMA M dimension and the
+// activation tile (M rounded up to 16 rows) the N dimension.
 #include "sk_common.cuh"
 #include "sk_epilogue.cuh"
 
@@ -26,37 +28,33 @@ namespace {
 using namespace skptx;
 
 constexpr int BM = SK_BM;
-constexpr int BN = 128;
 constexpr int BK = 64;
-constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16384
-constexpr int Q_BLOCK_BYTES = BN * BK / 2;   // 4096
-constexpr int SZ_BLOCK_BYTES = BN * 2 + BN;  // 384
-constexpr int B_STAGE_BYTES = BN * BK * 2;   // 16384
-constexpr int LS = 8;                        // load stages (A tile + packed block)
-constexpr int BS = 3;                        // dequantised B stages
-constexpr int NUM_THREADS = 320;
-constexpr int DQ_THREADS = 128;
+constexpr int Q_BLOCK_BYTES = 128 * BK / 2;    // 4096: packed nibbles of 128 weight rows x 64 K
+constexpr int SZ_BLOCK_BYTES = 128 * 2 + 128;  // 384: fp16 scales + uint8 zero-points of a group
+constexpr int W_STAGE_BYTES = 128 * BK * 2;    // 16384: dequantised fp16 stage
+constexpr int MAX_LS = 12;                     // load stages (activation tile + packed block)
+constexpr int BS = 3;                          // dequantised weight stages
+constexpr int DQ_WARPS = 8;
+constexpr int DQ_THREADS = DQ_WARPS * 32;
+constexpr int NUM_THREADS = 64 + SK_EPI_THREADS + DQ_THREADS;
 constexpr int DQ_BAR_ID = 2;
-constexpr int TMEM_COLS = 2 * BN;
-constexpr int OFF_Q = LS * A_STAGE_BYTES;
-constexpr int OFF_SZ = OFF_Q + LS * Q_BLOCK_BYTES;
-constexpr int OFF_B = OFF_SZ + LS * SZ_BLOCK_BYTES;   // 166,912 = 163 * 1024
-constexpr int PIPE_BYTES = OFF_B + BS * B_STAGE_BYTES;
-constexpr int SMEM_BYTES = PIPE_BYTES + 1024 + 256;
-static_assert(OFF_B % 1024 == 0, "dequantised stages must start on a swizzle atom");
+constexpr int CTRL_BYTES = 512;
+constexpr int SMEM_LIMIT = 232448;
 
 struct Ctrl {
-  uint64_t load_full[LS];
-  uint64_t load_empty[LS];
-  uint64_t b_full[BS];
-  uint64_t b_empty[BS];
+  uint64_t load_full[MAX_LS];
+  uint64_t load_empty[MAX_LS];
+  uint64_t w_full[BS];
+  uint64_t w_empty[BS];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t bcast;
+  uint32_t ok[2];
+  SkPending pend[2];
 };
-static_assert(sizeof(Ctrl) <= 256, "Ctrl must fit its reserved space");
+static_assert(sizeof(Ctrl) <= CTRL_BYTES, "Ctrl must fit its reserved space");
 
 // Eight uint4 values of one packed word -> eight fp16 (q - z) * s, in K order.
 // zmagic = half2(1024 + z), s2 = half2(s, s).  The subtraction is exact and the
@@ -81,6 +79,9 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 zmagic, __half
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// Shared memory: [BS dequantised weight stages][LS activation stages][LS packed blocks]
+// [LS group blocks][Ctrl].  p.col_stage_bytes holds the activation stage size in both
+// operand orders (128 rows normally, bn rows when the operands are swapped).
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __restrict__ qblocks,
                      const uint8_t* __restrict__ szblocks, __half* __restrict__ C, const SkParams p) {
@@ -88,11 +89,16 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
-  const uint32_t sA = base;
-  const uint32_t sQ = base + OFF_Q;
-  const uint32_t sSZ = base + OFF_SZ;
-  const uint32_t sB = base + OFF_B;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + PIPE_BYTES);
+  const int LS = p.stages;
+  const int a_stage_bytes = p.row_tx_bytes;        // activation tile bytes per stage
+  const int off_a = BS * W_STAGE_BYTES;
+  const int off_q = off_a + LS * a_stage_bytes;
+  const int off_sz = off_q + LS * Q_BLOCK_BYTES;
+  const uint32_t sW = base;
+  const uint32_t sA = base + off_a;
+  const uint32_t sQ = base + off_q;
+  const uint32_t sSZ = base + off_sz;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + off_sz + LS * SZ_BLOCK_BYTES);
   volatile uint32_t* abort_flag = &ctrl->abort;
 
   const int warp = threadIdx.x >> 5;
@@ -101,6 +107,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const SkSched& s = p.sched;
   const int kblocks = s.iters_per_tile;  // K / 64
   const int groups = kblocks >> 1;       // K / 128
+  const bool swapped = p.transposed != 0;
+  if (threadIdx.x == 0) sk_trace(p, 0);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < LS; ++i) {
@@ -108,8 +116,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       mbar_init(smem_u32(&ctrl->load_empty[i]), 2);  // dequant warps + MMA commit
     }
     for (int i = 0; i < BS; ++i) {
-      mbar_init(smem_u32(&ctrl->b_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->b_empty[i]), 1);
+      mbar_init(smem_u32(&ctrl->w_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->w_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
@@ -117,54 +125,60 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     }
     ctrl->abort = 0u;
     ctrl->bcast = 0u;
+    ctrl->pend[0].tile = -1;
+    ctrl->pend[1].tile = -1;
     fence_mbar_init();
     fence_proxy_async_smem();
     prefetch_tensormap(&tmA);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+    tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+  if (threadIdx.x == 0) sk_trace(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
     if (lane == 0) {
+      bool traced = false;
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
       int ls = 0;
       uint32_t lph = 0;
       bool ok = true;
+      const uint32_t tx = a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
       while (ok && sk_next(s, pid, cur, seg)) {
-        int tm, tn;
-        sk_tile_mn(s, seg.tile, tm, tn);
-        const int m0 = tm * BM;
+        int tr, tc;
+        sk_tile_mn(s, seg.tile, tr, tc);
+        const int nblk = swapped ? tr : tc;                  // 128-row block of the weight
+        const int a_row0 = swapped ? tc * p.bn : tr * BM;    // first activation row of the tile
         for (int k = seg.k0; k < seg.k1; ++k) {
           const uint32_t full = smem_u32(&ctrl->load_full[ls]);
           if (!sk_wait_bar(smem_u32(&ctrl->load_empty[ls]), lph ^ 1u, abort_flag, p, ls, 0)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, p.a_tx_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES);
-          tma_load_2d(sA + ls * A_STAGE_BYTES, &tmA, full, k * BK, m0);
+          mbar_arrive_expect_tx(full, tx);
+          tma_load_2d(sA + ls * a_stage_bytes, &tmA, full, k * BK, a_row0);
           bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
-                       qblocks + (static_cast<size_t>(tn) * kblocks + k) * Q_BLOCK_BYTES,
+                       qblocks + (static_cast<size_t>(nblk) * kblocks + k) * Q_BLOCK_BYTES,
                        Q_BLOCK_BYTES, full);
           bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
-                       szblocks + (static_cast<size_t>(tn) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
+                       szblocks + (static_cast<size_t>(nblk) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
                        SZ_BLOCK_BYTES, full);
           if (++ls == LS) { ls = 0; lph ^= 1u; }
+          if (!traced) { sk_trace(p, 2); traced = true; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t IDESC = umma_idesc_f16(BM, BN, 0);
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
@@ -174,27 +188,30 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       while (ok && sk_next(s, pid, cur, seg)) {
         const uint32_t buf = nseg & 1u;
         const uint32_t acc_ph = (nseg >> 1) & 1u;
-        if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 32 + buf, 1))
+        if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
         for (int k = seg.k0; k < seg.k1; ++k) {
-          if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 8 + ls, 1) ||
-              !sk_wait_bar(smem_u32(&ctrl->b_full[bs]), bph, abort_flag, p, 16 + bs, 1)) {
+          if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 32 + ls, 1) ||
+              !sk_wait_bar(smem_u32(&ctrl->w_full[bs]), bph, abort_flag, p, 48 + bs, 1)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = sA + ls * A_STAGE_BYTES;
-          const uint32_t b_addr = sB + bs * B_STAGE_BYTES;
+          if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
+          const uint32_t act = sA + ls * a_stage_bytes;
+          const uint32_t wgt = sW + bs * W_STAGE_BYTES;
+          const uint32_t a_addr = swapped ? wgt : act;   // UMMA M side
+          const uint32_t b_addr = swapped ? act : wgt;   // UMMA N side
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
             const uint64_t da = umma_desc_sw128(a_addr + kk * 32, 16, 1024);
             const uint64_t db = umma_desc_sw128(b_addr + kk * 32, 16, 1024);
-            umma_f16_ss(d_tmem, da, db, IDESC, (k > seg.k0 || kk > 0) ? 1u : 0u);
+            umma_f16_ss(d_tmem, da, db, p.idesc, (k > seg.k0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&ctrl->load_empty[ls]));
-          umma_commit(smem_u32(&ctrl->b_empty[bs]));
+          umma_commit(smem_u32(&ctrl->w_empty[bs]));
           if (++ls == LS) { ls = 0; lph ^= 1u; }
           if (++bs == BS) { bs = 0; bph ^= 1u; }
         }
@@ -202,14 +219,19 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
         umma_commit(smem_u32(&ctrl->tmem_full[buf]));
         ++nseg;
       }
+      sk_trace(p, 4);
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------- epilogue
-    sk_epilogue_loop<BN>(p, C, pid, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                         smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag);
+    sk_epilogue_loop(p, C, pid, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                     smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   } else {
     // ------------------------------------------------------------- dequantise
-    const int r = (warp - 6) * 32 + lane;  // weight row inside the tile
+    // Thread (h, r): weight row r of the tile, K half h (32 values = 4 packed words).
+    const int dtid = (warp - 6) * 32 + lane;
+    const int h = dtid >> 7;
+    const int r = dtid & 127;
+    const int sw = r & 7;
     SkCursor cur;
     sk_cursor_init(s, pid, cur);
     SkSeg seg;
@@ -219,31 +241,30 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     while (sk_next(s, pid, cur, seg)) {
       for (int k = seg.k0; k < seg.k1; ++k) {
         if (!dead) {
-          if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 40 + ls, 3) ||
-              !sk_wait_bar(smem_u32(&ctrl->b_empty[bs]), bph ^ 1u, abort_flag, p, 48 + bs, 3))
+          if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 64 + ls, 3) ||
+              !sk_wait_bar(smem_u32(&ctrl->w_empty[bs]), bph ^ 1u, abort_flag, p, 80 + bs, 3))
             dead = true;
         }
         if (!dead) {
-          const uint8_t* q = smem + OFF_Q + ls * Q_BLOCK_BYTES;
-          const uint8_t* sz = smem + OFF_SZ + ls * SZ_BLOCK_BYTES;
-          const uint4 w0 = *reinterpret_cast<const uint4*>(q + r * 16);
-          const uint4 w1 = *reinterpret_cast<const uint4*>(q + 2048 + r * 16);
+          const uint8_t* q = smem + off_q + ls * Q_BLOCK_BYTES;
+          const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
+          const uint4 w = *reinterpret_cast<const uint4*>(q + h * 2048 + r * 16);
           const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
           const uint32_t z = sz[256 + r];
           const __half2 s2 = __half2half2(sc);
           const uint32_t zm = 0x64006400u | z | (z << 16);
           const __half2 zmagic = *reinterpret_cast<const __half2*>(&zm);
-          uint8_t* brow = smem + OFF_B + bs * B_STAGE_BYTES + r * 128;
-          const int sw = r & 7;
-          const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          uint8_t* wrow = smem + bs * W_STAGE_BYTES + r * 128;
+          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4*>(brow + ((c ^ sw) << 4)) = dequant_word(words[c], zmagic, s2);
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(wrow + (((h * 4 + j) ^ sw) << 4)) =
+                dequant_word(words[j], zmagic, s2);
           fence_proxy_async_smem();  // generic-proxy stores -> visible to the UMMA reads
         }
         named_bar_sync(DQ_BAR_ID, DQ_THREADS);
-        if (r == 0) {
-          mbar_arrive(smem_u32(&ctrl->b_full[bs]));
+        if (dtid == 0) {
+          mbar_arrive(smem_u32(&ctrl->w_full[bs]));
           mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
         }
         if (++ls == LS) { ls = 0; lph ^= 1u; }
@@ -255,6 +276,9 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   // ------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
+  // the split tiles it took part in.
+  sk_reduce_pending(p, C, pid, ctrl->pend, ctrl->ok);
   if (warp == 1) {
     if (*abort_flag) {
       const unsigned long long t0 = globaltimer_ns();
@@ -262,7 +286,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     }
     tc_fence_after();
     __syncwarp();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    tmem_dealloc(tmem_base, p.tmem_cols);
+    if (lane == 0) sk_trace(p, 7);
   }
 }
 
@@ -357,6 +382,8 @@ inline int q4_nblocks(int N) { return (N + 255) / 256 * 2; }
 
 int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                      uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
+void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_stages,
+                         int reserved_bytes);
 
 extern "C" size_t sk_q4_bytes(int N, int K) {
   if (N <= 0 || K <= 0 || (K % 128) != 0) return 0;
@@ -404,7 +431,6 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
                              void* ws, size_t ws_bytes, void* stream) {
   if (!prob || !A || !packed || !C) return SK_ERR_ARG;
   if (prob->fixup != SK_FIXUP_ATOMIC && prob->fixup != SK_FIXUP_BLOCK_REDUCE) return SK_ERR_ARG;
-  if (prob->tile_n != 0 && prob->tile_n != BN) return SK_ERR_ARG;
   int num_sms = 0, dev_sms = 0;
   int st = sk_resolve_grid(prob, &num_sms, &dev_sms);
   if (st != SK_OK) return st;
@@ -417,40 +443,53 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   if (!ws || ws_bytes < sk_ws_total_bytes(dev_sms)) return SK_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return SK_ERR_ALIGN;
 
-  sk_problem q = *prob;
-  q.tile_n = BN;
   SkParams p;
   memset(&p, 0, sizeof(p));
-  st = sk_make_sched(&q, 1, num_sms, nullptr, &p.sched);
+  SkPlan plan;
+  st = sk_make_sched(prob, 2, num_sms, nullptr, &p.sched, &plan);
   if (st != SK_OK) return st;
   p.M = M; p.N = N; p.K = K;
   p.lda = prob->lda; p.ldb = 0; p.ldc = prob->ldc;
+  p.rows = plan.rows; p.cols = plan.cols;
+  p.transposed = plan.swap;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
   p.drop_flag_cta = prob->test_drop_flag_cta;
   p.timeout_ns = (prob->fixup_timeout_us > 0 ? static_cast<unsigned long long>(prob->fixup_timeout_us)
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);
+  p.trace = sk_trace_buffer();
+  // The activation tile has 128 rows normally, bn rows when the operands are swapped.
+  const int a_rows = plan.swap ? plan.bn : BM;
+  const int a_stage_bytes = a_rows * BK * 2;
+  sk_fill_tile_params(&p, plan.bn, 0, 1, 0);   // TMEM layout only; stages set below
+  int ls = (SMEM_LIMIT - 1024 - CTRL_BYTES - BS * W_STAGE_BYTES) /
+           (a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES);
+  if (ls > MAX_LS) ls = MAX_LS;
+  p.stages = ls;
+  p.row_tx_bytes = a_stage_bytes;
+  p.col_stage_bytes = a_stage_bytes;
+  p.idesc = umma_idesc_f16(BM, plan.bn, 0);
 
   CUtensorMap tmA;
-  const int a_rows = M >= BM ? BM : ((M + 7) & ~7);
-  p.a_tx_bytes = a_rows * BK * 2;
   st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, a_rows);
   if (st != SK_OK) return st;
   const int nb = q4_nblocks(N), kb = K / 64;
   const uint8_t* qb = static_cast<const uint8_t*>(packed);
   const uint8_t* sz = qb + static_cast<size_t>(nb) * kb * Q_BLOCK_BYTES;
 
+  const int smem_bytes = BS * W_STAGE_BYTES + ls * (a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES) +
+                         1024 + CTRL_BYTES;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(sk_gemm_w4a16_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
-  sk_gemm_w4a16_kernel<<<p.sched.grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+  sk_gemm_w4a16_kernel<<<p.sched.grid, NUM_THREADS, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
       tmA, qb, sz, static_cast<__half*>(C), p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return sk_set_cuda_error(e);

@@ -96,26 +96,46 @@ def device_info(device: int = 0) -> dict:
 
 
 # --------------------------------------------------------------------------- helpers
-def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, tile_n, num_sms, group_m,
-             timeout_us, drop_flag_cta) -> L.SkProblem:
+_OPTION_KEYS = ("tile_m", "tile_n", "num_sms", "group_m", "out", "timeout_us", "_drop_flag_cta")
+
+
+def _options(kw: dict) -> dict:
+    """Common keyword arguments of every GEMM entry point:
+    tile_m / tile_n  tile extents (None = choose; tile_m < 128 puts the weights on the UMMA
+                     M dimension, the short-M form), num_sms (grid bound), group_m (tile
+                     rasterisation), out (result buffer), timeout_us (bound of every device
+                     wait), _drop_flag_cta (test hook)."""
+    unknown = set(kw) - set(_OPTION_KEYS)
+    if unknown:
+        raise TypeError(f"unexpected keyword argument(s): {sorted(unknown)}")
+    o = {k: kw.get(k) for k in _OPTION_KEYS}
+    if o["_drop_flag_cta"] is None:
+        o["_drop_flag_cta"] = -1
+    return o
+
+
+def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkProblem:
     if schedule not in L.SCHEDULES:
         raise ValueError(f"schedule must be one of {sorted(L.SCHEDULES)}, got {schedule!r}")
     if fixup not in L.FIXUPS:
         raise ValueError(f"fixup must be one of {sorted(L.FIXUPS)}, got {fixup!r}")
     return L.SkProblem(M=M, N=N, K=K, lda=lda, ldb=ldb, ldc=ldc, layout=L.LAYOUTS[layout],
                        schedule=L.SCHEDULES[schedule], fixup=L.FIXUPS[fixup],
-                       tile_n=int(tile_n or 0), num_sms=int(num_sms or 0),
-                       group_m=int(group_m or 0), fixup_timeout_us=int(timeout_us or 0),
-                       test_drop_flag_cta=int(drop_flag_cta))
+                       tile_m=int(o["tile_m"] or 0), tile_n=int(o["tile_n"] or 0),
+                       num_sms=int(o["num_sms"] or 0), group_m=int(o["group_m"] or 0),
+                       fixup_timeout_us=int(o["timeout_us"] or 0),
+                       test_drop_flag_cta=int(o["_drop_flag_cta"]))
 
 
 def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "hybrid",
-                  tile_n: int | None = None, num_sms: int = 148, group_m: int | None = None) -> dict:
-    """Host scheduler integers (streamk_fp16.py:83-113) for a problem; needs no GPU."""
-    prob = _problem(M, N, K, K, K, N, "nt", schedule, "atomic", tile_n, 0, group_m, 0, -1)
+                  num_sms: int = 148, **kw) -> dict:
+    """Host scheduler integers (streamk_fp16.py:83-113) and the tile plan for a problem;
+    needs no GPU.  kind: "f32", "f16" or "w4a16"."""
+    o = _options(kw)
+    prob = _problem(M, N, K, K, K, N, "nt", schedule, "atomic", o)
     info = L.SkScheduleInfo()
-    L.check(L.load().sk_schedule(C.byref(prob), 0 if kind == "f32" else 1, num_sms, C.byref(info)),
-            "sk_schedule")
+    kinds = {"f32": 0, "f16": 1, "w4a16": 2}
+    L.check(L.load().sk_schedule(C.byref(prob), kinds[kind], num_sms, C.byref(info)), "sk_schedule")
     return info.as_dict()
 
 
@@ -164,14 +184,13 @@ def _aligned16(t: torch.Tensor) -> torch.Tensor:
 
 # --------------------------------------------------------------------------- fp32
 def streamk_fp32(A: torch.Tensor, B: torch.Tensor, *, fixup: str = "atomic",
-                 schedule: str = "hybrid", trans_b: bool = False, num_sms: int | None = None,
-                 group_m: int | None = None, out: torch.Tensor | None = None,
-                 timeout_us: int | None = None, _drop_flag_cta: int = -1) -> torch.Tensor:
+                 schedule: str = "hybrid", trans_b: bool = False, **kw) -> torch.Tensor:
     """C = A @ B in fp32 (FFMA, no TF32).  A [M,K]; B [K,N] (or [N,K] with trans_b).
 
     Mirrors `tl_matmul_streamk(..., "float32", "float32", "float32", ...)` of
     streamk_fp32.py:57-202.  `schedule="hybrid"` is the reference's split.
     """
+    o = _options(kw)
     _check_matrix("A", A, torch.float32)
     _check_matrix("B", B, torch.float32)
     A = _rowmajor(A)
@@ -183,9 +202,9 @@ def streamk_fp32(A: torch.Tensor, B: torch.Tensor, *, fixup: str = "atomic",
         Kb, N = B.shape
     if K != Kb:
         raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} B {tuple(B.shape)}")
-    Cout = _out(out, M, N, torch.float32, A.device)
+    Cout = _out(o["out"], M, N, torch.float32, A.device)
     prob = _problem(M, N, K, A.stride(0), B.stride(0), Cout.stride(0), "nt" if trans_b else "nn",
-                    schedule, fixup, 0, num_sms, group_m, timeout_us, _drop_flag_cta)
+                    schedule, fixup, o)
     with torch.cuda.device(A.device):
         ws = _workspace(A.device)
         L.check(L.load().sk_gemm_f32(C.byref(prob), A.data_ptr(), B.data_ptr(), Cout.data_ptr(),
@@ -195,8 +214,8 @@ def streamk_fp32(A: torch.Tensor, B: torch.Tensor, *, fixup: str = "atomic",
 
 
 # --------------------------------------------------------------------------- fp16
-def _gemm_f16(A, B, layout, *, fixup, schedule, tile_n, num_sms, group_m, out, timeout_us,
-              _drop_flag_cta, N=None):
+def _gemm_f16(A, B, layout, fixup, schedule, kw):
+    o = _options(kw)
     _check_matrix("A", A, torch.float16)
     M, K = A.shape
     if layout == "ladder":
@@ -222,9 +241,8 @@ def _gemm_f16(A, B, layout, *, fixup, schedule, tile_n, num_sms, group_m, out, t
             # NN: rows of B are K; the N pitch must be a multiple of 8 halves
             Bt = _aligned16(_rowmajor(_pad_k8(B, 0)))
         ldb = Bt.stride(0)
-    Cout = _out(out, M, N, torch.float16, A.device)
-    prob = _problem(M, N, A.shape[1], A.stride(0), ldb, Cout.stride(0), layout, schedule, fixup,
-                    tile_n, num_sms, group_m, timeout_us, _drop_flag_cta)
+    Cout = _out(o["out"], M, N, torch.float16, A.device)
+    prob = _problem(M, N, A.shape[1], A.stride(0), ldb, Cout.stride(0), layout, schedule, fixup, o)
     with torch.cuda.device(A.device):
         ws = _workspace(A.device)
         L.check(L.load().sk_gemm_f16(C.byref(prob), A.data_ptr(), Bt.data_ptr(), Cout.data_ptr(),
@@ -233,22 +251,19 @@ def _gemm_f16(A, B, layout, *, fixup, schedule, tile_n, num_sms, group_m, out, t
     return Cout
 
 
-def streamk_fp16_nt(A, B, *, fixup="atomic", schedule="hybrid", tile_n=None, num_sms=None,
-                    group_m=None, out=None, timeout_us=None, _drop_flag_cta=-1):
+def streamk_fp16_nt(A, B, *, fixup="atomic", schedule="hybrid", **kw):
     """C = A @ B.T, fp16 in, fp32 accumulate, fp16 out.  A [M,K], B [N,K].
 
     Mirrors `tl_matmul_streamk(M, N, K, streamk_tiles, "float16", "float16", ...)` +
     `tl_mod(A, B, C)` of streamk_fp16.py:116-387 and streamk_fp16_nt.py:57-192.
+    Keyword options: see _options().
     """
-    return _gemm_f16(A, B, "nt", fixup=fixup, schedule=schedule, tile_n=tile_n, num_sms=num_sms,
-                     group_m=group_m, out=out, timeout_us=timeout_us, _drop_flag_cta=_drop_flag_cta)
+    return _gemm_f16(A, B, "nt", fixup, schedule, kw)
 
 
-def streamk_fp16_nn(A, B, *, fixup="atomic", schedule="hybrid", tile_n=None, num_sms=None,
-                    group_m=None, out=None, timeout_us=None, _drop_flag_cta=-1):
+def streamk_fp16_nn(A, B, *, fixup="atomic", schedule="hybrid", **kw):
     """C = A @ B, fp16.  A [M,K], B [K,N]  (streamk_fp16_nn.py:57-177)."""
-    return _gemm_f16(A, B, "nn", fixup=fixup, schedule=schedule, tile_n=tile_n, num_sms=num_sms,
-                     group_m=group_m, out=out, timeout_us=timeout_us, _drop_flag_cta=_drop_flag_cta)
+    return _gemm_f16(A, B, "nn", fixup, schedule, kw)
 
 
 def streamk_fp16_atomic(A, B, **kw):
@@ -289,12 +304,9 @@ def ladder_prepack(B: torch.Tensor) -> LadderWeight:
     return LadderWeight(out, N, K)
 
 
-def streamk_fp16_ladder(A, LB: LadderWeight, *, fixup="atomic", schedule="hybrid", tile_n=None,
-                        num_sms=None, group_m=None, out=None, timeout_us=None, _drop_flag_cta=-1):
+def streamk_fp16_ladder(A, LB: LadderWeight, *, fixup="atomic", schedule="hybrid", **kw):
     """C = A @ W.T with W pre-laid-out (streamk_fp16_ladder.py:137-486)."""
-    return _gemm_f16(A, LB, "ladder", fixup=fixup, schedule=schedule, tile_n=tile_n,
-                     num_sms=num_sms, group_m=group_m, out=out, timeout_us=timeout_us,
-                     _drop_flag_cta=_drop_flag_cta)
+    return _gemm_f16(A, LB, "ladder", fixup, schedule, kw)
 
 
 def streamk_fp16_ladder_block_reduce(A, LB: LadderWeight, **kw):
@@ -365,12 +377,11 @@ def dequant_w4(QLB: PackedQ4) -> torch.Tensor:
 
 
 def streamk_fp16_ladder_block_reduce_q4(A, QLB: PackedQ4, *, fixup="block_reduce",
-                                        schedule="hybrid", tile_n=None, num_sms=None,
-                                        group_m=None, out=None, timeout_us=None,
-                                        _drop_flag_cta=-1):
+                                        schedule="hybrid", **kw):
     """W4A16: C = A @ ((q - z) * s).T, fp16 activations, uint4 weights.
 
     Mirrors `tl_mod(A, QLB, C)` of streamk_fp16_ladder_block_reduce_q4.py:143-599."""
+    o = _options(kw)
     _check_matrix("A", A, torch.float16)
     if not isinstance(QLB, PackedQ4):
         raise TypeError("QLB must come from q4_prepack()")
@@ -378,9 +389,8 @@ def streamk_fp16_ladder_block_reduce_q4(A, QLB: PackedQ4, *, fixup="block_reduce
     if K != QLB.K:
         raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} weight K={QLB.K}")
     A = _aligned16(_rowmajor(A))
-    Cout = _out(out, M, QLB.N, torch.float16, A.device)
-    prob = _problem(M, QLB.N, K, A.stride(0), 0, Cout.stride(0), "nt", schedule, fixup, tile_n,
-                    num_sms, group_m, timeout_us, _drop_flag_cta)
+    Cout = _out(o["out"], M, QLB.N, torch.float16, A.device)
+    prob = _problem(M, QLB.N, K, A.stride(0), 0, Cout.stride(0), "nt", schedule, fixup, o)
     with torch.cuda.device(A.device):
         ws = _workspace(A.device)
         L.check(L.load().sk_gemm_w4a16(C.byref(prob), A.data_ptr(), QLB.data.data_ptr(),

@@ -109,6 +109,33 @@ def test_fp16_grid_sizes(sms):
                ref, TOL16)
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64])
+def test_fp16_short_m_swapped_operands(M):
+    """Short M: the weights feed the UMMA M dimension and C is stored transposed."""
+    N, K = 1000, 1032
+    A, B = _rand16(M, N, K, seed=M)
+    ref = oracle.gemm_ref(A, B, "nt")
+    assert sk.schedule_info(M, N, K)["swap_ab"] == 1
+    for fixup in FIXUPS:
+        for schedule in SCHEDULES:
+            _check(sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), fixup=fixup, schedule=schedule), ref, TOL16)
+    # the same problem with the operands in the ordinary order, and swapped with several row tiles
+    _check(sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), tile_m=128, schedule="streamk"), ref, TOL16)
+    LB = sk.ladder_prepack(B.to(DEV))
+    _check(sk.streamk_fp16_ladder(A.to(DEV), LB, schedule="streamk", fixup="block_reduce"), ref, TOL16)
+    Bn = B.t().contiguous()
+    _check(sk.streamk_fp16_nn(A.to(DEV), Bn.to(DEV), schedule="streamk"), ref, TOL16)
+
+
+def test_fp16_explicit_swap_with_several_m_tiles():
+    A, B = _rand16(200, 520, 1000, seed=77)
+    ref = oracle.gemm_ref(A, B, "nt")
+    for tile_m in (16, 64, 112, 208, 256):
+        for fixup in FIXUPS:
+            _check(sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), tile_m=tile_m, fixup=fixup, schedule="streamk"),
+                   ref, TOL16)
+
+
 def test_fp16_odd_k_is_padded():
     A, B = _rand16(20, 40, 77, seed=3)
     _check(sk.streamk_fp16_nt(A.to(DEV), B.to(DEV)), oracle.gemm_ref(A, B, "nt"), TOL16)
@@ -181,6 +208,18 @@ def test_w4a16_gemm(shape):
     for schedule, fixup in (("dp", "atomic"), ("streamk", "block_reduce"), ("hybrid", "atomic"),
                             ("hybrid_dp_first", "block_reduce")):
         _check(sk.streamk_fp16_ladder_block_reduce_q4(A, P, schedule=schedule, fixup=fixup), ref, TOL16)
+
+
+def test_w4a16_both_operand_orders():
+    c = oracle.make_case(4, shape=(48, 640, 1024))
+    ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
+    P = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
+    A = c["A"].to(DEV)
+    assert sk.schedule_info(48, 640, 1024, kind="w4a16")["swap_ab"] == 1
+    for tile_m in (None, 128, 16, 64):
+        for fixup in FIXUPS:
+            _check(sk.streamk_fp16_ladder_block_reduce_q4(A, P, schedule="streamk", fixup=fixup, tile_m=tile_m),
+                   ref, TOL16)
 
 
 def test_w4a16_reference_semantics_no_scale_no_zero():

@@ -102,3 +102,39 @@ def test_bad_arguments(lib):
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_ARG
     prob = L.SkProblem(M=4, N=4, K=4, schedule=1, tile_n=64)
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_ARG
+
+
+def test_short_m_swaps_operands(lib):
+    from streamk_b200 import _lib as L
+    for M, want_tm in ((1, 16), (16, 16), (17, 32), (33, 48), (64, 64)):
+        prob = L.SkProblem(M=M, N=4096, K=4096, schedule=1)
+        info = L.SkScheduleInfo()
+        assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+        d = info.as_dict()
+        assert (d["swap_ab"], d["tile_m"], d["tile_n"]) == (1, want_tm, 128)
+        assert (d["tiles_m"], d["tiles_n"], d["total_tiles"]) == (1, 32, 32)
+        assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0      # W4A16 too
+        assert info.swap_ab == 1
+    prob = L.SkProblem(M=65, N=4096, K=4096, schedule=1)
+    info = L.SkScheduleInfo()
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    assert (info.swap_ab, info.tile_m, info.tile_n) == (0, 128, 128)
+    # explicit forms
+    prob = L.SkProblem(M=200, N=4096, K=4096, schedule=1, tile_m=208)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    assert (info.swap_ab, info.tile_m, info.tiles_m, info.tiles_n) == (1, 208, 1, 32)
+    prob = L.SkProblem(M=16, N=4096, K=4096, schedule=1, tile_m=128)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    assert info.swap_ab == 0
+    prob = L.SkProblem(M=16, N=4096, K=4096, schedule=1, tile_m=24)      # not a multiple of 16
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_ARG
+    # tile coordinates are reported in logical (M, N) order either way
+    prob = L.SkProblem(M=100, N=1000, K=512, schedule=1, tile_m=64)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    seen = set()
+    tm, tn = C.c_int(), C.c_int()
+    for t in range(info.total_tiles):
+        assert lib.sk_tile_coords(C.byref(info), t, C.byref(tm), C.byref(tn)) == 0
+        assert 0 <= tm.value < info.tiles_m == 2 and 0 <= tn.value < info.tiles_n == 8
+        seen.add((tm.value, tn.value))
+    assert len(seen) == 16
