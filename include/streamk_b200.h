@@ -144,6 +144,21 @@ int sk_poll_status(const void* ws, sk_status* host_out, void* stream);
 int sk_gemm_f32(const sk_problem* p, const float* A, const float* B, float* C,
                 void* ws, size_t ws_bytes, void* stream);
 
+/* No counterpart in the reference.  sk_gemm_f32 for callers that cannot hand over a
+ * workspace because they must not allocate: hosts with a memory budget fixed at start-up,
+ * code in regions where cudaMalloc is forbidden, plugin interfaces that pass operands
+ * only.  The fixup scratch is a fixed array inside the library image (about 6 MB, held by
+ * every GPU that loads the library until the process exits), sized for 16 persistent
+ * CTAs: num_sms == 0 means 16 here and num_sms > 16 is refused with SK_ERR_LIMIT.  The
+ * call allocates nothing (no cudaMalloc / cudaFree, no allocating library routine).  The
+ * first call on a device looks the array's address up (cudaGetSymbolAddress); make that
+ * first call outside stream capture.  All calls on a device share the one array: calls
+ * that can overlap on the GPU (different streams, different host threads) race and must
+ * be serialised by the caller.  host_status may be NULL; otherwise the device status
+ * word is copied into it asynchronously (valid once the stream is synchronised).       */
+int sk_gemm_f32_noalloc(const sk_problem* p, const float* A, const float* B, float* C,
+                        sk_status* host_status, void* stream);
+
 /* C[M,N] = A[M,K] . op(B), fp16 in / fp32 accumulate in TMEM / fp16 out on
  * tcgen05 tensor cores.  Replaces tl_mod(A, B, C) of streamk_fp16.py:116-387
  * (NT), streamk_fp16_nn.py (NN), streamk_fp16_block_reduce.py and

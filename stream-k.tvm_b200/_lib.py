@@ -64,6 +64,7 @@ SIGNATURES = {
     "sk_workspace_init": (C.c_int, [_P, C.c_size_t, _P]),
     "sk_poll_status": (C.c_int, [_P, C.POINTER(SkStatus), _P]),
     "sk_gemm_f32": (C.c_int, [C.POINTER(SkProblem), _P, _P, _P, _P, C.c_size_t, _P]),
+    "sk_gemm_f32_noalloc": (C.c_int, [C.POINTER(SkProblem), _P, _P, _P, C.POINTER(SkStatus), _P]),
     "sk_gemm_f16": (C.c_int, [C.POINTER(SkProblem), _P, _P, _P, _P, C.c_size_t, _P]),
     "sk_ladder_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "sk_prepack_ladder": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P]),

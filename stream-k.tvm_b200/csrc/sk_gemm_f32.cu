@@ -214,3 +214,111 @@ extern "C" int sk_gemm_f32(const sk_problem* prob, const float* A, const float* 
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }
+
+// ---------------------------------------------------------------------------------
+// sk_gemm_f32_noalloc: the same kernel for callers that must not allocate.
+//
+// Some hosts of this library cannot provide a workspace: code running under a memory
+// budget fixed at start-up, inside a region where cudaMalloc is forbidden (it
+// synchronises the device and cannot appear during stream capture), or behind a plugin
+// interface that hands over nothing but operand pointers.  For them the fixup scratch
+// lives in the library image itself, in the array below.  It is sized for at most
+// SK_NOALLOC_MAX_CTAS persistent CTAs, and every GPU that loads the library carries these
+// ~6 MB until the process exits, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------------
+#include <mutex>
+
+namespace {
+
+constexpr int SK_NOALLOC_MAX_CTAS = 16;
+constexpr size_t SK_NOALLOC_HEADER = 1024;   // status word, counters, done, flag_head, flag_tail
+constexpr size_t SK_NOALLOC_BYTES =
+    SK_NOALLOC_HEADER + 3 * static_cast<size_t>(SK_NOALLOC_MAX_CTAS) * SK_SLOT_BYTES;
+static_assert(SK_WS_HEADER + 4 * sizeof(uint32_t) * SK_NOALLOC_MAX_CTAS <= SK_NOALLOC_HEADER,
+              "header does not fit");
+
+// In host code this name is only a handle for the runtime: it is not a device address and
+// must never be passed to a kernel.  The address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SK_NOALLOC_BYTES];
+
+std::mutex g_noalloc_mutex;
+void* g_noalloc_ptr[64] = {nullptr};   // per device, filled on that device's first call
+
+}  // namespace
+
+extern "C" int sk_gemm_f32_noalloc(const sk_problem* prob, const float* A, const float* B, float* C,
+                                   sk_status* host_status, void* stream) {
+  if (!prob || !A || !B || !C) return SK_ERR_ARG;
+  if (prob->layout != SK_LAYOUT_NN && prob->layout != SK_LAYOUT_NT) return SK_ERR_ARG;
+  if (prob->fixup != SK_FIXUP_ATOMIC && prob->fixup != SK_FIXUP_BLOCK_REDUCE) return SK_ERR_ARG;
+  // The scratch holds slots for SK_NOALLOC_MAX_CTAS CTAs: a larger grid is refused, and
+  // "all SMs" (num_sms == 0) means the maximum here.
+  if (prob->num_sms > SK_NOALLOC_MAX_CTAS) return SK_ERR_LIMIT;
+  sk_problem q = *prob;
+  if (q.num_sms <= 0) q.num_sms = SK_NOALLOC_MAX_CTAS;
+  int num_sms = 0, dev_sms = 0;
+  int st = sk_resolve_grid(&q, &num_sms, &dev_sms);
+  if (st != SK_OK) return st;
+  SkParams p;
+  memset(&p, 0, sizeof(p));
+  st = sk_make_sched(&q, 0, num_sms, nullptr, &p.sched, nullptr);
+  if (st != SK_OK) return st;
+  if (p.sched.grid > SK_NOALLOC_MAX_CTAS) return SK_ERR_LIMIT;
+  const bool nt = q.layout == SK_LAYOUT_NT;
+  if (q.lda < q.K || q.ldc < q.N || q.ldb < (nt ? q.K : q.N)) return SK_ERR_SHAPE;
+
+  // Set-up, once per device, with that device current: ask the runtime where the array
+  // lives on this device.  (Also the reason the first call on a device should be made
+  // outside stream capture: the lookup may load the module.)
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  if (dev < 0 || dev >= 64) return SK_ERR_ARG;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (e != cudaSuccess) return sk_set_cuda_error(e);
+      g_noalloc_ptr[dev] = ptr;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  char* base = static_cast<char*>(scratch);
+  SkWorkspace w;
+  w.status = reinterpret_cast<uint32_t*>(base);
+  w.counters = reinterpret_cast<uint32_t*>(base + SK_WS_HEADER);
+  w.done = w.counters + SK_NOALLOC_MAX_CTAS;
+  w.flag_head = w.done + SK_NOALLOC_MAX_CTAS;
+  w.flag_tail = w.flag_head + SK_NOALLOC_MAX_CTAS;
+  w.acc_slots = reinterpret_cast<float*>(base + SK_NOALLOC_HEADER);
+  w.part_slots = w.acc_slots + static_cast<size_t>(SK_NOALLOC_MAX_CTAS) * SK_SLOT_FLOATS;
+
+  // The array keeps whatever the previous call left.  Status word, counters, flags and the
+  // accumulation slots must start at zero (an earlier call that timed out may have left
+  // them dirty); the partial slots need no clearing.  Stream-ordered, allocates nothing.
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  e = cudaMemsetAsync(base, 0,
+                      SK_NOALLOC_HEADER + static_cast<size_t>(SK_NOALLOC_MAX_CTAS) * SK_SLOT_BYTES, cs);
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+
+  p.M = q.M; p.N = q.N; p.K = q.K;
+  p.lda = q.lda; p.ldb = q.ldb; p.ldc = q.ldc;
+  p.fixup = q.fixup;
+  p.drop_flag_cta = q.test_drop_flag_cta;
+  p.timeout_ns = (q.fixup_timeout_us > 0 ? static_cast<unsigned long long>(q.fixup_timeout_us)
+                                         : 2000000ULL) * 1000ULL;
+  p.ws = w;
+  if (nt)
+    sk_gemm_f32_kernel<true><<<p.sched.grid, THREADS, 0, cs>>>(A, B, C, p);
+  else
+    sk_gemm_f32_kernel<false><<<p.sched.grid, THREADS, 0, cs>>>(A, B, C, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  if (host_status) {
+    e = cudaMemcpyAsync(host_status, w.status, sizeof(sk_status), cudaMemcpyDeviceToHost, cs);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+  }
+  return SK_OK;
+}
