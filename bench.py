@@ -48,8 +48,9 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """Samples nvidia-smi clocks and throttle reasons; stop(t0, t1) keeps the samples whose
+    timestamp falls inside the timed region [t0, t1] (wall clock, seconds)."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -61,12 +62,13 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                 "-i", str(self.gpu), "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
                 text=True)
         except OSError:
             self.proc = None
 
-    def stop(self) -> dict:
+    def stop(self, t0: float, t1: float) -> dict:
+        import datetime
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -75,23 +77,32 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, smmax, power, reasons = [], [], [], set()
+        rows = []
         for line in out.strip().split("\n"):
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); smmax.append(float(f[2])); power.append(float(f[3]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), float(f[3]), f[5:9]))
             except ValueError:
                 continue
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        note = "samples inside the timed region"
+        if not inside:                       # region shorter than the sampling period
+            inside = [r for r in rows if t0 - 0.05 <= r[0] <= t1 + 0.05] or rows
+            note = "no sample fell inside the timed region; nearest samples used"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        reasons = set()
+        for r in inside:
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                "sw_power_cap"), f[5:9]):
+                                "sw_power_cap"), r[4]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smmax), "samples": len(sm),
-                "power_w_max": max(power), "reasons": sorted(reasons)}
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": max(r[2] for r in inside),
+                "samples": len(inside), "power_w_max": max(r[3] for r in inside),
+                "reasons": sorted(reasons), "note": note}
 
 
 def cpu_gemm_sample(A_rows, B, reps: int) -> tuple[float, int]:
@@ -287,7 +298,7 @@ def run_sweep(path: str, peaks: dict) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", default=None, help="also time configs 2-4 and write the table here")
@@ -330,25 +341,27 @@ def main() -> None:
     A, B = make_operands(rank, world, dev)
     C = torch.empty(M5, n_slab, dtype=torch.float16, device=dev)
     step = lambda: sk.streamk_fp16_nt(A, B, out=C, schedule=args.schedule, fixup=args.fixup)
-    info = sk.schedule_info(M5, n_slab, K5, schedule=args.schedule,
-                            num_sms=torch.cuda.get_device_properties(dev).multi_processor_count)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    info = sk.schedule_info(M5, n_slab, K5, kind="f16_pairs", schedule=args.schedule, num_sms=sms // 2)
 
     # ---- device-resident timing -------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         step()
     sk.check_status()
-    sampler = ClockSampler(local_rank)
     barrier()
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    t_wall1 = time.time()
     my_ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
     total_ms = max_over_ranks(my_ms)
     sk.check_status()
     flops_total = 2.0 * M5 * N5 * K5
@@ -358,6 +371,19 @@ def main() -> None:
     rows = torch.arange(0, M5, M5 // 16, device=dev)[:16]
     ref = A[rows].float() @ B.float().t()
     check = float((C[rows].float() - ref).abs().max() / ref.abs().max())
+
+    # cuBLAS fp16 on the same operands, for context (library data-parallel GEMM)
+    for _ in range(3):
+        torch.matmul(A, B.t(), out=C)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        torch.matmul(A, B.t(), out=C)
+    e1.record()
+    barrier()
+    cublas_ms = max_over_ranks(e0.elapsed_time(e1))
+    cublas_tflops = flops_total * args.steps / (cublas_ms * 1e-3) / 1e12
+    step()
 
     # ---- end to end: host buffers in, host result out ---------------------------
     e2e_steps = max(1, min(args.steps, 5))
@@ -418,7 +444,7 @@ def main() -> None:
                 "frac": achieved / peaks[peak_key], "traffic": traffic,
                 "peak_source": f"{peaks['source']} {peak_key}",
                 "frac_of_nominal_2250": achieved / NOMINAL_TFLOPS,
-                "kernel": "sk_gemm_f16_kernel<256, NT>"}
+                "kernel": "sk_gemm_f16_2cta_kernel (256x256x64 tiles, CTA pairs)"}
 
     cpu_baseline = None
     if world == 1:
@@ -436,7 +462,7 @@ def main() -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
         "config": {"workload": f"cfg5 fp16 NT GEMM M={M5} N={N5} K={K5}, N sharded {world}-way",
-                   "schedule": args.schedule, "fixup": args.fixup, "tile": [128, info["tile_n"], 64],
+                   "schedule": args.schedule, "fixup": args.fixup, "tile": [info["tile_m"], info["tile_n"], 64],
                    "sk_tiles": info["sk_tiles"], "dp_tiles": info["dp_tiles"],
                    "l2": "operands (>= 0.25 GB per GPU) exceed the 126 MB L2; no flush needed"},
         "per_gpu_tflops": value / world,
@@ -444,6 +470,7 @@ def main() -> None:
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": args.steps, "clocks": clocks, "check_rel_err": check,
+        "cublas_fp16_tflops_same_operands": cublas_tflops,
     }
     if gather_ms is not None:
         out["gemm_plus_allgather_ms"] = gather_ms

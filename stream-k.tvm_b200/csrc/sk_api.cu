@@ -83,6 +83,8 @@ int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out) 
 
 // Chooses the tile shape and whether the operands are swapped.
 //   kernel_kind 0 (fp32 SIMT): 64 x 64 x 16 tiles, never swapped.
+//   kernel_kind 3 (fp16 UMMA, CTA pairs): 256 x 256 x 64 tiles, one per pair of CTAs;
+//   `num_sms` is then the number of pairs.
 //   kernel_kind 1/2 (fp16 / W4A16 UMMA): the UMMA M dimension is always 128.  Normally it
 //   runs along M and the tile is 128 x tile_n (128 or 256).  For short M the weights take
 //   the UMMA M dimension instead (128 along N) and the tile spans tile_m = M rounded up to
@@ -90,6 +92,10 @@ int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out) 
 static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* plan) {
   if (kernel_kind == 0) {
     plan->swap = 0; plan->bn = 64; plan->rows = p->M; plan->cols = p->N;
+    return SK_OK;
+  }
+  if (kernel_kind == 3) {   // CTA pairs: 256 x 256 tiles
+    plan->swap = 0; plan->bn = 256; plan->rows = p->M; plan->cols = p->N;
     return SK_OK;
   }
   int tm = p->tile_m, tn = p->tile_n;
@@ -128,7 +134,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   SkPlan plan;
   int st = make_plan(p, kernel_kind, num_sms, &plan);
   if (st != SK_OK) return st;
-  const int tr = kernel_kind == 0 ? 64 : 128;   // tile extent along kernel-space rows
+  const int tr = kernel_kind == 0 ? 64 : kernel_kind == 3 ? 256 : 128;   // tile rows (kernel space)
   const int tk = kernel_kind == 0 ? 16 : 64;
   const long long tiles_r = (plan.rows + tr - 1) / tr;
   const long long tiles_c = (plan.cols + plan.bn - 1) / plan.bn;
@@ -156,7 +162,10 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   else grid = S < P ? S : P;
   if (grid < 1) grid = 1;
   int gm = p->group_m;
-  if (gm <= 0) gm = (tiles_r > 1 && tiles_c > 1) ? (tiles_r < 16 ? static_cast<int>(tiles_r) : 16) : 1;
+  // Bands of about 2048 rows: a wave of CTAs then shares ~8 row panels and ~9 column panels
+  // of the operands, which keeps its footprint inside L2.
+  const int band = kernel_kind == 3 ? 8 : 16;
+  if (gm <= 0) gm = (tiles_r > 1 && tiles_c > 1) ? (tiles_r < band ? static_cast<int>(tiles_r) : band) : 1;
   if (gm > tiles_r) gm = static_cast<int>(tiles_r);
 
   SkSched sc;
@@ -193,7 +202,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
 extern "C" int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms,
                            sk_schedule_info* out) {
   if (!out) return SK_ERR_ARG;
-  if (kernel_kind < 0 || kernel_kind > 2) return SK_ERR_ARG;
+  if (kernel_kind < 0 || kernel_kind > 3) return SK_ERR_ARG;
   return sk_make_sched(p, kernel_kind, num_sms, out, nullptr, nullptr);
 }
 

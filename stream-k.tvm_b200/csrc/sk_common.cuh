@@ -70,6 +70,7 @@ struct SkParams {
   int lda, ldb, ldc;
   int rows, cols;          // kernel-space extents
   int transposed;          // 1: element (row, col) of the tile goes to C[col][row]
+  int unit_ctas;           // CTAs that share one scheduling unit: 1, or 2 (CTA pair, 256-row tiles)
   int bn;                  // UMMA N = tile extent along cols (multiple of 16, <= 256)
   int acc_stride;          // TMEM columns between the two accumulators
   int tmem_cols;           // TMEM columns allocated (power of two >= 32)

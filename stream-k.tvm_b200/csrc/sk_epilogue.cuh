@@ -115,9 +115,9 @@ struct SkPending {
 // thread) fetches all contributors of an item at once, a shallow one many items at once.
 template <int U, int V>
 __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __restrict__ C,
-                                                   int first, int last, int r0, int c0,
-                                                   int rows_valid, int begin, int end, int tid,
-                                                   int nthreads) {
+                                                   int first, int last, int rank, int r0,
+                                                   int c0, int rows_valid, int begin, int end,
+                                                   int tid, int nthreads) {
   for (int base = begin + tid; base < end; base += U * nthreads) {
     float4 acc[U];
     bool on[U];
@@ -135,7 +135,8 @@ __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __
         if (c <= last) {
           // partial of contributor c: the first one's tail slot, everybody else's head slot
           const float4* src = reinterpret_cast<const float4*>(
-              p.ws.part_slots + static_cast<size_t>(2 * c + (c == first ? 1 : 0)) * SK_SLOT_FLOATS);
+              p.ws.part_slots +
+              static_cast<size_t>(2 * (c * p.unit_ctas + rank) + (c == first ? 1 : 0)) * SK_SLOT_FLOATS);
 #pragma unroll
           for (int u = 0; u < U; ++u)
             if (on[u]) x[v][u] = __ldcg(src + base + u * nthreads);
@@ -162,33 +163,35 @@ __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __
 }
 
 __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __restrict__ C,
-                                                const SkPending& pd, int pid, int tid, int nthreads) {
+                                                const SkPending& pd, int pid, int rank, int tid,
+                                                int nthreads) {
   const SkSched& s = p.sched;
   const int first = pd.first, last = pd.last;
   const int n = last - first + 1;
   int tr, tc;
   sk_tile_mn(s, pd.tile, tr, tc);
-  const int r0 = tr * SK_BM, c0 = tc * p.bn;
+  const int r0 = (tr * p.unit_ctas + rank) * SK_BM, c0 = tc * p.bn;
   int valid_cols = p.cols - c0;
   if (valid_cols > p.bn) valid_cols = p.bn;
   int rows_valid = p.rows - r0;
   if (rows_valid > SK_BM) rows_valid = SK_BM;
-  const int L = ((valid_cols + 3) >> 2) * SK_BM;  // float4 items of the tile
+  const int L = ((valid_cols + 3) >> 2) * SK_BM;  // float4 items of this CTA's part of the tile
   const int j = pid - first;
   const int begin = static_cast<int>(static_cast<long long>(j) * L / n);
   const int end = static_cast<int>(static_cast<long long>(j + 1) * L / n);
   // The summation order (0 + p_first + p_first+1 + ...) is the same in every variant.
-  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else             sk_reduce_items_uv<1, 16>(p, C, first, last, r0, c0, rows_valid, begin, end, tid, nthreads);
+  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
 }
 
 // Deferred block-reduce of the (at most two) split tiles this CTA took part in (see the
 // header comment).  Called by EVERY thread of the CTA after all roles have finished;
 // pend[0] is the tile the CTA started, pend[1] the tile it continued; ok[] is scratch.
 __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __restrict__ C, int pid,
-                                                  const SkPending* pend, volatile uint32_t* ok) {
+                                                  int rank, const SkPending* pend,
+                                                  volatile uint32_t* ok) {
   using namespace skptx;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   if (pend[0].tile < 0 && pend[1].tile < 0) return;   // uniform over the CTA
@@ -201,9 +204,10 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
     const int t = i < n0 ? 0 : 1;
     const int k = i < n0 ? i : i - n0;
     const int first = pend[t].first;
-    const uint32_t* flag = (k == 0) ? (p.ws.flag_tail + first) : (p.ws.flag_head + first + k);
+    const int id = (first + k) * p.unit_ctas + rank;   // workspace index of that contributor
+    const uint32_t* flag = (k == 0) ? (p.ws.flag_tail + id) : (p.ws.flag_head + id);
     if (!sk_wait_flag(flag, p.timeout_ns)) {
-      sk_report(p.ws.status, SK_ERR_FIXUP_TIMEOUT, pend[t].tile, first + k);
+      sk_report(p.ws.status, SK_ERR_FIXUP_TIMEOUT, pend[t].tile, id);
       ok[t] = 0u;
     }
   }
@@ -212,18 +216,19 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
   // 2. reduce this CTA's slice of each tile
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    if (pend[t].tile >= 0 && ok[t] != 0u) sk_reduce_items(p, C, pend[t], pid, tid, nthreads);
+    if (pend[t].tile >= 0 && ok[t] != 0u) sk_reduce_items(p, C, pend[t], pid, rank, tid, nthreads);
     if (tid == 0) sk_trace(p, 9 + t);
   }
   // 3. everybody has read what it needs; the last contributor to get here re-arms the flags
   __syncthreads();
   if (tid < 2 && pend[tid].tile >= 0) {
     const int first = pend[tid].first, last = pend[tid].last;
-    const uint32_t old = atom_add_acqrel_u32(p.ws.done + first, 1u);
+    const int uc = p.unit_ctas;
+    const uint32_t old = atom_add_acqrel_u32(p.ws.done + first * uc + rank, 1u);
     if (old == static_cast<uint32_t>(last - first) && ok[tid] != 0u) {
-      p.ws.flag_tail[first] = 0u;
-      for (int peer = first + 1; peer <= last; ++peer) p.ws.flag_head[peer] = 0u;
-      p.ws.done[first] = 0u;
+      p.ws.flag_tail[first * uc + rank] = 0u;
+      for (int peer = first + 1; peer <= last; ++peer) p.ws.flag_head[peer * uc + rank] = 0u;
+      p.ws.done[first * uc + rank] = 0u;
     }
   }
   if (tid == 0) sk_trace(p, 11);
@@ -234,7 +239,7 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
 // tmem_empty_bar are the shared-memory addresses of two consecutive mbarriers each
 // (one per accumulator).
 __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __restrict__ C, int pid,
-                                                 int warp, int lane, uint32_t tmem_base,
+                                                 int rank, int warp, int lane, uint32_t tmem_base,
                                                  uint32_t tmem_full_bar, uint32_t tmem_empty_bar,
                                                  volatile uint32_t* bcast,
                                                  volatile uint32_t* abort_flag,
@@ -259,7 +264,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     ++nseg;
     int tr, tc;
     sk_tile_mn(s, seg.tile, tr, tc);
-    const int r0 = tr * BM, c0 = tc * p.bn;
+    const int r0 = (tr * p.unit_ctas + rank) * BM, c0 = tc * p.bn;
     const int grow = r0 + row;
     const bool row_ok = grow < p.rows;
     const bool warp_ok = (r0 + q * 32) < p.rows;  // warp-uniform
@@ -282,8 +287,10 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     if (nseg == 1 && etid == 0) sk_trace(p, 5);
     const uint32_t t_addr = tmem_base + buf * p.acc_stride + (static_cast<uint32_t>(q * 32) << 16);
 
-    float* acc_slot = p.ws.acc_slots + static_cast<size_t>(first) * SK_SLOT_FLOATS;
-    float* my_part = p.ws.part_slots + static_cast<size_t>(2 * pid + (is_tail ? 1 : 0)) * SK_SLOT_FLOATS;
+    const int me = pid * p.unit_ctas + rank;             // workspace index of this CTA
+    const int first_id = first * p.unit_ctas + rank;     // ... of the tile's first contributor
+    float* acc_slot = p.ws.acc_slots + static_cast<size_t>(first_id) * SK_SLOT_FLOATS;
+    float* my_part = p.ws.part_slots + static_cast<size_t>(2 * me + (is_tail ? 1 : 0)) * SK_SLOT_FLOATS;
 
     if (warp_ok && !dead) {
       for (int c = 0; c < nchunks; ++c) {
@@ -316,14 +323,18 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     // hand the accumulator back to the MMA warp
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(tmem_empty_bar + 8u * buf);
+    if (lane == 0) {
+      // with CTA pairs the barrier lives in the leader CTA (a shared::cluster address)
+      if (p.unit_ctas == 2) mbar_arrive_cluster(tmem_empty_bar + 8u * buf);
+      else mbar_arrive(tmem_empty_bar + 8u * buf);
+    }
 
     if (whole) continue;
     if (p.fixup == SK_FIXUP_ATOMIC) {
       __threadfence();
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);
       if (etid == 0) {
-        const uint32_t old = atom_add_acqrel_u32(p.ws.counters + first, 1u);
+        const uint32_t old = atom_add_acqrel_u32(p.ws.counters + first_id, 1u);
         *bcast = (old == static_cast<uint32_t>(last - first)) ? 1u : 0u;
       }
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);
@@ -353,15 +364,15 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
             }
           }
         }
-        if (etid == 0) p.ws.counters[first] = 0u;
+        if (etid == 0) p.ws.counters[first_id] = 0u;
       }
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);  // bcast is reused by the next segment
     } else {
       // publish the partial; never wait here
       __threadfence();
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);
-      if (etid == 0 && pid != p.drop_flag_cta)
-        st_release_u32(is_tail ? (p.ws.flag_tail + pid) : (p.ws.flag_head + pid), 1u);
+      if (etid == 0 && me != p.drop_flag_cta)
+        st_release_u32(is_tail ? (p.ws.flag_tail + me) : (p.ws.flag_head + me), 1u);
       SkPending& pd = is_tail ? tail : head;
       pd.tile = seg.tile; pd.first = first; pd.last = last;
     }

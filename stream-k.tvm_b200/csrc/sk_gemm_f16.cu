@@ -193,7 +193,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     }
   } else {
     // ------------------------------------------------------------- epilogue
-    sk_epilogue_loop(p, C, pid, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+    sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                      smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   }
 
@@ -202,7 +202,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   __syncthreads();
   // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
   // the split tiles it took part in.
-  sk_reduce_pending(p, C, pid, ctrl->pend, ctrl->ok);
+  sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
   if (warp == 1) {
     if (*abort_flag) {
       // A wait ran out: give copies and MMAs still in flight time to land before
@@ -271,6 +271,19 @@ void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_sta
   p->stages = stages;
 }
 
+int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, void* C, SkParams* p,
+                       void* stream);
+
+// CTA pairs pay off once the problem fills every pair with several 256 x 256 tiles; they
+// are asked for explicitly with tile_m = 256.
+static bool use_cta_pairs(const sk_problem* prob, int num_sms) {
+  if (prob->layout != SK_LAYOUT_NT || (num_sms & 1) != 0) return false;
+  if (prob->tile_m == 256) return prob->tile_n == 0 || prob->tile_n == 256;
+  if (prob->tile_m != 0 || prob->tile_n != 0) return false;
+  const long long tiles = static_cast<long long>((prob->M + 255) / 256) * ((prob->N + 255) / 256);
+  return tiles >= 2LL * (num_sms / 2);
+}
+
 extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B, void* C, void* ws,
                            size_t ws_bytes, void* stream) {
   if (!prob || !A || !B || !C) return SK_ERR_ARG;
@@ -282,7 +295,14 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   SkParams p;
   memset(&p, 0, sizeof(p));
   SkPlan plan;
-  st = sk_make_sched(prob, 1, num_sms, nullptr, &p.sched, &plan);
+  const bool pairs = use_cta_pairs(prob, num_sms);
+  if (pairs) {
+    sk_problem q = *prob;
+    q.tile_m = 0; q.tile_n = 0;
+    st = sk_make_sched(&q, 3, num_sms / 2, nullptr, &p.sched, &plan);
+  } else {
+    st = sk_make_sched(prob, 1, num_sms, nullptr, &p.sched, &plan);
+  }
   if (st != SK_OK) return st;
   const int layout = prob->layout;
   const int M = prob->M, N = prob->N, K = prob->K;
@@ -302,6 +322,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   p.lda = prob->lda; p.ldb = prob->ldb; p.ldc = prob->ldc;
   p.rows = plan.rows; p.cols = plan.cols;
   p.transposed = plan.swap;
+  p.unit_ctas = 1;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
   p.drop_flag_cta = prob->test_drop_flag_cta;
@@ -309,6 +330,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);  // layout fixed per device, whatever the grid
   p.trace = sk_trace_buffer();
+  if (pairs) return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
   sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, 0);
   if (p.stages < 2) return SK_ERR_SHAPE;
 

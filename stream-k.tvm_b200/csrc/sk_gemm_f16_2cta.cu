@@ -1,0 +1,239 @@
+// fp16 NT Stream-K GEMM with CTA pairs (tcgen05 cta_group::2) for large problems.
+//
+// Same persistent Stream-K structure as sk_gemm_f16.cu (it stands in for the same
+// reference kernels, streamk_fp16.py:116-373), but the scheduling unit is a cluster of
+// two CTAs on one TPC that computes a 256 x 256 tile: each CTA loads its own 128 rows of
+// A and its own 128 rows of B (half of the tile's columns) per K step, one thread of the
+// leader CTA issues a 256 x 256 x 16 UMMA that reads both CTAs' shared memory, and each
+// CTA ends up with its 128 x 256 half of the accumulator in its own TMEM.  Per flop a CTA
+// pulls 2/3 of the bytes the single-CTA kernel does, so the same shared-memory budget
+// covers 1.5x the load latency.  No load is multicast: each CTA fetches what it needs.
+//
+// Roles per CTA as in sk_gemm_f16.cu; the MMA warp of the second CTA only takes part in
+// the tensor-memory allocation.
+#include "sk_common.cuh"
+#include "sk_epilogue.cuh"
+
+namespace {
+
+using namespace skptx;
+
+constexpr int BM = SK_BM;            // rows per CTA
+constexpr int BN = 256;              // tile columns (both CTAs see all of them in TMEM)
+constexpr int BK = 64;
+constexpr int A_STAGE_BYTES = BM * BK * 2;         // 16 KB
+constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;   // 16 KB: this CTA's half of the B tile
+constexpr int STAGES = 7;              // 7 x 32 KB = 224 KB of the 227 KB a CTA may use
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int PIPE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+constexpr int CTRL_BYTES = 512;
+constexpr int SMEM_BYTES = PIPE_BYTES + 1024 + CTRL_BYTES;
+
+struct Ctrl {
+  uint64_t full[STAGES];      // used in the leader CTA: both CTAs' loads complete here
+  uint64_t empty[STAGES];     // one per CTA, released by the leader's multicast commit
+  uint64_t tmem_full[2];      // one per CTA, multicast commit
+  uint64_t tmem_empty[2];     // used in the leader CTA: 8 arrivals (4 epilogue warps x 2 CTAs)
+  uint32_t tmem_base;
+  uint32_t abort;
+  uint32_t bcast;
+  uint32_t ok[2];
+  SkPending pend[2];
+};
+static_assert(sizeof(Ctrl) <= CTRL_BYTES, "Ctrl must fit its reserved space");
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        __half* __restrict__ C, const SkParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t sA = base;
+  const uint32_t sB = base + STAGES * A_STAGE_BYTES;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + PIPE_BYTES);
+  volatile uint32_t* abort_flag = &ctrl->abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());   // 0 = leader of the pair
+  const int unit = blockIdx.x >> 1;                        // the pair's index in the schedule
+  const SkSched& s = p.sched;
+  if (threadIdx.x == 0) sk_trace(p, 0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(smem_u32(&ctrl->full[i]), 1);
+      mbar_init(smem_u32(&ctrl->empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[i]), 8);
+    }
+    ctrl->abort = 0u;
+    ctrl->bcast = 0u;
+    ctrl->pend[0].tile = -1;
+    ctrl->pend[1].tile = -1;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the partner's barriers are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+  if (threadIdx.x == 0) sk_trace(p, 1);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer (both CTAs)
+    if (lane == 0) {
+      SkCursor cur;
+      sk_cursor_init(s, unit, cur);
+      SkSeg seg;
+      int stage = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      bool traced = false;
+      while (ok && sk_next(s, unit, cur, seg)) {
+        int tr, tc;
+        sk_tile_mn(s, seg.tile, tr, tc);
+        const int a_row0 = (tr * 2 + rank) * BM;          // this CTA's 128 rows of A
+        const int b_row0 = tc * BN + rank * (BN / 2);     // this CTA's 128 rows of B
+        for (int k = seg.k0; k < seg.k1; ++k) {
+          if (!sk_wait_bar(smem_u32(&ctrl->empty[stage]), ph ^ 1u, abort_flag, p, stage, 0)) {
+            ok = false;
+            break;
+          }
+          // Both CTAs' loads complete on the leader's barrier; the leader expects all four.
+          const uint32_t full_leader = mapa_shared(smem_u32(&ctrl->full[stage]), 0);
+          if (rank == 0)
+            mbar_arrive_expect_tx(smem_u32(&ctrl->full[stage]), 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+          tma_load_2d_pair(sA + stage * A_STAGE_BYTES, &tmA, full_leader, k * BK, a_row0);
+          tma_load_2d_pair(sB + stage * B_STAGE_BYTES, &tmB, full_leader, k * BK, b_row0);
+          if (++stage == STAGES) { stage = 0; ph ^= 1u; }
+          if (!traced) { sk_trace(p, 2); traced = true; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      SkCursor cur;
+      sk_cursor_init(s, unit, cur);
+      SkSeg seg;
+      int stage = 0;
+      uint32_t ph = 0;
+      uint32_t nseg = 0;
+      bool ok = true;
+      while (ok && sk_next(s, unit, cur, seg)) {
+        const uint32_t buf = nseg & 1u;
+        const uint32_t acc_ph = (nseg >> 1) & 1u;
+        if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int k = seg.k0; k < seg.k1; ++k) {
+          if (!sk_wait_bar(smem_u32(&ctrl->full[stage]), ph, abort_flag, p, 32 + stage, 1)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
+          const uint32_t a_addr = sA + stage * A_STAGE_BYTES;
+          const uint32_t b_addr = sB + stage * B_STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = umma_desc_sw128(a_addr + kk * 32, 16, 1024);
+            const uint64_t db = umma_desc_sw128(b_addr + kk * 32, 16, 1024);
+            umma_f16_ss_pair(d_tmem, da, db, p.idesc, (k > seg.k0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(smem_u32(&ctrl->empty[stage]));   // frees the stage in both CTAs
+          if (++stage == STAGES) { stage = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_pair(smem_u32(&ctrl->tmem_full[buf]));   // accumulator ready in both CTAs
+        ++nseg;
+      }
+      sk_trace(p, 4);
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (both CTAs)
+    sk_epilogue_loop(p, C, unit, rank, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                     mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0), &ctrl->bcast, abort_flag,
+                     ctrl->pend);
+  }
+
+  // ------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  sk_reduce_pending(p, C, unit, rank, ctrl->pend, ctrl->ok);
+  // Neither CTA may leave while its partner can still signal its barriers or read its
+  // shared memory.
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    if (*abort_flag) {
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ULL) __nanosleep(1000);
+    }
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    if (lane == 0) sk_trace(p, 7);
+  }
+}
+
+}  // namespace
+
+int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                     uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
+
+// Launch with CTA pairs.  `units` persistent pairs; p->sched must have been built for
+// 256-row tiles and `units` schedulable units.
+int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, void* C, SkParams* p,
+                       void* stream) {
+  CUtensorMap tmA, tmB;
+  int st = sk_make_tmap_f16(&tmA, A, prob->M, prob->K, prob->lda, BK, BM);
+  if (st != SK_OK) return st;
+  st = sk_make_tmap_f16(&tmB, B, prob->N, prob->K, prob->ldb, BK, BN / 2);
+  if (st != SK_OK) return st;
+  p->unit_ctas = 2;
+  p->bn = BN;
+  p->acc_stride = BN;
+  p->tmem_cols = TMEM_COLS;
+  p->stages = STAGES;
+  p->idesc = umma_idesc_f16(2 * BM, BN, 0);
+
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    attr_set[dev & 63] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * p->sched.grid, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, sk_gemm_f16_2cta_kernel, tmA, tmB, static_cast<__half*>(C), *p);
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
+}

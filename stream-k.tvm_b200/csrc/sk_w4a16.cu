@@ -223,7 +223,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------- epilogue
-    sk_epilogue_loop(p, C, pid, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+    sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                      smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   } else {
     // ------------------------------------------------------------- dequantise
@@ -278,7 +278,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   __syncthreads();
   // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
   // the split tiles it took part in.
-  sk_reduce_pending(p, C, pid, ctrl->pend, ctrl->ok);
+  sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
   if (warp == 1) {
     if (*abort_flag) {
       const unsigned long long t0 = globaltimer_ns();
@@ -452,6 +452,7 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   p.lda = prob->lda; p.ldb = 0; p.ldc = prob->ldc;
   p.rows = plan.rows; p.cols = plan.cols;
   p.transposed = plan.swap;
+  p.unit_ctas = 1;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
   p.drop_flag_cta = prob->test_drop_flag_cta;

@@ -130,11 +130,12 @@ def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkPr
 def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "hybrid",
                   num_sms: int = 148, **kw) -> dict:
     """Host scheduler integers (streamk_fp16.py:83-113) and the tile plan for a problem;
-    needs no GPU.  kind: "f32", "f16" or "w4a16"."""
+    needs no GPU.  kind: "f32", "f16", "w4a16", or "f16_pairs" (the CTA-pair kernel the fp16 NT
+    entry point picks for large problems; num_sms is then the number of pairs)."""
     o = _options(kw)
     prob = _problem(M, N, K, K, K, N, "nt", schedule, "atomic", o)
     info = L.SkScheduleInfo()
-    kinds = {"f32": 0, "f16": 1, "w4a16": 2}
+    kinds = {"f32": 0, "f16": 1, "w4a16": 2, "f16_pairs": 3}
     L.check(L.load().sk_schedule(C.byref(prob), kinds[kind], num_sms, C.byref(info)), "sk_schedule")
     return info.as_dict()
 
