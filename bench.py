@@ -241,18 +241,22 @@ def run_sweep(path: str, peaks: dict) -> None:
         flops, nbytes = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
         est = max(nbytes / 6.5e3, flops / 1.5e9) / 1e3 + 3
         ref = oracle.gemm_ref(c["A"], c["B"], "nt")
-        variants = [("streamk", "atomic"), ("streamk", "block_reduce"), ("hybrid", "atomic"), ("dp", "atomic")]
-        for schedule, fixup in variants:
-            for tile_n in (128, 256):
-                if tile_n == 256 and N * M < 256 * 4096:
-                    continue
-                fn = lambda i: sk.streamk_fp16_nt(A, Bs[i], schedule=schedule, fixup=fixup, out=out, tile_n=tile_n)
-                fn(0)
-                sk.check_status()
-                err = oracle.rel_err(out, ref)
-                us = time_rotating(fn, copies, est)
-                record(cfg, "streamk_fp16_nt", M, N, K, f"{schedule}/{fixup}/bn{tile_n}", us, flops, nbytes,
-                       {"rel_err": float(f"{err:.3e}")})
+        # tile None = the library's own choice (operands swapped for M <= 64, CTA pairs for
+        # large problems); explicit 128 x 256 tiles are timed as well where they make sense
+        variants = [("streamk", "atomic", None), ("streamk", "block_reduce", None),
+                    ("hybrid", "block_reduce", None), ("dp", "atomic", None)]
+        if M > 64 and N * M >= 256 * 4096:
+            variants += [("streamk", "block_reduce", 256), ("dp", "atomic", 256)]
+        for schedule, fixup, tile_n in variants:
+            fn = lambda i: sk.streamk_fp16_nt(A, Bs[i], schedule=schedule, fixup=fixup, out=out, tile_n=tile_n)
+            fn(0)
+            sk.check_status()
+            err = oracle.rel_err(out, ref)
+            us = time_rotating(fn, copies, est)
+            info = sk.schedule_info(M, N, K, schedule=schedule, tile_n=tile_n)
+            record(cfg, "streamk_fp16_nt", M, N, K,
+                   f"{schedule}/{fixup}/tile{info['tile_m']}x{info['tile_n']}", us, flops, nbytes,
+                   {"rel_err": float(f"{err:.3e}")})
         fn = lambda i: torch.matmul(A, Bs[i].t(), out=out)
         us = time_rotating(fn, copies, est)
         record(cfg, "cublas torch.matmul", M, N, K, "data-parallel library GEMM", us, flops, nbytes)
@@ -433,7 +437,11 @@ def main() -> None:
     launch_ms = my_ms / args.steps
     achieved = 2.0 * M5 * n_slab * K5 / (launch_ms * 1e-3) / 1e12
     timed_s = total_ms * 1e-3
-    peak_key = "bf16_tflops" if timed_s < 1.0 else "bf16_tflops_sustained"
+    # The kernel is timed back to back: once that lasts long enough for the power cap to set
+    # the clock (sw_power_cap seen, or a quarter second of sustained work) the sustained
+    # cuBLAS figure is the like-for-like peak; a short burst is compared with the burst one.
+    capped = bool(clocks and "sw_power_cap" in (clocks.get("reasons") or []))
+    peak_key = "bf16_tflops_sustained" if (capped or timed_s >= 0.25) else "bf16_tflops"
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "ncu_traffic.json")
     if os.path.exists(tpath):
@@ -443,6 +451,7 @@ def main() -> None:
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks[peak_key], "unit": "TFLOP/s",
                 "frac": achieved / peaks[peak_key], "traffic": traffic,
                 "peak_source": f"{peaks['source']} {peak_key}",
+                "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
                 "frac_of_nominal_2250": achieved / NOMINAL_TFLOPS,
                 "kernel": "sk_gemm_f16_2cta_kernel (256x256x64 tiles, CTA pairs)"}
 

@@ -11,6 +11,9 @@ int sk_set_cuda_error(cudaError_t e) {
 }
 
 static unsigned long long* g_trace = nullptr;
+static int g_debug_mode = 0;
+int sk_debug_mode() { return g_debug_mode; }
+extern "C" int sk_debug_set_mode(int m) { g_debug_mode = m; return 0; }
 unsigned long long* sk_trace_buffer() { return g_trace; }
 
 // Debugging aid (not part of the reference surface): later launches of the tensor-core
@@ -122,7 +125,9 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
       tn = (t256 >= 2LL * num_sms) ? 256 : 128;
     }
   }
-  if (tn != 128 && !(tn == 256 && kernel_kind == 1)) return SK_ERR_ARG;
+  // fp16: any multiple of 16 up to 256 (NN and ladder weights come in 128-row units: checked
+  // by the caller); W4A16 dequantises 128 weight rows per stage.
+  if (kernel_kind == 2 ? tn != 128 : (tn < 16 || tn > 256 || (tn & 15) != 0)) return SK_ERR_ARG;
   plan->swap = 0; plan->bn = tn; plan->rows = p->M; plan->cols = p->N;
   return SK_OK;
 }

@@ -75,6 +75,7 @@ struct SkParams {
   int acc_stride;          // TMEM columns between the two accumulators
   int tmem_cols;           // TMEM columns allocated (power of two >= 32)
   int stages;              // shared-memory pipeline depth
+  int w_stages;            // W4A16: depth of the dequantised-weight ring
   int col_stage_bytes;     // bn * 128
   int row_tx_bytes, col_tx_bytes;   // bytes the loads of one stage deliver per operand
   int row_loader, col_loader;       // SK_LOAD_*
@@ -88,6 +89,7 @@ struct SkParams {
   const void* row_img;     // SK_LOAD_IMAGE sources
   const void* col_img;
   unsigned long long* trace;  // debugging: 16 timestamps per CTA, or null
+  int debug_mode;
 };
 
 // Debugging aid: record %globaltimer at a numbered point of this CTA's life.
@@ -130,3 +132,4 @@ int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out);
 int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
                   SkSched* s, SkPlan* plan);
 unsigned long long* sk_trace_buffer();
+int sk_debug_mode();

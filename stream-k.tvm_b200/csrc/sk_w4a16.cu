@@ -33,19 +33,18 @@ constexpr int Q_BLOCK_BYTES = 128 * BK / 2;    // 4096: packed nibbles of 128 we
 constexpr int SZ_BLOCK_BYTES = 128 * 2 + 128;  // 384: fp16 scales + uint8 zero-points of a group
 constexpr int W_STAGE_BYTES = 128 * BK * 2;    // 16384: dequantised fp16 stage
 constexpr int MAX_LS = 12;                     // load stages (activation tile + packed block)
-constexpr int BS = 3;                          // dequantised weight stages
+constexpr int MAX_BS = 8;                      // dequantised weight stages (ring depth chosen per launch)
 constexpr int DQ_WARPS = 8;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
 constexpr int NUM_THREADS = 64 + SK_EPI_THREADS + DQ_THREADS;
-constexpr int DQ_BAR_ID = 2;
 constexpr int CTRL_BYTES = 512;
 constexpr int SMEM_LIMIT = 232448;
 
 struct Ctrl {
   uint64_t load_full[MAX_LS];
   uint64_t load_empty[MAX_LS];
-  uint64_t w_full[BS];
-  uint64_t w_empty[BS];
+  uint64_t w_full[MAX_BS];
+  uint64_t w_empty[MAX_BS];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -80,7 +79,7 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 zmagic, __half
 }
 
 // Shared memory: [BS dequantised weight stages][LS activation stages][LS packed blocks]
-// [LS group blocks][Ctrl].  p.col_stage_bytes holds the activation stage size in both
+// [LS group blocks][Ctrl]; BS and LS are chosen per launch.  p.col_stage_bytes holds the activation stage size in both
 // operand orders (128 rows normally, bn rows when the operands are swapped).
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __restrict__ qblocks,
@@ -90,6 +89,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
   const int LS = p.stages;
+  const int BS = p.w_stages;
   const int a_stage_bytes = p.row_tx_bytes;        // activation tile bytes per stage
   const int off_a = BS * W_STAGE_BYTES;
   const int off_q = off_a + LS * a_stage_bytes;
@@ -113,10 +113,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   if (threadIdx.x == 0) {
     for (int i = 0; i < LS; ++i) {
       mbar_init(smem_u32(&ctrl->load_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->load_empty[i]), 2);  // dequant warps + MMA commit
+      mbar_init(smem_u32(&ctrl->load_empty[i]), DQ_WARPS + 1);  // each dequant warp + MMA commit
     }
     for (int i = 0; i < BS; ++i) {
-      mbar_init(smem_u32(&ctrl->w_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->w_full[i]), DQ_WARPS);   // one arrival per dequant warp
       mbar_init(smem_u32(&ctrl->w_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -151,7 +151,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       int ls = 0;
       uint32_t lph = 0;
       bool ok = true;
-      const uint32_t tx = a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
+      const uint32_t tx = p.debug_mode == 2 ? a_stage_bytes : a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
       while (ok && sk_next(s, pid, cur, seg)) {
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
@@ -165,10 +165,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           }
           mbar_arrive_expect_tx(full, tx);
           tma_load_2d(sA + ls * a_stage_bytes, &tmA, full, k * BK, a_row0);
-          bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
+          if (p.debug_mode != 2) bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
                        qblocks + (static_cast<size_t>(nblk) * kblocks + k) * Q_BLOCK_BYTES,
                        Q_BLOCK_BYTES, full);
-          bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
+          if (p.debug_mode != 2) bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
                        szblocks + (static_cast<size_t>(nblk) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
                        SZ_BLOCK_BYTES, full);
           if (++ls == LS) { ls = 0; lph ^= 1u; }
@@ -245,7 +245,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
               !sk_wait_bar(smem_u32(&ctrl->w_empty[bs]), bph ^ 1u, abort_flag, p, 80 + bs, 3))
             dead = true;
         }
-        if (!dead) {
+        if (!dead && p.debug_mode != 1) {
           const uint8_t* q = smem + off_q + ls * Q_BLOCK_BYTES;
           const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
           const uint4 w = *reinterpret_cast<const uint4*>(q + h * 2048 + r * 16);
@@ -262,8 +262,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
                 dequant_word(words[j], zmagic, s2);
           fence_proxy_async_smem();  // generic-proxy stores -> visible to the UMMA reads
         }
-        named_bar_sync(DQ_BAR_ID, DQ_THREADS);
-        if (dtid == 0) {
+        // Each warp hands over its own 32 rows x one K half: no CTA-wide barrier, the warps
+        // run through the stages independently of one another.
+        __syncwarp();
+        if (lane == 0) {
           mbar_arrive(smem_u32(&ctrl->w_full[bs]));
           mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
         }
@@ -460,14 +462,26 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);
   p.trace = sk_trace_buffer();
+  p.debug_mode = sk_debug_mode();
   // The activation tile has 128 rows normally, bn rows when the operands are swapped.
   const int a_rows = plan.swap ? plan.bn : BM;
   const int a_stage_bytes = a_rows * BK * 2;
   sk_fill_tile_params(&p, plan.bn, 0, 1, 0);   // TMEM layout only; stages set below
-  int ls = (SMEM_LIMIT - 1024 - CTRL_BYTES - BS * W_STAGE_BYTES) /
-           (a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES);
+  // Two rings share the shared memory: load stages (activation tile + packed block) and
+  // dequantised weight stages.  The chain dequantise -> MMA -> release runs once per K step
+  // and takes over a microsecond end to end, so the weight ring has to be deep as well: take
+  // the deepest weight ring that still leaves at least as many load stages.
+  const int budget = SMEM_LIMIT - 1024 - CTRL_BYTES;
+  const int load_stage = a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
+  int ls = 0, bs = 3;
+  for (int b = MAX_BS; b >= 3; --b) {
+    const int l = (budget - b * W_STAGE_BYTES) / load_stage;
+    if (l >= b || b == 3) { bs = b; ls = l; break; }
+  }
   if (ls > MAX_LS) ls = MAX_LS;
+  if (ls < 2) return SK_ERR_SHAPE;
   p.stages = ls;
+  p.w_stages = bs;
   p.row_tx_bytes = a_stage_bytes;
   p.col_stage_bytes = a_stage_bytes;
   p.idesc = umma_idesc_f16(BM, plan.bn, 0);
@@ -479,8 +493,7 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   const uint8_t* qb = static_cast<const uint8_t*>(packed);
   const uint8_t* sz = qb + static_cast<size_t>(nb) * kb * Q_BLOCK_BYTES;
 
-  const int smem_bytes = BS * W_STAGE_BYTES + ls * (a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES) +
-                         1024 + CTRL_BYTES;
+  const int smem_bytes = bs * W_STAGE_BYTES + ls * load_stage + 1024 + CTRL_BYTES;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);

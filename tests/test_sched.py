@@ -100,7 +100,7 @@ def test_bad_arguments(lib):
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_SHAPE
     prob = L.SkProblem(M=4, N=4, K=4, schedule=9)
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_ARG
-    prob = L.SkProblem(M=4, N=4, K=4, schedule=1, tile_n=64)
+    prob = L.SkProblem(M=4, N=4, K=4, schedule=1, tile_n=72)
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_ARG
 
 
