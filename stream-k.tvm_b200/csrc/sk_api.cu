@@ -11,9 +11,6 @@ int sk_set_cuda_error(cudaError_t e) {
 }
 
 static unsigned long long* g_trace = nullptr;
-static int g_debug_mode = 0;
-int sk_debug_mode() { return g_debug_mode; }
-extern "C" int sk_debug_set_mode(int m) { g_debug_mode = m; return 0; }
 unsigned long long* sk_trace_buffer() { return g_trace; }
 
 // Debugging aid (not part of the reference surface): later launches of the tensor-core

@@ -89,7 +89,6 @@ struct SkParams {
   const void* row_img;     // SK_LOAD_IMAGE sources
   const void* col_img;
   unsigned long long* trace;  // debugging: 16 timestamps per CTA, or null
-  int debug_mode;
 };
 
 // Debugging aid: record %globaltimer at a numbered point of this CTA's life.
@@ -132,4 +131,3 @@ int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out);
 int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
                   SkSched* s, SkPlan* plan);
 unsigned long long* sk_trace_buffer();
-int sk_debug_mode();

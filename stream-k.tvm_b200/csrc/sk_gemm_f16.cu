@@ -123,21 +123,31 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       uint32_t ph = 0;
       bool ok = true;
       const uint32_t tx = p.row_tx_bytes + p.col_tx_bytes;
+      // This one thread feeds the whole SM: keep its loop short.  The common case (both
+      // operands K-major behind tensor maps) issues exactly two TMA instructions per step.
+      const bool both_tma_k = p.row_loader == SK_LOAD_TMA_K && p.col_loader == SK_LOAD_TMA_K;
+      const int col_stage_bytes = p.col_stage_bytes;
+      const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
       while (ok && sk_next(s, pid, cur, seg)) {
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
         const int r0 = tr * BM, c0 = tc * p.bn;
         for (int k = seg.k0; k < seg.k1; ++k) {
-          const uint32_t full = smem_u32(&ctrl->full[stage]);
-          if (!sk_wait_bar(smem_u32(&ctrl->empty[stage]), ph ^ 1u, abort_flag, p, stage, 0)) {
+          const uint32_t full = full0 + 8u * stage;
+          if (!sk_wait_bar(empty0 + 8u * stage, ph ^ 1u, abort_flag, p, stage, 0)) {
             ok = false;
             break;
           }
           mbar_arrive_expect_tx(full, tx);
-          load_operand(p.row_loader, sRow + stage * ROW_STAGE_BYTES, &tmRow, p.row_img, full, r0, k,
-                       BM, s.iters_per_tile);
-          load_operand(p.col_loader, sCol + stage * p.col_stage_bytes, &tmCol, p.col_img, full, c0, k,
-                       p.bn, s.iters_per_tile);
+          if (both_tma_k) {
+            tma_load_2d(sRow + stage * ROW_STAGE_BYTES, &tmRow, full, k * BK, r0);
+            tma_load_2d(sCol + stage * col_stage_bytes, &tmCol, full, k * BK, c0);
+          } else {
+            load_operand(p.row_loader, sRow + stage * ROW_STAGE_BYTES, &tmRow, p.row_img, full, r0, k,
+                         BM, s.iters_per_tile);
+            load_operand(p.col_loader, sCol + stage * col_stage_bytes, &tmCol, p.col_img, full, c0, k,
+                         p.bn, s.iters_per_tile);
+          }
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
           if (!traced) { sk_trace(p, 2); traced = true; }
         }
@@ -158,31 +168,38 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       // 16 rows of K = 2048 B.
       const bool row_mn = p.row_loader == SK_LOAD_TMA_MN;
       const bool col_mn = p.col_loader == SK_LOAD_TMA_MN;
-      const uint32_t row_kstep = row_mn ? 2048u : 32u, row_lbo = row_mn ? 8192u : 16u;
-      const uint32_t col_kstep = col_mn ? 2048u : 32u, col_lbo = col_mn ? 8192u : 16u;
+      const uint32_t row_kstep16 = (row_mn ? 2048u : 32u) >> 4, col_kstep16 = (col_mn ? 2048u : 32u) >> 4;
+      const uint64_t row_hi = umma_desc_sw128_hi(row_mn ? 8192u : 16u, 1024);
+      const uint64_t col_hi = umma_desc_sw128_hi(col_mn ? 8192u : 16u, 1024);
+      const uint32_t row_lo0 = umma_desc_lo(sRow), col_lo0 = umma_desc_lo(sCol);
+      const uint32_t col_stage16 = static_cast<uint32_t>(p.col_stage_bytes) >> 4;
+      const uint32_t idesc = p.idesc;
+      const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
+      const uint32_t acc_stride = p.acc_stride;
       while (ok && sk_next(s, pid, cur, seg)) {
         const uint32_t buf = nseg & 1u;
         const uint32_t acc_ph = (nseg >> 1) & 1u;
         if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
+        const uint32_t d_tmem = tmem_base + buf * acc_stride;
+        uint32_t accumulate = 0u;   // the segment's first UMMA overwrites the accumulator
         for (int k = seg.k0; k < seg.k1; ++k) {
-          if (!sk_wait_bar(smem_u32(&ctrl->full[stage]), ph, abort_flag, p, 32 + stage, 1)) {
+          if (!sk_wait_bar(full0 + 8u * stage, ph, abort_flag, p, 32 + stage, 1)) {
             ok = false;
             break;
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          const uint32_t a_addr = sRow + stage * ROW_STAGE_BYTES;
-          const uint32_t b_addr = sCol + stage * p.col_stage_bytes;
+          const uint32_t a_lo = row_lo0 + stage * (ROW_STAGE_BYTES >> 4);
+          const uint32_t b_lo = col_lo0 + stage * col_stage16;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t da = umma_desc_sw128(a_addr + kk * row_kstep, row_lbo, 1024);
-            const uint64_t db = umma_desc_sw128(b_addr + kk * col_kstep, col_lbo, 1024);
-            umma_f16_ss(d_tmem, da, db, p.idesc, (k > seg.k0 || kk > 0) ? 1u : 0u);
+            umma_f16_ss(d_tmem, row_hi | (a_lo + kk * row_kstep16), col_hi | (b_lo + kk * col_kstep16),
+                        idesc, accumulate);
+            accumulate = 1u;
           }
-          umma_commit(smem_u32(&ctrl->empty[stage]));  // frees the stage when the MMAs retire
+          umma_commit(empty0 + 8u * stage);  // frees the stage when the MMAs retire
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
         }
         if (!ok) break;

@@ -101,20 +101,21 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       uint32_t ph = 0;
       bool ok = true;
       bool traced = false;
+      const uint32_t full0_leader = mapa_shared(smem_u32(&ctrl->full[0]), 0);
+      const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
       while (ok && sk_next(s, unit, cur, seg)) {
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
         const int a_row0 = (tr * 2 + rank) * BM;          // this CTA's 128 rows of A
         const int b_row0 = tc * BN + rank * (BN / 2);     // this CTA's 128 rows of B
         for (int k = seg.k0; k < seg.k1; ++k) {
-          if (!sk_wait_bar(smem_u32(&ctrl->empty[stage]), ph ^ 1u, abort_flag, p, stage, 0)) {
+          if (!sk_wait_bar(empty0 + 8u * stage, ph ^ 1u, abort_flag, p, stage, 0)) {
             ok = false;
             break;
           }
           // Both CTAs' loads complete on the leader's barrier; the leader expects all four.
-          const uint32_t full_leader = mapa_shared(smem_u32(&ctrl->full[stage]), 0);
-          if (rank == 0)
-            mbar_arrive_expect_tx(smem_u32(&ctrl->full[stage]), 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+          const uint32_t full_leader = full0_leader + 8u * stage;
+          if (rank == 0) mbar_arrive_expect_tx(full0 + 8u * stage, 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
           tma_load_2d_pair(sA + stage * A_STAGE_BYTES, &tmA, full_leader, k * BK, a_row0);
           tma_load_2d_pair(sB + stage * B_STAGE_BYTES, &tmB, full_leader, k * BK, b_row0);
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
@@ -132,6 +133,10 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       uint32_t ph = 0;
       uint32_t nseg = 0;
       bool ok = true;
+      const uint64_t desc_hi = umma_desc_sw128_hi(16, 1024);
+      const uint32_t a_lo0 = umma_desc_lo(sA), b_lo0 = umma_desc_lo(sB);
+      const uint32_t idesc = p.idesc;
+      const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
       while (ok && sk_next(s, unit, cur, seg)) {
         const uint32_t buf = nseg & 1u;
         const uint32_t acc_ph = (nseg >> 1) & 1u;
@@ -139,22 +144,22 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
+        uint32_t accumulate = 0u;
         for (int k = seg.k0; k < seg.k1; ++k) {
-          if (!sk_wait_bar(smem_u32(&ctrl->full[stage]), ph, abort_flag, p, 32 + stage, 1)) {
+          if (!sk_wait_bar(full0 + 8u * stage, ph, abort_flag, p, 32 + stage, 1)) {
             ok = false;
             break;
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          const uint32_t a_addr = sA + stage * A_STAGE_BYTES;
-          const uint32_t b_addr = sB + stage * B_STAGE_BYTES;
+          const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (B_STAGE_BYTES >> 4);
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t da = umma_desc_sw128(a_addr + kk * 32, 16, 1024);
-            const uint64_t db = umma_desc_sw128(b_addr + kk * 32, 16, 1024);
-            umma_f16_ss_pair(d_tmem, da, db, p.idesc, (k > seg.k0 || kk > 0) ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
+            accumulate = 1u;
           }
-          umma_commit_pair(smem_u32(&ctrl->empty[stage]));   // frees the stage in both CTAs
+          umma_commit_pair(empty0 + 8u * stage);   // frees the stage in both CTAs
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
         }
         if (!ok) break;

@@ -172,6 +172,16 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
   return d;
 }
 
+// The same descriptor split into the part that never changes for an operand (offsets,
+// version, swizzle mode) and the 14-bit start-address field: the MMA-issuing thread runs a
+// long dependent instruction chain, so the per-UMMA descriptor is one add and one OR.
+__device__ __forceinline__ uint64_t umma_desc_sw128_hi(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return umma_desc_sw128(0u, lbo_bytes, sbo_bytes);
+}
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) {
+  return (smem_addr & 0x3FFFFu) >> 4;
+}
+
 // Instruction descriptor for kind::f16, fp16 A/B, fp32 D.
 //   [4,6) D format 1=f32   [7,10) A format 0=f16   [10,13) B format 0=f16
 //   [15] A major (0=K)     [16] B major (0=K, 1=MN)

@@ -151,7 +151,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       int ls = 0;
       uint32_t lph = 0;
       bool ok = true;
-      const uint32_t tx = p.debug_mode == 2 ? a_stage_bytes : a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
+      const uint32_t tx = a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
       while (ok && sk_next(s, pid, cur, seg)) {
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
@@ -165,10 +165,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           }
           mbar_arrive_expect_tx(full, tx);
           tma_load_2d(sA + ls * a_stage_bytes, &tmA, full, k * BK, a_row0);
-          if (p.debug_mode != 2) bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
+          bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
                        qblocks + (static_cast<size_t>(nblk) * kblocks + k) * Q_BLOCK_BYTES,
                        Q_BLOCK_BYTES, full);
-          if (p.debug_mode != 2) bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
+          bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
                        szblocks + (static_cast<size_t>(nblk) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
                        SZ_BLOCK_BYTES, full);
           if (++ls == LS) { ls = 0; lph ^= 1u; }
@@ -185,6 +185,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       int ls = 0, bs = 0;
       uint32_t lph = 0, bph = 0, nseg = 0;
       bool ok = true;
+      const uint64_t desc_hi = umma_desc_sw128_hi(16, 1024);
+      const uint32_t act_lo0 = umma_desc_lo(sA), wgt_lo0 = umma_desc_lo(sW);
+      const uint32_t act_stage16 = static_cast<uint32_t>(a_stage_bytes) >> 4;
+      const uint32_t idesc = p.idesc;
       while (ok && sk_next(s, pid, cur, seg)) {
         const uint32_t buf = nseg & 1u;
         const uint32_t acc_ph = (nseg >> 1) & 1u;
@@ -192,6 +196,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
+        uint32_t accumulate = 0u;
         for (int k = seg.k0; k < seg.k1; ++k) {
           if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 32 + ls, 1) ||
               !sk_wait_bar(smem_u32(&ctrl->w_full[bs]), bph, abort_flag, p, 48 + bs, 1)) {
@@ -200,15 +205,14 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          const uint32_t act = sA + ls * a_stage_bytes;
-          const uint32_t wgt = sW + bs * W_STAGE_BYTES;
-          const uint32_t a_addr = swapped ? wgt : act;   // UMMA M side
-          const uint32_t b_addr = swapped ? act : wgt;   // UMMA N side
+          const uint32_t act = act_lo0 + ls * act_stage16;
+          const uint32_t wgt = wgt_lo0 + bs * (W_STAGE_BYTES >> 4);
+          const uint32_t a_lo = swapped ? wgt : act;   // UMMA M side
+          const uint32_t b_lo = swapped ? act : wgt;   // UMMA N side
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t da = umma_desc_sw128(a_addr + kk * 32, 16, 1024);
-            const uint64_t db = umma_desc_sw128(b_addr + kk * 32, 16, 1024);
-            umma_f16_ss(d_tmem, da, db, p.idesc, (k > seg.k0 || kk > 0) ? 1u : 0u);
+            umma_f16_ss(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
+            accumulate = 1u;
           }
           umma_commit(smem_u32(&ctrl->load_empty[ls]));
           umma_commit(smem_u32(&ctrl->w_empty[bs]));
@@ -245,7 +249,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
               !sk_wait_bar(smem_u32(&ctrl->w_empty[bs]), bph ^ 1u, abort_flag, p, 80 + bs, 3))
             dead = true;
         }
-        if (!dead && p.debug_mode != 1) {
+        if (!dead) {
           const uint8_t* q = smem + off_q + ls * Q_BLOCK_BYTES;
           const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
           const uint4 w = *reinterpret_cast<const uint4*>(q + h * 2048 + r * 16);
@@ -462,7 +466,6 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);
   p.trace = sk_trace_buffer();
-  p.debug_mode = sk_debug_mode();
   // The activation tile has 128 rows normally, bn rows when the operands are swapped.
   const int a_rows = plan.swap ? plan.bn : BM;
   const int a_stage_bytes = a_rows * BK * 2;
