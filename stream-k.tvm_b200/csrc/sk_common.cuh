@@ -75,6 +75,7 @@ struct SkParams {
   int acc_stride;          // TMEM columns between the two accumulators
   int tmem_cols;           // TMEM columns allocated (power of two >= 32)
   int stages;              // shared-memory pipeline depth
+  int kgroup;              // K steps (of 64) that travel together through one pipeline stage
   int w_stages;            // W4A16: depth of the dequantised-weight ring
   int col_stage_bytes;     // bn * 128
   int row_tx_bytes, col_tx_bytes;   // bytes the loads of one stage deliver per operand

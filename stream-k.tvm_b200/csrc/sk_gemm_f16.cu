@@ -7,7 +7,7 @@
 // tiles x K-iterations (sk_sched.h).  Inside a CTA three roles run in lock-step
 // over the same segment list, synchronised by mbarriers only:
 //
-//   warp 0      producer : TMA loads of the A and B stage tiles (128-byte swizzle)
+//   warps 0, 6  producers: TMA loads of the two operands' stage tiles (128-byte swizzle)
 //   warp 1      MMA      : one thread issues tcgen05.mma, accumulators in TMEM
 //                          (two buffers, so a segment's epilogue overlaps the
 //                          next segment's mainloop)
@@ -28,7 +28,7 @@ using namespace skptx;
 constexpr int BM = SK_BM;
 constexpr int BK = 64;
 constexpr int ROW_STAGE_BYTES = BM * BK * 2;   // 16 KB: 128 rows x 128 B
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 224;   // warps: 0 row-operand producer, 1 MMA, 2..5 epilogue, 6 col-operand producer
 constexpr int MAX_STAGES = 12;
 constexpr int CTRL_BYTES = 512;
 constexpr int SMEM_LIMIT = 232448;             // 227 KB opt-in maximum per CTA
@@ -73,9 +73,10 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw_addr);
   const int STAGES = p.stages;
+  const int G = p.kgroup;               // K steps per pipeline stage
   const uint32_t sRow = base;
-  const uint32_t sCol = base + STAGES * ROW_STAGE_BYTES;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * (ROW_STAGE_BYTES + p.col_stage_bytes));
+  const uint32_t sCol = base + STAGES * G * ROW_STAGE_BYTES;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * G * (ROW_STAGE_BYTES + p.col_stage_bytes));
   volatile uint32_t* abort_flag = &ctrl->abort;
 
   const int warp = threadIdx.x >> 5;
@@ -112,9 +113,14 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
   if (threadIdx.x == 0) sk_trace(p, 1);
 
-  if (warp == 0) {
-    // ------------------------------------------------------------- producer
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------- producers
+    // Issuing a TMA instruction costs its thread tens of nanoseconds, and for narrow tiles
+    // that, not bandwidth, bounds the K-step rate.  So two threads in two warps share the
+    // work: warp 0 loads the row operand (and announces the stage's byte count), warp 6 the
+    // column operand.  Both wait on the same "stage free" barrier.
     if (lane == 0) {
+      const bool is_row = warp == 0;
       bool traced = false;
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
@@ -123,33 +129,34 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       uint32_t ph = 0;
       bool ok = true;
       const uint32_t tx = p.row_tx_bytes + p.col_tx_bytes;
-      // This one thread feeds the whole SM: keep its loop short.  The common case (both
-      // operands K-major behind tensor maps) issues exactly two TMA instructions per step.
-      const bool both_tma_k = p.row_loader == SK_LOAD_TMA_K && p.col_loader == SK_LOAD_TMA_K;
-      const int col_stage_bytes = p.col_stage_bytes;
+      const int loader = is_row ? p.row_loader : p.col_loader;
+      const CUtensorMap* tm = is_row ? &tmRow : &tmCol;
+      const void* img = is_row ? p.row_img : p.col_img;
+      const int stage_bytes = is_row ? ROW_STAGE_BYTES : p.col_stage_bytes;
+      const uint32_t dst0 = is_row ? sRow : sCol;
+      const int tile_rows = is_row ? BM : p.bn;
       const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
       while (ok && sk_next(s, pid, cur, seg)) {
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
-        const int r0 = tr * BM, c0 = tc * p.bn;
-        for (int k = seg.k0; k < seg.k1; ++k) {
+        const int first_row = is_row ? tr * BM : tc * p.bn;
+        for (int k = seg.k0; k < seg.k1;) {
+          // up to G consecutive K steps share one stage: one barrier round trip for all
+          const int n = (seg.k1 - k) < G ? (seg.k1 - k) : G;
           const uint32_t full = full0 + 8u * stage;
-          if (!sk_wait_bar(empty0 + 8u * stage, ph ^ 1u, abort_flag, p, stage, 0)) {
+          if (!sk_wait_bar(empty0 + 8u * stage, ph ^ 1u, abort_flag, p, stage, is_row ? 0 : 4)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, tx);
-          if (both_tma_k) {
-            tma_load_2d(sRow + stage * ROW_STAGE_BYTES, &tmRow, full, k * BK, r0);
-            tma_load_2d(sCol + stage * col_stage_bytes, &tmCol, full, k * BK, c0);
-          } else {
-            load_operand(p.row_loader, sRow + stage * ROW_STAGE_BYTES, &tmRow, p.row_img, full, r0, k,
-                         BM, s.iters_per_tile);
-            load_operand(p.col_loader, sCol + stage * col_stage_bytes, &tmCol, p.col_img, full, c0, k,
-                         p.bn, s.iters_per_tile);
+          if (is_row) mbar_arrive_expect_tx(full, n * tx);
+          for (int j = 0; j < n; ++j) {
+            const uint32_t dst = dst0 + (stage * G + j) * stage_bytes;
+            if (loader == SK_LOAD_TMA_K) tma_load_2d(dst, tm, full, (k + j) * BK, first_row);
+            else load_operand(loader, dst, tm, img, full, first_row, k + j, tile_rows, s.iters_per_tile);
           }
+          k += n;
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
-          if (!traced) { sk_trace(p, 2); traced = true; }
+          if (is_row && !traced) { sk_trace(p, 2); traced = true; }
         }
       }
     }
@@ -184,22 +191,26 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * acc_stride;
         uint32_t accumulate = 0u;   // the segment's first UMMA overwrites the accumulator
-        for (int k = seg.k0; k < seg.k1; ++k) {
+        for (int k = seg.k0; k < seg.k1;) {
+          const int n = (seg.k1 - k) < G ? (seg.k1 - k) : G;
           if (!sk_wait_bar(full0 + 8u * stage, ph, abort_flag, p, 32 + stage, 1)) {
             ok = false;
             break;
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          const uint32_t a_lo = row_lo0 + stage * (ROW_STAGE_BYTES >> 4);
-          const uint32_t b_lo = col_lo0 + stage * col_stage16;
+          for (int j = 0; j < n; ++j) {
+            const uint32_t a_lo = row_lo0 + (stage * G + j) * (ROW_STAGE_BYTES >> 4);
+            const uint32_t b_lo = col_lo0 + (stage * G + j) * col_stage16;
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            umma_f16_ss(d_tmem, row_hi | (a_lo + kk * row_kstep16), col_hi | (b_lo + kk * col_kstep16),
-                        idesc, accumulate);
-            accumulate = 1u;
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              umma_f16_ss(d_tmem, row_hi | (a_lo + kk * row_kstep16), col_hi | (b_lo + kk * col_kstep16),
+                          idesc, accumulate);
+              accumulate = 1u;
+            }
           }
           umma_commit(empty0 + 8u * stage);  // frees the stage when the MMAs retire
+          k += n;
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
         }
         if (!ok) break;
@@ -208,7 +219,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       }
       sk_trace(p, 4);
     }
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------- epilogue
     sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                      smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
@@ -350,6 +361,12 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   if (pairs) return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
   sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, 0);
   if (p.stages < 2) return SK_ERR_SHAPE;
+  // Very narrow tiles walked whole (data-parallel, long K) are bounded by the per-stage
+  // barrier round trip of the issuing threads, not by bandwidth: four K steps then share a
+  // stage.  Measured: 1.3x there; Stream-K segments are short and HBM-bound and lose from the
+  // coarser stages, so they keep one K step per stage.
+  p.kgroup = (prob->schedule == SK_SCHED_DP && p.stages >= 12) ? 4 : 1;
+  p.stages /= p.kgroup;
 
   // Which matrix feeds which side of the UMMA.  Activations A are always K-major; the
   // weight operand is K-major (NT), MN-major (NN) or a pre-laid-out image (LADDER).
@@ -384,7 +401,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
             (p.row_loader == SK_LOAD_TMA_MN ? (1u << 15) : 0u) |
             (p.col_loader == SK_LOAD_TMA_MN ? (1u << 16) : 0u);
 
-  const int smem_bytes = p.stages * (ROW_STAGE_BYTES + p.col_stage_bytes) + 1024 + CTRL_BYTES;
+  const int smem_bytes = p.stages * p.kgroup * (ROW_STAGE_BYTES + p.col_stage_bytes) + 1024 + CTRL_BYTES;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
