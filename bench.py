@@ -243,8 +243,9 @@ def run_sweep(path: str, peaks: dict) -> None:
         ref = oracle.gemm_ref(c["A"], c["B"], "nt")
         # tile None = the library's own choice (operands swapped for M <= 64, CTA pairs for
         # large problems); explicit 128 x 256 tiles are timed as well where they make sense
-        variants = [("streamk", "atomic", None), ("streamk", "block_reduce", None),
-                    ("hybrid", "block_reduce", None), ("dp", "atomic", None)]
+        variants = [("auto", "block_reduce", None), ("streamk", "atomic", None),
+                    ("streamk", "block_reduce", None), ("hybrid", "block_reduce", None),
+                    ("dp", "atomic", None)]
         if M > 64 and N * M >= 256 * 4096:
             variants += [("streamk", "block_reduce", 256), ("dp", "atomic", 256)]
         for schedule, fixup, tile_n in variants:
@@ -274,7 +275,8 @@ def run_sweep(path: str, peaks: dict) -> None:
         nbytes = 2.0 * M * K + N * K / 2 + 3.0 * N * K / 128 + 2.0 * M * N
         est = max(nbytes / 6.5e3, flops / 1.5e9) / 1e3 + 3
         ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
-        for schedule, fixup in (("streamk", "block_reduce"), ("hybrid", "block_reduce"), ("streamk", "atomic")):
+        for schedule, fixup in (("auto", "block_reduce"), ("streamk", "block_reduce"),
+                                ("hybrid", "block_reduce"), ("streamk", "atomic")):
             fn = lambda i: sk.streamk_fp16_ladder_block_reduce_q4(A, Ps[i], schedule=schedule, fixup=fixup, out=out)
             fn(0)
             sk.check_status()
@@ -306,7 +308,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sweep", default=None, help="also time configs 2-4 and write the table here")
-    ap.add_argument("--schedule", default=os.environ.get("SK_BENCH_SCHEDULE", "hybrid"))
+    ap.add_argument("--schedule", default=os.environ.get("SK_BENCH_SCHEDULE", "auto"))
     ap.add_argument("--fixup", default=os.environ.get("SK_BENCH_FIXUP", "block_reduce"))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -471,7 +473,9 @@ def main() -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
         "config": {"workload": f"cfg5 fp16 NT GEMM M={M5} N={N5} K={K5}, N sharded {world}-way",
-                   "schedule": args.schedule, "fixup": args.fixup, "tile": [info["tile_m"], info["tile_n"], 64],
+                   "schedule": {v: k for k, v in __import__("streamk_b200")._lib.SCHEDULES.items()}[info["schedule"]]
+                   + (" (auto)" if args.schedule == "auto" else ""),
+                   "fixup": args.fixup, "tile": [info["tile_m"], info["tile_n"], 64],
                    "sk_tiles": info["sk_tiles"], "dp_tiles": info["dp_tiles"],
                    "l2": "operands (>= 0.25 GB per GPU) exceed the 126 MB L2; no flush needed"},
         "per_gpu_tflops": value / world,

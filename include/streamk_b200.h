@@ -44,7 +44,8 @@ enum { SK_SCHED_STREAMK = 0,        /* every tile is Stream-K'd                 
        SK_SCHED_HYBRID = 1,         /* reference order: SK tiles first, then DP waves
                                        (streamk_fp16.py:98-113, 353-371)                          */
        SK_SCHED_HYBRID_DP_FIRST = 2,/* same tile split, DP waves first, SK remainder last         */
-       SK_SCHED_DP = 3              /* plain data-parallel: one whole tile per CTA per wave       */ };
+       SK_SCHED_DP = 3,             /* plain data-parallel: one whole tile per CTA per wave       */
+       SK_SCHED_AUTO = 4            /* the library picks schedule (and open tile sizes) by shape  */ };
 
 enum { SK_FIXUP_ATOMIC = 0,        /* fp32 red.global.add into a self-cleaning workspace
                                       (replaces T.atomic_addx2, streamk_fp16.py:248-255)          */
@@ -83,6 +84,7 @@ typedef struct sk_schedule_info {
   int32_t dp_first;
   int32_t group_m;
   int32_t swap_ab;             /* 1: weights feed the UMMA M dimension          */
+  int32_t schedule;            /* the schedule used (SK_SCHED_AUTO resolved)    */
 } sk_schedule_info;
 
 typedef struct sk_device_info {

@@ -129,6 +129,41 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
   return SK_OK;
 }
 
+// SK_SCHED_AUTO: replace the schedule (and, if the caller left them open, the tile) by the
+// choice that measured best on B200 for this kind of shape.  The rules of thumb behind it:
+//  * a fixup costs a few microseconds of L2 round trips, so when whole tiles alone can keep
+//    most SMs busy, run them data-parallel with the tile width fitted to the SM count;
+//  * otherwise every SM has to stream (a single SM ingests only ~110 GB/s): Stream-K;
+//  * large problems: the reference's hybrid split.
+void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
+  if (q->schedule != SK_SCHED_AUTO) return;
+  q->schedule = SK_SCHED_HYBRID;
+  if (kernel_kind == 0 || kernel_kind == 3) return;
+  const bool tiles_open = q->tile_m == 0 && q->tile_n == 0;
+  const long long t256 = static_cast<long long>((q->M + 255) / 256) * ((q->N + 255) / 256);
+  if (t256 >= num_sms) return;                       // large: hybrid (CTA pairs when eligible)
+  if (q->M <= 64 && (tiles_open || (q->tile_m != 0 && q->tile_m != 128))) {
+    // operands swapped: one tile per 128 weight rows
+    const int tiles = (q->N + 127) / 128;
+    // (the W4A16 mainloop's K-step rate is set by its dequantise hand-over, so it always
+    // wants every SM: Stream-K)
+    q->schedule = (kernel_kind == 1 && 2 * tiles >= num_sms) ? SK_SCHED_DP : SK_SCHED_STREAMK;
+    return;
+  }
+  const int tiles_m = (q->M + 127) / 128;
+  if (kernel_kind == 1 && tiles_open && tiles_m <= num_sms) {
+    // widest column count per tile row that still gives every tile its own SM
+    const int per_row = num_sms / tiles_m;
+    int bn = ((q->N + per_row - 1) / per_row + 15) & ~15;
+    if (bn >= 80 && bn <= 256 && q->layout == SK_LAYOUT_NT) {
+      q->schedule = SK_SCHED_DP; q->tile_m = 128; q->tile_n = bn;
+      return;
+    }
+  }
+  q->schedule = SK_SCHED_STREAMK;
+  if (tiles_open) { q->tile_m = 128; q->tile_n = 128; }
+}
+
 int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
                   SkSched* s, SkPlan* plan_out) {
   if (!p || num_sms <= 0) return SK_ERR_ARG;
@@ -203,9 +238,13 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
 
 extern "C" int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms,
                            sk_schedule_info* out) {
-  if (!out) return SK_ERR_ARG;
+  if (!out || !p) return SK_ERR_ARG;
   if (kernel_kind < 0 || kernel_kind > 3) return SK_ERR_ARG;
-  return sk_make_sched(p, kernel_kind, num_sms, out, nullptr, nullptr);
+  sk_problem q = *p;
+  sk_resolve_auto(&q, kernel_kind, num_sms);
+  const int st = sk_make_sched(&q, kernel_kind, num_sms, out, nullptr, nullptr);
+  if (st == SK_OK) out->schedule = q.schedule;
+  return st;
 }
 
 // Kernel-space schedule (rows = the 128-wide UMMA M side) from the logical description.

@@ -132,3 +132,4 @@ int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out);
 int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
                   SkSched* s, SkPlan* plan);
 unsigned long long* sk_trace_buffer();
+void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms);

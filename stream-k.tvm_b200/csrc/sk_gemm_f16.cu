@@ -320,6 +320,9 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   int num_sms = 0, dev_sms = 0;
   int st = sk_resolve_grid(prob, &num_sms, &dev_sms);
   if (st != SK_OK) return st;
+  sk_problem resolved = *prob;   // SK_SCHED_AUTO -> a concrete schedule and tile
+  sk_resolve_auto(&resolved, 1, num_sms);
+  prob = &resolved;
   SkParams p;
   memset(&p, 0, sizeof(p));
   SkPlan plan;
@@ -362,10 +365,10 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, 0);
   if (p.stages < 2) return SK_ERR_SHAPE;
   // Very narrow tiles walked whole (data-parallel, long K) are bounded by the per-stage
-  // barrier round trip of the issuing threads, not by bandwidth: four K steps then share a
-  // stage.  Measured: 1.3x there; Stream-K segments are short and HBM-bound and lose from the
+  // barrier round trip of the issuing threads, not by bandwidth: two or four K steps then
+  // share a stage.  Measured: 1.3x there; Stream-K segments are short and HBM-bound and lose from the
   // coarser stages, so they keep one K step per stage.
-  p.kgroup = (prob->schedule == SK_SCHED_DP && p.stages >= 12) ? 4 : 1;
+  p.kgroup = prob->schedule != SK_SCHED_DP ? 1 : p.stages >= 12 ? 4 : p.stages >= 8 ? 2 : 1;
   p.stages /= p.kgroup;
 
   // Which matrix feeds which side of the UMMA.  Activations A are always K-major; the

@@ -189,6 +189,9 @@ extern "C" int sk_gemm_f32(const sk_problem* prob, const float* A, const float* 
   int num_sms = 0, dev_sms = 0;
   int st = sk_resolve_grid(prob, &num_sms, &dev_sms);
   if (st != SK_OK) return st;
+  sk_problem resolved = *prob;   // SK_SCHED_AUTO -> a concrete schedule and tile
+  sk_resolve_auto(&resolved, 0, num_sms);
+  prob = &resolved;
   SkParams p;
   memset(&p, 0, sizeof(p));
   st = sk_make_sched(prob, 0, num_sms, nullptr, &p.sched, nullptr);
@@ -256,6 +259,7 @@ extern "C" int sk_gemm_f32_noalloc(const sk_problem* prob, const float* A, const
   if (prob->num_sms > SK_NOALLOC_MAX_CTAS) return SK_ERR_LIMIT;
   sk_problem q = *prob;
   if (q.num_sms <= 0) q.num_sms = SK_NOALLOC_MAX_CTAS;
+  sk_resolve_auto(&q, 0, q.num_sms);
   int num_sms = 0, dev_sms = 0;
   int st = sk_resolve_grid(&q, &num_sms, &dev_sms);
   if (st != SK_OK) return st;

@@ -440,6 +440,9 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   int num_sms = 0, dev_sms = 0;
   int st = sk_resolve_grid(prob, &num_sms, &dev_sms);
   if (st != SK_OK) return st;
+  sk_problem resolved = *prob;   // SK_SCHED_AUTO -> a concrete schedule and tile
+  sk_resolve_auto(&resolved, 2, num_sms);
+  prob = &resolved;
   const int M = prob->M, N = prob->N, K = prob->K;
   if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0) return SK_ERR_SHAPE;
   if (prob->lda < K || prob->ldc < N) return SK_ERR_SHAPE;

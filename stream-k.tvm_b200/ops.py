@@ -127,7 +127,7 @@ def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkPr
                        test_drop_flag_cta=int(o["_drop_flag_cta"]))
 
 
-def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "hybrid",
+def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "auto",
                   num_sms: int = 148, **kw) -> dict:
     """Host scheduler integers (streamk_fp16.py:83-113) and the tile plan for a problem;
     needs no GPU.  kind: "f32", "f16", "w4a16", or "f16_pairs" (the CTA-pair kernel the fp16 NT
@@ -185,7 +185,7 @@ def _aligned16(t: torch.Tensor) -> torch.Tensor:
 
 # --------------------------------------------------------------------------- fp32
 def streamk_fp32(A: torch.Tensor, B: torch.Tensor, *, fixup: str = "atomic",
-                 schedule: str = "hybrid", trans_b: bool = False, **kw) -> torch.Tensor:
+                 schedule: str = "auto", trans_b: bool = False, **kw) -> torch.Tensor:
     """C = A @ B in fp32 (FFMA, no TF32).  A [M,K]; B [K,N] (or [N,K] with trans_b).
 
     Mirrors `tl_matmul_streamk(..., "float32", "float32", "float32", ...)` of
@@ -252,17 +252,19 @@ def _gemm_f16(A, B, layout, fixup, schedule, kw):
     return Cout
 
 
-def streamk_fp16_nt(A, B, *, fixup="atomic", schedule="hybrid", **kw):
+def streamk_fp16_nt(A, B, *, fixup="block_reduce", schedule="auto", **kw):
     """C = A @ B.T, fp16 in, fp32 accumulate, fp16 out.  A [M,K], B [N,K].
 
     Mirrors `tl_matmul_streamk(M, N, K, streamk_tiles, "float16", "float16", ...)` +
     `tl_mod(A, B, C)` of streamk_fp16.py:116-387 and streamk_fp16_nt.py:57-192.
+    schedule: "auto" (the library picks by shape), "hybrid" (the reference's split),
+    "hybrid_dp_first", "streamk", "dp".  fixup: "block_reduce" (deterministic) or "atomic".
     Keyword options: see _options().
     """
     return _gemm_f16(A, B, "nt", fixup, schedule, kw)
 
 
-def streamk_fp16_nn(A, B, *, fixup="atomic", schedule="hybrid", **kw):
+def streamk_fp16_nn(A, B, *, fixup="block_reduce", schedule="auto", **kw):
     """C = A @ B, fp16.  A [M,K], B [K,N]  (streamk_fp16_nn.py:57-177)."""
     return _gemm_f16(A, B, "nn", fixup, schedule, kw)
 
@@ -305,7 +307,7 @@ def ladder_prepack(B: torch.Tensor) -> LadderWeight:
     return LadderWeight(out, N, K)
 
 
-def streamk_fp16_ladder(A, LB: LadderWeight, *, fixup="atomic", schedule="hybrid", **kw):
+def streamk_fp16_ladder(A, LB: LadderWeight, *, fixup="block_reduce", schedule="auto", **kw):
     """C = A @ W.T with W pre-laid-out (streamk_fp16_ladder.py:137-486)."""
     return _gemm_f16(A, LB, "ladder", fixup, schedule, kw)
 
@@ -378,7 +380,7 @@ def dequant_w4(QLB: PackedQ4) -> torch.Tensor:
 
 
 def streamk_fp16_ladder_block_reduce_q4(A, QLB: PackedQ4, *, fixup="block_reduce",
-                                        schedule="hybrid", **kw):
+                                        schedule="auto", **kw):
     """W4A16: C = A @ ((q - z) * s).T, fp16 activations, uint4 weights.
 
     Mirrors `tl_mod(A, QLB, C)` of streamk_fp16_ladder_block_reduce_q4.py:143-599."""

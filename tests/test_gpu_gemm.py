@@ -17,7 +17,7 @@ DEV = "cuda"
 TOL16 = 1e-2
 TOL32 = 1e-4
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
-SCHEDULES = ("streamk", "hybrid", "hybrid_dp_first", "dp")
+SCHEDULES = ("streamk", "hybrid", "hybrid_dp_first", "dp", "auto")
 FIXUPS = ("atomic", "block_reduce")
 
 

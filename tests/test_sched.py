@@ -138,3 +138,26 @@ def test_short_m_swaps_operands(lib):
         assert 0 <= tm.value < info.tiles_m == 2 and 0 <= tn.value < info.tiles_n == 8
         seen.add((tm.value, tn.value))
     assert len(seen) == 16
+
+
+def test_auto_schedule_resolution(lib):
+    from streamk_b200 import _lib as L
+    AUTO = L.SCHEDULES["auto"]
+    def plan(M, N, K, kind=1):
+        prob = L.SkProblem(M=M, N=N, K=K, schedule=AUTO, layout=1)
+        info = L.SkScheduleInfo()
+        assert lib.sk_schedule(C.byref(prob), kind, 148, C.byref(info)) == 0
+        return info.as_dict()
+    names = {v: k for k, v in L.SCHEDULES.items()}
+    d = plan(16, 4096, 4096)          # 32 swapped tiles: every SM has to stream
+    assert (names[d["schedule"]], d["swap_ab"]) == ("streamk", 1)
+    d = plan(16, 12288, 4096)         # 96 swapped tiles: whole tiles keep most SMs busy
+    assert (names[d["schedule"]], d["swap_ab"], d["total_tiles"]) == ("dp", 1, 96)
+    d = plan(256, 12288, 4096)        # tile width fitted to 74 columns per tile row
+    assert names[d["schedule"]] == "dp" and d["tile_n"] == 176 and d["total_tiles"] <= 148
+    d = plan(128, 4096, 4096)         # too narrow to fit: Stream-K on 128 x 128 tiles
+    assert (names[d["schedule"]], d["tile_m"], d["tile_n"]) == ("streamk", 128, 128)
+    d = plan(8192, 28672, 8192, kind=3)
+    assert names[d["schedule"]] == "hybrid" and d["tile_m"] == 256
+    cov = oracle.coverage(plan(300, 5000, 1000))
+    assert set(cov.values()) == {1}
