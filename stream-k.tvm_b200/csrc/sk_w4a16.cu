@@ -31,7 +31,9 @@ constexpr int BM = SK_BM;
 constexpr int BK = 64;
 constexpr int Q_BLOCK_BYTES = 128 * BK / 2;    // 4096: packed nibbles of 128 weight rows x 64 K
 constexpr int SZ_BLOCK_BYTES = 128 * 2 + 128;  // 384: fp16 scales + uint8 zero-points of a group
-constexpr int W_STAGE_BYTES = 128 * BK * 2;    // 16384: dequantised fp16 stage
+constexpr int W_SLAB_BYTES = 128 * BK * 2;     // 16384: dequantised fp16 tile of one K step
+constexpr int KG = 2;                          // K steps per stage = one scale group (128 along K)
+constexpr int W_STAGE_BYTES = KG * W_SLAB_BYTES;
 constexpr int MAX_LS = 12;                     // load stages (activation tile + packed block)
 constexpr int MAX_BS = 8;                      // dequantised weight stages (ring depth chosen per launch)
 constexpr int DQ_WARPS = 8;
@@ -90,10 +92,11 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   uint8_t* smem = smem_raw + (base - raw_addr);
   const int LS = p.stages;
   const int BS = p.w_stages;
-  const int a_stage_bytes = p.row_tx_bytes;        // activation tile bytes per stage
+  const int a_tile_bytes = p.row_tx_bytes;         // activation tile bytes of one K step
+  const int a_stage_bytes = KG * a_tile_bytes;
   const int off_a = BS * W_STAGE_BYTES;
   const int off_q = off_a + LS * a_stage_bytes;
-  const int off_sz = off_q + LS * Q_BLOCK_BYTES;
+  const int off_sz = off_q + LS * KG * Q_BLOCK_BYTES;
   const uint32_t sW = base;
   const uint32_t sA = base + off_a;
   const uint32_t sQ = base + off_q;
@@ -151,26 +154,30 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       int ls = 0;
       uint32_t lph = 0;
       bool ok = true;
-      const uint32_t tx = a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
       while (ok && sk_next(s, pid, cur, seg)) {
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
         const int nblk = swapped ? tr : tc;                  // 128-row block of the weight
         const int a_row0 = swapped ? tc * p.bn : tr * BM;    // first activation row of the tile
-        for (int k = seg.k0; k < seg.k1; ++k) {
+        for (int k = seg.k0; k < seg.k1;) {
+          // A stage carries the K steps of one scale group (two, unless the segment starts
+          // or ends inside the group): one barrier round trip, one packed copy, one group block.
+          const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
           const uint32_t full = smem_u32(&ctrl->load_full[ls]);
           if (!sk_wait_bar(smem_u32(&ctrl->load_empty[ls]), lph ^ 1u, abort_flag, p, ls, 0)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, tx);
-          tma_load_2d(sA + ls * a_stage_bytes, &tmA, full, k * BK, a_row0);
-          bulk_load_1d(sQ + ls * Q_BLOCK_BYTES,
+          mbar_arrive_expect_tx(full, n * (a_tile_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES);
+          for (int j = 0; j < n; ++j)
+            tma_load_2d(sA + ls * a_stage_bytes + j * a_tile_bytes, &tmA, full, (k + j) * BK, a_row0);
+          bulk_load_1d(sQ + ls * KG * Q_BLOCK_BYTES,
                        qblocks + (static_cast<size_t>(nblk) * kblocks + k) * Q_BLOCK_BYTES,
-                       Q_BLOCK_BYTES, full);
+                       n * Q_BLOCK_BYTES, full);
           bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
                        szblocks + (static_cast<size_t>(nblk) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
                        SZ_BLOCK_BYTES, full);
+          k += n;
           if (++ls == LS) { ls = 0; lph ^= 1u; }
           if (!traced) { sk_trace(p, 2); traced = true; }
         }
@@ -187,7 +194,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       bool ok = true;
       const uint64_t desc_hi = umma_desc_sw128_hi(16, 1024);
       const uint32_t act_lo0 = umma_desc_lo(sA), wgt_lo0 = umma_desc_lo(sW);
-      const uint32_t act_stage16 = static_cast<uint32_t>(a_stage_bytes) >> 4;
+      const uint32_t act_tile16 = static_cast<uint32_t>(a_tile_bytes) >> 4;
       const uint32_t idesc = p.idesc;
       while (ok && sk_next(s, pid, cur, seg)) {
         const uint32_t buf = nseg & 1u;
@@ -197,7 +204,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
         uint32_t accumulate = 0u;
-        for (int k = seg.k0; k < seg.k1; ++k) {
+        for (int k = seg.k0; k < seg.k1;) {
+          const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
           if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 32 + ls, 1) ||
               !sk_wait_bar(smem_u32(&ctrl->w_full[bs]), bph, abort_flag, p, 48 + bs, 1)) {
             ok = false;
@@ -205,17 +213,20 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          const uint32_t act = act_lo0 + ls * act_stage16;
-          const uint32_t wgt = wgt_lo0 + bs * (W_STAGE_BYTES >> 4);
-          const uint32_t a_lo = swapped ? wgt : act;   // UMMA M side
-          const uint32_t b_lo = swapped ? act : wgt;   // UMMA N side
+          for (int j = 0; j < n; ++j) {
+            const uint32_t act = act_lo0 + (ls * KG + j) * act_tile16;
+            const uint32_t wgt = wgt_lo0 + (bs * KG + j) * (W_SLAB_BYTES >> 4);
+            const uint32_t a_lo = swapped ? wgt : act;   // UMMA M side
+            const uint32_t b_lo = swapped ? act : wgt;   // UMMA N side
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            umma_f16_ss(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
-            accumulate = 1u;
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              umma_f16_ss(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
+              accumulate = 1u;
+            }
           }
           umma_commit(smem_u32(&ctrl->load_empty[ls]));
           umma_commit(smem_u32(&ctrl->w_empty[bs]));
+          k += n;
           if (++ls == LS) { ls = 0; lph ^= 1u; }
           if (++bs == BS) { bs = 0; bph ^= 1u; }
         }
@@ -243,27 +254,30 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     uint32_t lph = 0, bph = 0;
     bool dead = false;
     while (sk_next(s, pid, cur, seg)) {
-      for (int k = seg.k0; k < seg.k1; ++k) {
+      for (int k = seg.k0; k < seg.k1;) {
+        const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
         if (!dead) {
           if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 64 + ls, 3) ||
               !sk_wait_bar(smem_u32(&ctrl->w_empty[bs]), bph ^ 1u, abort_flag, p, 80 + bs, 3))
             dead = true;
         }
         if (!dead) {
-          const uint8_t* q = smem + off_q + ls * Q_BLOCK_BYTES;
           const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
-          const uint4 w = *reinterpret_cast<const uint4*>(q + h * 2048 + r * 16);
           const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
           const uint32_t z = sz[256 + r];
           const __half2 s2 = __half2half2(sc);
           const uint32_t zm = 0x64006400u | z | (z << 16);
           const __half2 zmagic = *reinterpret_cast<const __half2*>(&zm);
-          uint8_t* wrow = smem + bs * W_STAGE_BYTES + r * 128;
-          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+          for (int j = 0; j < n; ++j) {
+            const uint8_t* q = smem + off_q + (ls * KG + j) * Q_BLOCK_BYTES;
+            const uint4 w = *reinterpret_cast<const uint4*>(q + h * 2048 + r * 16);
+            uint8_t* wrow = smem + (bs * KG + j) * W_SLAB_BYTES + r * 128;
+            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(wrow + (((h * 4 + j) ^ sw) << 4)) =
-                dequant_word(words[j], zmagic, s2);
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(wrow + (((h * 4 + i) ^ sw) << 4)) =
+                  dequant_word(words[i], zmagic, s2);
+          }
           fence_proxy_async_smem();  // generic-proxy stores -> visible to the UMMA reads
         }
         // Each warp hands over its own 32 rows x one K half: no CTA-wide barrier, the warps
@@ -273,6 +287,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           mbar_arrive(smem_u32(&ctrl->w_full[bs]));
           mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
         }
+        k += n;
         if (++ls == LS) { ls = 0; lph ^= 1u; }
         if (++bs == BS) { bs = 0; bph ^= 1u; }
       }
@@ -478,13 +493,13 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   // and takes over a microsecond end to end, so the weight ring has to be deep as well: take
   // the deepest weight ring that still leaves at least as many load stages.
   const int budget = SMEM_LIMIT - 1024 - CTRL_BYTES;
-  const int load_stage = a_stage_bytes + Q_BLOCK_BYTES + SZ_BLOCK_BYTES;
-  int ls = 0, bs = 3;
-  for (int b = MAX_BS; b >= 3; --b) {
+  const int load_stage = KG * (a_stage_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES;
+  int ls = 0, bs = 2;
+  for (int b = 4; b >= 2; --b) {
     const int l = (budget - b * W_STAGE_BYTES) / load_stage;
-    if (l >= b || b == 3) { bs = b; ls = l; break; }
+    if (l >= b || b == 2) { bs = b; ls = l; break; }
   }
-  if (ls > MAX_LS) ls = MAX_LS;
+  if (ls > 8) ls = 8;
   if (ls < 2) return SK_ERR_SHAPE;
   p.stages = ls;
   p.w_stages = bs;
