@@ -23,10 +23,11 @@ constexpr int BN = 256;              // tile columns (both CTAs see all of them 
 constexpr int BK = 64;
 constexpr int A_STAGE_BYTES = BM * BK * 2;         // 16 KB
 constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;   // 16 KB: this CTA's half of the B tile
-constexpr int STAGES = 7;              // 7 x 32 KB = 224 KB of the 227 KB a CTA may use
+constexpr int KG = 2;                  // K steps that share a pipeline stage (one barrier round trip)
+constexpr int STAGES = 3;              // 3 x 2 x 32 KB = 192 KB
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int PIPE_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+constexpr int PIPE_BYTES = STAGES * KG * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int CTRL_BYTES = 512;
 constexpr int SMEM_BYTES = PIPE_BYTES + 1024 + CTRL_BYTES;
 
@@ -51,7 +52,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
   const uint32_t sA = base;
-  const uint32_t sB = base + STAGES * A_STAGE_BYTES;
+  const uint32_t sB = base + STAGES * KG * A_STAGE_BYTES;
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + PIPE_BYTES);
   volatile uint32_t* abort_flag = &ctrl->abort;
 
@@ -108,16 +109,20 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         sk_tile_mn(s, seg.tile, tr, tc);
         const int a_row0 = (tr * 2 + rank) * BM;          // this CTA's 128 rows of A
         const int b_row0 = tc * BN + rank * (BN / 2);     // this CTA's 128 rows of B
-        for (int k = seg.k0; k < seg.k1; ++k) {
+        for (int k = seg.k0; k < seg.k1;) {
+          const int n = (seg.k1 - k) < KG ? (seg.k1 - k) : KG;
           if (!sk_wait_bar(empty0 + 8u * stage, ph ^ 1u, abort_flag, p, stage, 0)) {
             ok = false;
             break;
           }
-          // Both CTAs' loads complete on the leader's barrier; the leader expects all four.
+          // Both CTAs' loads complete on the leader's barrier; the leader expects all of them.
           const uint32_t full_leader = full0_leader + 8u * stage;
-          if (rank == 0) mbar_arrive_expect_tx(full0 + 8u * stage, 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
-          tma_load_2d_pair(sA + stage * A_STAGE_BYTES, &tmA, full_leader, k * BK, a_row0);
-          tma_load_2d_pair(sB + stage * B_STAGE_BYTES, &tmB, full_leader, k * BK, b_row0);
+          if (rank == 0) mbar_arrive_expect_tx(full0 + 8u * stage, n * 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+          for (int j = 0; j < n; ++j) {
+            tma_load_2d_pair(sA + (stage * KG + j) * A_STAGE_BYTES, &tmA, full_leader, (k + j) * BK, a_row0);
+            tma_load_2d_pair(sB + (stage * KG + j) * B_STAGE_BYTES, &tmB, full_leader, (k + j) * BK, b_row0);
+          }
+          k += n;
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
           if (!traced) { sk_trace(p, 2); traced = true; }
         }
@@ -145,21 +150,25 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         uint32_t accumulate = 0u;
-        for (int k = seg.k0; k < seg.k1; ++k) {
+        for (int k = seg.k0; k < seg.k1;) {
+          const int n = (seg.k1 - k) < KG ? (seg.k1 - k) : KG;
           if (!sk_wait_bar(full0 + 8u * stage, ph, abort_flag, p, 32 + stage, 1)) {
             ok = false;
             break;
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
-          const uint32_t b_lo = b_lo0 + stage * (B_STAGE_BYTES >> 4);
+          for (int j = 0; j < n; ++j) {
+            const uint32_t a_lo = a_lo0 + (stage * KG + j) * (A_STAGE_BYTES >> 4);
+            const uint32_t b_lo = b_lo0 + (stage * KG + j) * (B_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            umma_f16_ss_pair(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
-            accumulate = 1u;
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              umma_f16_ss_pair(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
+              accumulate = 1u;
+            }
           }
           umma_commit_pair(empty0 + 8u * stage);   // frees the stage in both CTAs
+          k += n;
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
         }
         if (!ok) break;
