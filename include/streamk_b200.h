@@ -45,7 +45,15 @@ enum { SK_SCHED_STREAMK = 0,        /* every tile is Stream-K'd                 
                                        (streamk_fp16.py:98-113, 353-371)                          */
        SK_SCHED_HYBRID_DP_FIRST = 2,/* same tile split, DP waves first, SK remainder last         */
        SK_SCHED_DP = 3,             /* plain data-parallel: one whole tile per CTA per wave       */
-       SK_SCHED_AUTO = 4            /* the library picks schedule (and open tile sizes) by shape  */ };
+       SK_SCHED_AUTO = 4,           /* the library picks schedule (and open tile sizes) by shape  */
+       SK_SCHED_CLUSTER = 5         /* split-K inside a thread-block cluster: every tile is walked
+                                       by the 2, 4 or 8 CTAs of one cluster (the largest size with
+                                       tiles x size <= num_sms), CTA r taking K iterations
+                                       [r*I/size, (r+1)*I/size); the partial tiles meet in the
+                                       cluster's distributed shared memory and are summed in CTA
+                                       order, so no workspace traffic and a bitwise reproducible
+                                       result.  fp16 entry points only; `fixup` is ignored.  No
+                                       counterpart in the reference.                              */ };
 
 enum { SK_FIXUP_ATOMIC = 0,        /* fp32 red.global.add into a self-cleaning workspace
                                       (replaces T.atomic_addx2, streamk_fp16.py:248-255)          */
@@ -85,6 +93,7 @@ typedef struct sk_schedule_info {
   int32_t group_m;
   int32_t swap_ab;             /* 1: weights feed the UMMA M dimension          */
   int32_t schedule;            /* the schedule used (SK_SCHED_AUTO resolved)    */
+  int32_t cluster;             /* SK_SCHED_CLUSTER: CTAs per tile; else 0       */
 } sk_schedule_info;
 
 typedef struct sk_device_info {

@@ -24,5 +24,5 @@ Parity status
   s = 1, z = 0 case.
 """
 from .gemm_ref import gemm_ref, unpack_u4, pack_u4_int32, dequant_ref, w4a16_ref, rel_err  # noqa: F401
-from .sched_ref import reference_schedule, cta_segments, coverage, tile_coords  # noqa: F401
+from .sched_ref import reference_schedule, cta_segments, cluster_segments, coverage, tile_coords  # noqa: F401
 from .inputs import make_case, CONFIGS  # noqa: F401

@@ -49,11 +49,26 @@ def cta_segments(pid: int, *, sk_tiles: int, total_tiles: int, iters_per_tile: i
     return dp + sk if dp_first else sk + dp
 
 
+def cluster_segments(pid: int, *, iters_per_tile: int, cluster: int):
+    """Split-K inside a thread-block cluster (no counterpart in the reference): CTA `pid`
+    is rank r = pid % cluster of tile pid // cluster and walks K iterations
+    [r*I // cluster, (r+1)*I // cluster) of it; nothing if that range is empty."""
+    tile, r = divmod(pid, cluster)
+    k0, k1 = r * iters_per_tile // cluster, (r + 1) * iters_per_tile // cluster
+    return [(tile, k0, k1)] if k1 > k0 else []
+
+
 def coverage(sched: dict) -> dict:
     """(tile, k) -> number of times covered, over all CTAs of a schedule described by the
     library's sk_schedule_info fields."""
     cover: dict = {}
     for pid in range(sched["grid"]):
+        if sched.get("cluster", 0) > 0:
+            for tile, k0, k1 in cluster_segments(pid, iters_per_tile=sched["iters_per_tile"],
+                                                 cluster=sched["cluster"]):
+                for k in range(k0, k1):
+                    cover[(tile, k)] = cover.get((tile, k), 0) + 1
+            continue
         for tile, k0, k1 in cta_segments(pid, sk_tiles=sched["sk_tiles"],
                                          total_tiles=sched["total_tiles"],
                                          iters_per_tile=sched["iters_per_tile"],

@@ -16,7 +16,7 @@ SK_ERR_ARCH, SK_ERR_ALIGN, SK_ERR_SHAPE, SK_ERR_WORKSPACE, SK_ERR_LAUNCH = 1, 2,
 SK_ERR_FIXUP_TIMEOUT, SK_ERR_PIPE_TIMEOUT, SK_ERR_ARG, SK_ERR_LIMIT = 6, 7, 8, 9
 
 LAYOUTS = {"nn": 0, "nt": 1, "ladder": 2}
-SCHEDULES = {"streamk": 0, "hybrid": 1, "hybrid_dp_first": 2, "dp": 3, "auto": 4}
+SCHEDULES = {"streamk": 0, "hybrid": 1, "hybrid_dp_first": 2, "dp": 3, "auto": 4, "cluster": 5}
 FIXUPS = {"atomic": 0, "block_reduce": 1}
 
 
@@ -30,7 +30,7 @@ class SkScheduleInfo(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "tile_m", "tile_n", "tile_k", "tiles_m", "tiles_n", "total_tiles", "iters_per_tile",
         "sk_tiles", "dp_tiles", "grid", "sk_iters_per_cta", "sk_iters_rem", "dp_waves",
-        "dp_first", "group_m", "swap_ab", "schedule")]
+        "dp_first", "group_m", "swap_ab", "schedule", "cluster")]
 
     def as_dict(self) -> dict:
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -189,6 +189,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
       if (total - T > P) T += P;
       break;
     case SK_SCHED_DP: T = 0; break;
+    case SK_SCHED_CLUSTER: T = total; break;
     default: return SK_ERR_ARG;
   }
   const long long S = T * I;
@@ -198,6 +199,15 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   if (dp > 0) grid = dp < P && T == 0 ? dp : P;
   else grid = S < P ? S : P;
   if (grid < 1) grid = 1;
+  int split = 0;
+  if (p->schedule == SK_SCHED_CLUSTER) {
+    // the largest portable cluster that still gives every tile its own cluster in one wave
+    if (kernel_kind != 1) return SK_ERR_ARG;
+    if (2 * total > P) return SK_ERR_SHAPE;
+    split = 2;
+    while (split < 8 && 2 * split * total <= P) split *= 2;
+    grid = total * split;
+  }
   int gm = p->group_m;
   // Bands of about 2048 rows: a wave of CTAs then shares ~8 row panels and ~9 column panels
   // of the operands, which keeps its footprint inside L2.
@@ -212,8 +222,9 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   sc.iters_per_tile = static_cast<int>(I);
   sc.sk_tiles = static_cast<int>(T);
   sc.grid = static_cast<int>(grid);
-  sc.sk_f = static_cast<int>(S / grid);
-  sc.sk_r = static_cast<int>(S % grid);
+  sc.sk_f = static_cast<int>(split ? I / split : S / grid);
+  sc.sk_r = static_cast<int>(split ? I % split : S % grid);
+  sc.split = split;
   sc.dp_first = p->schedule == SK_SCHED_HYBRID_DP_FIRST ? 1 : 0;
   sc.group_m = gm;
   if (s) *s = sc;
@@ -232,6 +243,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
     info->dp_waves = static_cast<int>((dp + grid - 1) / grid);
     info->dp_first = sc.dp_first;
     info->group_m = gm;
+    info->cluster = split;
   }
   return SK_OK;
 }
@@ -256,6 +268,7 @@ static SkSched sched_from_info(const sk_schedule_info* i) {
   s.iters_per_tile = i->iters_per_tile; s.sk_tiles = i->sk_tiles; s.grid = i->grid;
   s.sk_f = i->sk_iters_per_cta; s.sk_r = i->sk_iters_rem; s.dp_first = i->dp_first;
   s.group_m = i->group_m;
+  s.split = i->cluster;
   return s;
 }
 

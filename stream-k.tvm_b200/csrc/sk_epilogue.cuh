@@ -383,3 +383,102 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     pend_out[1] = head;
   }
 }
+
+// ---------------------------------------------------------------------------------------
+// SK_SCHED_CLUSTER: the CTAs of one thread-block cluster each hold a partial sum of the
+// SAME tile (sk_sched.h, `split`).  The partials meet in distributed shared memory instead
+// of the global workspace: the tile's float4 column groups ("quads", 4 columns x 128 rows)
+// are dealt out in runs of `per` to the cluster's CTAs; every CTA stores each quad of its
+// partial into the owner's receive buffer, slot [sender], and after one cluster barrier each
+// CTA sums its own quads over the senders in CTA order and writes them to C.
+//
+// Receive buffer of a CTA: float4 index (sender * per + local quad) * 128 + row.
+// ---------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ int sk_cluster_quads_per_cta(int bn, int split) {
+  return ((bn >> 2) + split - 1) / split;
+}
+__host__ __device__ __forceinline__ int sk_cluster_recv_bytes(int bn, int split) {
+  return split * sk_cluster_quads_per_cta(bn, split) * SK_BM * 16;
+}
+
+// Runs on the four epilogue warps.  `has_work`: this CTA's K range is not empty (an empty
+// one contributes zeros).  Returns after the partial has been handed to the owners; the
+// caller then meets the cluster barrier.
+__device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int warp, int lane,
+                                                uint32_t tmem_base, uint32_t tmem_full_bar,
+                                                uint32_t recv_base, volatile uint32_t* abort_flag,
+                                                bool has_work) {
+  using namespace skptx;
+  const int S = p.sched.split;
+  const int q = warp & 3;
+  const int row = q * 32 + lane;
+  const int per = sk_cluster_quads_per_cta(p.bn, S);
+  bool live = has_work;
+  if (has_work) {
+    const bool got = sk_wait_bar(tmem_full_bar, 0u, abort_flag, p, 24, 2);
+    if (!__all_sync(0xffffffffu, got)) live = false;
+  }
+  tc_fence_after();
+  if (warp == 2 && lane == 0) sk_trace(p, 5);
+  cluster_wait();   // second half of the start-up barrier: every CTA of the cluster is resident
+  const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  const uint32_t my_off = static_cast<uint32_t>((rank * per) * SK_BM + row) * 16u;
+  int owner = 0, lq = 0;
+  uint32_t dst = mapa_shared(recv_base, 0) + my_off;
+  for (int c = 0; c < p.bn; c += 32) {
+    float v[32];
+    if (live) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_addr + c, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (c + 4 * j < p.bn) {
+        st_cluster_v4(dst + static_cast<uint32_t>(lq) * (SK_BM * 16u), v[4 * j], v[4 * j + 1], v[4 * j + 2],
+                      v[4 * j + 3]);
+        if (++lq == per) {
+          lq = 0;
+          if (++owner < S) dst = mapa_shared(recv_base, owner) + my_off;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+}
+
+// Runs on every thread of the CTA after the cluster barrier.
+__device__ __forceinline__ void sk_cluster_reduce(const SkParams& p, __half* __restrict__ C, int tile,
+                                                  int rank, uint32_t recv_base) {
+  using namespace skptx;
+  const SkSched& s = p.sched;
+  const int S = s.split;
+  const int per = sk_cluster_quads_per_cta(p.bn, S);
+  int tr, tc;
+  sk_tile_mn(s, tile, tr, tc);
+  const int r0 = tr * SK_BM, c0 = tc * p.bn;
+  int valid_cols = p.cols - c0;
+  if (valid_cols > p.bn) valid_cols = p.bn;
+  int nq = ((valid_cols + 3) >> 2) - rank * per;   // quads of this CTA that hold real columns
+  if (nq > per) nq = per;
+  int rows_valid = p.rows - r0;
+  if (rows_valid > SK_BM) rows_valid = SK_BM;
+  const int items = nq * SK_BM;
+  const uint32_t slot_stride = static_cast<uint32_t>(per) * SK_BM * 16u;
+  for (int i = threadIdx.x; i < items; i += blockDim.x) {
+    const int row = i & (SK_BM - 1), lq = i >> 7;
+    if (row >= rows_valid) continue;
+    const uint32_t a = recv_base + static_cast<uint32_t>(i) * 16u;
+    float4 acc = ld_shared_v4(a);
+    for (int snd = 1; snd < S; ++snd) {
+      const float4 x = ld_shared_v4(a + snd * slot_stride);
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    sk_store4(C, p, r0 + row, c0 + (rank * per + lq) * 4, acc);
+  }
+}

@@ -84,6 +84,12 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   const int pid = blockIdx.x;
   const SkSched& s = p.sched;
   if (threadIdx.x == 0) sk_trace(p, 0);
+  // Split-K inside a cluster: the partial tiles meet in a receive buffer behind the control
+  // block.  First half of a start-up cluster barrier; the second half comes right before a
+  // thread's first access to another CTA's shared memory (or at teardown).
+  const bool clustered = s.split > 0;
+  const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
+  if (clustered) cluster_arrive();
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -221,16 +227,31 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     }
   } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------- epilogue
-    sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                     smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
+    if (clustered)
+      sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
+                      smem_u32(&ctrl->tmem_full[0]), recv_base, abort_flag,
+                      sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
+    else
+      sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                       smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   }
 
   // ------------------------------------------------------------- teardown
   tc_fence_before();
+  if (clustered) {
+    // Every partial of the tile has reached its owners once the whole cluster is here.  A CTA
+    // reads only its own shared memory afterwards, so it may leave as soon as it is done.
+    if (!(warp >= 2 && warp < 6)) cluster_wait();   // start-up barrier, second half
+    __syncwarp();
+    cluster_arrive();
+    cluster_wait();
+    if (threadIdx.x == 0) sk_trace(p, 6);
+    sk_cluster_reduce(p, C, pid / s.split, static_cast<int>(cluster_ctarank()), recv_base);
+  }
   __syncthreads();
   // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
   // the split tiles it took part in.
-  sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+  if (!clustered) sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
   if (warp == 1) {
     if (*abort_flag) {
       // A wait ran out: give copies and MMAs still in flight time to land before
@@ -326,7 +347,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   SkParams p;
   memset(&p, 0, sizeof(p));
   SkPlan plan;
-  const bool pairs = use_cta_pairs(prob, num_sms);
+  const bool pairs = prob->schedule != SK_SCHED_CLUSTER && use_cta_pairs(prob, num_sms);
   if (pairs) {
     sk_problem q = *prob;
     q.tile_m = 0; q.tile_n = 0;
@@ -362,7 +383,9 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   p.ws = sk_ws_carve(ws, dev_sms);  // layout fixed per device, whatever the grid
   p.trace = sk_trace_buffer();
   if (pairs) return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
-  sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, 0);
+  const int split = p.sched.split;   // SK_SCHED_CLUSTER: CTAs per tile
+  const int recv_bytes = split ? sk_cluster_recv_bytes(plan.bn, split) : 0;
+  sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, recv_bytes);
   if (p.stages < 2) return SK_ERR_SHAPE;
   // Very narrow tiles walked whole (data-parallel, long K) are bounded by the per-stage
   // barrier round trip of the issuing threads, not by bandwidth: two or four K steps then
@@ -404,7 +427,8 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
             (p.row_loader == SK_LOAD_TMA_MN ? (1u << 15) : 0u) |
             (p.col_loader == SK_LOAD_TMA_MN ? (1u << 16) : 0u);
 
-  const int smem_bytes = p.stages * p.kgroup * (ROW_STAGE_BYTES + p.col_stage_bytes) + 1024 + CTRL_BYTES;
+  const int smem_bytes =
+      p.stages * p.kgroup * (ROW_STAGE_BYTES + p.col_stage_bytes) + 1024 + CTRL_BYTES + recv_bytes;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -414,9 +438,28 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
+  cudaError_t e;
+  if (split) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(p.sched.grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = split;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, sk_gemm_f16_kernel, tmRow, tmCol, static_cast<__half*>(C), p);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    return SK_OK;
+  }
   sk_gemm_f16_kernel<<<p.sched.grid, NUM_THREADS, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
       tmRow, tmCol, static_cast<__half*>(C), p);
-  cudaError_t e = cudaGetLastError();
+  e = cudaGetLastError();
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

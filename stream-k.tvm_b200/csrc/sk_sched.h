@@ -21,6 +21,9 @@ struct SkSched {
   int sk_r;       // CTAs that get one more          "streamk_partial_tiles"
   int dp_first;   // 1: data-parallel waves before the Stream-K part
   int group_m;    // rasterisation group height in tiles (1 = row-major)
+  int split;      // > 0: every tile is split over the `split` CTAs of one thread-block cluster
+                  //      (grid = total_tiles * split), CTA r of the cluster walking K iterations
+                  //      [r*I/split, (r+1)*I/split) of its tile; 0: the Stream-K interval rule
 };
 
 struct SkSeg {
@@ -36,11 +39,20 @@ struct SkCursor {
 
 // First iteration of CTA p: p*f + min(p, r)   (streamk_fp16.py:176-181)
 SK_HD int sk_cta_begin(const SkSched& s, int p) {
+  if (s.split > 0) {
+    const int t = p / s.split, r = p - t * s.split;
+    return t * s.iters_per_tile + static_cast<int>(static_cast<long long>(r) * s.iters_per_tile / s.split);
+  }
   return p * s.sk_f + (p < s.sk_r ? p : s.sk_r);
 }
 
 // Inverse of sk_cta_begin: which CTA executes Stream-K iteration i.
 SK_HD int sk_cta_of(const SkSched& s, int i) {
+  if (s.split > 0) {
+    const int I = s.iters_per_tile;
+    const int t = i / I, k = i - t * I;
+    return t * s.split + static_cast<int>((static_cast<long long>(k + 1) * s.split - 1) / I);
+  }
   const int big = s.sk_r * (s.sk_f + 1);
   if (i < big) return i / (s.sk_f + 1);
   return s.sk_r + (i - big) / s.sk_f;   // sk_f > 0 here, else i < big always

@@ -165,6 +165,39 @@ def test_fp16_ladder(shape):
         _check(sk.streamk_fp16_ladder_block_reduce(A.to(DEV), LB, tile_n=tile_n), ref, TOL16)
 
 
+@pytest.mark.parametrize("shape", [
+    (384, 384, 8192),                    # configuration 2: 9 tiles, clusters of 8
+    (16, 4096, 4096), (128, 4096, 4096), (256, 4096, 4096), (1, 4096, 11008),   # 4, 4, 2, 4 CTAs per tile
+    (7, 300, 64), (33, 129, 200), (100, 1000, 520), (300, 260, 1000), (128, 512, 128)])
+def test_fp16_cluster_split_k(shape):
+    """SK_SCHED_CLUSTER: the partial tiles of a cluster meet in distributed shared memory.
+    Ragged shapes, fewer K iterations than CTAs (empty ranks), every layout; bitwise reproducible."""
+    M, N, K = shape
+    A, B = _rand16(M, N, K, seed=M + 3 * N + K)
+    ref = oracle.gemm_ref(A, B, "nt")
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    first = sk.streamk_fp16_nt(Ad, Bd, schedule="cluster")
+    _check(first, ref, TOL16)
+    info = sk.schedule_info(M, N, K, schedule="cluster")
+    assert info["cluster"] in (2, 4, 8) and info["grid"] == info["total_tiles"] * info["cluster"]
+    for _ in range(3):
+        assert torch.equal(sk.streamk_fp16_nt(Ad, Bd, schedule="cluster"), first)
+    if N * K <= 1 << 20:
+        for sms in (2 * info["total_tiles"], 4 * info["total_tiles"]):     # smaller clusters
+            _check(sk.streamk_fp16_nt(Ad, Bd, schedule="cluster", num_sms=sms), ref, TOL16)
+        _check(sk.streamk_fp16_nn(Ad, B.t().contiguous().to(DEV), schedule="cluster"), ref, TOL16)
+        _check(sk.streamk_fp16_ladder(Ad, sk.ladder_prepack(Bd), schedule="cluster"), ref, TOL16)
+        if M > 64:
+            for tile_n in (96, 256):
+                _check(sk.streamk_fp16_nt(Ad, Bd, schedule="cluster", tile_m=128, tile_n=tile_n), ref, TOL16)
+
+
+def test_fp16_cluster_needs_room_for_two_ctas_per_tile():
+    A, B = _rand16(256, 8192, 256, seed=1)     # 128 tiles: no cluster of 2 per tile fits 148 SMs
+    with pytest.raises(Exception):
+        sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), schedule="cluster")
+
+
 def test_fp16_config3_sample_of_the_sweep():
     # the full 24-shape sweep is the benchmark's job; parity on its extremes here
     for case in (0, 7, 22):

@@ -161,3 +161,45 @@ def test_auto_schedule_resolution(lib):
     assert names[d["schedule"]] == "hybrid" and d["tile_m"] == 256
     cov = oracle.coverage(plan(300, 5000, 1000))
     assert set(cov.values()) == {1}
+
+
+def test_cluster_split(lib):
+    """SK_SCHED_CLUSTER: cluster size from the SM budget, K ranges per rank, coverage."""
+    from streamk_b200 import _lib as L
+    d, info = _sched(lib, 384, 384, 8192, 1, "cluster", 148)
+    assert (d["total_tiles"], d["cluster"], d["grid"]) == (9, 8, 72)
+    d, info = _sched(lib, 128, 4096, 4096, 1, "cluster", 148)
+    assert (d["total_tiles"], d["cluster"], d["grid"], d["sk_iters_per_cta"]) == (32, 4, 128, 16)
+    d, info = _sched(lib, 256, 4096, 4096, 1, "cluster", 148)
+    assert (d["total_tiles"], d["cluster"], d["grid"]) == (64, 2, 128)
+    d, info = _sched(lib, 16, 4096, 4096, 1, "cluster", 64)       # the SM budget caps the size
+    assert (d["swap_ab"], d["cluster"], d["grid"]) == (1, 2, 64)
+    rnd = random.Random(11)
+    for _ in range(40):
+        M, N, K = rnd.randint(1, 600), rnd.randint(1, 1200), rnd.randint(1, 3000)
+        prob = L.SkProblem(M=M, N=N, K=K, lda=K, ldb=K, ldc=N, layout=1, schedule=L.SCHEDULES["cluster"])
+        info = L.SkScheduleInfo()
+        st = lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info))
+        d = info.as_dict()
+        if st != 0:   # more tiles than half the SMs: no cluster fits
+            tiles = -(-M // 128) * -(-N // 128) if M > 64 else -(-N // 128)
+            assert st == L.SK_ERR_SHAPE and 2 * tiles > 148
+            continue
+        assert d["cluster"] in (2, 4, 8) and d["grid"] == d["total_tiles"] * d["cluster"] <= 148
+        assert d["cluster"] == 8 or 2 * d["cluster"] * d["total_tiles"] > 148
+        cov = oracle.coverage(d)
+        assert len(cov) == d["total_tiles"] * d["iters_per_tile"] and set(cov.values()) == {1}
+        b, e = C.c_int64(), C.c_int64()
+        for p in range(d["grid"]):
+            assert lib.sk_cta_interval(C.byref(info), p, C.byref(b), C.byref(e)) == 0
+            segs = oracle.cluster_segments(p, iters_per_tile=d["iters_per_tile"], cluster=d["cluster"])
+            I = d["iters_per_tile"]
+            if segs:
+                t, k0, k1 = segs[0]
+                assert (b.value, e.value) == (t * I + k0, t * I + k1)
+            else:
+                assert b.value == e.value
+    # other kernels do not take it
+    prob = L.SkProblem(M=128, N=512, K=512, schedule=L.SCHEDULES["cluster"])
+    assert lib.sk_schedule(C.byref(prob), 0, 148, C.byref(info)) == L.SK_ERR_ARG
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == L.SK_ERR_ARG
