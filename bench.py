@@ -248,6 +248,12 @@ def run_sweep(path: str, peaks: dict) -> None:
                     ("dp", "atomic", None)]
         if M > 64 and N * M >= 256 * 4096:
             variants += [("streamk", "block_reduce", 256), ("dp", "atomic", 256)]
+        # split-K inside clusters, where there are few enough tiles for it
+        try:
+            if sk.schedule_info(M, N, K, schedule="cluster")["cluster"] > 0:
+                variants.append(("cluster", "block_reduce", None))
+        except sk.StreamKError:
+            pass
         for schedule, fixup, tile_n in variants:
             fn = lambda i: sk.streamk_fp16_nt(A, Bs[i], schedule=schedule, fixup=fixup, out=out, tile_n=tile_n)
             fn(0)
@@ -255,8 +261,11 @@ def run_sweep(path: str, peaks: dict) -> None:
             err = oracle.rel_err(out, ref)
             us = time_rotating(fn, copies, est)
             info = sk.schedule_info(M, N, K, schedule=schedule, tile_n=tile_n)
+            names = {v: k for k, v in sk.SCHEDULES.items()}
+            how = f"cluster of {info['cluster']}" if info["cluster"] else fixup
+            label = schedule if schedule != "auto" else f"auto={names[info['schedule']]}"
             record(cfg, "streamk_fp16_nt", M, N, K,
-                   f"{schedule}/{fixup}/tile{info['tile_m']}x{info['tile_n']}", us, flops, nbytes,
+                   f"{label}/{how}/tile{info['tile_m']}x{info['tile_n']}", us, flops, nbytes,
                    {"rel_err": float(f"{err:.3e}")})
         fn = lambda i: torch.matmul(A, Bs[i].t(), out=out)
         us = time_rotating(fn, copies, est)

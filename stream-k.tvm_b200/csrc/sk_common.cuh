@@ -81,6 +81,8 @@ struct SkParams {
   int row_tx_bytes, col_tx_bytes;   // bytes the loads of one stage deliver per operand
   int row_loader, col_loader;       // SK_LOAD_*
   uint32_t idesc;          // UMMA instruction descriptor
+  int cl_per;              // SK_SCHED_CLUSTER: float4 column groups of the tile that each CTA reduces
+  SkDiv cl_per_div;        // / cl_per
   SkSched sched;
   int fixup;               // SK_FIXUP_*
   int c_vec_ok;            // C rows can take 16-byte stores

@@ -387,44 +387,114 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
 // ---------------------------------------------------------------------------------------
 // SK_SCHED_CLUSTER: the CTAs of one thread-block cluster each hold a partial sum of the
 // SAME tile (sk_sched.h, `split`).  The partials meet in distributed shared memory instead
-// of the global workspace: the tile's float4 column groups ("quads", 4 columns x 128 rows)
-// are dealt out in runs of `per` to the cluster's CTAs; every CTA stores each quad of its
-// partial into the owner's receive buffer, slot [sender], and after one cluster barrier each
-// CTA sums its own quads over the senders in CTA order and writes them to C.
+// of the global workspace.  The tile's float4 column groups ("quads", 4 columns x 128 rows)
+// are dealt out in runs of `per` to the cluster's CTAs.  A CTA
+//   1. copies its accumulator from tensor memory into a staging area (the operand ring,
+//      idle by then), one contiguous chunk per destination CTA, its own chunk straight into
+//      its receive buffer;
+//   2. sends every other chunk with one bulk shared-to-shared copy, whose bytes are counted
+//      on an mbarrier of the destination;
+//   3. waits (bounded) on its own mbarrier for the S-1 chunks addressed to it, sums its quads
+//      over the senders in CTA order (bitwise reproducible) and writes them to C.
+// Two cluster barriers frame this: one at start-up (nobody writes into a CTA before its
+// mbarrier exists; its arrivals are spread over the start of the mainloop, where they cost
+// nothing) and one at the end (nobody leaves while its outgoing copies may still be read from
+// its staging area; its latency overlaps step 3's arithmetic).
 //
-// Receive buffer of a CTA: float4 index (sender * per + local quad) * 128 + row.
+// Chunk layout, same in the staging area and in a receive slot: quad q of the chunk starts
+// at q * SK_CL_QUAD_BYTES, row r of it 16*r bytes further.  The 16 bytes of padding per quad
+// let a quarter warp read one row of eight quads without a bank conflict.  A receive buffer
+// is S such chunks, indexed by sender.
 // ---------------------------------------------------------------------------------------
+constexpr int SK_CL_QUAD_BYTES = SK_BM * 16 + 16;
+
 __host__ __device__ __forceinline__ int sk_cluster_quads_per_cta(int bn, int split) {
   return ((bn >> 2) + split - 1) / split;
 }
+// bytes of a receive buffer, and of the staging area
 __host__ __device__ __forceinline__ int sk_cluster_recv_bytes(int bn, int split) {
-  return split * sk_cluster_quads_per_cta(bn, split) * SK_BM * 16;
+  return split * sk_cluster_quads_per_cta(bn, split) * SK_CL_QUAD_BYTES;
 }
 
-// Runs on the four epilogue warps.  `has_work`: this CTA's K range is not empty (an empty
-// one contributes zeros).  Returns after the partial has been handed to the owners; the
-// caller then meets the cluster barrier.
+// Steps 1 and 2; runs on the four epilogue warps.  `has_work`: this CTA's K range is not
+// empty (an empty one contributes zeros).  recv_bar: this CTA's mbarrier, initialised with
+// five arrivals (one per epilogue warp here, one with the expected byte count).
+// Chunks are sent as soon as they are staged, so one travels while the next is being staged.
 __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int warp, int lane,
                                                 uint32_t tmem_base, uint32_t tmem_full_bar,
-                                                uint32_t recv_base, volatile uint32_t* abort_flag,
+                                                uint32_t stage_base, uint32_t recv_base,
+                                                uint32_t recv_bar, volatile uint32_t* abort_flag,
                                                 bool has_work) {
   using namespace skptx;
   const int S = p.sched.split;
   const int q = warp & 3;
-  const int row = q * 32 + lane;
-  const int per = sk_cluster_quads_per_cta(p.bn, S);
+  const int per = p.cl_per;
+  const uint32_t chunk_bytes = static_cast<uint32_t>(per) * SK_CL_QUAD_BYTES;
+  const uint32_t row_off = static_cast<uint32_t>(q * 32 + lane) * 16u;
   bool live = has_work;
+  cluster_arrive_relaxed();   // start-up barrier of the cluster, first half
   if (has_work) {
     const bool got = sk_wait_bar(tmem_full_bar, 0u, abort_flag, p, 24, 2);
     if (!__all_sync(0xffffffffu, got)) live = false;
   }
   tc_fence_after();
   if (warp == 2 && lane == 0) sk_trace(p, 5);
-  cluster_wait();   // second half of the start-up barrier: every CTA of the cluster is resident
+  cluster_wait();             // second half: every CTA's mbarrier exists
   const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-  const uint32_t my_off = static_cast<uint32_t>((rank * per) * SK_BM + row) * 16u;
-  int owner = 0, lq = 0;
-  uint32_t dst = mapa_shared(recv_base, 0) + my_off;
+  if (per >= 8) {
+    // Wide chunks (a 32-column read never spans two of them): one chunk after the other,
+    // starting with the next CTA's, so that the senders do not all aim at the same
+    // destination at once (measured: 0.9 us on a 128 x 128 tile split four ways); the CTA's
+    // own chunk comes last and goes straight into its receive buffer.
+    const int Q = p.bn >> 2;
+    for (int i = 1; i <= S; ++i) {
+      int owner = rank + i;
+      if (owner >= S) owner -= S;
+      const bool mine = owner == rank;
+      const int q0 = owner * per;
+      int q1 = q0 + per;
+      if (q1 > Q) q1 = Q;
+      const uint32_t dst0 =
+          (mine ? recv_base : stage_base) + static_cast<uint32_t>(owner) * chunk_bytes + row_off;
+      for (int qq = q0; qq < q1; qq += 8) {
+        float v[32];
+        if (live) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + 4 * qq, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        const uint32_t dst = dst0 + static_cast<uint32_t>(qq - q0) * SK_CL_QUAD_BYTES;
+        const int nquad = q1 - qq;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nquad)
+            st_shared_v4(dst + j * SK_CL_QUAD_BYTES, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      }
+      if (!mine) {
+        fence_proxy_async_smem();               // the bulk copy reads what was just written
+        named_bar_sync(SK_EPI_BAR_ID, SK_EPI_THREADS);
+        if (lane == 0 && ((i - 1) & 3) == warp - 2)
+          bulk_copy_to_cluster(mapa_shared(recv_base + static_cast<uint32_t>(rank) * chunk_bytes, owner),
+                               stage_base + static_cast<uint32_t>(owner) * chunk_bytes, chunk_bytes,
+                               mapa_shared(recv_bar, owner));
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(recv_bar);
+    if (warp == 2 && lane == 0) sk_trace(p, 10);
+    return;
+  }
+  // Narrow chunks: the accumulator is read 32 columns at a time in column order, and whatever
+  // chunks that completes are sent at once.
+  int owner = 0, lq = 0;      // destination CTA and quad inside its chunk of the next quad
+  int sent = 0;               // chunks [0, sent) are on their way (or are this CTA's own)
+  uint32_t dst = (rank == 0 ? recv_base : stage_base) + row_off;
   for (int c = 0; c < p.bn; c += 32) {
     float v[32];
     if (live) {
@@ -440,27 +510,43 @@ __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       if (c + 4 * j < p.bn) {
-        st_cluster_v4(dst + static_cast<uint32_t>(lq) * (SK_BM * 16u), v[4 * j], v[4 * j + 1], v[4 * j + 2],
-                      v[4 * j + 3]);
+        st_shared_v4(dst, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        dst += SK_CL_QUAD_BYTES;
         if (++lq == per) {
           lq = 0;
-          if (++owner < S) dst = mapa_shared(recv_base, owner) + my_off;
+          ++owner;
+          // the CTA's own chunk goes straight into its receive buffer
+          dst = (owner == rank ? recv_base : stage_base) + static_cast<uint32_t>(owner) * chunk_bytes + row_off;
         }
       }
     }
+    const int done = (c + 32 >= p.bn) ? S : owner;   // chunks [0, done) are complete
+    if (done > sent) {
+      fence_proxy_async_smem();               // the bulk copies read what was just written
+      named_bar_sync(SK_EPI_BAR_ID, SK_EPI_THREADS);
+      if (lane == 0)
+        for (int ch = sent + warp - 2; ch < done; ch += 4)
+          if (ch != rank)
+            bulk_copy_to_cluster(mapa_shared(recv_base + static_cast<uint32_t>(rank) * chunk_bytes, ch),
+                                 stage_base + static_cast<uint32_t>(ch) * chunk_bytes, chunk_bytes,
+                                 mapa_shared(recv_bar, ch));
+      sent = done;
+    }
   }
   tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(recv_bar);        // this warp's share of the CTA's own chunk is in place
+  if (warp == 2 && lane == 0) sk_trace(p, 10);
 }
 
-// Runs on every thread of the CTA after the cluster barrier.
-__device__ __forceinline__ void sk_cluster_reduce(const SkParams& p, __half* __restrict__ C, int tile,
-                                                  int rank, uint32_t recv_base) {
+// Step 3; runs on every thread of the CTA once its receive mbarrier has completed.
+template <int S>
+__device__ __forceinline__ void sk_cluster_reduce_s(const SkParams& p, __half* __restrict__ C, int tile,
+                                                    int rank, uint32_t recv_base) {
   using namespace skptx;
-  const SkSched& s = p.sched;
-  const int S = s.split;
-  const int per = sk_cluster_quads_per_cta(p.bn, S);
+  const int per = p.cl_per;
   int tr, tc;
-  sk_tile_mn(s, tile, tr, tc);
+  sk_tile_mn(p.sched, tile, tr, tc);
   const int r0 = tr * SK_BM, c0 = tc * p.bn;
   int valid_cols = p.cols - c0;
   if (valid_cols > p.bn) valid_cols = p.bn;
@@ -468,17 +554,35 @@ __device__ __forceinline__ void sk_cluster_reduce(const SkParams& p, __half* __r
   if (nq > per) nq = per;
   int rows_valid = p.rows - r0;
   if (rows_valid > SK_BM) rows_valid = SK_BM;
-  const int items = nq * SK_BM;
-  const uint32_t slot_stride = static_cast<uint32_t>(per) * SK_BM * 16u;
+  const uint32_t chunk_bytes = static_cast<uint32_t>(per) * SK_CL_QUAD_BYTES;
+  const int items = per * SK_BM;
+  const int gcol0 = c0 + rank * per * 4;
   for (int i = threadIdx.x; i < items; i += blockDim.x) {
-    const int row = i & (SK_BM - 1), lq = i >> 7;
-    if (row >= rows_valid) continue;
-    const uint32_t a = recv_base + static_cast<uint32_t>(i) * 16u;
-    float4 acc = ld_shared_v4(a);
-    for (int snd = 1; snd < S; ++snd) {
-      const float4 x = ld_shared_v4(a + snd * slot_stride);
-      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    // Consecutive lanes take consecutive rows when C is stored transposed (rows are then
+    // contiguous in memory), consecutive quads of one row otherwise.
+    int row, lq;
+    if (p.transposed) {
+      row = i & (SK_BM - 1); lq = i >> 7;
+    } else {
+      row = sk_div(i, p.cl_per_div); lq = i - row * per;
     }
-    sk_store4(C, p, r0 + row, c0 + (rank * per + lq) * 4, acc);
+    if (row >= rows_valid || lq >= nq) continue;
+    const uint32_t a = recv_base + static_cast<uint32_t>(lq) * SK_CL_QUAD_BYTES + static_cast<uint32_t>(row) * 16u;
+    float4 x[S];
+#pragma unroll
+    for (int snd = 0; snd < S; ++snd) x[snd] = ld_shared_v4(a + snd * chunk_bytes);
+    float4 acc = x[0];
+#pragma unroll
+    for (int snd = 1; snd < S; ++snd) { acc.x += x[snd].x; acc.y += x[snd].y; acc.z += x[snd].z; acc.w += x[snd].w; }
+    sk_store4(C, p, r0 + row, gcol0 + lq * 4, acc);
+  }
+}
+
+__device__ __forceinline__ void sk_cluster_reduce(const SkParams& p, __half* __restrict__ C, int tile,
+                                                  int rank, uint32_t recv_base) {
+  switch (p.sched.split) {
+    case 2: sk_cluster_reduce_s<2>(p, C, tile, rank, recv_base); break;
+    case 4: sk_cluster_reduce_s<4>(p, C, tile, rank, recv_base); break;
+    default: sk_cluster_reduce_s<8>(p, C, tile, rank, recv_base); break;
   }
 }

@@ -38,6 +38,7 @@ struct Ctrl {
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t recv_full;      // SK_SCHED_CLUSTER: the partial tiles of the other CTAs have arrived
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t bcast;
@@ -84,14 +85,18 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   const int pid = blockIdx.x;
   const SkSched& s = p.sched;
   if (threadIdx.x == 0) sk_trace(p, 0);
-  // Split-K inside a cluster: the partial tiles meet in a receive buffer behind the control
-  // block.  First half of a start-up cluster barrier; the second half comes right before a
-  // thread's first access to another CTA's shared memory (or at teardown).
+  // Split-K inside a cluster: the partial tiles meet in a receive buffer behind the control block.
   const bool clustered = s.split > 0;
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
-  if (clustered) cluster_arrive();
 
+  // Start-up.  The time from kernel entry to the first load is pure latency on every small
+  // problem, so the two producer warps wait for nothing but the mbarriers (a 64-thread named
+  // barrier with thread 0, which initialises them); the tensor-memory allocation runs beside
+  // the first loads and is awaited by the MMA and epilogue warps only.
+  constexpr int BAR_PRODUCERS = 2, BAR_CONSUMERS = 3;
+  if (threadIdx.x == 6 * 32 && p.col_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmCol);
   if (threadIdx.x == 0) {
+    if (p.row_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmRow);
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(smem_u32(&ctrl->full[i]), 1);
       mbar_init(smem_u32(&ctrl->empty[i]), 1);
@@ -100,23 +105,32 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
       mbar_init(smem_u32(&ctrl->tmem_empty[i]), 4);  // one arrival per epilogue warp
     }
+    if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
     ctrl->abort = 0u;
     ctrl->bcast = 0u;
     ctrl->pend[0].tile = -1;
     ctrl->pend[1].tile = -1;
     fence_mbar_init();
     fence_proxy_async_smem();
-    if (p.row_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmRow);
-    if (p.col_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmCol);
+    if (clustered)
+      mbar_arrive_expect_tx(smem_u32(&ctrl->recv_full),
+                            static_cast<uint32_t>((s.split - 1) * p.cl_per) * SK_CL_QUAD_BYTES);
   }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
-    tmem_relinquish();
+  uint32_t tmem_base = 0;
+  if (warp == 0 || warp == 6) {
+    __syncwarp();
+    if (warp == 0) named_bar_arrive(BAR_CONSUMERS, NUM_THREADS - 32);   // warps 0..5
+    named_bar_sync(BAR_PRODUCERS, 64);
+  } else {
+    if (warp == 1) {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    named_bar_sync(BAR_CONSUMERS, NUM_THREADS - 32);
+    tc_fence_after();
+    tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
   if (threadIdx.x == 0) sk_trace(p, 1);
 
   if (warp == 0 || warp == 6) {
@@ -128,6 +142,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     if (lane == 0) {
       const bool is_row = warp == 0;
       bool traced = false;
+      bool arrived = false;
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
@@ -161,10 +176,24 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
             else load_operand(loader, dst, tm, img, full, first_row, k + j, tile_rows, s.iters_per_tile);
           }
           k += n;
-          if (++stage == STAGES) { stage = 0; ph ^= 1u; }
+          if (++stage == STAGES) {
+            stage = 0; ph ^= 1u;
+            // the ring is full for the first time: a good moment for this thread's share of
+            // the cluster's start-up barrier
+            // (thread 0 initialised the mbarriers the other CTAs will signal: it releases)
+            if (clustered && !arrived) {
+              if (is_row) cluster_arrive(); else cluster_arrive_relaxed();
+              arrived = true;
+            }
+          }
           if (is_row && !traced) { sk_trace(p, 2); traced = true; }
         }
       }
+      if (clustered && !arrived) {
+        if (is_row) cluster_arrive(); else cluster_arrive_relaxed();
+      }
+    } else if (clustered) {
+      cluster_arrive_relaxed();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
@@ -176,6 +205,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       uint32_t ph = 0;
       uint32_t nseg = 0;
       bool ok = true;
+      bool arrived = false;
       // K-major operand: 8-row groups 1024 B apart, 16 halves of K = 32 B.
       // MN-major operand: 64-wide chunks 8192 B apart, 8-row K groups 1024 B apart,
       // 16 rows of K = 2048 B.
@@ -218,19 +248,24 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
           umma_commit(empty0 + 8u * stage);  // frees the stage when the MMAs retire
           k += n;
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
+          // start-up barrier of the cluster: while the pipeline is still filling
+          if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
         }
         if (!ok) break;
         umma_commit(smem_u32(&ctrl->tmem_full[buf]));
         ++nseg;
       }
       sk_trace(p, 4);
+      if (clustered && !arrived) cluster_arrive_relaxed();
+    } else if (clustered) {
+      cluster_arrive_relaxed();
     }
   } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------- epilogue
-    if (clustered)
+    if (clustered)   // (takes part in the cluster's start-up barrier on its own)
       sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
-                      smem_u32(&ctrl->tmem_full[0]), recv_base, abort_flag,
-                      sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
+                      smem_u32(&ctrl->tmem_full[0]), sRow, recv_base, smem_u32(&ctrl->recv_full),
+                      abort_flag, sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
     else
       sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                        smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
@@ -238,20 +273,21 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
 
   // ------------------------------------------------------------- teardown
   tc_fence_before();
+  bool reduce_ok = true;
   if (clustered) {
-    // Every partial of the tile has reached its owners once the whole cluster is here.  A CTA
-    // reads only its own shared memory afterwards, so it may leave as soon as it is done.
     if (!(warp >= 2 && warp < 6)) cluster_wait();   // start-up barrier, second half
     __syncwarp();
+    // the chunks of the other CTAs, and the epilogue warps' own one
+    if (threadIdx.x == 0) sk_trace(p, 11);
+    reduce_ok = sk_wait_bar(smem_u32(&ctrl->recv_full), 0u, abort_flag, p, 40, 3);
+    // Final barrier: nobody leaves while a copy out of its staging area may be in flight.
+    // Arrive now, wait after the reduction.
     cluster_arrive();
-    cluster_wait();
     if (threadIdx.x == 0) sk_trace(p, 6);
-    sk_cluster_reduce(p, C, pid / s.split, static_cast<int>(cluster_ctarank()), recv_base);
+  } else {
+    __syncthreads();
   }
-  __syncthreads();
-  // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
-  // the split tiles it took part in.
-  if (!clustered) sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+  // The accumulators have been read: the tensor memory can go back while the rest reduces.
   if (warp == 1) {
     if (*abort_flag) {
       // A wait ran out: give copies and MMAs still in flight time to land before
@@ -262,8 +298,18 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     tc_fence_after();
     __syncwarp();
     tmem_dealloc(tmem_base, p.tmem_cols);
-    if (lane == 0) sk_trace(p, 7);
   }
+  if (clustered) {
+    if (reduce_ok)
+      sk_cluster_reduce(p, C, pid >> s.split_log2, static_cast<int>(cluster_ctarank()), recv_base);
+    if (threadIdx.x == 0) sk_trace(p, 12);
+    cluster_wait();
+  } else {
+    // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
+    // the split tiles it took part in.
+    sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+  }
+  if (threadIdx.x == 32) sk_trace(p, 7);
 }
 
 // ---------------------------------------------------------------- host side
@@ -385,8 +431,12 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   if (pairs) return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
   const int split = p.sched.split;   // SK_SCHED_CLUSTER: CTAs per tile
   const int recv_bytes = split ? sk_cluster_recv_bytes(plan.bn, split) : 0;
+  p.cl_per = split ? sk_cluster_quads_per_cta(plan.bn, split) : 1;
+  p.cl_per_div = sk_div_make(p.cl_per);
   sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, recv_bytes);
   if (p.stages < 2) return SK_ERR_SHAPE;
+  // the staging area of the cluster exchange lives in the operand ring
+  if (split && p.stages * (ROW_STAGE_BYTES + p.col_stage_bytes) < recv_bytes) return SK_ERR_SHAPE;
   // Very narrow tiles walked whole (data-parallel, long K) are bounded by the per-stage
   // barrier round trip of the issuing threads, not by bandwidth: two or four K steps then
   // share a stage.  Measured: 1.3x there; Stream-K segments are short and HBM-bound and lose from the

@@ -62,14 +62,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
 }
+// arrival that orders nothing (the waiters need nothing this thread wrote)
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-}
-// 16-byte store into the shared memory of a CTA of the cluster (address from mapa_shared).
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
 }
 __device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
   float4 v;
@@ -120,6 +118,20 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
       : "memory");
+}
+// Bulk copy from this CTA's shared memory into the shared memory of a CTA of the cluster;
+// the bytes are counted on an mbarrier of the destination CTA.  dst and bar are
+// shared::cluster addresses (mapa_shared), src a shared::cta address; 16-byte granules.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst, uint32_t src, uint32_t bytes,
+                                                     uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "r"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05
@@ -277,6 +289,11 @@ __device__ __forceinline__ uint32_t atom_add_acqrel_u32(uint32_t* p, uint32_t v)
 }
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Count towards a named barrier without waiting for it (what was written before is visible
+// to the threads that bar.sync on it).
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 }  // namespace skptx

@@ -13,6 +13,35 @@
 #define SK_HD inline
 #endif
 
+// Division by a number known on the host, as multiply-high and shift (valid for
+// 0 <= n < 2^31): the device walks the schedule in a single thread, where a plain integer
+// division is some thirty dependent instructions.
+struct SkDiv {
+  uint32_t mul;   // 0: the divisor is 1
+  uint32_t shr;
+};
+
+SK_HD SkDiv sk_div_make(int d) {
+  SkDiv v;
+  v.mul = 0; v.shr = 0;
+  if (d <= 1) return v;
+  int l = 0;
+  while ((1u << l) < static_cast<uint32_t>(d)) ++l;   // ceil(log2 d)
+  const int p = 31 + l;
+  v.mul = static_cast<uint32_t>(((1ull << p) + static_cast<uint32_t>(d) - 1) / static_cast<uint32_t>(d));
+  v.shr = static_cast<uint32_t>(p - 32);
+  return v;
+}
+
+SK_HD int sk_div(int n, const SkDiv& d) {
+  if (d.mul == 0) return n;
+#if defined(__CUDA_ARCH__)
+  return static_cast<int>(__umulhi(static_cast<uint32_t>(n), d.mul) >> d.shr);
+#else
+  return static_cast<int>(static_cast<uint32_t>((static_cast<uint64_t>(static_cast<uint32_t>(n)) * d.mul) >> 32) >> d.shr);
+#endif
+}
+
 struct SkSched {
   int tiles_m, tiles_n, total_tiles, iters_per_tile;
   int sk_tiles;   // tiles [0, sk_tiles) are Stream-K'd
@@ -24,7 +53,31 @@ struct SkSched {
   int split;      // > 0: every tile is split over the `split` CTAs of one thread-block cluster
                   //      (grid = total_tiles * split), CTA r of the cluster walking K iterations
                   //      [r*I/split, (r+1)*I/split) of its tile; 0: the Stream-K interval rule
+  // derived by sk_sched_finish()
+  int split_log2; // split is a power of two
+  SkDiv d_ipt;    // / iters_per_tile
+  SkDiv d_tn;     // / tiles_n
+  SkDiv d_width;  // / (group_m * tiles_n)
+  SkDiv d_gm;     // / group_m
+  SkDiv d_glast;  // / height of the ragged last band
+  SkDiv d_f1;     // / (sk_f + 1)
+  SkDiv d_f;      // / sk_f
 };
+
+// Fill the derived fields once the others are set.
+SK_HD void sk_sched_finish(SkSched& s) {
+  s.split_log2 = 0;
+  while ((1 << s.split_log2) < s.split) ++s.split_log2;
+  s.d_ipt = sk_div_make(s.iters_per_tile);
+  s.d_tn = sk_div_make(s.tiles_n);
+  const int gm = s.group_m > 1 ? s.group_m : 1;
+  s.d_width = sk_div_make(gm * s.tiles_n);
+  s.d_gm = sk_div_make(gm);
+  const int last = s.tiles_m % gm;
+  s.d_glast = sk_div_make(last ? last : gm);
+  s.d_f1 = sk_div_make(s.sk_f + 1);
+  s.d_f = sk_div_make(s.sk_f > 0 ? s.sk_f : 1);
+}
 
 struct SkSeg {
   int tile;
@@ -40,8 +93,9 @@ struct SkCursor {
 // First iteration of CTA p: p*f + min(p, r)   (streamk_fp16.py:176-181)
 SK_HD int sk_cta_begin(const SkSched& s, int p) {
   if (s.split > 0) {
-    const int t = p / s.split, r = p - t * s.split;
-    return t * s.iters_per_tile + static_cast<int>(static_cast<long long>(r) * s.iters_per_tile / s.split);
+    const int t = p >> s.split_log2, r = p & (s.split - 1);
+    // r < split <= 16 and iters_per_tile < 2^27: the product fits 32 bits
+    return t * s.iters_per_tile + ((r * s.iters_per_tile) >> s.split_log2);
   }
   return p * s.sk_f + (p < s.sk_r ? p : s.sk_r);
 }
@@ -49,13 +103,12 @@ SK_HD int sk_cta_begin(const SkSched& s, int p) {
 // Inverse of sk_cta_begin: which CTA executes Stream-K iteration i.
 SK_HD int sk_cta_of(const SkSched& s, int i) {
   if (s.split > 0) {
-    const int I = s.iters_per_tile;
-    const int t = i / I, k = i - t * I;
-    return t * s.split + static_cast<int>((static_cast<long long>(k + 1) * s.split - 1) / I);
+    const int t = sk_div(i, s.d_ipt), k = i - t * s.iters_per_tile;
+    return t * s.split + sk_div((k + 1) * s.split - 1, s.d_ipt);
   }
   const int big = s.sk_r * (s.sk_f + 1);
-  if (i < big) return i / (s.sk_f + 1);
-  return s.sk_r + (i - big) / s.sk_f;   // sk_f > 0 here, else i < big always
+  if (i < big) return sk_div(i, s.d_f1);
+  return s.sk_r + sk_div(i - big, s.d_f);   // sk_f > 0 here, else i < big always
 }
 
 // Tile id -> tile coordinates.  group_m == 1 is the reference's row-major order
@@ -63,17 +116,17 @@ SK_HD int sk_cta_of(const SkSched& s, int i) {
 // group_m tile rows so that a wave of CTAs shares A and B panels in L2.
 SK_HD void sk_tile_mn(const SkSched& s, int tile, int& tm, int& tn) {
   if (s.group_m <= 1) {
-    tm = tile / s.tiles_n;
+    tm = sk_div(tile, s.d_tn);
     tn = tile - tm * s.tiles_n;
     return;
   }
-  const int width = s.group_m * s.tiles_n;
-  const int g = tile / width;
+  const int g = sk_div(tile, s.d_width);
   const int first_m = g * s.group_m;
   const int rem = s.tiles_m - first_m;
-  const int gsize = rem < s.group_m ? rem : s.group_m;
-  const int in_g = tile - g * width;
-  tn = in_g / gsize;
+  const bool full = rem >= s.group_m;
+  const int gsize = full ? s.group_m : rem;
+  const int in_g = tile - g * (s.group_m * s.tiles_n);
+  tn = sk_div(in_g, full ? s.d_gm : s.d_glast);
   tm = first_m + (in_g - tn * gsize);
 }
 
@@ -91,7 +144,7 @@ SK_HD bool sk_next(const SkSched& s, int pid, SkCursor& c, SkSeg& seg) {
     if (sk_phase) {
       if (c.it < c.it_end) {
         const int I = s.iters_per_tile;
-        const int tile = c.it / I;
+        const int tile = sk_div(c.it, s.d_ipt);
         const int k0 = c.it - tile * I;
         int k1 = k0 + (c.it_end - c.it);
         if (k1 > I) k1 = I;

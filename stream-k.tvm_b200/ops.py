@@ -23,10 +23,12 @@ __all__ = [
     "streamk_fp16_block_reduce", "ladder_prepack", "streamk_fp16_ladder",
     "streamk_fp16_ladder_block_reduce", "q4_prepack", "dequant_w4",
     "streamk_fp16_ladder_block_reduce_q4", "schedule_info", "check_status",
-    "reset_workspace", "device_info", "LadderWeight", "PackedQ4", "StreamKError",
+    "reset_workspace", "device_info", "LadderWeight", "PackedQ4", "StreamKError", "SCHEDULES", "FIXUPS",
 ]
 
 StreamKError = L.StreamKError
+SCHEDULES = L.SCHEDULES   # name -> SK_SCHED_* value
+FIXUPS = L.FIXUPS
 GROUP_SIZE = 128
 
 

@@ -188,7 +188,7 @@ def test_fp16_cluster_split_k(shape):
         _check(sk.streamk_fp16_nn(Ad, B.t().contiguous().to(DEV), schedule="cluster"), ref, TOL16)
         _check(sk.streamk_fp16_ladder(Ad, sk.ladder_prepack(Bd), schedule="cluster"), ref, TOL16)
         if M > 64:
-            for tile_n in (96, 256):
+            for tile_n in (48, 96, 192):     # (wider tiles leave no room for the exchange buffers)
                 _check(sk.streamk_fp16_nt(Ad, Bd, schedule="cluster", tile_m=128, tile_n=tile_n), ref, TOL16)
 
 

@@ -149,13 +149,21 @@ def test_auto_schedule_resolution(lib):
         assert lib.sk_schedule(C.byref(prob), kind, 148, C.byref(info)) == 0
         return info.as_dict()
     names = {v: k for k, v in L.SCHEDULES.items()}
-    d = plan(16, 4096, 4096)          # 32 swapped tiles: every SM has to stream
+    d = plan(16, 4096, 4096)          # 32 swapped tiles: every SM has to stream; clusters of 4
+    assert (names[d["schedule"]], d["swap_ab"], d["cluster"], d["grid"]) == ("cluster", 1, 4, 128)
+    d = plan(16, 4096, 4096, kind=2)  # (the W4A16 kernel has no cluster exchange)
     assert (names[d["schedule"]], d["swap_ab"]) == ("streamk", 1)
+    d = plan(16, 4096, 256)           # shallow K: nothing to split
+    assert names[d["schedule"]] == "streamk"
     d = plan(16, 12288, 4096)         # 96 swapped tiles: whole tiles keep most SMs busy
     assert (names[d["schedule"]], d["swap_ab"], d["total_tiles"]) == ("dp", 1, 96)
     d = plan(256, 12288, 4096)        # tile width fitted to 74 columns per tile row
     assert names[d["schedule"]] == "dp" and d["tile_n"] == 176 and d["total_tiles"] <= 148
-    d = plan(128, 4096, 4096)         # too narrow to fit: Stream-K on 128 x 128 tiles
+    d = plan(128, 4096, 4096)         # 32 tiles: clusters of 4 on 128 x 128 tiles
+    assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["cluster"]) == ("cluster", 128, 128, 4)
+    d = plan(128, 9000, 4096)         # 71 tiles: clusters of 2
+    assert (names[d["schedule"]], d["cluster"], d["grid"]) == ("cluster", 2, 142)
+    d = plan(128, 4096, 256)          # shallow K and too narrow to fit whole tiles: Stream-K
     assert (names[d["schedule"]], d["tile_m"], d["tile_n"]) == ("streamk", 128, 128)
     d = plan(8192, 28672, 8192, kind=3)
     assert names[d["schedule"]] == "hybrid" and d["tile_m"] == 256
