@@ -90,44 +90,58 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
   // Start-up.  The time from kernel entry to the first load is pure latency on every small
-  // problem, so the two producer warps wait for nothing but the mbarriers (a 64-thread named
-  // barrier with thread 0, which initialises them); the tensor-memory allocation runs beside
-  // the first loads and is awaited by the MMA and epilogue warps only.
+  // problem, and a lone thread retires a dependent instruction only every few cycles, so the
+  // work is spread: an epilogue warp (idle until the first tile is done) initialises the
+  // mbarriers, one per lane; meanwhile the producer and MMA threads work out their first
+  // segment.  The producers then wait for nothing but the mbarriers (named barrier
+  // BAR_PRODUCERS); the tensor-memory allocation runs beside the first loads and is awaited
+  // by the MMA and epilogue warps only (BAR_CONSUMERS).
   constexpr int BAR_PRODUCERS = 2, BAR_CONSUMERS = 3;
+  if (threadIdx.x == 0 && p.row_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmRow);
   if (threadIdx.x == 6 * 32 && p.col_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmCol);
-  if (threadIdx.x == 0) {
-    if (p.row_loader != SK_LOAD_IMAGE) prefetch_tensormap(&tmRow);
-    for (int i = 0; i < STAGES; ++i) {
-      mbar_init(smem_u32(&ctrl->full[i]), 1);
-      mbar_init(smem_u32(&ctrl->empty[i]), 1);
-    }
-    for (int i = 0; i < 2; ++i) {
+  if (warp == 2) {
+    if (lane < STAGES) {
+      mbar_init(smem_u32(&ctrl->full[lane]), 1);
+      mbar_init(smem_u32(&ctrl->empty[lane]), 1);
+    } else if (lane < STAGES + 2) {
+      const int i = lane - STAGES;
       mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
       mbar_init(smem_u32(&ctrl->tmem_empty[i]), 4);  // one arrival per epilogue warp
+    } else if (lane == STAGES + 2) {
+      if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
+      ctrl->abort = 0u;
+      ctrl->bcast = 0u;
+      ctrl->pend[0].tile = -1;
+      ctrl->pend[1].tile = -1;
     }
-    if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
-    ctrl->abort = 0u;
-    ctrl->bcast = 0u;
-    ctrl->pend[0].tile = -1;
-    ctrl->pend[1].tile = -1;
     fence_mbar_init();
     fence_proxy_async_smem();
-    if (clustered)
+    __syncwarp();
+    named_bar_arrive(BAR_PRODUCERS, 96);      // warps 0 and 6 wait on it
+    if (clustered && lane == STAGES + 2)
       mbar_arrive_expect_tx(smem_u32(&ctrl->recv_full),
                             static_cast<uint32_t>((s.split - 1) * p.cl_per) * SK_CL_QUAD_BYTES);
   }
+  // first segment of this CTA, for the threads that walk the segment list from the start
+  SkCursor cur;
+  SkSeg seg;
+  bool have = false;
+  int tr = 0, tc = 0;
+  if (lane == 0 && (warp == 0 || warp == 1 || warp == 6)) {
+    sk_cursor_init(s, pid, cur);
+    have = sk_next(s, pid, cur, seg);
+    if (have) sk_tile_mn(s, seg.tile, tr, tc);
+  }
   uint32_t tmem_base = 0;
   if (warp == 0 || warp == 6) {
-    __syncwarp();
-    if (warp == 0) named_bar_arrive(BAR_CONSUMERS, NUM_THREADS - 32);   // warps 0..5
-    named_bar_sync(BAR_PRODUCERS, 64);
+    named_bar_sync(BAR_PRODUCERS, 96);
   } else {
     if (warp == 1) {
       tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
       tmem_relinquish();
     }
     tc_fence_before();
-    named_bar_sync(BAR_CONSUMERS, NUM_THREADS - 32);
+    named_bar_sync(BAR_CONSUMERS, NUM_THREADS - 64);   // warps 1..5
     tc_fence_after();
     tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
   }
@@ -143,9 +157,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       const bool is_row = warp == 0;
       bool traced = false;
       bool arrived = false;
-      SkCursor cur;
-      sk_cursor_init(s, pid, cur);
-      SkSeg seg;
+      bool first_seg = true;
       int stage = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -157,9 +169,9 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       const uint32_t dst0 = is_row ? sRow : sCol;
       const int tile_rows = is_row ? BM : p.bn;
       const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
-      while (ok && sk_next(s, pid, cur, seg)) {
-        int tr, tc;
-        sk_tile_mn(s, seg.tile, tr, tc);
+      for (; ok && have; have = sk_next(s, pid, cur, seg)) {
+        if (!first_seg) sk_tile_mn(s, seg.tile, tr, tc);   // (the first segment's are known already)
+        first_seg = false;
         const int first_row = is_row ? tr * BM : tc * p.bn;
         for (int k = seg.k0; k < seg.k1;) {
           // up to G consecutive K steps share one stage: one barrier round trip for all
@@ -198,9 +210,6 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      SkCursor cur;
-      sk_cursor_init(s, pid, cur);
-      SkSeg seg;
       int stage = 0;
       uint32_t ph = 0;
       uint32_t nseg = 0;
@@ -219,7 +228,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       const uint32_t idesc = p.idesc;
       const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
       const uint32_t acc_stride = p.acc_stride;
-      while (ok && sk_next(s, pid, cur, seg)) {
+      for (; ok && have; have = sk_next(s, pid, cur, seg)) {
         const uint32_t buf = nseg & 1u;
         const uint32_t acc_ph = (nseg >> 1) & 1u;
         if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
