@@ -52,7 +52,7 @@ enum { SK_SCHED_STREAMK = 0,        /* every tile is Stream-K'd                 
                                        [r*I/size, (r+1)*I/size); the partial tiles meet in the
                                        cluster's distributed shared memory and are summed in CTA
                                        order, so no workspace traffic and a bitwise reproducible
-                                       result.  fp16 entry points only; `fixup` is ignored.  No
+                                       result.  fp16 and W4A16 entry points; `fixup` is ignored.  No
                                        counterpart in the reference.                              */ };
 
 enum { SK_FIXUP_ATOMIC = 0,        /* fp32 red.global.add into a self-cleaning workspace

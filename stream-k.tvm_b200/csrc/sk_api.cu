@@ -142,14 +142,14 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
   const bool tiles_open = q->tile_m == 0 && q->tile_n == 0;
   const long long t256 = static_cast<long long>((q->M + 255) / 256) * ((q->N + 255) / 256);
   if (t256 >= num_sms) return;                       // large: hybrid (CTA pairs when eligible)
-  if (kernel_kind == 1 && (q->K + 63) / 64 >= 8) {
+  if ((kernel_kind == 1 || kernel_kind == 2) && (q->K + 63) / 64 >= 8) {
     // Few tiles and a deep K: split every tile over the CTAs of a cluster.  Measured 15-25 %
     // ahead of Stream-K with either workspace fixup wherever it applies (at most half as many
     // tiles as SMs): the partials never leave the SMs and no flag is polled.
     sk_problem c = *q;
     c.schedule = SK_SCHED_CLUSTER;
     if (tiles_open && c.M > 64) { c.tile_m = 128; c.tile_n = 128; }
-    if (sk_make_sched(&c, 1, num_sms, nullptr, nullptr, nullptr) == SK_OK) {
+    if (sk_make_sched(&c, kernel_kind, num_sms, nullptr, nullptr, nullptr) == SK_OK) {
       *q = c;
       return;
     }
@@ -214,7 +214,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   int split = 0;
   if (p->schedule == SK_SCHED_CLUSTER) {
     // the largest portable cluster that still gives every tile its own cluster in one wave
-    if (kernel_kind != 1) return SK_ERR_ARG;
+    if (kernel_kind != 1 && kernel_kind != 2) return SK_ERR_ARG;
     if (2 * total > P) return SK_ERR_SHAPE;
     if (plan.bn > 192) return SK_ERR_SHAPE;   // exchange buffers of wider tiles do not fit beside the ring
     split = 2;

@@ -446,11 +446,13 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   if (p.stages < 2) return SK_ERR_SHAPE;
   // the staging area of the cluster exchange lives in the operand ring
   if (split && p.stages * (ROW_STAGE_BYTES + p.col_stage_bytes) < recv_bytes) return SK_ERR_SHAPE;
-  // Very narrow tiles walked whole (data-parallel, long K) are bounded by the per-stage
-  // barrier round trip of the issuing threads, not by bandwidth: two or four K steps then
-  // share a stage.  Measured: 1.3x there; Stream-K segments are short and HBM-bound and lose from the
-  // coarser stages, so they keep one K step per stage.
-  p.kgroup = prob->schedule != SK_SCHED_DP ? 1 : p.stages >= 12 ? 4 : p.stages >= 8 ? 2 : 1;
+  // Very narrow tiles walked in long runs of K (data-parallel, or split over a cluster) are
+  // bounded by the per-stage barrier round trip of the issuing threads, not by bandwidth: two
+  // or four K steps then share a stage, which also asks DRAM for 256 or 512 contiguous bytes
+  // of a weight row at a time.  Measured: 1.1-1.3x there.  Stream-K segments are short and
+  // lose from the coarser stages, and so do wide tiles (few stages): one K step per stage.
+  const bool long_runs = prob->schedule == SK_SCHED_DP || prob->schedule == SK_SCHED_CLUSTER;
+  p.kgroup = !long_runs ? 1 : p.stages >= 12 ? 4 : p.stages >= 8 ? 2 : 1;
   p.stages /= p.kgroup;
 
   // Which matrix feeds which side of the UMMA.  Activations A are always K-major; the

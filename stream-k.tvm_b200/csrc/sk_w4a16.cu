@@ -49,6 +49,7 @@ struct Ctrl {
   uint64_t w_empty[MAX_BS];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t recv_full;      // SK_SCHED_CLUSTER: the partial tiles of the other CTAs have arrived
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t bcast;
@@ -112,8 +113,13 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const int groups = kblocks >> 1;       // K / 128
   const bool swapped = p.transposed != 0;
   if (threadIdx.x == 0) sk_trace(p, 0);
+  // Split-K inside a cluster (sk_epilogue.cuh): receive buffer behind the control block,
+  // staging area in the rings, which are idle by then.
+  const bool clustered = s.split > 0;
+  const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
   if (threadIdx.x == 0) {
+    if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
     for (int i = 0; i < LS; ++i) {
       mbar_init(smem_u32(&ctrl->load_full[i]), 1);
       mbar_init(smem_u32(&ctrl->load_empty[i]), DQ_WARPS + 1);  // each dequant warp + MMA commit
@@ -133,6 +139,9 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     fence_mbar_init();
     fence_proxy_async_smem();
     prefetch_tensormap(&tmA);
+    if (clustered)
+      mbar_arrive_expect_tx(smem_u32(&ctrl->recv_full),
+                            static_cast<uint32_t>((s.split - 1) * p.cl_per) * SK_CL_QUAD_BYTES);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
@@ -148,6 +157,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     // ------------------------------------------------------------- producer
     if (lane == 0) {
       bool traced = false;
+      bool arrived = false;   // this thread's share of the cluster's start-up barrier
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
@@ -178,10 +188,18 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
                        szblocks + (static_cast<size_t>(nblk) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
                        SZ_BLOCK_BYTES, full);
           k += n;
-          if (++ls == LS) { ls = 0; lph ^= 1u; }
+          if (++ls == LS) {
+            ls = 0; lph ^= 1u;
+            // ring full for the first time; this thread initialised the mbarriers the other
+            // CTAs will signal, so its arrival releases
+            if (clustered && !arrived) { cluster_arrive(); arrived = true; }
+          }
           if (!traced) { sk_trace(p, 2); traced = true; }
         }
       }
+      if (clustered && !arrived) cluster_arrive();
+    } else if (clustered) {
+      cluster_arrive_relaxed();
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
@@ -192,6 +210,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       int ls = 0, bs = 0;
       uint32_t lph = 0, bph = 0, nseg = 0;
       bool ok = true;
+      bool arrived = false;
       const uint64_t desc_hi = umma_desc_sw128_hi(16, 1024);
       const uint32_t act_lo0 = umma_desc_lo(sA), wgt_lo0 = umma_desc_lo(sW);
       const uint32_t act_tile16 = static_cast<uint32_t>(a_tile_bytes) >> 4;
@@ -229,17 +248,26 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           k += n;
           if (++ls == LS) { ls = 0; lph ^= 1u; }
           if (++bs == BS) { bs = 0; bph ^= 1u; }
+          if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
         }
         if (!ok) break;
         umma_commit(smem_u32(&ctrl->tmem_full[buf]));
         ++nseg;
       }
       sk_trace(p, 4);
+      if (clustered && !arrived) cluster_arrive_relaxed();
+    } else if (clustered) {
+      cluster_arrive_relaxed();
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------- epilogue
-    sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                     smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
+    if (clustered)   // (takes part in the cluster's start-up barrier on its own)
+      sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
+                      smem_u32(&ctrl->tmem_full[0]), sW, recv_base, smem_u32(&ctrl->recv_full),
+                      abort_flag, sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
+    else
+      sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                       smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   } else {
     // ------------------------------------------------------------- dequantise
     // Thread (h, r): weight row r of the tile, K half h (32 values = 4 packed words).
@@ -253,6 +281,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     int ls = 0, bs = 0;
     uint32_t lph = 0, bph = 0;
     bool dead = false;
+    if (clustered) cluster_arrive_relaxed();
     while (sk_next(s, pid, cur, seg)) {
       for (int k = seg.k0; k < seg.k1;) {
         const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
@@ -296,10 +325,20 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
 
   // ------------------------------------------------------------- teardown
   tc_fence_before();
-  __syncthreads();
-  // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
-  // the split tiles it took part in.
-  sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+  bool reduce_ok = true;
+  if (clustered) {
+    if (!(warp >= 2 && warp < 6)) cluster_wait();   // start-up barrier, second half
+    __syncwarp();
+    // the chunks of the other CTAs, and the epilogue warps' own one
+    reduce_ok = sk_wait_bar(smem_u32(&ctrl->recv_full), 0u, abort_flag, p, 40, 3);
+    // Final barrier: nobody leaves while a copy out of its staging area may be in flight.
+    // Arrive now, wait after the reduction.
+    cluster_arrive();
+    if (threadIdx.x == 0) sk_trace(p, 6);
+  } else {
+    __syncthreads();
+  }
+  // The accumulators have been read: the tensor memory can go back while the rest reduces.
   if (warp == 1) {
     if (*abort_flag) {
       const unsigned long long t0 = globaltimer_ns();
@@ -308,8 +347,17 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     tc_fence_after();
     __syncwarp();
     tmem_dealloc(tmem_base, p.tmem_cols);
-    if (lane == 0) sk_trace(p, 7);
   }
+  if (clustered) {
+    if (reduce_ok)
+      sk_cluster_reduce(p, C, pid >> s.split_log2, static_cast<int>(cluster_ctarank()), recv_base);
+    cluster_wait();
+  } else {
+    // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
+    // the split tiles it took part in.
+    sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+  }
+  if (threadIdx.x == 32) sk_trace(p, 7);
 }
 
 // ---------------------------------------------------------------- prepack / dequant
@@ -492,7 +540,11 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   // dequantised weight stages.  The chain dequantise -> MMA -> release runs once per K step
   // and takes over a microsecond end to end, so the weight ring has to be deep as well: take
   // the deepest weight ring that still leaves at least as many load stages.
-  const int budget = SMEM_LIMIT - 1024 - CTRL_BYTES;
+  const int split = p.sched.split;   // SK_SCHED_CLUSTER: CTAs per tile
+  const int recv_bytes = split ? sk_cluster_recv_bytes(plan.bn, split) : 0;
+  p.cl_per = split ? sk_cluster_quads_per_cta(plan.bn, split) : 1;
+  p.cl_per_div = sk_div_make(p.cl_per);
+  const int budget = SMEM_LIMIT - 1024 - CTRL_BYTES - recv_bytes;
   const int load_stage = KG * (a_stage_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES;
   int ls = 0, bs = 2;
   for (int b = 4; b >= 2; --b) {
@@ -514,7 +566,9 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   const uint8_t* qb = static_cast<const uint8_t*>(packed);
   const uint8_t* sz = qb + static_cast<size_t>(nb) * kb * Q_BLOCK_BYTES;
 
-  const int smem_bytes = bs * W_STAGE_BYTES + ls * load_stage + 1024 + CTRL_BYTES;
+  // the staging area of the cluster exchange lives in the rings
+  if (split && bs * W_STAGE_BYTES + ls * load_stage < recv_bytes) return SK_ERR_SHAPE;
+  const int smem_bytes = bs * W_STAGE_BYTES + ls * load_stage + 1024 + CTRL_BYTES + recv_bytes;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -524,9 +578,28 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
+  cudaError_t e;
+  if (split) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(p.sched.grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = split;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, sk_gemm_w4a16_kernel, tmA, qb, sz, static_cast<__half*>(C), p);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    return SK_OK;
+  }
   sk_gemm_w4a16_kernel<<<p.sched.grid, NUM_THREADS, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
       tmA, qb, sz, static_cast<__half*>(C), p);
-  cudaError_t e = cudaGetLastError();
+  e = cudaGetLastError();
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

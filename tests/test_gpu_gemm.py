@@ -243,6 +243,27 @@ def test_w4a16_gemm(shape):
         _check(sk.streamk_fp16_ladder_block_reduce_q4(A, P, schedule=schedule, fixup=fixup), ref, TOL16)
 
 
+@pytest.mark.parametrize("shape", [(16, 512, 512), (33, 300, 256), (1, 4096, 4096), (128, 4096, 4096),
+                                   (16, 4096, 11008), (128, 128, 128), (200, 700, 1280)])
+def test_w4a16_cluster_split_k(shape):
+    """SK_SCHED_CLUSTER on the W4A16 kernel: K ranges that start inside a scale group, empty
+    ranks, both operand orders; bitwise reproducible."""
+    M, N, K = shape
+    c = oracle.make_case(4, shape=shape)
+    ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
+    P = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
+    A = c["A"].to(DEV)
+    first = sk.streamk_fp16_ladder_block_reduce_q4(A, P, schedule="cluster")
+    _check(first, ref, TOL16)
+    info = sk.schedule_info(M, N, K, kind="w4a16", schedule="cluster")
+    assert info["cluster"] in (2, 4, 8) and info["grid"] == info["total_tiles"] * info["cluster"]
+    for _ in range(2):
+        assert torch.equal(sk.streamk_fp16_ladder_block_reduce_q4(A, P, schedule="cluster"), first)
+    if N * K <= 1 << 20:
+        for sms in (2 * info["total_tiles"], 4 * info["total_tiles"]):
+            _check(sk.streamk_fp16_ladder_block_reduce_q4(A, P, schedule="cluster", num_sms=sms), ref, TOL16)
+
+
 def test_w4a16_both_operand_orders():
     c = oracle.make_case(4, shape=(48, 640, 1024))
     ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])

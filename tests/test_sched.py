@@ -151,8 +151,8 @@ def test_auto_schedule_resolution(lib):
     names = {v: k for k, v in L.SCHEDULES.items()}
     d = plan(16, 4096, 4096)          # 32 swapped tiles: every SM has to stream; clusters of 4
     assert (names[d["schedule"]], d["swap_ab"], d["cluster"], d["grid"]) == ("cluster", 1, 4, 128)
-    d = plan(16, 4096, 4096, kind=2)  # (the W4A16 kernel has no cluster exchange)
-    assert (names[d["schedule"]], d["swap_ab"]) == ("streamk", 1)
+    d = plan(16, 4096, 4096, kind=2)  # the W4A16 kernel alike
+    assert (names[d["schedule"]], d["swap_ab"], d["cluster"]) == ("cluster", 1, 4)
     d = plan(16, 4096, 256)           # shallow K: nothing to split
     assert names[d["schedule"]] == "streamk"
     d = plan(16, 12288, 4096)         # 96 swapped tiles: whole tiles keep most SMs busy
@@ -210,4 +210,5 @@ def test_cluster_split(lib):
     # other kernels do not take it
     prob = L.SkProblem(M=128, N=512, K=512, schedule=L.SCHEDULES["cluster"])
     assert lib.sk_schedule(C.byref(prob), 0, 148, C.byref(info)) == L.SK_ERR_ARG
-    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == L.SK_ERR_ARG
+    assert lib.sk_schedule(C.byref(prob), 3, 74, C.byref(info)) == L.SK_ERR_ARG
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and info.cluster == 8
