@@ -238,6 +238,14 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
 // warp may read).  Leaves the split tiles still to be reduced in pend_out[0..1].  tmem_full_bar /
 // tmem_empty_bar are the shared-memory addresses of two consecutive mbarriers each
 // (one per accumulator).
+// MODE: which fixup code the instantiation carries.  SK_EPI_ANY decides at run time from
+// p.fixup; SK_EPI_ATOMIC / SK_EPI_BLOCK_REDUCE carry one; SK_EPI_WHOLE none (data-parallel
+// schedule: every segment is a whole tile).  Short kernels pay an instruction-cache miss for
+// every line of code they touch, so their instantiations carry only what can run.
+constexpr int SK_EPI_ANY = -1, SK_EPI_ATOMIC = SK_FIXUP_ATOMIC, SK_EPI_BLOCK_REDUCE = SK_FIXUP_BLOCK_REDUCE,
+              SK_EPI_WHOLE = 2;
+
+template <int MODE = SK_EPI_ANY>
 __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __restrict__ C, int pid,
                                                  int rank, int warp, int lane, uint32_t tmem_base,
                                                  uint32_t tmem_full_bar, uint32_t tmem_empty_bar,
@@ -271,7 +279,8 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     int valid_cols = p.cols - c0;
     if (valid_cols > p.bn) valid_cols = p.bn;
     const int nchunks = (valid_cols + 31) >> 5;
-    const bool whole = (seg.k0 == 0 && seg.k1 == s.iters_per_tile);
+    const bool whole = MODE == SK_EPI_WHOLE || (seg.k0 == 0 && seg.k1 == s.iters_per_tile);
+    const bool atomic = MODE == SK_EPI_ATOMIC || (MODE == SK_EPI_ANY && p.fixup == SK_FIXUP_ATOMIC);
     int first = 0, last = 0;
     if (!whole) sk_tile_ctas(s, seg.tile, first, last);
     const bool is_tail = !whole && seg.k0 == 0;   // this CTA starts the tile (its "owner")
@@ -305,7 +314,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
         if (nv > 32) nv = 32;
         if (whole) {
           sk_store_chunk(C, p, grow, c0 + c * 32, nv, v);
-        } else if (p.fixup == SK_FIXUP_ATOMIC) {
+        } else if (atomic) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             if (4 * j < nv)
@@ -330,7 +339,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     }
 
     if (whole) continue;
-    if (p.fixup == SK_FIXUP_ATOMIC) {
+    if (atomic) {
       __threadfence();
       named_bar_sync(EPI_BAR_ID, EPI_THREADS);
       if (etid == 0) {

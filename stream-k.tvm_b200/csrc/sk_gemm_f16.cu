@@ -66,6 +66,15 @@ __device__ __forceinline__ void load_operand(int loader, uint32_t dst, const CUt
   }
 }
 
+// MODE SK_MODE_CLUSTER: the kernel of SK_SCHED_CLUSTER (one segment per CTA, exchange through
+// distributed shared memory); otherwise the persistent Stream-K / data-parallel kernel with one
+// of the workspace fixups (SK_EPI_ATOMIC, SK_EPI_BLOCK_REDUCE) or, for the data-parallel
+// schedule, none (SK_EPI_WHOLE).  Four instantiations, so that none carries another's code: on
+// small problems the kernel runs for microseconds and every instruction-cache line it touches
+// is a miss.
+constexpr int SK_MODE_CLUSTER = 3;   // besides SK_EPI_ATOMIC, SK_EPI_BLOCK_REDUCE, SK_EPI_WHOLE
+
+template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_constant__ CUtensorMap tmCol,
                    __half* __restrict__ C, const SkParams p) {
@@ -86,7 +95,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   const SkSched& s = p.sched;
   if (threadIdx.x == 0) sk_trace(p, 0);
   // Split-K inside a cluster: the partial tiles meet in a receive buffer behind the control block.
-  const bool clustered = s.split > 0;
+  constexpr bool clustered = MODE == SK_MODE_CLUSTER;
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
   // Start-up.  The time from kernel entry to the first load is pure latency on every small
@@ -271,19 +280,19 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     }
   } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------- epilogue
-    if (clustered)   // (takes part in the cluster's start-up barrier on its own)
+    if constexpr (clustered)   // (takes part in the cluster's start-up barrier on its own)
       sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
                       smem_u32(&ctrl->tmem_full[0]), sRow, recv_base, smem_u32(&ctrl->recv_full),
                       abort_flag, sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
     else
-      sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                       smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
+      sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                             smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   }
 
   // ------------------------------------------------------------- teardown
   tc_fence_before();
   bool reduce_ok = true;
-  if (clustered) {
+  if constexpr (clustered) {
     if (!(warp >= 2 && warp < 6)) cluster_wait();   // start-up barrier, second half
     __syncwarp();
     // the chunks of the other CTAs, and the epilogue warps' own one
@@ -308,7 +317,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     __syncwarp();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
-  if (clustered) {
+  if constexpr (clustered) {
     if (reduce_ok)
       sk_cluster_reduce(p, C, pid >> s.split_log2, static_cast<int>(cluster_ctarank()), recv_base);
     if (threadIdx.x == 0) sk_trace(p, 12);
@@ -316,7 +325,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   } else {
     // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
     // the split tiles it took part in.
-    sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+    if constexpr (MODE == SK_EPI_BLOCK_REDUCE) sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
   }
   if (threadIdx.x == 32) sk_trace(p, 7);
 }
@@ -494,8 +503,14 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(sk_gemm_f16_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    cudaError_t e = cudaSuccess;
+    const void* kernels[4] = {
+        reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_EPI_ATOMIC>),
+        reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_EPI_BLOCK_REDUCE>),
+        reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_EPI_WHOLE>),
+        reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_MODE_CLUSTER>)};
+    for (int i = 0; i < 4 && e == cudaSuccess; ++i)
+      e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
@@ -514,12 +529,18 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, sk_gemm_f16_kernel, tmRow, tmCol, static_cast<__half*>(C), p);
+    e = cudaLaunchKernelEx(&cfg, sk_gemm_f16_kernel<SK_MODE_CLUSTER>, tmRow, tmCol, static_cast<__half*>(C), p);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     return SK_OK;
   }
-  sk_gemm_f16_kernel<<<p.sched.grid, NUM_THREADS, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
-      tmRow, tmCol, static_cast<__half*>(C), p);
+  const cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  __half* Ch = static_cast<__half*>(C);
+  if (prob->schedule == SK_SCHED_DP)   // whole tiles only: no fixup code
+    sk_gemm_f16_kernel<SK_EPI_WHOLE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmRow, tmCol, Ch, p);
+  else if (prob->fixup == SK_FIXUP_ATOMIC)
+    sk_gemm_f16_kernel<SK_EPI_ATOMIC><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmRow, tmCol, Ch, p);
+  else
+    sk_gemm_f16_kernel<SK_EPI_BLOCK_REDUCE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmRow, tmCol, Ch, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;

@@ -84,6 +84,11 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 zmagic, __half
 // Shared memory: [BS dequantised weight stages][LS activation stages][LS packed blocks]
 // [LS group blocks][Ctrl]; BS and LS are chosen per launch.  p.col_stage_bytes holds the activation stage size in both
 // operand orders (128 rows normally, bn rows when the operands are swapped).
+// MODE as in the fp16 kernel: SK_EPI_ATOMIC, SK_EPI_BLOCK_REDUCE, SK_EPI_WHOLE (data-parallel
+// schedule, no fixup code) or SK_MODE_CLUSTER; one instantiation each.
+constexpr int SK_MODE_CLUSTER = 3;
+
+template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __restrict__ qblocks,
                      const uint8_t* __restrict__ szblocks, __half* __restrict__ C, const SkParams p) {
@@ -115,7 +120,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   if (threadIdx.x == 0) sk_trace(p, 0);
   // Split-K inside a cluster (sk_epilogue.cuh): receive buffer behind the control block,
   // staging area in the rings, which are idle by then.
-  const bool clustered = s.split > 0;
+  constexpr bool clustered = MODE == SK_MODE_CLUSTER;
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
   if (threadIdx.x == 0) {
@@ -261,13 +266,13 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------- epilogue
-    if (clustered)   // (takes part in the cluster's start-up barrier on its own)
+    if constexpr (clustered)   // (takes part in the cluster's start-up barrier on its own)
       sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
                       smem_u32(&ctrl->tmem_full[0]), sW, recv_base, smem_u32(&ctrl->recv_full),
                       abort_flag, sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
     else
-      sk_epilogue_loop(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                       smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
+      sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+                             smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   } else {
     // ------------------------------------------------------------- dequantise
     // Thread (h, r): weight row r of the tile, K half h (32 values = 4 packed words).
@@ -326,7 +331,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   // ------------------------------------------------------------- teardown
   tc_fence_before();
   bool reduce_ok = true;
-  if (clustered) {
+  if constexpr (clustered) {
     if (!(warp >= 2 && warp < 6)) cluster_wait();   // start-up barrier, second half
     __syncwarp();
     // the chunks of the other CTAs, and the epilogue warps' own one
@@ -348,14 +353,14 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     __syncwarp();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
-  if (clustered) {
+  if constexpr (clustered) {
     if (reduce_ok)
       sk_cluster_reduce(p, C, pid >> s.split_log2, static_cast<int>(cluster_ctarank()), recv_base);
     cluster_wait();
   } else {
     // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
     // the split tiles it took part in.
-    sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+    if constexpr (MODE == SK_EPI_BLOCK_REDUCE) sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
   }
   if (threadIdx.x == 32) sk_trace(p, 7);
 }
@@ -573,8 +578,14 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(sk_gemm_w4a16_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    cudaError_t e = cudaSuccess;
+    const void* kernels[4] = {
+        reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_EPI_ATOMIC>),
+        reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_EPI_BLOCK_REDUCE>),
+        reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_EPI_WHOLE>),
+        reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_MODE_CLUSTER>)};
+    for (int i = 0; i < 4 && e == cudaSuccess; ++i)
+      e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
@@ -593,12 +604,18 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, sk_gemm_w4a16_kernel, tmA, qb, sz, static_cast<__half*>(C), p);
+    e = cudaLaunchKernelEx(&cfg, sk_gemm_w4a16_kernel<SK_MODE_CLUSTER>, tmA, qb, sz, static_cast<__half*>(C), p);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     return SK_OK;
   }
-  sk_gemm_w4a16_kernel<<<p.sched.grid, NUM_THREADS, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
-      tmA, qb, sz, static_cast<__half*>(C), p);
+  const cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  __half* Ch = static_cast<__half*>(C);
+  if (prob->schedule == SK_SCHED_DP)   // whole tiles only: no fixup code
+    sk_gemm_w4a16_kernel<SK_EPI_WHOLE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmA, qb, sz, Ch, p);
+  else if (prob->fixup == SK_FIXUP_ATOMIC)
+    sk_gemm_w4a16_kernel<SK_EPI_ATOMIC><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmA, qb, sz, Ch, p);
+  else
+    sk_gemm_w4a16_kernel<SK_EPI_BLOCK_REDUCE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmA, qb, sz, Ch, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
