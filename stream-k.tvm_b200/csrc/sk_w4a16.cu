@@ -37,6 +37,8 @@ constexpr int W_STAGE_BYTES = KG * W_SLAB_BYTES;
 constexpr int MAX_LS = 12;                     // load stages (activation tile + packed block)
 constexpr int MAX_BS = 8;                      // dequantised weight stages (ring depth chosen per launch)
 constexpr int DQ_WARPS = 8;
+constexpr int DQ_GROUPS = 4;                   // groups of DQ_WARPS / DQ_GROUPS warps, one stage each at a time
+constexpr int DQ_GROUP_WARPS = DQ_WARPS / DQ_GROUPS;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
 constexpr int NUM_THREADS = 64 + SK_EPI_THREADS + DQ_THREADS;
 constexpr int CTRL_BYTES = 512;
@@ -127,10 +129,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
     for (int i = 0; i < LS; ++i) {
       mbar_init(smem_u32(&ctrl->load_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->load_empty[i]), DQ_WARPS + 1);  // each dequant warp + MMA commit
+      mbar_init(smem_u32(&ctrl->load_empty[i]), DQ_GROUP_WARPS + 1);  // the stage's dequant warps + MMA commit
     }
     for (int i = 0; i < BS; ++i) {
-      mbar_init(smem_u32(&ctrl->w_full[i]), DQ_WARPS);   // one arrival per dequant warp
+      mbar_init(smem_u32(&ctrl->w_full[i]), DQ_GROUP_WARPS);   // one arrival per dequant warp of the stage's group
       mbar_init(smem_u32(&ctrl->w_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -275,52 +277,80 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
                              smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   } else {
     // ------------------------------------------------------------- dequantise
-    // Thread (h, r): weight row r of the tile, K half h (32 values = 4 packed words).
-    const int dtid = (warp - 6) * 32 + lane;
-    const int h = dtid >> 7;
-    const int r = dtid & 127;
-    const int sw = r & 7;
+    // The eight warps form four groups of two, and group g takes stages g, g+4, g+8, ... whole.
+    // A stage costs a group far more in fixed latencies (two barrier waits, the loads of the
+    // packed words, scales and zero-points, the proxy fence, the arrivals) than in arithmetic,
+    // so what counts is how many stages are in flight at once, not how many threads share one:
+    // with every warp working on every stage, as a first version did, the stage rate was one
+    // warp's latency chain (0.8 us per stage, whatever was removed from it).
+    // Thread t of a group handles the 16-byte units u = t, t+64, t+128, t+192 of a K step:
+    // unit u = weight row u & 127, K half u >> 7 (32 values = 4 packed words).
+    const int dw = warp - 6;
+    const int grp = dw >> 1;
+    const int t = (dw & 1) * 32 + lane;
     SkCursor cur;
     sk_cursor_init(s, pid, cur);
     SkSeg seg;
     int ls = 0, bs = 0;
     uint32_t lph = 0, bph = 0;
+    uint32_t sidx = 0;   // running stage number
     bool dead = false;
     if (clustered) cluster_arrive_relaxed();
     while (sk_next(s, pid, cur, seg)) {
       for (int k = seg.k0; k < seg.k1;) {
         const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
+        // Every warp watches every stage's barriers complete, in order, also those of the
+        // stages it does not work on: a parity wait only tells a phase from its neighbours, and
+        // a group that skipped phases could take a slot's previous use for the awaited one
+        // (its stages are four apart, the rings may be shorter).  Both barriers of a foreign
+        // stage complete before those of the group's own next stage, so this costs no time.
         if (!dead) {
           if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 64 + ls, 3) ||
               !sk_wait_bar(smem_u32(&ctrl->w_empty[bs]), bph ^ 1u, abort_flag, p, 80 + bs, 3))
             dead = true;
         }
-        if (!dead) {
-          const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
-          const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
-          const uint32_t z = sz[256 + r];
-          const __half2 s2 = __half2half2(sc);
-          const uint32_t zm = 0x64006400u | z | (z << 16);
-          const __half2 zmagic = *reinterpret_cast<const __half2*>(&zm);
-          for (int j = 0; j < n; ++j) {
-            const uint8_t* q = smem + off_q + (ls * KG + j) * Q_BLOCK_BYTES;
-            const uint4 w = *reinterpret_cast<const uint4*>(q + h * 2048 + r * 16);
-            uint8_t* wrow = smem + (bs * KG + j) * W_SLAB_BYTES + r * 128;
-            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+        if ((sidx & (DQ_GROUPS - 1)) == static_cast<uint32_t>(grp)) {
+          if (!dead) {
+            const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
+            // rows t and t + 64
+            __half2 s2[2], zmagic[2];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              *reinterpret_cast<uint4*>(wrow + (((h * 4 + i) ^ sw) << 4)) =
-                  dequant_word(words[i], zmagic, s2);
+            for (int e = 0; e < 2; ++e) {
+              const int r = t + 64 * e;
+              const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
+              const uint32_t z = sz[256 + r];
+              s2[e] = __half2half2(sc);
+              const uint32_t zm = 0x64006400u | z | (z << 16);
+              zmagic[e] = *reinterpret_cast<const __half2*>(&zm);
+            }
+            for (int j = 0; j < n; ++j) {
+              const uint8_t* q = smem + off_q + (ls * KG + j) * Q_BLOCK_BYTES;
+              uint8_t* slab = smem + (bs * KG + j) * W_SLAB_BYTES;
+              uint4 w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint4*>(q + (t + 64 * i) * 16);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int u = t + 64 * i;
+                const int r = u & 127, h = u >> 7, e = i & 1;
+                uint8_t* wrow = slab + r * 128;
+                const int sw = r & 7;
+                const uint32_t words[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                  *reinterpret_cast<uint4*>(wrow + (((h * 4 + c) ^ sw) << 4)) =
+                      dequant_word(words[c], zmagic[e], s2[e]);
+              }
+            }
+            fence_proxy_async_smem();  // generic-proxy stores -> visible to the UMMA reads
           }
-          fence_proxy_async_smem();  // generic-proxy stores -> visible to the UMMA reads
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&ctrl->w_full[bs]));
+            mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
+          }
         }
-        // Each warp hands over its own 32 rows x one K half: no CTA-wide barrier, the warps
-        // run through the stages independently of one another.
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(smem_u32(&ctrl->w_full[bs]));
-          mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
-        }
+        ++sidx;
         k += n;
         if (++ls == LS) { ls = 0; lph ^= 1u; }
         if (++bs == BS) { bs = 0; bph ^= 1u; }
