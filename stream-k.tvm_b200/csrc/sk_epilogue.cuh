@@ -238,6 +238,23 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
 // warp may read).  Leaves the split tiles still to be reduced in pend_out[0..1].  tmem_full_bar /
 // tmem_empty_bar are the shared-memory addresses of two consecutive mbarriers each
 // (one per accumulator).
+// 32 accumulator columns of this thread's row; with b_off != 0 the sum of the two accumulators
+// that two MMA-issuing threads filled (sk_gemm_f16.cu).
+__device__ __forceinline__ void sk_load_acc(uint32_t taddr, uint32_t b_off, float (&v)[32]) {
+  using namespace skptx;
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  if (b_off != 0) {
+    tmem_ld_32x32(taddr + b_off, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(r[j]);
+  }
+}
+
 // MODE: which fixup code the instantiation carries.  SK_EPI_ANY decides at run time from
 // p.fixup; SK_EPI_ATOMIC / SK_EPI_BLOCK_REDUCE carry one; SK_EPI_WHOLE none (data-parallel
 // schedule: every segment is a whole tile).  Short kernels pay an instruction-cache miss for
@@ -301,14 +318,12 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     float* acc_slot = p.ws.acc_slots + static_cast<size_t>(first_id) * SK_SLOT_FLOATS;
     float* my_part = p.ws.part_slots + static_cast<size_t>(2 * me + (is_tail ? 1 : 0)) * SK_SLOT_FLOATS;
 
+    // two MMA issuers: the second one's accumulator holds every other stage of the segment
+    const bool two = p.acc_b_off != 0 && (seg.k1 - seg.k0) > p.kgroup;
     if (warp_ok && !dead) {
       for (int c = 0; c < nchunks; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c * 32, r);
-        tmem_ld_wait();
         float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        sk_load_acc(t_addr + c * 32, two ? p.acc_b_off : 0, v);
         if (!row_ok) continue;
         int nv = valid_cols - c * 32;
         if (nv > 32) nv = 32;
@@ -425,21 +440,22 @@ __host__ __device__ __forceinline__ int sk_cluster_recv_bytes(int bn, int split)
   return split * sk_cluster_quads_per_cta(bn, split) * SK_CL_QUAD_BYTES;
 }
 
-// Steps 1 and 2; runs on the four epilogue warps.  `has_work`: this CTA's K range is not
-// empty (an empty one contributes zeros).  recv_bar: this CTA's mbarrier, initialised with
+// Steps 1 and 2; runs on the four epilogue warps.  k_iters: K iterations of this CTA's range
+// (an empty one contributes zeros).  recv_bar: this CTA's mbarrier, initialised with
 // five arrivals (one per epilogue warp here, one with the expected byte count).
 // Chunks are sent as soon as they are staged, so one travels while the next is being staged.
 __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int warp, int lane,
                                                 uint32_t tmem_base, uint32_t tmem_full_bar,
                                                 uint32_t stage_base, uint32_t recv_base,
                                                 uint32_t recv_bar, volatile uint32_t* abort_flag,
-                                                bool has_work) {
+                                                int k_iters) {
   using namespace skptx;
   const int S = p.sched.split;
   const int q = warp & 3;
   const int per = p.cl_per;
   const uint32_t chunk_bytes = static_cast<uint32_t>(per) * SK_CL_QUAD_BYTES;
   const uint32_t row_off = static_cast<uint32_t>(q * 32 + lane) * 16u;
+  const bool has_work = k_iters > 0;
   bool live = has_work;
   cluster_arrive_relaxed();   // start-up barrier of the cluster, first half
   if (has_work) {
@@ -450,6 +466,8 @@ __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int
   if (warp == 2 && lane == 0) sk_trace(p, 5);
   cluster_wait();             // second half: every CTA's mbarrier exists
   const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  // two MMA issuers: the second accumulator is in use if the CTA's K range has a second stage
+  const uint32_t b_off = (p.acc_b_off != 0 && k_iters > p.kgroup) ? static_cast<uint32_t>(p.acc_b_off) : 0u;
   if (per >= 8) {
     // Wide chunks (a 32-column read never spans two of them): one chunk after the other,
     // starting with the next CTA's, so that the senders do not all aim at the same
@@ -468,11 +486,7 @@ __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int
       for (int qq = q0; qq < q1; qq += 8) {
         float v[32];
         if (live) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_addr + 4 * qq, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          sk_load_acc(t_addr + 4 * qq, b_off, v);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
@@ -507,11 +521,7 @@ __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int
   for (int c = 0; c < p.bn; c += 32) {
     float v[32];
     if (live) {
-      uint32_t r[32];
-      tmem_ld_32x32(t_addr + c, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      sk_load_acc(t_addr + c, b_off, v);
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = 0.f;

@@ -28,7 +28,7 @@ using namespace skptx;
 constexpr int BM = SK_BM;
 constexpr int BK = 64;
 constexpr int ROW_STAGE_BYTES = BM * BK * 2;   // 16 KB: 128 rows x 128 B
-constexpr int NUM_THREADS = 224;   // warps: 0 row-operand producer, 1 MMA, 2..5 epilogue, 6 col-operand producer
+constexpr int NUM_THREADS = 256;   // warps: 0 row-operand producer, 1 MMA, 2..5 epilogue, 6 col-operand producer, 7 second MMA issuer
 constexpr int MAX_STAGES = 12;
 constexpr int CTRL_BYTES = 512;
 constexpr int SMEM_LIMIT = 232448;             // 227 KB opt-in maximum per CTA
@@ -114,7 +114,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       mbar_init(smem_u32(&ctrl->empty[lane]), 1);
     } else if (lane < STAGES + 2) {
       const int i = lane - STAGES;
-      mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_full[i]), p.acc_b_off ? 2 : 1);   // one arrival per MMA issuer
       mbar_init(smem_u32(&ctrl->tmem_empty[i]), 4);  // one arrival per epilogue warp
     } else if (lane == STAGES + 2) {
       if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
@@ -136,7 +136,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   SkSeg seg;
   bool have = false;
   int tr = 0, tc = 0;
-  if (lane == 0 && (warp == 0 || warp == 1 || warp == 6)) {
+  if (lane == 0 && (warp == 0 || warp == 1 || warp == 6 || warp == 7)) {
     sk_cursor_init(s, pid, cur);
     have = sk_next(s, pid, cur, seg);
     if (have) sk_tile_mn(s, seg.tile, tr, tc);
@@ -216,9 +216,15 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     } else if (clustered) {
       cluster_arrive_relaxed();
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 7) {
+    // ------------------------------------------------------------- MMA issuers
+    // Issuing a UMMA costs its thread about 50 ns whatever the tile width, which bounds the
+    // K-step rate of narrow tiles.  With room in tensor memory for two accumulators per
+    // buffer (p.acc_b_off), a second thread in a warp of another scheduler takes every other
+    // stage of a segment and accumulates on its own; the epilogue adds the two.
+    const uint32_t me = warp == 1 ? 0u : 1u;
+    if (lane == 0 && (me == 0u || p.acc_b_off != 0)) {
+      const bool dual = p.acc_b_off != 0;
       int stage = 0;
       uint32_t ph = 0;
       uint32_t nseg = 0;
@@ -243,13 +249,23 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
         if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * acc_stride;
-        uint32_t accumulate = 0u;   // the segment's first UMMA overwrites the accumulator
-        for (int k = seg.k0; k < seg.k1;) {
+        const uint32_t d_tmem = tmem_base + buf * acc_stride + me * p.acc_b_off;
+        uint32_t accumulate = 0u;   // this thread's first UMMA of the segment overwrites its accumulator
+        uint32_t si = 0;            // stage number inside the segment
+        for (int k = seg.k0; k < seg.k1; ++si) {
           const int n = (seg.k1 - k) < G ? (seg.k1 - k) : G;
+          // Both issuers watch every stage's barrier complete, in order: a parity wait only
+          // tells a phase from its neighbours, and loads may land out of order, so a thread
+          // that skipped the other's stages could take a slot's previous use for the one it
+          // waits for.
           if (!sk_wait_bar(full0 + 8u * stage, ph, abort_flag, p, 32 + stage, 1)) {
             ok = false;
             break;
+          }
+          if (dual && (si & 1u) != me) {   // the other issuer's stage
+            k += n;
+            if (++stage == STAGES) { stage = 0; ph ^= 1u; }
+            continue;
           }
           tc_fence_after();
           if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
@@ -270,10 +286,12 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
           if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+        // (a thread that issued nothing in this segment has nothing to wait for)
+        if (accumulate) umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+        else mbar_arrive(smem_u32(&ctrl->tmem_full[buf]));
         ++nseg;
       }
-      sk_trace(p, 4);
+      if (me == 0u) sk_trace(p, 4);
       if (clustered && !arrived) cluster_arrive_relaxed();
     } else if (clustered) {
       cluster_arrive_relaxed();
@@ -283,7 +301,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     if constexpr (clustered)   // (takes part in the cluster's start-up barrier on its own)
       sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
                       smem_u32(&ctrl->tmem_full[0]), sRow, recv_base, smem_u32(&ctrl->recv_full),
-                      abort_flag, sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
+                      abort_flag, sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
     else
       sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                              smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
@@ -372,9 +390,13 @@ int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
 
 // Fields of SkParams that depend only on the tile width: TMEM layout and pipeline depth.
 void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_stages,
-                         int reserved_bytes) {
+                         int reserved_bytes, bool two_issuers) {
   p->bn = bn;
-  p->acc_stride = (bn + 31) & ~31;
+  const int acc_cols = (bn + 31) & ~31;
+  // two accumulators per buffer when the kernel has two MMA issuers and tensor memory has room
+  const bool dual = two_issuers && 4 * acc_cols <= 512;
+  p->acc_b_off = dual ? acc_cols : 0;
+  p->acc_stride = dual ? 2 * acc_cols : acc_cols;
   int cols = 32;
   while (cols < 2 * p->acc_stride) cols <<= 1;
   p->tmem_cols = cols;
@@ -451,7 +473,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   const int recv_bytes = split ? sk_cluster_recv_bytes(plan.bn, split) : 0;
   p.cl_per = split ? sk_cluster_quads_per_cta(plan.bn, split) : 1;
   p.cl_per_div = sk_div_make(p.cl_per);
-  sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, recv_bytes);
+  sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, recv_bytes, true);
   if (p.stages < 2) return SK_ERR_SHAPE;
   // the staging area of the cluster exchange lives in the operand ring
   if (split && p.stages * (ROW_STAGE_BYTES + p.col_stage_bytes) < recv_bytes) return SK_ERR_SHAPE;

@@ -271,7 +271,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     if constexpr (clustered)   // (takes part in the cluster's start-up barrier on its own)
       sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
                       smem_u32(&ctrl->tmem_full[0]), sW, recv_base, smem_u32(&ctrl->recv_full),
-                      abort_flag, sk_cta_begin(s, pid) < sk_cta_begin(s, pid + 1));
+                      abort_flag, sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
     else
       sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                              smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
@@ -487,7 +487,7 @@ inline int q4_nblocks(int N) { return (N + 255) / 256 * 2; }
 int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                      uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
 void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_stages,
-                         int reserved_bytes);
+                         int reserved_bytes, bool two_issuers);
 
 extern "C" size_t sk_q4_bytes(int N, int K) {
   if (N <= 0 || K <= 0 || (K % 128) != 0) return 0;
@@ -570,7 +570,7 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   // The activation tile has 128 rows normally, bn rows when the operands are swapped.
   const int a_rows = plan.swap ? plan.bn : BM;
   const int a_stage_bytes = a_rows * BK * 2;
-  sk_fill_tile_params(&p, plan.bn, 0, 1, 0);   // TMEM layout only; stages set below
+  sk_fill_tile_params(&p, plan.bn, 0, 1, 0, false);   // TMEM layout only; stages set below
   // Two rings share the shared memory: load stages (activation tile + packed block) and
   // dequantised weight stages.  The chain dequantise -> MMA -> release runs once per K step
   // and takes over a microsecond end to end, so the weight ring has to be deep as well: take
