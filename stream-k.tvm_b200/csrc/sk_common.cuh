@@ -73,6 +73,8 @@ struct SkParams {
   int unit_ctas;           // CTAs that share one scheduling unit: 1, or 2 (CTA pair, 256-row tiles)
   int bn;                  // UMMA N = tile extent along cols (multiple of 16, <= 256)
   int acc_stride;          // TMEM columns between the two accumulators
+  int kpair;               // 1: a stage is the K steps of one scale group (W4A16): two, or one at an odd
+                           //    start / the end of a segment; 0: kgroup K steps per stage
   int acc_b_off;           // > 0: two MMA-issuing threads take alternate stages of a segment, the second
                            //      accumulating at this column offset; the epilogue adds the two
   int tmem_cols;           // TMEM columns allocated (power of two >= 32)

@@ -238,6 +238,15 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
 // warp may read).  Leaves the split tiles still to be reduced in pend_out[0..1].  tmem_full_bar /
 // tmem_empty_bar are the shared-memory addresses of two consecutive mbarriers each
 // (one per accumulator).
+// Does the segment [k0, k1) span at least two pipeline stages, i.e. did the second MMA issuer
+// (if the kernel runs two, p.acc_b_off != 0) accumulate anything for it?
+__device__ __forceinline__ bool sk_second_acc_used(const SkParams& p, int k0, int k1) {
+  if (p.acc_b_off == 0) return false;
+  const int len = k1 - k0;
+  if (p.kpair) return (k0 & 1) ? len >= 2 : len >= 3;
+  return len > p.kgroup;
+}
+
 // 32 accumulator columns of this thread's row; with b_off != 0 the sum of the two accumulators
 // that two MMA-issuing threads filled (sk_gemm_f16.cu).
 __device__ __forceinline__ void sk_load_acc(uint32_t taddr, uint32_t b_off, float (&v)[32]) {
@@ -319,7 +328,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     float* my_part = p.ws.part_slots + static_cast<size_t>(2 * me + (is_tail ? 1 : 0)) * SK_SLOT_FLOATS;
 
     // two MMA issuers: the second one's accumulator holds every other stage of the segment
-    const bool two = p.acc_b_off != 0 && (seg.k1 - seg.k0) > p.kgroup;
+    const bool two = sk_second_acc_used(p, seg.k0, seg.k1);
     if (warp_ok && !dead) {
       for (int c = 0; c < nchunks; ++c) {
         float v[32];
@@ -440,15 +449,15 @@ __host__ __device__ __forceinline__ int sk_cluster_recv_bytes(int bn, int split)
   return split * sk_cluster_quads_per_cta(bn, split) * SK_CL_QUAD_BYTES;
 }
 
-// Steps 1 and 2; runs on the four epilogue warps.  k_iters: K iterations of this CTA's range
-// (an empty one contributes zeros).  recv_bar: this CTA's mbarrier, initialised with
+// Steps 1 and 2; runs on the four epilogue warps.  k_begin, k_iters: this CTA's range of K
+// iterations (an empty one contributes zeros).  recv_bar: this CTA's mbarrier, initialised with
 // five arrivals (one per epilogue warp here, one with the expected byte count).
 // Chunks are sent as soon as they are staged, so one travels while the next is being staged.
 __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int warp, int lane,
                                                 uint32_t tmem_base, uint32_t tmem_full_bar,
                                                 uint32_t stage_base, uint32_t recv_base,
                                                 uint32_t recv_bar, volatile uint32_t* abort_flag,
-                                                int k_iters) {
+                                                int k_begin, int k_iters) {
   using namespace skptx;
   const int S = p.sched.split;
   const int q = warp & 3;
@@ -467,7 +476,7 @@ __device__ __forceinline__ void sk_cluster_send(const SkParams& p, int rank, int
   cluster_wait();             // second half: every CTA's mbarrier exists
   const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
   // two MMA issuers: the second accumulator is in use if the CTA's K range has a second stage
-  const uint32_t b_off = (p.acc_b_off != 0 && k_iters > p.kgroup) ? static_cast<uint32_t>(p.acc_b_off) : 0u;
+  const uint32_t b_off = sk_second_acc_used(p, k_begin, k_begin + k_iters) ? static_cast<uint32_t>(p.acc_b_off) : 0u;
   if (per >= 8) {
     // Wide chunks (a 32-column read never spans two of them): one chunk after the other,
     // starting with the next CTA's, so that the senders do not all aim at the same

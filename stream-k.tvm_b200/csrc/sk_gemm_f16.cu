@@ -301,7 +301,8 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     if constexpr (clustered)   // (takes part in the cluster's start-up barrier on its own)
       sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
                       smem_u32(&ctrl->tmem_full[0]), sRow, recv_base, smem_u32(&ctrl->recv_full),
-                      abort_flag, sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
+                      abort_flag, sk_cta_begin(s, pid) % s.iters_per_tile,
+                      sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
     else
       sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                              smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);

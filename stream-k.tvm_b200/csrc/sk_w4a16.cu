@@ -40,7 +40,8 @@ constexpr int DQ_WARPS = 8;
 constexpr int DQ_GROUPS = 4;                   // groups of DQ_WARPS / DQ_GROUPS warps, one stage each at a time
 constexpr int DQ_GROUP_WARPS = DQ_WARPS / DQ_GROUPS;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
-constexpr int NUM_THREADS = 64 + SK_EPI_THREADS + DQ_THREADS;
+constexpr int NUM_THREADS = 64 + SK_EPI_THREADS + DQ_THREADS + 32;   // + warp 14, the second MMA issuer
+constexpr int MMA_B_WARP = 6 + DQ_WARPS;
 constexpr int CTRL_BYTES = 512;
 constexpr int SMEM_LIMIT = 232448;
 
@@ -136,7 +137,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       mbar_init(smem_u32(&ctrl->w_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_full[i]), p.acc_b_off ? 2 : 1);   // one arrival per MMA issuer
       mbar_init(smem_u32(&ctrl->tmem_empty[i]), 4);
     }
     ctrl->abort = 0u;
@@ -208,9 +209,15 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     } else if (clustered) {
       cluster_arrive_relaxed();
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == MMA_B_WARP) {
+    // ------------------------------------------------------------- MMA issuers
+    // Issuing a UMMA costs its thread about 50 ns, and with eight per stage this thread was
+    // the mainloop's limit.  With room in tensor memory for two accumulators per buffer
+    // (p.acc_b_off), a second thread takes every other stage of a segment and accumulates on
+    // its own; the epilogue adds the two.
+    const uint32_t me = warp == 1 ? 0u : 1u;
+    if (lane == 0 && (me == 0u || p.acc_b_off != 0)) {
+      const bool dual = p.acc_b_off != 0;
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
@@ -228,40 +235,46 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
         if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-        uint32_t accumulate = 0u;
-        for (int k = seg.k0; k < seg.k1;) {
+        const uint32_t d_tmem = tmem_base + buf * p.acc_stride + me * p.acc_b_off;
+        uint32_t accumulate = 0u;   // this thread's first UMMA of the segment overwrites its accumulator
+        uint32_t si = 0;            // stage number inside the segment
+        for (int k = seg.k0; k < seg.k1; ++si) {
           const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
+          // (both issuers watch every stage's barriers complete, in order: see the dequant warps)
           if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 32 + ls, 1) ||
               !sk_wait_bar(smem_u32(&ctrl->w_full[bs]), bph, abort_flag, p, 48 + bs, 1)) {
             ok = false;
             break;
           }
-          tc_fence_after();
-          if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
-          for (int j = 0; j < n; ++j) {
-            const uint32_t act = act_lo0 + (ls * KG + j) * act_tile16;
-            const uint32_t wgt = wgt_lo0 + (bs * KG + j) * (W_SLAB_BYTES >> 4);
-            const uint32_t a_lo = swapped ? wgt : act;   // UMMA M side
-            const uint32_t b_lo = swapped ? act : wgt;   // UMMA N side
+          if (!dual || (si & 1u) == me) {
+            tc_fence_after();
+            if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
+            for (int j = 0; j < n; ++j) {
+              const uint32_t act = act_lo0 + (ls * KG + j) * act_tile16;
+              const uint32_t wgt = wgt_lo0 + (bs * KG + j) * (W_SLAB_BYTES >> 4);
+              const uint32_t a_lo = swapped ? wgt : act;   // UMMA M side
+              const uint32_t b_lo = swapped ? act : wgt;   // UMMA N side
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk) {
-              umma_f16_ss(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
-              accumulate = 1u;
+              for (int kk = 0; kk < BK / 16; ++kk) {
+                umma_f16_ss(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
+                accumulate = 1u;
+              }
             }
+            umma_commit(smem_u32(&ctrl->load_empty[ls]));
+            umma_commit(smem_u32(&ctrl->w_empty[bs]));
+            if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
           }
-          umma_commit(smem_u32(&ctrl->load_empty[ls]));
-          umma_commit(smem_u32(&ctrl->w_empty[bs]));
           k += n;
           if (++ls == LS) { ls = 0; lph ^= 1u; }
           if (++bs == BS) { bs = 0; bph ^= 1u; }
-          if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+        // (a thread that issued nothing in this segment has nothing to wait for)
+        if (accumulate) umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+        else mbar_arrive(smem_u32(&ctrl->tmem_full[buf]));
         ++nseg;
       }
-      sk_trace(p, 4);
+      if (me == 0u) sk_trace(p, 4);
       if (clustered && !arrived) cluster_arrive_relaxed();
     } else if (clustered) {
       cluster_arrive_relaxed();
@@ -271,7 +284,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     if constexpr (clustered)   // (takes part in the cluster's start-up barrier on its own)
       sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
                       smem_u32(&ctrl->tmem_full[0]), sW, recv_base, smem_u32(&ctrl->recv_full),
-                      abort_flag, sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
+                      abort_flag, sk_cta_begin(s, pid) % s.iters_per_tile,
+                      sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
     else
       sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                              smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
@@ -570,7 +584,9 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   // The activation tile has 128 rows normally, bn rows when the operands are swapped.
   const int a_rows = plan.swap ? plan.bn : BM;
   const int a_stage_bytes = a_rows * BK * 2;
-  sk_fill_tile_params(&p, plan.bn, 0, 1, 0, false);   // TMEM layout only; stages set below
+  // (two MMA issuers pay off for the narrow UMMAs of the swapped order only: measured)
+  sk_fill_tile_params(&p, plan.bn, 0, 1, 0, plan.swap != 0);   // TMEM layout only; stages set below
+  p.kpair = 1;
   // Two rings share the shared memory: load stages (activation tile + packed block) and
   // dequantised weight stages.  The chain dequantise -> MMA -> release runs once per K step
   // and takes over a microsecond end to end, so the weight ring has to be deep as well: take
