@@ -70,7 +70,10 @@ typedef struct sk_problem {
                                  16..256 (multiple of 16) = operands swapped: the
                                  weights feed the UMMA M dimension and the tile
                                  spans tile_m rows of C (for short M)          */
-  int32_t tile_n;             /* 0 = choose; 128 or 256 (128 when swapped)     */
+  int32_t tile_n;             /* 0 = choose; columns of C per tile: a multiple of 16 up
+                                 to 256 (W4A16: 128).  Operands swapped: weight rows
+                                 per tile, 128, or for fp16 NT a multiple of 8 from
+                                 16 to 128                                      */
   int32_t num_sms;            /* 0 = all SMs of the device; else grid size    */
   int32_t group_m;            /* 0 = choose; tile rasterisation group height  */
   int32_t fixup_timeout_us;   /* 0 = default (2 s); bound of every device wait */

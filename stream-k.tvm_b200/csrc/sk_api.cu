@@ -91,11 +91,11 @@ int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out) 
 //   16 along M: no tensor-core work, shared memory or epilogue lanes are spent on padding.
 static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* plan) {
   if (kernel_kind == 0) {
-    plan->swap = 0; plan->bn = 64; plan->rows = p->M; plan->cols = p->N;
+    plan->swap = 0; plan->bn = 64; plan->bm = 64; plan->rows = p->M; plan->cols = p->N;
     return SK_OK;
   }
   if (kernel_kind == 3) {   // CTA pairs: 256 x 256 tiles
-    plan->swap = 0; plan->bn = 256; plan->rows = p->M; plan->cols = p->N;
+    plan->swap = 0; plan->bn = 256; plan->bm = 128; plan->rows = p->M; plan->cols = p->N;
     return SK_OK;
   }
   int tm = p->tile_m, tn = p->tile_n;
@@ -106,10 +106,14 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
   else if (tm == 128 && tn == 0 && p->M <= 64) swap = false;
   else swap = false;
   if (swap) {
-    if (tn != 0 && tn != 128) return SK_ERR_ARG;
+    // tile_n = weight rows per tile: 128, or for fp16 NT any multiple of 8 from 16 (the TMA
+    // box then has fewer rows; the UMMA still spans 128, the rest of its rows is ignored)
+    if (tn == 0) tn = 128;
+    const bool fitted_ok = kernel_kind == 1 && p->layout == SK_LAYOUT_NT;
+    if (tn != 128 && !(fitted_ok && tn >= 16 && tn < 128 && (tn & 7) == 0)) return SK_ERR_ARG;
     if (tm == 0) tm = (p->M + 15) & ~15;
     if (tm < 16 || tm > 256 || (tm & 15) != 0) return SK_ERR_ARG;
-    plan->swap = 1; plan->bn = tm; plan->rows = p->N; plan->cols = p->M;
+    plan->swap = 1; plan->bn = tm; plan->bm = tn; plan->rows = p->N; plan->cols = p->M;
     return SK_OK;
   }
   if (tn == 0) {
@@ -125,7 +129,7 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
   // fp16: any multiple of 16 up to 256 (NN and ladder weights come in 128-row units: checked
   // by the caller); W4A16 dequantises 128 weight rows per stage.
   if (kernel_kind == 2 ? tn != 128 : (tn < 16 || tn > 256 || (tn & 15) != 0)) return SK_ERR_ARG;
-  plan->swap = 0; plan->bn = tn; plan->rows = p->M; plan->cols = p->N;
+  plan->swap = 0; plan->bn = tn; plan->bm = 128; plan->rows = p->M; plan->cols = p->N;
   return SK_OK;
 }
 
@@ -160,6 +164,15 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
     // (the W4A16 mainloop's K-step rate is set by its dequantise hand-over, so it always
     // wants every SM: Stream-K)
     q->schedule = (kernel_kind == 1 && 2 * tiles >= num_sms) ? SK_SCHED_DP : SK_SCHED_STREAMK;
+    if (q->schedule == SK_SCHED_DP && tiles_open && q->layout == SK_LAYOUT_NT && tiles < num_sms) {
+      // fewer weight rows per tile, so that (nearly) every SM gets a tile of its own: a single
+      // SM ingests only ~110 GB/s, and 86 tiles of 128 rows leave 62 SMs idle
+      const int bm = ((q->N + num_sms - 1) / num_sms + 7) & ~7;
+      if (bm >= 64 && bm < 128) {
+        q->tile_m = (q->M + 15) & ~15;
+        q->tile_n = bm;
+      }
+    }
     return;
   }
   const int tiles_m = (q->M + 127) / 128;
@@ -183,7 +196,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   SkPlan plan;
   int st = make_plan(p, kernel_kind, num_sms, &plan);
   if (st != SK_OK) return st;
-  const int tr = kernel_kind == 0 ? 64 : kernel_kind == 3 ? 256 : 128;   // tile rows (kernel space)
+  const int tr = kernel_kind == 0 ? 64 : kernel_kind == 3 ? 256 : plan.bm;   // tile rows (kernel space)
   const int tk = kernel_kind == 0 ? 16 : 64;
   const long long tiles_r = (plan.rows + tr - 1) / tr;
   const long long tiles_c = (plan.cols + plan.bn - 1) / plan.bn;

@@ -73,6 +73,8 @@ struct SkParams {
   int unit_ctas;           // CTAs that share one scheduling unit: 1, or 2 (CTA pair, 256-row tiles)
   int bn;                  // UMMA N = tile extent along cols (multiple of 16, <= 256)
   int acc_stride;          // TMEM columns between the two accumulators
+  int bm;                  // rows of the UMMA M side a tile covers (tile pitch): 128, or fewer when the
+                           //    weight tile is fitted to the SM count (rows beyond it hold stale data)
   int kpair;               // 1: a stage is the K steps of one scale group (W4A16): two, or one at an odd
                            //    start / the end of a segment; 0: kgroup K steps per stage
   int acc_b_off;           // > 0: two MMA-issuing threads take alternate stages of a segment, the second
@@ -131,6 +133,7 @@ struct SkPlan {
   int swap;          // operands swapped (weights feed the UMMA M dimension)
   int bn;            // tile extent along kernel-space cols
   int rows, cols;    // kernel-space extents
+  int bm;            // tile extent along kernel-space rows (128 unless fitted, see SkParams::bm)
 };
 int sk_set_cuda_error(cudaError_t e);
 int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out);

@@ -170,11 +170,11 @@ __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __res
   const int n = last - first + 1;
   int tr, tc;
   sk_tile_mn(s, pd.tile, tr, tc);
-  const int r0 = (tr * p.unit_ctas + rank) * SK_BM, c0 = tc * p.bn;
+  const int r0 = (tr * p.unit_ctas + rank) * p.bm, c0 = tc * p.bn;
   int valid_cols = p.cols - c0;
   if (valid_cols > p.bn) valid_cols = p.bn;
   int rows_valid = p.rows - r0;
-  if (rows_valid > SK_BM) rows_valid = SK_BM;
+  if (rows_valid > p.bm) rows_valid = p.bm;
   const int L = ((valid_cols + 3) >> 2) * SK_BM;  // float4 items of this CTA's part of the tile
   const int j = pid - first;
   const int begin = static_cast<int>(static_cast<long long>(j) * L / n);
@@ -298,10 +298,10 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     ++nseg;
     int tr, tc;
     sk_tile_mn(s, seg.tile, tr, tc);
-    const int r0 = (tr * p.unit_ctas + rank) * BM, c0 = tc * p.bn;
+    const int r0 = (tr * p.unit_ctas + rank) * p.bm, c0 = tc * p.bn;
     const int grow = r0 + row;
-    const bool row_ok = grow < p.rows;
-    const bool warp_ok = (r0 + q * 32) < p.rows;  // warp-uniform
+    const bool row_ok = row < p.bm && grow < p.rows;   // (rows past the tile pitch hold stale data)
+    const bool warp_ok = q * 32 < p.bm && (r0 + q * 32) < p.rows;  // warp-uniform
     int valid_cols = p.cols - c0;
     if (valid_cols > p.bn) valid_cols = p.bn;
     const int nchunks = (valid_cols + 31) >> 5;
@@ -376,7 +376,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
         // threads share the work whatever the number of valid rows
         __threadfence();
         int rows_valid = p.rows - r0;
-        if (rows_valid > BM) rows_valid = BM;
+        if (rows_valid > p.bm) rows_valid = p.bm;
         const int L = ((valid_cols + 3) >> 2) * BM;
         float4* slot4 = reinterpret_cast<float4*>(acc_slot);
         const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -575,13 +575,13 @@ __device__ __forceinline__ void sk_cluster_reduce_s(const SkParams& p, __half* _
   const int per = p.cl_per;
   int tr, tc;
   sk_tile_mn(p.sched, tile, tr, tc);
-  const int r0 = tr * SK_BM, c0 = tc * p.bn;
+  const int r0 = tr * p.bm, c0 = tc * p.bn;
   int valid_cols = p.cols - c0;
   if (valid_cols > p.bn) valid_cols = p.bn;
   int nq = ((valid_cols + 3) >> 2) - rank * per;   // quads of this CTA that hold real columns
   if (nq > per) nq = per;
   int rows_valid = p.rows - r0;
-  if (rows_valid > SK_BM) rows_valid = SK_BM;
+  if (rows_valid > p.bm) rows_valid = p.bm;
   const uint32_t chunk_bytes = static_cast<uint32_t>(per) * SK_CL_QUAD_BYTES;
   const int items = per * SK_BM;
   const int gcol0 = c0 + rank * per * 4;

@@ -181,7 +181,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
       for (; ok && have; have = sk_next(s, pid, cur, seg)) {
         if (!first_seg) sk_tile_mn(s, seg.tile, tr, tc);   // (the first segment's are known already)
         first_seg = false;
-        const int first_row = is_row ? tr * BM : tc * p.bn;
+        const int first_row = is_row ? tr * p.bm : tc * p.bn;
         for (int k = seg.k0; k < seg.k1;) {
           // up to G consecutive K steps share one stage: one barrier round trip for all
           const int n = (seg.k1 - k) < G ? (seg.k1 - k) : G;
@@ -463,6 +463,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   p.rows = plan.rows; p.cols = plan.cols;
   p.transposed = plan.swap;
   p.unit_ctas = 1;
+  p.bm = plan.bm;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
   p.drop_flag_cta = prob->test_drop_flag_cta;
@@ -503,19 +504,19 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   if (!plan.swap) {
     p.row_loader = SK_LOAD_TMA_K;
     p.col_loader = w_loader;
-    st = sk_make_tmap_f16(&tmRow, A, M, K, prob->lda, BK, BM);
+    st = sk_make_tmap_f16(&tmRow, A, M, K, prob->lda, BK, plan.bm);
     if (st == SK_OK) st = weight_map(&tmCol, plan.bn);
     p.col_img = B;
     if (w_loader != SK_LOAD_TMA_K && (plan.bn % 128) != 0) return SK_ERR_ARG;
   } else {
     p.row_loader = w_loader;
     p.col_loader = SK_LOAD_TMA_K;
-    st = weight_map(&tmRow, BM);
+    st = weight_map(&tmRow, plan.bm);
     if (st == SK_OK) st = sk_make_tmap_f16(&tmCol, A, M, K, prob->lda, BK, plan.bn);
     p.row_img = B;
   }
   if (st != SK_OK) return st;
-  p.row_tx_bytes = ROW_STAGE_BYTES;
+  p.row_tx_bytes = plan.bm * BK * 2;   // the TMA box of the M-side operand has plan.bm rows
   p.col_tx_bytes = p.col_stage_bytes;
   p.idesc = umma_idesc_f16(BM, plan.bn, 0) |
             (p.row_loader == SK_LOAD_TMA_MN ? (1u << 15) : 0u) |

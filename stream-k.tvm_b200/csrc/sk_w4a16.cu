@@ -574,6 +574,7 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   p.rows = plan.rows; p.cols = plan.cols;
   p.transposed = plan.swap;
   p.unit_ctas = 1;
+  p.bm = BM;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
   p.drop_flag_cta = prob->test_drop_flag_cta;

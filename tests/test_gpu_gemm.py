@@ -127,6 +127,32 @@ def test_fp16_short_m_swapped_operands(M):
     _check(sk.streamk_fp16_nn(A.to(DEV), Bn.to(DEV), schedule="streamk"), ref, TOL16)
 
 
+@pytest.mark.parametrize("M", [1, 16, 40, 64])
+def test_fp16_swapped_with_fitted_weight_tiles(M):
+    """Swapped operands with fewer than 128 weight rows per tile (tile_n < 128): the UMMA
+    still spans 128 rows, whose tail holds stale data that must never reach C."""
+    N, K = 1000, 1032
+    A, B = _rand16(M, N, K, seed=100 + M)
+    ref = oracle.gemm_ref(A, B, "nt")
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    tm = (M + 15) // 16 * 16
+    for tile_n in (24, 80, 104, 120):
+        info = sk.schedule_info(M, N, K, schedule="streamk", tile_m=tm, tile_n=tile_n)
+        assert (info["swap_ab"], info["tile_n"], info["tiles_n"]) == (1, tile_n, -(-N // tile_n))
+        for schedule in SCHEDULES:
+            for fixup in FIXUPS:
+                _check(sk.streamk_fp16_nt(Ad, Bd, tile_m=tm, tile_n=tile_n, schedule=schedule, fixup=fixup), ref, TOL16)
+        if info["total_tiles"] * 2 <= 148:
+            _check(sk.streamk_fp16_nt(Ad, Bd, tile_m=tm, tile_n=tile_n, schedule="cluster"), ref, TOL16)
+    # the library's own choice for many weight rows: data-parallel tiles of fitted height
+    A2, B2 = _rand16(M, 11008, 512, seed=7)
+    info = sk.schedule_info(M, 11008, 512)
+    assert (info["swap_ab"], info["tile_n"], info["total_tiles"]) == (1, 80, 138)
+    _check(sk.streamk_fp16_nt(A2.to(DEV), B2.to(DEV)), oracle.gemm_ref(A2, B2, "nt"), TOL16)
+    with pytest.raises(Exception):     # other layouts come in 128-row units
+        sk.streamk_fp16_nn(Ad, B.t().contiguous().to(DEV), tile_m=tm, tile_n=80)
+
+
 def test_fp16_explicit_swap_with_several_m_tiles():
     A, B = _rand16(200, 520, 1000, seed=77)
     ref = oracle.gemm_ref(A, B, "nt")

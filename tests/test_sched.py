@@ -155,8 +155,12 @@ def test_auto_schedule_resolution(lib):
     assert (names[d["schedule"]], d["swap_ab"], d["cluster"]) == ("cluster", 1, 4)
     d = plan(16, 4096, 256)           # shallow K: nothing to split
     assert names[d["schedule"]] == "streamk"
-    d = plan(16, 12288, 4096)         # 96 swapped tiles: whole tiles keep most SMs busy
-    assert (names[d["schedule"]], d["swap_ab"], d["total_tiles"]) == ("dp", 1, 96)
+    d = plan(16, 12288, 4096)         # whole swapped tiles, 88 weight rows each: 140 of 148 SMs busy
+    assert (names[d["schedule"]], d["swap_ab"], d["tile_n"], d["total_tiles"]) == ("dp", 1, 88, 140)
+    d = plan(16, 11008, 4096)
+    assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["total_tiles"]) == ("dp", 16, 80, 138)
+    d = plan(16, 12288, 4096, kind=2)  # (W4A16 weights come in blocks of 128 rows)
+    assert (d["swap_ab"], d["tile_n"], d["total_tiles"]) == (1, 128, 96)
     d = plan(256, 12288, 4096)        # tile width fitted to 74 columns per tile row
     assert names[d["schedule"]] == "dp" and d["tile_n"] == 176 and d["total_tiles"] <= 148
     d = plan(128, 4096, 4096)         # 32 tiles: clusters of 4 on 128 x 128 tiles
