@@ -254,8 +254,14 @@ def run_sweep(path: str, peaks: dict) -> None:
                 variants.append(("cluster", "block_reduce", None))
         except sk.StreamKError:
             pass
+        # the library's choice once more, launched with SK_FLAG_PDL: in a chain of launches the
+        # start-up of one overlaps the tail of the one before (what the graph replay times)
+        variants.append(("auto+pdl", "block_reduce", None))
         for schedule, fixup, tile_n in variants:
-            fn = lambda i: sk.streamk_fp16_nt(A, Bs[i], schedule=schedule, fixup=fixup, out=out, tile_n=tile_n)
+            pdl = schedule.endswith("+pdl")
+            schedule = schedule.split("+")[0]
+            fn = lambda i: sk.streamk_fp16_nt(A, Bs[i], schedule=schedule, fixup=fixup, out=out, tile_n=tile_n,
+                                              pdl=pdl)
             fn(0)
             sk.check_status()
             err = oracle.rel_err(out, ref)
@@ -264,6 +270,8 @@ def run_sweep(path: str, peaks: dict) -> None:
             names = {v: k for k, v in sk.SCHEDULES.items()}
             how = f"cluster of {info['cluster']}" if info["cluster"] else fixup
             label = schedule if schedule != "auto" else f"auto={names[info['schedule']]}"
+            if pdl:
+                label = "pdl " + label
             record(cfg, "streamk_fp16_nt", M, N, K,
                    f"{label}/{how}/tile{info['tile_m']}x{info['tile_n']}", us, flops, nbytes,
                    {"rel_err": float(f"{err:.3e}")})
@@ -285,13 +293,16 @@ def run_sweep(path: str, peaks: dict) -> None:
         est = max(nbytes / 6.5e3, flops / 1.5e9) / 1e3 + 3
         ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
         for schedule, fixup in (("auto", "block_reduce"), ("streamk", "block_reduce"),
-                                ("hybrid", "block_reduce"), ("streamk", "atomic")):
-            fn = lambda i: sk.streamk_fp16_ladder_block_reduce_q4(A, Ps[i], schedule=schedule, fixup=fixup, out=out)
+                                ("hybrid", "block_reduce"), ("streamk", "atomic"), ("auto+pdl", "block_reduce")):
+            pdl = schedule.endswith("+pdl")
+            schedule = schedule.split("+")[0]
+            fn = lambda i: sk.streamk_fp16_ladder_block_reduce_q4(A, Ps[i], schedule=schedule, fixup=fixup, out=out,
+                                                                  pdl=pdl)
             fn(0)
             sk.check_status()
             err = oracle.rel_err(out, ref)
             us = time_rotating(fn, copies, est)
-            record(4, "streamk_fp16_ladder_block_reduce_q4", M, N, K, f"{schedule}/{fixup}", us, flops, nbytes,
+            record(4, "streamk_fp16_ladder_block_reduce_q4", M, N, K, f"{'pdl ' if pdl else ''}{schedule}/{fixup}", us, flops, nbytes,
                    {"rel_err": float(f"{err:.3e}")})
         W = sk.dequant_w4(P0)
         Ws = [W.clone() for _ in range(min(copies, int(math.ceil(2 * l2 / (2 * N * K))) + 1))]

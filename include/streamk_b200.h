@@ -80,7 +80,18 @@ typedef struct sk_problem {
   int32_t test_drop_flag_cta; /* -1 = off. Test only: this CTA never publishes
                                  its block-reduce flag, so its tile owner runs
                                  into the bounded wait and reports a timeout. */
+  int32_t flags;              /* SK_FLAG_* bits                                */
 } sk_problem;
+
+/* sk_problem.flags */
+enum { SK_FLAG_PDL = 1 /* fp16 / W4A16 entry points: launch with programmatic stream
+                          serialisation.  The kernel's start-up (mbarrier set-up, tensor-memory
+                          allocation, scheduling arithmetic) may then overlap the tail of the
+                          kernel before it in the stream if that kernel lets its dependents go
+                          early (these kernels do, at entry); nothing touches global memory
+                          before the preceding kernel has completed (griddepcontrol.wait), so
+                          results and stream order are unchanged.  Worth 1-2 us per launch in a
+                          chain of small GEMMs.                                            */ };
 
 /* Host scheduler result: the integers of streamk_fp16.py:83-113 plus the
  * derived per-CTA split, exposed so callers and tests can inspect them.     */

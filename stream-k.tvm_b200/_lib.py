@@ -18,12 +18,13 @@ SK_ERR_FIXUP_TIMEOUT, SK_ERR_PIPE_TIMEOUT, SK_ERR_ARG, SK_ERR_LIMIT = 6, 7, 8, 9
 LAYOUTS = {"nn": 0, "nt": 1, "ladder": 2}
 SCHEDULES = {"streamk": 0, "hybrid": 1, "hybrid_dp_first": 2, "dp": 3, "auto": 4, "cluster": 5}
 FIXUPS = {"atomic": 0, "block_reduce": 1}
+SK_FLAG_PDL = 1
 
 
 class SkProblem(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "M", "N", "K", "lda", "ldb", "ldc", "layout", "schedule", "fixup", "tile_m", "tile_n", "num_sms",
-        "group_m", "fixup_timeout_us", "test_drop_flag_cta")]
+        "group_m", "fixup_timeout_us", "test_drop_flag_cta", "flags")]
 
 
 class SkScheduleInfo(C.Structure):

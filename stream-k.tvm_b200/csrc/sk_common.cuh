@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "../../include/streamk_b200.h"
 #include "sk_ptx.cuh"
@@ -142,3 +143,33 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
                   SkSched* s, SkPlan* plan);
 unsigned long long* sk_trace_buffer();
 void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms);
+
+// One launch path for the tensor-core kernels: optional cluster dimension (SK_SCHED_CLUSTER, CTA
+// pairs) and optional programmatic stream serialisation (SK_FLAG_PDL).
+template <typename... KArgs, typename... Args>
+inline cudaError_t sk_launch(void (*kernel)(KArgs...), int grid, int block, size_t smem,
+                             cudaStream_t stream, int cluster, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (cluster > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = cluster;
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}

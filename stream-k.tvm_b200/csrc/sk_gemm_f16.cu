@@ -93,7 +93,10 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   const int lane = threadIdx.x & 31;
   const int pid = blockIdx.x;
   const SkSched& s = p.sched;
-  if (threadIdx.x == 0) sk_trace(p, 0);
+  if (threadIdx.x == 0) {
+    sk_trace(p, 0);
+    griddep_launch_dependents();   // the next kernel of the stream may begin its own start-up
+  }
   // Split-K inside a cluster: the partial tiles meet in a receive buffer behind the control block.
   constexpr bool clustered = MODE == SK_MODE_CLUSTER;
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
@@ -155,6 +158,9 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
   }
   if (threadIdx.x == 0) sk_trace(p, 1);
+  // Everything up to here touched only this CTA's shared and tensor memory; global memory is
+  // the previous kernel's until it has completed (a no-op unless launched with SK_FLAG_PDL).
+  griddep_wait();
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------- producers
@@ -539,34 +545,22 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
-  cudaError_t e;
-  if (split) {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(p.sched.grid);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = split;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, sk_gemm_f16_kernel<SK_MODE_CLUSTER>, tmRow, tmCol, static_cast<__half*>(C), p);
-    if (e != cudaSuccess) return sk_set_cuda_error(e);
-    return SK_OK;
-  }
   const cudaStream_t cs = static_cast<cudaStream_t>(stream);
   __half* Ch = static_cast<__half*>(C);
-  if (prob->schedule == SK_SCHED_DP)   // whole tiles only: no fixup code
-    sk_gemm_f16_kernel<SK_EPI_WHOLE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmRow, tmCol, Ch, p);
+  const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
+  cudaError_t e;
+  if (split)
+    e = sk_launch(sk_gemm_f16_kernel<SK_MODE_CLUSTER>, p.sched.grid, NUM_THREADS, smem_bytes, cs, split, pdl,
+                  tmRow, tmCol, Ch, p);
+  else if (prob->schedule == SK_SCHED_DP)   // whole tiles only: no fixup code
+    e = sk_launch(sk_gemm_f16_kernel<SK_EPI_WHOLE>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
+                  tmRow, tmCol, Ch, p);
   else if (prob->fixup == SK_FIXUP_ATOMIC)
-    sk_gemm_f16_kernel<SK_EPI_ATOMIC><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmRow, tmCol, Ch, p);
+    e = sk_launch(sk_gemm_f16_kernel<SK_EPI_ATOMIC>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
+                  tmRow, tmCol, Ch, p);
   else
-    sk_gemm_f16_kernel<SK_EPI_BLOCK_REDUCE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmRow, tmCol, Ch, p);
-  e = cudaGetLastError();
+    e = sk_launch(sk_gemm_f16_kernel<SK_EPI_BLOCK_REDUCE>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
+                  tmRow, tmCol, Ch, p);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

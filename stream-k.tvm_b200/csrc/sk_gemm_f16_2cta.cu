@@ -61,7 +61,10 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const int rank = static_cast<int>(cluster_ctarank());   // 0 = leader of the pair
   const int unit = blockIdx.x >> 1;                        // the pair's index in the schedule
   const SkSched& s = p.sched;
-  if (threadIdx.x == 0) sk_trace(p, 0);
+  if (threadIdx.x == 0) {
+    sk_trace(p, 0);
+    griddep_launch_dependents();   // the next kernel of the stream may begin its own start-up
+  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -91,6 +94,8 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
   if (threadIdx.x == 0) sk_trace(p, 1);
+  // global memory is the previous kernel's until it has completed (no-op without SK_FLAG_PDL)
+  griddep_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer (both CTAs)
@@ -234,20 +239,9 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(2 * p->sched.grid, 1, 1);
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, sk_gemm_f16_2cta_kernel, tmA, tmB, static_cast<__half*>(C), *p);
+  cudaError_t e = sk_launch(sk_gemm_f16_2cta_kernel, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
+                            static_cast<cudaStream_t>(stream), 2, (prob->flags & SK_FLAG_PDL) != 0, tmA, tmB,
+                            static_cast<__half*>(C), *p);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

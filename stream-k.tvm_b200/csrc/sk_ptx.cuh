@@ -287,6 +287,15 @@ __device__ __forceinline__ uint32_t atom_add_acqrel_u32(uint32_t* p, uint32_t v)
                : "memory");
   return old;
 }
+// Programmatic dependent launch (no-ops unless the kernel was launched with the attribute):
+// let the next kernel of the stream begin its start-up / wait until the previous kernel of
+// the stream has completed and its memory is visible.
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -120,7 +120,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const int kblocks = s.iters_per_tile;  // K / 64
   const int groups = kblocks >> 1;       // K / 128
   const bool swapped = p.transposed != 0;
-  if (threadIdx.x == 0) sk_trace(p, 0);
+  if (threadIdx.x == 0) {
+    sk_trace(p, 0);
+    griddep_launch_dependents();   // the next kernel of the stream may begin its own start-up
+  }
   // Split-K inside a cluster (sk_epilogue.cuh): receive buffer behind the control block,
   // staging area in the rings, which are idle by then.
   constexpr bool clustered = MODE == SK_MODE_CLUSTER;
@@ -160,6 +163,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
   if (threadIdx.x == 0) sk_trace(p, 1);
+  // global memory is the previous kernel's until it has completed (no-op without SK_FLAG_PDL)
+  griddep_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
@@ -636,34 +641,22 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
-  cudaError_t e;
-  if (split) {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(p.sched.grid);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = split;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, sk_gemm_w4a16_kernel<SK_MODE_CLUSTER>, tmA, qb, sz, static_cast<__half*>(C), p);
-    if (e != cudaSuccess) return sk_set_cuda_error(e);
-    return SK_OK;
-  }
   const cudaStream_t cs = static_cast<cudaStream_t>(stream);
   __half* Ch = static_cast<__half*>(C);
-  if (prob->schedule == SK_SCHED_DP)   // whole tiles only: no fixup code
-    sk_gemm_w4a16_kernel<SK_EPI_WHOLE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmA, qb, sz, Ch, p);
+  const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
+  cudaError_t e;
+  if (split)
+    e = sk_launch(sk_gemm_w4a16_kernel<SK_MODE_CLUSTER>, p.sched.grid, NUM_THREADS, smem_bytes, cs, split, pdl,
+                  tmA, qb, sz, Ch, p);
+  else if (prob->schedule == SK_SCHED_DP)   // whole tiles only: no fixup code
+    e = sk_launch(sk_gemm_w4a16_kernel<SK_EPI_WHOLE>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
+                  tmA, qb, sz, Ch, p);
   else if (prob->fixup == SK_FIXUP_ATOMIC)
-    sk_gemm_w4a16_kernel<SK_EPI_ATOMIC><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmA, qb, sz, Ch, p);
+    e = sk_launch(sk_gemm_w4a16_kernel<SK_EPI_ATOMIC>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
+                  tmA, qb, sz, Ch, p);
   else
-    sk_gemm_w4a16_kernel<SK_EPI_BLOCK_REDUCE><<<p.sched.grid, NUM_THREADS, smem_bytes, cs>>>(tmA, qb, sz, Ch, p);
-  e = cudaGetLastError();
+    e = sk_launch(sk_gemm_w4a16_kernel<SK_EPI_BLOCK_REDUCE>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
+                  tmA, qb, sz, Ch, p);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

@@ -98,7 +98,7 @@ def device_info(device: int = 0) -> dict:
 
 
 # --------------------------------------------------------------------------- helpers
-_OPTION_KEYS = ("tile_m", "tile_n", "num_sms", "group_m", "out", "timeout_us", "_drop_flag_cta")
+_OPTION_KEYS = ("tile_m", "tile_n", "num_sms", "group_m", "out", "timeout_us", "pdl", "_drop_flag_cta")
 
 
 def _options(kw: dict) -> dict:
@@ -106,7 +106,9 @@ def _options(kw: dict) -> dict:
     tile_m / tile_n  tile extents (None = choose; tile_m < 128 puts the weights on the UMMA
                      M dimension, the short-M form), num_sms (grid bound), group_m (tile
                      rasterisation), out (result buffer), timeout_us (bound of every device
-                     wait), _drop_flag_cta (test hook)."""
+                     wait), pdl (True: programmatic dependent launch, the kernel's start-up may
+                     overlap the tail of the previous kernel of the stream; fp16 / W4A16),
+                     _drop_flag_cta (test hook)."""
     unknown = set(kw) - set(_OPTION_KEYS)
     if unknown:
         raise TypeError(f"unexpected keyword argument(s): {sorted(unknown)}")
@@ -126,7 +128,8 @@ def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkPr
                        tile_m=int(o["tile_m"] or 0), tile_n=int(o["tile_n"] or 0),
                        num_sms=int(o["num_sms"] or 0), group_m=int(o["group_m"] or 0),
                        fixup_timeout_us=int(o["timeout_us"] or 0),
-                       test_drop_flag_cta=int(o["_drop_flag_cta"]))
+                       test_drop_flag_cta=int(o["_drop_flag_cta"]),
+                       flags=L.SK_FLAG_PDL if o["pdl"] else 0)
 
 
 def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "auto",

@@ -234,6 +234,36 @@ def test_fp16_config3_sample_of_the_sweep():
             _check(sk.streamk_fp16_nt(A, B, schedule=schedule, fixup="block_reduce"), ref, TOL16)
 
 
+def test_programmatic_dependent_launch_changes_nothing_but_timing():
+    """SK_FLAG_PDL: same bits as a plain launch, whatever runs before it in the stream (a torch
+    kernel that knows nothing of it, another launch of this library, a copy)."""
+    A, B = _rand16(48, 1000, 2056, seed=31)
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    A2, B2 = _rand16(300, 520, 1032, seed=32)
+    A2d, B2d = A2.to(DEV), B2.to(DEV)
+    c = oracle.make_case(4, shape=(16, 512, 512))
+    P = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
+    Aq = c["A"].to(DEV)
+    for schedule in ("auto", "streamk", "hybrid", "dp", "cluster"):
+        plain = sk.streamk_fp16_nt(Ad, Bd, schedule=schedule, fixup="block_reduce")
+        scratch = torch.zeros(1 << 20, device=DEV)
+        scratch.add_(1.0)                                   # a foreign kernel right before
+        a = sk.streamk_fp16_nt(Ad, Bd, schedule=schedule, fixup="block_reduce", pdl=True)
+        b = sk.streamk_fp16_nt(Ad, Bd, schedule=schedule, fixup="block_reduce", pdl=True)   # after one of ours
+        Ad2 = Ad.clone()                                    # a copy right before
+        d = sk.streamk_fp16_nt(Ad2, Bd, schedule=schedule, fixup="block_reduce", pdl=True)
+        assert torch.equal(a, plain) and torch.equal(b, plain) and torch.equal(d, plain)
+    if True:
+        plain = sk.streamk_fp16_nt(A2d, B2d, schedule="hybrid", fixup="block_reduce", tile_n=128)
+        outs = [sk.streamk_fp16_nt(A2d, B2d, schedule="hybrid", fixup="block_reduce", tile_n=128, pdl=True)
+                for _ in range(5)]
+        assert all(torch.equal(o, plain) for o in outs)
+        plain = sk.streamk_fp16_ladder_block_reduce_q4(Aq, P)
+        outs = [sk.streamk_fp16_ladder_block_reduce_q4(Aq, P, pdl=True) for _ in range(5)]
+        assert all(torch.equal(o, plain) for o in outs)
+    _check(a, oracle.gemm_ref(A, B, "nt"), TOL16)
+
+
 def test_out_argument_and_views():
     A, B = _rand16(64, 256, 256, seed=5)
     big = torch.zeros(64, 512, dtype=torch.float16, device=DEV)

@@ -37,12 +37,14 @@ def test_config5_full_size_single_gpu():
 @pytest.mark.parametrize("case", [
     ("f16", (16, 4096, 4096), "auto"), ("f16", (16, 11008, 4096), "auto"), ("f16", (256, 4096, 4096), "auto"),
     ("f16", (128, 4096, 4096), "streamk"), ("w4a16", (16, 4096, 11008), "auto"), ("w4a16", (16, 11008, 4096), "dp")])
-def test_back_to_back_launches_on_cold_weights(case):
+@pytest.mark.parametrize("pdl", [False, True])
+def test_back_to_back_launches_on_cold_weights(case, pdl):
     """Hundreds of launches without a host synchronisation in between, the weights rotating
     through more copies than the L2 holds (so loads land late and out of order, as in the
     benchmark's graph replays and unlike the small parity cases): every launch of a deterministic
     schedule must give the bits of the first, and no device wait may run out.  Guards the
-    pipeline's mbarrier phase tracking (two issuing threads, grouped dequantisation)."""
+    pipeline's mbarrier phase tracking (two issuing threads, grouped dequantisation) and, with
+    pdl, the overlap of a launch's start-up with the tail of the launch before it."""
     kind, (M, N, K), schedule = case
     g = torch.Generator(device=DEV).manual_seed(M + N)
     A = torch.randn(M, K, generator=g, device=DEV).half()
@@ -50,14 +52,15 @@ def test_back_to_back_launches_on_cold_weights(case):
     if kind == "f16":
         W0 = (0.02 * torch.randn(N, K, generator=g, device=DEV)).half()
         Ws = [W0.clone() for _ in range(copies)]
-        run = lambda i, out: sk.streamk_fp16_nt(A, Ws[i % copies], out=out, schedule=schedule, fixup="block_reduce")
+        run = lambda i, out: sk.streamk_fp16_nt(A, Ws[i % copies], out=out, schedule=schedule, fixup="block_reduce",
+                                                pdl=pdl)
     else:
         c = oracle.make_case(4, shape=(M, N, K))
         A = c["A"].to(DEV)
         P0 = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
         Ws = [P0] + [sk.PackedQ4(P0.data.clone(), N, K) for _ in range(copies - 1)]
         run = lambda i, out: sk.streamk_fp16_ladder_block_reduce_q4(A, Ws[i % copies], out=out, schedule=schedule,
-                                                                    fixup="block_reduce")
+                                                                    fixup="block_reduce", pdl=pdl)
     first = torch.empty(M, N, dtype=torch.float16, device=DEV)
     run(0, first)
     outs = [torch.empty_like(first) for _ in range(4)]
