@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory from the reference's own source.
 
-Run once in a container that has the reference checkout (default /root/reference):
+Run once where a checkout of the reference project (LeiWang1999/Stream-k.tvm) is at hand:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It executes, verbatim and on the CPU, the few self-contained host lines of the
 reference that pin behaviour on the hot path:
@@ -31,7 +31,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+REF = sys.argv[1]
 
 
 def _slice(path: str, first_marker: str, last_marker: str) -> str:
