@@ -111,6 +111,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// Ask L2 for a box of a tensor map ahead of the load proper (no completion, no destination:
+// a hint; L2 is the coherence point, so it can never make anything stale).
+__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+// Same hint for a contiguous range (16-byte aligned address, size % 16 == 0).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes)
+               : "memory");
+}
 // 1-D bulk copy global -> shared (16-byte aligned addresses, size % 16 == 0).
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
                                              uint32_t bar) {

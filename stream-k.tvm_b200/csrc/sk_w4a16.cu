@@ -158,6 +158,23 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
     tmem_relinquish();
   }
+  if (threadIdx.x == 64) {
+    // While the barriers are being set up (and, with SK_FLAG_PDL, while the previous kernel of
+    // the stream is still running) an idle thread asks L2 for the packed weights of the first
+    // stages (a hint; L2 is the coherence point, so nothing can go stale).
+    SkCursor c0;
+    sk_cursor_init(s, pid, c0);
+    SkSeg g0;
+    if (sk_next(s, pid, c0, g0)) {
+      int tr, tc;
+      sk_tile_mn(s, g0.tile, tr, tc);
+      const int nblk = swapped ? tr : tc;
+      int n = g0.k1 - g0.k0;
+      if (n > 8) n = 8;
+      bulk_prefetch_l2(qblocks + (static_cast<size_t>(nblk) * kblocks + g0.k0) * Q_BLOCK_BYTES,
+                       static_cast<uint32_t>(n) * Q_BLOCK_BYTES);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
