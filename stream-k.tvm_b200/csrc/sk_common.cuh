@@ -77,6 +77,7 @@ struct SkParams {
   int bm;                  // rows of the UMMA M side a tile covers (tile pitch): 128, or fewer when the
                            //    weight tile is fitted to the SM count (rows beyond it hold stale data)
   int prefetch_steps;      // K steps whose boxes the producers ask L2 for before the pipeline is up
+  int c_tma;               // 1: whole tiles leave through shared memory and TMA stores (tensor map of C given)
   int kpair;               // 1: a stage is the K steps of one scale group (W4A16): two, or one at an odd
                            //    start / the end of a segment; 0: kgroup K steps per stage
   int acc_b_off;           // > 0: two MMA-issuing threads take alternate stages of a segment, the second

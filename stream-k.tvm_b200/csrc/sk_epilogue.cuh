@@ -271,13 +271,60 @@ __device__ __forceinline__ void sk_load_acc(uint32_t taddr, uint32_t b_off, floa
 constexpr int SK_EPI_ANY = -1, SK_EPI_ATOMIC = SK_FIXUP_ATOMIC, SK_EPI_BLOCK_REDUCE = SK_FIXUP_BLOCK_REDUCE,
               SK_EPI_WHOLE = 2;
 
+// Staging area of the TMA-store path: per epilogue warp two buffers of 32 rows x 128 bytes
+// (64 fp16 columns, 128-byte swizzle), 1024-byte aligned.
+constexpr int SK_CSTAGE_BYTES = 4 * 2 * 4096;
+
+// Whole tile, 64 columns at a time: accumulator -> fp16 -> swizzled staging buffer -> one TMA
+// store of a 64 x 32 box per warp (full 128-byte lines, issued asynchronously), instead of
+// sixteen-byte stores to 32 different rows per instruction.  Returns the number of columns
+// handled (a multiple of 64; the rest of the tile goes through sk_store_chunk).
+__device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtensorMap* tmC, uint32_t cstage,
+                                                 int warp_slot, int lane, uint32_t t_addr, uint32_t b_off,
+                                                 int grow0, int gcol0, int valid_cols, uint32_t& groups) {
+  using namespace skptx;
+  const int full = valid_cols >> 6;
+  for (int g = 0; g < full; ++g, ++groups) {
+    const uint32_t buf = cstage + static_cast<uint32_t>(warp_slot * 2 + (groups & 1u)) * 4096u;
+    // the store issued from this buffer two groups ago must have read it
+    if (lane == 0) tma_store_wait_read<1>();
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float v[32];
+      sk_load_acc(t_addr + g * 64 + h * 32, b_off, v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
+        __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
+        __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
+        __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
+        const uint32_t chunk = static_cast<uint32_t>(h * 4 + j);   // 16-byte chunk of the 128-byte row
+        const uint32_t a = buf + static_cast<uint32_t>(lane) * 128u + ((chunk ^ (static_cast<uint32_t>(lane) & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
+                     "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                     "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+                     : "memory");
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tmC, buf, gcol0 + g * 64, grow0);
+      tma_store_commit();
+    }
+  }
+  return full * 64;
+}
+
 template <int MODE = SK_EPI_ANY>
 __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __restrict__ C, int pid,
                                                  int rank, int warp, int lane, uint32_t tmem_base,
                                                  uint32_t tmem_full_bar, uint32_t tmem_empty_bar,
                                                  volatile uint32_t* bcast,
                                                  volatile uint32_t* abort_flag,
-                                                 SkPending* pend_out) {
+                                                 SkPending* pend_out,
+                                                 const CUtensorMap* tmC = nullptr, uint32_t cstage = 0) {
   using namespace skptx;
   constexpr int BM = SK_BM;
   constexpr int EPI_THREADS = SK_EPI_THREADS;
@@ -290,6 +337,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
   sk_cursor_init(s, pid, cur);
   SkSeg seg;
   uint32_t nseg = 0;
+  uint32_t tma_groups = 0;   // TMA store groups this warp has issued
   bool dead = false;
   SkPending head{-1, 0, 0}, tail{-1, 0, 0};
   while (sk_next(s, pid, cur, seg)) {
@@ -329,8 +377,12 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
 
     // two MMA issuers: the second one's accumulator holds every other stage of the segment
     const bool two = sk_second_acc_used(p, seg.k0, seg.k1);
+    int c_first = 0;   // first 32-column chunk that still has to go through the register path
+    if (whole && p.c_tma && cstage != 0 && warp_ok && !dead)
+      c_first = sk_store_tile_tma(p, tmC, cstage, (warp - 2) & 3, lane, t_addr, two ? p.acc_b_off : 0,
+                                  r0 + q * 32, c0, valid_cols, tma_groups) >> 5;
     if (warp_ok && !dead) {
-      for (int c = 0; c < nchunks; ++c) {
+      for (int c = c_first; c < nchunks; ++c) {
         float v[32];
         sk_load_acc(t_addr + c * 32, two ? p.acc_b_off : 0, v);
         if (!row_ok) continue;
@@ -410,6 +462,8 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
       pd.tile = seg.tile; pd.first = first; pd.last = last;
     }
   }
+  // the staging buffers must outlive the stores that read them
+  if (p.c_tma && cstage != 0 && lane == 0) tma_store_wait_read<0>();
   if (etid == 0) {
     sk_trace(p, 6);
     pend_out[0] = tail;   // reduced by the whole CTA once every role is done

@@ -77,7 +77,7 @@ constexpr int SK_MODE_CLUSTER = 3;   // besides SK_EPI_ATOMIC, SK_EPI_BLOCK_REDU
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_constant__ CUtensorMap tmCol,
-                   __half* __restrict__ C, const SkParams p) {
+                   const __grid_constant__ CUtensorMap tmC, __half* __restrict__ C, const SkParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -325,7 +325,8 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
                       sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
     else
       sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                             smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
+                             smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend, &tmC,
+                             p.c_tma ? smem_u32(ctrl) + 1024u : 0u);   // staging behind the control block
   }
 
   // ------------------------------------------------------------- teardown
@@ -493,7 +494,10 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   p.trace = sk_trace_buffer();
   if (pairs) return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
   const int split = p.sched.split;   // SK_SCHED_CLUSTER: CTAs per tile
-  const int recv_bytes = split ? sk_cluster_recv_bytes(plan.bn, split) : 0;
+  // Whole tiles of a row-major C leave through shared memory and TMA stores (not the
+  // transposed store of the swapped order, not the cluster schedule's reduction).
+  p.c_tma = (!plan.swap && !split && p.c_vec_ok) ? 1 : 0;
+  const int recv_bytes = split ? sk_cluster_recv_bytes(plan.bn, split) : p.c_tma ? 512 + SK_CSTAGE_BYTES : 0;
   p.cl_per = split ? sk_cluster_quads_per_cta(plan.bn, split) : 1;
   p.cl_per_div = sk_div_make(p.cl_per);
   sk_fill_tile_params(&p, plan.bn, ROW_STAGE_BYTES, MAX_STAGES, recv_bytes, true);
@@ -536,6 +540,12 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
     p.row_img = B;
   }
   if (st != SK_OK) return st;
+  CUtensorMap tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  if (p.c_tma) {
+    st = sk_make_tmap_f16(&tmC, C, M, N, prob->ldc, 64, 32);
+    if (st != SK_OK) return st;
+  }
   p.row_tx_bytes = plan.bm * BK * 2;   // the TMA box of the M-side operand has plan.bm rows
   p.col_tx_bytes = p.col_stage_bytes;
   p.idesc = umma_idesc_f16(BM, plan.bn, 0) |
@@ -572,16 +582,16 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   cudaError_t e;
   if (split)
     e = sk_launch(sk_gemm_f16_kernel<SK_MODE_CLUSTER>, p.sched.grid, NUM_THREADS, smem_bytes, cs, split, pdl,
-                  tmRow, tmCol, Ch, p);
+                  tmRow, tmCol, tmC, Ch, p);
   else if (prob->schedule == SK_SCHED_DP)   // whole tiles only: no fixup code
     e = sk_launch(sk_gemm_f16_kernel<SK_EPI_WHOLE>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
-                  tmRow, tmCol, Ch, p);
+                  tmRow, tmCol, tmC, Ch, p);
   else if (prob->fixup == SK_FIXUP_ATOMIC)
     e = sk_launch(sk_gemm_f16_kernel<SK_EPI_ATOMIC>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
-                  tmRow, tmCol, Ch, p);
+                  tmRow, tmCol, tmC, Ch, p);
   else
     e = sk_launch(sk_gemm_f16_kernel<SK_EPI_BLOCK_REDUCE>, p.sched.grid, NUM_THREADS, smem_bytes, cs, 1, pdl,
-                  tmRow, tmCol, Ch, p);
+                  tmRow, tmCol, tmC, Ch, p);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

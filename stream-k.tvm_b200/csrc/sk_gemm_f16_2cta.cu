@@ -29,7 +29,8 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int PIPE_BYTES = STAGES * KG * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int CTRL_BYTES = 512;
-constexpr int SMEM_BYTES = PIPE_BYTES + 1024 + CTRL_BYTES;
+constexpr int SMEM_BYTES = PIPE_BYTES + 1024 + CTRL_BYTES + 512 + SK_CSTAGE_BYTES;   // ... + TMA-store staging
+static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
 struct Ctrl {
   uint64_t full[STAGES];      // used in the leader CTA: both CTAs' loads complete here
@@ -46,7 +47,7 @@ static_assert(sizeof(Ctrl) <= CTRL_BYTES, "Ctrl must fit its reserved space");
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        __half* __restrict__ C, const SkParams p) {
+                        const __grid_constant__ CUtensorMap tmC, __half* __restrict__ C, const SkParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -186,7 +187,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     // ------------------------------------------------------------- epilogue (both CTAs)
     sk_epilogue_loop(p, C, unit, rank, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
                      mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0), &ctrl->bcast, abort_flag,
-                     ctrl->pend);
+                     ctrl->pend, &tmC, p.c_tma ? smem_u32(ctrl) + 1024u : 0u);
   }
 
   // ------------------------------------------------------------- teardown
@@ -222,6 +223,10 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   int st = sk_make_tmap_f16(&tmA, A, prob->M, prob->K, prob->lda, BK, BM);
   if (st != SK_OK) return st;
   st = sk_make_tmap_f16(&tmB, B, prob->N, prob->K, prob->ldb, BK, BN / 2);
+  CUtensorMap tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  p->c_tma = p->c_vec_ok;   // whole tiles leave through shared memory and TMA stores
+  if (st == SK_OK && p->c_tma) st = sk_make_tmap_f16(&tmC, C, prob->M, prob->N, prob->ldc, 64, 32);
   if (st != SK_OK) return st;
   p->unit_ctas = 2;
   p->bn = BN;
@@ -241,7 +246,7 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   }
   cudaError_t e = sk_launch(sk_gemm_f16_2cta_kernel, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
                             static_cast<cudaStream_t>(stream), 2, (prob->flags & SK_FLAG_PDL) != 0, tmA, tmB,
-                            static_cast<__half*>(C), *p);
+                            tmC, static_cast<__half*>(C), *p);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

@@ -111,6 +111,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// 2-D tiled store shared -> global (bulk-group completion).  Coordinates must not be negative;
+// what lies outside the tensor is not written.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Wait until all but the N most recent store groups of this thread have read their source.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 // Ask L2 for a box of a tensor map ahead of the load proper (no completion, no destination:
 // a hint; L2 is the coherence point, so it can never make anything stale).
 __device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
