@@ -251,6 +251,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   sc.sk_f = static_cast<int>(split ? I / split : S / grid);
   sc.sk_r = static_cast<int>(split ? I % split : S % grid);
   sc.split = split;
+  sc.wide_base = -1;
   sc.dp_first = p->schedule == SK_SCHED_HYBRID_DP_FIRST ? 1 : 0;
   sc.group_m = gm;
   sk_sched_finish(sc);
@@ -296,6 +297,7 @@ static SkSched sched_from_info(const sk_schedule_info* i) {
   s.sk_f = i->sk_iters_per_cta; s.sk_r = i->sk_iters_rem; s.dp_first = i->dp_first;
   s.group_m = i->group_m;
   s.split = i->cluster;
+  s.wide_base = -1;
   sk_sched_finish(s);
   return s;
 }

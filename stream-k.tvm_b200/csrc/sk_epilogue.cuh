@@ -324,7 +324,8 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
                                                  volatile uint32_t* bcast,
                                                  volatile uint32_t* abort_flag,
                                                  SkPending* pend_out,
-                                                 const CUtensorMap* tmC = nullptr, uint32_t cstage = 0) {
+                                                 const CUtensorMap* tmC = nullptr, uint32_t cstage = 0,
+                                                 uint32_t* nseg_out = nullptr) {
   using namespace skptx;
   constexpr int BM = SK_BM;
   constexpr int EPI_THREADS = SK_EPI_THREADS;
@@ -464,6 +465,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
   }
   // the staging buffers must outlive the stores that read them
   if (p.c_tma && cstage != 0 && lane == 0) tma_store_wait_read<0>();
+  if (nseg_out) *nseg_out = nseg;   // (a caller that goes on using the accumulator buffers)
   if (etid == 0) {
     sk_trace(p, 6);
     pend_out[0] = tail;   // reduced by the whole CTA once every role is done

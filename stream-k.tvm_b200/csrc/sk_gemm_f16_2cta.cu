@@ -32,9 +32,17 @@ constexpr int CTRL_BYTES = 512;
 constexpr int SMEM_BYTES = PIPE_BYTES + 1024 + CTRL_BYTES + 512 + SK_CSTAGE_BYTES;   // ... + TMA-store staging
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
+// Wide units (256 x 512: two column-adjacent tiles that share every A stage, one accumulator
+// buffer each): a ring of its own in the same shared memory, one K step per stage.
+constexpr int WSTAGES = 4;
+constexpr int W_STAGE_BYTES = A_STAGE_BYTES + 2 * B_STAGE_BYTES;   // 48 KB: A | B of half 0 | B of half 1
+static_assert(WSTAGES * W_STAGE_BYTES <= PIPE_BYTES, "the wide ring lives in the pipeline's memory");
+
 struct Ctrl {
   uint64_t full[STAGES];      // used in the leader CTA: both CTAs' loads complete here
   uint64_t empty[STAGES];     // one per CTA, released by the leader's multicast commit
+  uint64_t fullw[WSTAGES];    // the same pair for the wide ring
+  uint64_t emptyw[WSTAGES];
   uint64_t tmem_full[2];      // one per CTA, multicast commit
   uint64_t tmem_empty[2];     // used in the leader CTA: 8 arrivals (4 epilogue warps x 2 CTAs)
   uint32_t tmem_base;
@@ -71,6 +79,10 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(smem_u32(&ctrl->full[i]), 1);
       mbar_init(smem_u32(&ctrl->empty[i]), 1);
+    }
+    for (int i = 0; i < WSTAGES; ++i) {
+      mbar_init(smem_u32(&ctrl->fullw[i]), 1);
+      mbar_init(smem_u32(&ctrl->emptyw[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
@@ -133,6 +145,36 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           if (!traced) { sk_trace(p, 2); traced = true; }
         }
       }
+      if (ok && p.wide_units > 0) {
+        // ---- wide units.  First let the tiles' last stages drain: the wide ring reuses their memory.
+        for (int i = 0; i < STAGES && ok; ++i) {
+          ok = sk_wait_bar(empty0 + 8u * stage, ph ^ 1u, abort_flag, p, stage, 0);
+          if (++stage == STAGES) { stage = 0; ph ^= 1u; }
+        }
+        const uint32_t fullw0_leader = mapa_shared(smem_u32(&ctrl->fullw[0]), 0);
+        const uint32_t fullw0 = smem_u32(&ctrl->fullw[0]), emptyw0 = smem_u32(&ctrl->emptyw[0]);
+        int ws = 0;
+        uint32_t wph = 0;
+        for (int u = unit; ok && u < p.wide_units; u += s.grid) {
+          int tm, tnw;
+          sk_raster_mn(s, u, tm, tnw);
+          const int a_row0 = (tm * 2 + rank) * BM;
+          const int b_row0 = tnw * (2 * BN) + rank * (BN / 2);   // half 0; half 1 is BN rows further
+          for (int k = 0; k < s.iters_per_tile; ++k) {
+            if (!sk_wait_bar(emptyw0 + 8u * ws, wph ^ 1u, abort_flag, p, 8 + ws, 0)) {
+              ok = false;
+              break;
+            }
+            const uint32_t dst = base + ws * W_STAGE_BYTES;
+            const uint32_t full_leader = fullw0_leader + 8u * ws;
+            if (rank == 0) mbar_arrive_expect_tx(fullw0 + 8u * ws, 2 * W_STAGE_BYTES);
+            tma_load_2d_pair(dst, &tmA, full_leader, k * BK, a_row0);
+            tma_load_2d_pair(dst + A_STAGE_BYTES, &tmB, full_leader, k * BK, b_row0);
+            tma_load_2d_pair(dst + A_STAGE_BYTES + B_STAGE_BYTES, &tmB, full_leader, k * BK, b_row0 + BN);
+            if (++ws == WSTAGES) { ws = 0; wph ^= 1u; }
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (leader only)
@@ -181,13 +223,100 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         umma_commit_pair(smem_u32(&ctrl->tmem_full[buf]));   // accumulator ready in both CTAs
         ++nseg;
       }
+      if (ok && p.wide_units > 0) {
+        // ---- wide units: every A stage feeds two accumulators (25 % fewer bytes into the SM
+        // per flop, which is what bounds this kernel and what costs it power)
+        const uint32_t fullw0 = smem_u32(&ctrl->fullw[0]), emptyw0 = smem_u32(&ctrl->emptyw[0]);
+        const uint32_t w_lo0 = umma_desc_lo(base);
+        int ws = 0;
+        uint32_t wph = 0;
+        for (int u = unit; ok && u < p.wide_units; u += s.grid) {
+          const uint32_t buf0 = nseg & 1u, buf1 = buf0 ^ 1u;
+          if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf0]), ((nseg >> 1) & 1u) ^ 1u, abort_flag, p, 16 + buf0, 1) ||
+              !sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf1]), (((nseg + 1) >> 1) & 1u) ^ 1u, abort_flag, p, 16 + buf1, 1)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d0 = tmem_base + buf0 * BN, d1 = tmem_base + buf1 * BN;
+          uint32_t accumulate = 0u;
+          for (int k = 0; k < s.iters_per_tile; ++k) {
+            if (!sk_wait_bar(fullw0 + 8u * ws, wph, abort_flag, p, 40 + ws, 1)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_lo = w_lo0 + ws * (W_STAGE_BYTES >> 4);
+            const uint32_t b0_lo = a_lo + (A_STAGE_BYTES >> 4), b1_lo = b0_lo + (B_STAGE_BYTES >> 4);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)
+              umma_f16_ss_pair(d0, desc_hi | (a_lo + kk * 2), desc_hi | (b0_lo + kk * 2), idesc, kk ? 1u : accumulate);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk)
+              umma_f16_ss_pair(d1, desc_hi | (a_lo + kk * 2), desc_hi | (b1_lo + kk * 2), idesc, kk ? 1u : accumulate);
+            accumulate = 1u;
+            umma_commit_pair(emptyw0 + 8u * ws);
+            if (++ws == WSTAGES) { ws = 0; wph ^= 1u; }
+          }
+          if (!ok) break;
+          umma_commit_pair(smem_u32(&ctrl->tmem_full[buf0]));
+          umma_commit_pair(smem_u32(&ctrl->tmem_full[buf1]));
+          nseg += 2;
+        }
+      }
       sk_trace(p, 4);
     }
   } else {
     // ------------------------------------------------------------- epilogue (both CTAs)
-    sk_epilogue_loop(p, C, unit, rank, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
-                     mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0), &ctrl->bcast, abort_flag,
-                     ctrl->pend, &tmC, p.c_tma ? smem_u32(ctrl) + 1024u : 0u);
+    const uint32_t cstage = p.c_tma ? smem_u32(ctrl) + 1024u : 0u;
+    const uint32_t tmem_full0 = smem_u32(&ctrl->tmem_full[0]);
+    const uint32_t tmem_empty0 = mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0);
+    uint32_t nseg = 0;
+    sk_epilogue_loop(p, C, unit, rank, warp, lane, tmem_base, tmem_full0, tmem_empty0, &ctrl->bcast,
+                     abort_flag, ctrl->pend, &tmC, cstage, &nseg);
+    if (p.wide_units > 0) {
+      // ---- wide units: the two halves are two whole tiles in the two accumulator buffers
+      const int q = warp & 3;
+      const int row = q * 32 + lane;
+      uint32_t groups = 0;
+      bool dead = false;
+      for (int u = unit; u < p.wide_units; u += s.grid) {
+        int tm, tnw;
+        sk_raster_mn(s, u, tm, tnw);
+        const int r0 = (tm * 2 + rank) * BM;
+        const bool row_ok = r0 + row < p.rows;
+        const bool warp_ok = r0 + q * 32 < p.rows;
+        for (int h = 0; h < 2; ++h, ++nseg) {
+          const uint32_t buf = nseg & 1u;
+          if (!dead) {
+            const bool got = sk_wait_bar(tmem_full0 + 8u * buf, (nseg >> 1) & 1u, abort_flag, p, 24 + buf, 2);
+            if (!__all_sync(0xffffffffu, got)) dead = true;
+          }
+          tc_fence_after();
+          const int c0 = (2 * tnw + h) * BN;
+          int valid_cols = p.cols - c0;
+          if (valid_cols > BN) valid_cols = BN;
+          const uint32_t t_addr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+          if (warp_ok && !dead && valid_cols > 0) {
+            int c_first = 0;
+            if (cstage != 0)
+              c_first = sk_store_tile_tma(p, &tmC, cstage, (warp - 2) & 3, lane, t_addr, 0, r0 + q * 32, c0,
+                                          valid_cols, groups) >> 5;
+            for (int c = c_first; c < ((valid_cols + 31) >> 5); ++c) {
+              float v[32];
+              sk_load_acc(t_addr + c * 32, 0, v);
+              int nv = valid_cols - c * 32;
+              if (nv > 32) nv = 32;
+              if (row_ok) sk_store_chunk(C, p, r0 + row, c0 + c * 32, nv, v);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tmem_empty0 + 8u * buf);
+        }
+      }
+      if (cstage != 0 && lane == 0) tma_store_wait_read<0>();
+    }
   }
 
   // ------------------------------------------------------------- teardown
@@ -229,6 +358,32 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   if (st == SK_OK && p->c_tma) st = sk_make_tmap_f16(&tmC, C, prob->M, prob->N, prob->ldc, 64, 32);
   if (st != SK_OK) return st;
   p->unit_ctas = 2;
+  // Wide units: under the hybrid schedule with the library's own tile choice, as many full
+  // waves of 256 x 512 units (two column-adjacent tiles sharing their A stages) as fit are
+  // walked whole, one per pair and wave, after the Stream-K part, which takes the halves of the
+  // remaining units (sk_tile_mn, wide_base).
+  p->wide_units = 0;
+  {
+    SkSched& sc = p->sched;
+    const int pairs = sc.grid;
+    if (prob->schedule == SK_SCHED_HYBRID && prob->tile_m == 0 && (sc.tiles_n & 1) == 0 && sc.split == 0) {
+      const long long all_units = static_cast<long long>(sc.tiles_m) * (sc.tiles_n / 2);
+      const long long U = all_units / pairs * pairs;
+      if (U > 0) {
+        const long long rest = static_cast<long long>(sc.total_tiles) - 2 * U;
+        const long long S = rest * sc.iters_per_tile;
+        sc.tiles_n /= 2;
+        sc.total_tiles = static_cast<int>(rest);
+        sc.sk_tiles = static_cast<int>(rest);
+        sc.sk_f = static_cast<int>(S / pairs);
+        sc.sk_r = static_cast<int>(S % pairs);
+        sc.dp_first = 0;
+        sc.wide_base = static_cast<int>(U);
+        sk_sched_finish(sc);
+        p->wide_units = static_cast<int>(U);
+      }
+    }
+  }
   p->bn = BN;
   p->acc_stride = BN;
   p->tmem_cols = TMEM_COLS;

@@ -53,6 +53,7 @@ struct SkSched {
   int split;      // > 0: every tile is split over the `split` CTAs of one thread-block cluster
                   //      (grid = total_tiles * split), CTA r of the cluster walking K iterations
                   //      [r*I/split, (r+1)*I/split) of its tile; 0: the Stream-K interval rule
+  int wide_base;  // >= 0: see sk_tile_mn; -1: tiles are rasterised directly
   // derived by sk_sched_finish()
   int split_log2; // split is a power of two
   SkDiv d_ipt;    // / iters_per_tile
@@ -114,7 +115,7 @@ SK_HD int sk_cta_of(const SkSched& s, int i) {
 // Tile id -> tile coordinates.  group_m == 1 is the reference's row-major order
 // (streamk_fp16.py:192-193); group_m > 1 walks column-major inside bands of
 // group_m tile rows so that a wave of CTAs shares A and B panels in L2.
-SK_HD void sk_tile_mn(const SkSched& s, int tile, int& tm, int& tn) {
+SK_HD void sk_raster_mn(const SkSched& s, int tile, int& tm, int& tn) {
   if (s.group_m <= 1) {
     tm = sk_div(tile, s.d_tn);
     tn = tile - tm * s.tiles_n;
@@ -128,6 +129,19 @@ SK_HD void sk_tile_mn(const SkSched& s, int tile, int& tm, int& tn) {
   const int in_g = tile - g * (s.group_m * s.tiles_n);
   tn = sk_div(in_g, full ? s.d_gm : s.d_glast);
   tm = first_m + (in_g - tn * gsize);
+}
+
+// Tile id of the schedule -> tile coordinates.  With wide_base >= 0 (CTA-pair kernel, see
+// sk_gemm_f16_2cta.cu) the rasterised grid is one of UNITS two tiles wide, its first wide_base
+// units are walked whole by another part of the kernel, and the schedule's tiles are the halves
+// of the remaining units: tile t = half t & 1 of unit wide_base + t / 2.
+SK_HD void sk_tile_mn(const SkSched& s, int tile, int& tm, int& tn) {
+  if (s.wide_base < 0) {
+    sk_raster_mn(s, tile, tm, tn);
+    return;
+  }
+  sk_raster_mn(s, s.wide_base + (tile >> 1), tm, tn);
+  tn = 2 * tn + (tile & 1);
 }
 
 SK_HD void sk_cursor_init(const SkSched& s, int pid, SkCursor& c) {
