@@ -232,31 +232,63 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         uint32_t wph = 0;
         for (int u = unit; ok && u < p.wide_units; u += s.grid) {
           const uint32_t buf0 = nseg & 1u, buf1 = buf0 ^ 1u;
-          if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf0]), ((nseg >> 1) & 1u) ^ 1u, abort_flag, p, 16 + buf0, 1) ||
-              !sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf1]), (((nseg + 1) >> 1) & 1u) ^ 1u, abort_flag, p, 16 + buf1, 1)) {
+          const uint32_t empty1 = smem_u32(&ctrl->tmem_empty[buf1]);
+          const uint32_t empty1_ph = (((nseg + 1) >> 1) & 1u) ^ 1u;
+          if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf0]), ((nseg >> 1) & 1u) ^ 1u, abort_flag, p, 16 + buf0, 1)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t d0 = tmem_base + buf0 * BN, d1 = tmem_base + buf1 * BN;
-          uint32_t accumulate = 0u;
-          for (int k = 0; k < s.iters_per_tile; ++k) {
-            if (!sk_wait_bar(fullw0 + 8u * ws, wph, abort_flag, p, 40 + ws, 1)) {
-              ok = false;
-              break;
+          // The epilogue drains the first half's buffer, then the second's.  The first half
+          // starts as soon as its buffer is free and may run up to WSTAGES - 1 K steps ahead of
+          // the second (the stages stay held until the second half has read them too), so the
+          // second buffer's drain overlaps the start of this unit.
+          const int I = s.iters_per_tile;
+          int k0 = 0, k1 = 0;          // next K step of the first / second half
+          int ws1 = ws;                // stage of K step k1 (ws is the stage of k0)
+          bool h1_ready = false;
+          while (ok && k1 < I) {
+            // (once the second half may run it first catches up: a held stage is a stage the
+            // producer cannot refill)
+            if (k0 < I && (h1_ready ? k0 == k1 : k0 - k1 < WSTAGES - 1)) {
+              if (!sk_wait_bar(fullw0 + 8u * ws, wph, abort_flag, p, 40 + ws, 1)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const uint32_t a_lo = w_lo0 + ws * (W_STAGE_BYTES >> 4);
+              const uint32_t b_lo = a_lo + (A_STAGE_BYTES >> 4);
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma_f16_ss_pair(d0, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc,
+                                 (k0 | kk) ? 1u : 0u);
+              ++k0;
+              if (++ws == WSTAGES) { ws = 0; wph ^= 1u; }
             }
-            tc_fence_after();
-            const uint32_t a_lo = w_lo0 + ws * (W_STAGE_BYTES >> 4);
-            const uint32_t b0_lo = a_lo + (A_STAGE_BYTES >> 4), b1_lo = b0_lo + (B_STAGE_BYTES >> 4);
+            if (!h1_ready) {
+              if (mbar_try_wait(empty1, empty1_ph, 0u)) {
+                h1_ready = true;
+              } else if (k0 == I || k0 - k1 >= WSTAGES - 1) {   // cannot run further ahead: wait
+                if (!sk_wait_bar(empty1, empty1_ph, abort_flag, p, 16 + buf1, 1)) {
+                  ok = false;
+                  break;
+                }
+                h1_ready = true;
+              }
+              if (h1_ready) tc_fence_after();
+            }
+            if (h1_ready && k1 < k0) {
+              const uint32_t a_lo = w_lo0 + ws1 * (W_STAGE_BYTES >> 4);
+              const uint32_t b_lo = a_lo + ((A_STAGE_BYTES + B_STAGE_BYTES) >> 4);
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk)
-              umma_f16_ss_pair(d0, desc_hi | (a_lo + kk * 2), desc_hi | (b0_lo + kk * 2), idesc, kk ? 1u : accumulate);
-#pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk)
-              umma_f16_ss_pair(d1, desc_hi | (a_lo + kk * 2), desc_hi | (b1_lo + kk * 2), idesc, kk ? 1u : accumulate);
-            accumulate = 1u;
-            umma_commit_pair(emptyw0 + 8u * ws);
-            if (++ws == WSTAGES) { ws = 0; wph ^= 1u; }
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma_f16_ss_pair(d1, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc,
+                                 (k1 | kk) ? 1u : 0u);
+              umma_commit_pair(emptyw0 + 8u * ws1);   // both halves have read the stage
+              ++k1;
+              if (++ws1 == WSTAGES) ws1 = 0;
+            }
           }
           if (!ok) break;
           umma_commit_pair(smem_u32(&ctrl->tmem_full[buf0]));
