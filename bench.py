@@ -475,7 +475,7 @@ def main() -> None:
                 "peak_source": f"{peaks['source']} {peak_key}",
                 "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
                 "frac_of_nominal_2250": achieved / NOMINAL_TFLOPS,
-                "kernel": "sk_gemm_f16_2cta_kernel (256x256x64 tiles, CTA pairs)"}
+                "kernel": "sk_gemm_f16_2cta_kernel (CTA pairs; 256x256x64 tiles, data-parallel part in 256x512 units)"}
 
     cpu_baseline = None
     if world == 1:
@@ -497,6 +497,7 @@ def main() -> None:
                    + (" (auto)" if args.schedule == "auto" else ""),
                    "fixup": args.fixup, "tile": [info["tile_m"], info["tile_n"], 64],
                    "sk_tiles": info["sk_tiles"], "dp_tiles": info["dp_tiles"],
+                   "dp_units_256x512": info["wide_units"],
                    "l2": "operands (>= 0.25 GB per GPU) exceed the 126 MB L2; no flush needed"},
         "per_gpu_tflops": value / world,
         "roofline": roofline, "cpu_baseline": cpu_baseline,

@@ -108,6 +108,10 @@ typedef struct sk_schedule_info {
   int32_t swap_ab;             /* 1: weights feed the UMMA M dimension          */
   int32_t schedule;            /* the schedule used (SK_SCHED_AUTO resolved)    */
   int32_t cluster;             /* SK_SCHED_CLUSTER: CTAs per tile; else 0       */
+  int32_t wide_units;          /* CTA-pair kernel, hybrid schedule: the dp_tiles are walked as
+                                  this many units of two column-adjacent tiles (the first
+                                  wide_units units of the rasterised tiles_m x tiles_n/2 grid);
+                                  Stream-K tile t is then half t & 1 of unit wide_units + t/2  */
 } sk_schedule_info;
 
 typedef struct sk_device_info {

@@ -31,7 +31,7 @@ class SkScheduleInfo(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "tile_m", "tile_n", "tile_k", "tiles_m", "tiles_n", "total_tiles", "iters_per_tile",
         "sk_tiles", "dp_tiles", "grid", "sk_iters_per_cta", "sk_iters_rem", "dp_waves",
-        "dp_first", "group_m", "swap_ab", "schedule", "cluster")]
+        "dp_first", "group_m", "swap_ab", "schedule", "cluster", "wide_units")]
 
     def as_dict(self) -> dict:
         return {n: getattr(self, n) for n, _ in self._fields_}

@@ -254,6 +254,28 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   sc.wide_base = -1;
   sc.dp_first = p->schedule == SK_SCHED_HYBRID_DP_FIRST ? 1 : 0;
   sc.group_m = gm;
+  long long wide_units = 0;
+  if (kernel_kind == 3 && p->schedule == SK_SCHED_HYBRID && p->tile_m == 0 && (tiles_c & 1) == 0 &&
+      grid == P) {
+    // CTA pairs, hybrid schedule, the library's own tile choice: the data-parallel part is
+    // walked in units of two column-adjacent tiles that share every A stage (25 % fewer bytes
+    // into an SM per flop).  As many full waves of such 256 x 512 units as fit are taken from
+    // the front of the rasterised grid of units; the Stream-K part walks the halves of the
+    // remaining units (sk_tile_mn, wide_base) — fewer tiles than the reference's two-tile rule
+    // would give it, because a unit is two tiles.
+    wide_units = tiles_r * (tiles_c / 2) / P * P;
+    if (wide_units > 0) {
+      const long long rest = total - 2 * wide_units;
+      const long long Sw = rest * I;
+      sc.tiles_n = static_cast<int>(tiles_c / 2);
+      sc.total_tiles = static_cast<int>(rest);
+      sc.sk_tiles = static_cast<int>(rest);
+      sc.sk_f = static_cast<int>(Sw / P);
+      sc.sk_r = static_cast<int>(Sw % P);
+      sc.wide_base = static_cast<int>(wide_units);
+      T = rest;
+    }
+  }
   sk_sched_finish(sc);
   if (s) *s = sc;
   if (plan_out) *plan_out = plan;
@@ -263,12 +285,13 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
     info->tile_n = plan.swap ? tr : plan.bn;
     info->tile_k = tk;
     info->tiles_m = plan.swap ? sc.tiles_n : sc.tiles_m;
-    info->tiles_n = plan.swap ? sc.tiles_m : sc.tiles_n;
-    info->total_tiles = sc.total_tiles; info->iters_per_tile = sc.iters_per_tile;
-    info->sk_tiles = sc.sk_tiles; info->dp_tiles = static_cast<int>(dp);
+    info->tiles_n = plan.swap ? sc.tiles_m : static_cast<int>(tiles_c);
+    info->total_tiles = static_cast<int>(total); info->iters_per_tile = sc.iters_per_tile;
+    info->sk_tiles = sc.sk_tiles; info->dp_tiles = static_cast<int>(total - T);
+    info->wide_units = static_cast<int>(wide_units);
     info->grid = sc.grid;
     info->sk_iters_per_cta = sc.sk_f; info->sk_iters_rem = sc.sk_r;
-    info->dp_waves = static_cast<int>((dp + grid - 1) / grid);
+    info->dp_waves = wide_units ? static_cast<int>(wide_units / grid) : static_cast<int>((dp + grid - 1) / grid);
     info->dp_first = sc.dp_first;
     info->group_m = gm;
     info->cluster = split;
@@ -298,6 +321,11 @@ static SkSched sched_from_info(const sk_schedule_info* i) {
   s.group_m = i->group_m;
   s.split = i->cluster;
   s.wide_base = -1;
+  if (i->wide_units > 0) {   // CTA pairs: the schedule's tiles are halves of units two tiles wide
+    s.tiles_n = i->tiles_n / 2;
+    s.total_tiles = i->sk_tiles;
+    s.wide_base = i->wide_units;
+  }
   sk_sched_finish(s);
   return s;
 }

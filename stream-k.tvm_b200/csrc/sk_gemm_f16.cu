@@ -459,7 +459,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   const bool pairs = prob->schedule != SK_SCHED_CLUSTER && use_cta_pairs(prob, num_sms);
   if (pairs) {
     sk_problem q = *prob;
-    q.tile_m = 0; q.tile_n = 0;
+    q.tile_n = 0;   // (tile_m stays: 256 = asked for by the caller, 0 = the library's own choice)
     st = sk_make_sched(&q, 3, num_sms / 2, nullptr, &p.sched, &plan);
   } else {
     st = sk_make_sched(prob, 1, num_sms, nullptr, &p.sched, &plan);

@@ -390,32 +390,9 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   if (st == SK_OK && p->c_tma) st = sk_make_tmap_f16(&tmC, C, prob->M, prob->N, prob->ldc, 64, 32);
   if (st != SK_OK) return st;
   p->unit_ctas = 2;
-  // Wide units: under the hybrid schedule with the library's own tile choice, as many full
-  // waves of 256 x 512 units (two column-adjacent tiles sharing their A stages) as fit are
-  // walked whole, one per pair and wave, after the Stream-K part, which takes the halves of the
-  // remaining units (sk_tile_mn, wide_base).
-  p->wide_units = 0;
-  {
-    SkSched& sc = p->sched;
-    const int pairs = sc.grid;
-    if (prob->schedule == SK_SCHED_HYBRID && prob->tile_m == 0 && (sc.tiles_n & 1) == 0 && sc.split == 0) {
-      const long long all_units = static_cast<long long>(sc.tiles_m) * (sc.tiles_n / 2);
-      const long long U = all_units / pairs * pairs;
-      if (U > 0) {
-        const long long rest = static_cast<long long>(sc.total_tiles) - 2 * U;
-        const long long S = rest * sc.iters_per_tile;
-        sc.tiles_n /= 2;
-        sc.total_tiles = static_cast<int>(rest);
-        sc.sk_tiles = static_cast<int>(rest);
-        sc.sk_f = static_cast<int>(S / pairs);
-        sc.sk_r = static_cast<int>(S % pairs);
-        sc.dp_first = 0;
-        sc.wide_base = static_cast<int>(U);
-        sk_sched_finish(sc);
-        p->wide_units = static_cast<int>(U);
-      }
-    }
-  }
+  // Wide units (256 x 512, two column-adjacent tiles sharing every A stage): decided by the host
+  // scheduler (sk_make_sched), which leaves their count in wide_base.
+  p->wide_units = p->sched.wide_base > 0 ? p->sched.wide_base : 0;
   p->bn = BN;
   p->acc_stride = BN;
   p->tmem_cols = TMEM_COLS;

@@ -27,7 +27,7 @@ def test_binding_table_matches_header():
 def test_struct_sizes(lib):
     from streamk_b200 import _lib as L
     assert C.sizeof(L.SkProblem) == 16 * 4
-    assert C.sizeof(L.SkScheduleInfo) == 18 * 4
+    assert C.sizeof(L.SkScheduleInfo) == 19 * 4
     assert C.sizeof(L.SkStatus) == 16
 
 

@@ -70,3 +70,29 @@ def test_back_to_back_launches_on_cold_weights(case, pdl):
     sk.check_status()
     for o in outs:
         assert torch.equal(o, first)
+
+
+@pytest.mark.parametrize("shape", [(1024, 10240, 512), (1100, 10000, 520), (2048, 9728, 320), (512, 37888, 128)])
+def test_pair_kernel_wide_units(shape):
+    """The CTA-pair kernel's 256 x 512 units (hybrid schedule, the library's own tile choice):
+    against the fp32 product on every element, both fixups, bitwise reproducible with block
+    reduce, and level with the plain 256 x 256 path."""
+    M, N, K = shape
+    g = torch.Generator(device=DEV).manual_seed(M + N)
+    A = torch.randn(M, K, generator=g, device=DEV).half()
+    B = (torch.randn(N, K, generator=g, device=DEV) / K ** 0.5).half()
+    info = sk.schedule_info(M, N, K, kind="f16_pairs", schedule="hybrid", num_sms=74)
+    assert info["wide_units"] > 0 and info["wide_units"] % 74 == 0
+    ref = torch.matmul(A.float(), B.float().t())
+    scale = float(ref.abs().max())
+    first = sk.streamk_fp16_nt(A, B, fixup="block_reduce")
+    sk.check_status()
+    assert float((first.float() - ref).abs().max()) <= 1e-2 * scale
+    assert torch.equal(sk.streamk_fp16_nt(A, B, fixup="block_reduce"), first)
+    other = sk.streamk_fp16_nt(A, B, fixup="atomic")
+    sk.check_status()
+    assert float((other.float() - ref).abs().max()) <= 1e-2 * scale
+    plain = sk.streamk_fp16_nt(A, B, tile_m=256, schedule="hybrid", fixup="block_reduce")
+    assert float((plain.float() - first.float()).abs().max()) <= 1e-2 * scale
+    rows = torch.arange(0, M, max(M // 16, 1))[:16].to(DEV)
+    assert oracle.rel_err(first[rows], oracle.gemm_ref(A[rows].cpu(), B.cpu(), "nt")) <= 1e-2

@@ -216,3 +216,44 @@ def test_cluster_split(lib):
     assert lib.sk_schedule(C.byref(prob), 0, 148, C.byref(info)) == L.SK_ERR_ARG
     assert lib.sk_schedule(C.byref(prob), 3, 74, C.byref(info)) == L.SK_ERR_ARG
     assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and info.cluster == 8
+
+
+def test_pair_kernel_wide_units(lib):
+    """CTA-pair kernel, hybrid schedule: full waves of 256 x 512 units + Stream-K over the halves
+    of the remaining units; every 256 x 256 tile is covered exactly once."""
+    from streamk_b200 import _lib as L
+    def plan(M, N, K, pairs=74, **kw):
+        prob = L.SkProblem(M=M, N=N, K=K, lda=K, ldb=K, ldc=N, layout=1, schedule=L.SCHEDULES["hybrid"], **kw)
+        info = L.SkScheduleInfo()
+        assert lib.sk_schedule(C.byref(prob), 3, pairs, C.byref(info)) == 0
+        return info.as_dict(), info
+    d, info = plan(8192, 28672, 8192)      # configuration 5: 32 x 112 tiles = 32 x 56 units
+    assert (d["total_tiles"], d["wide_units"], d["dp_tiles"], d["sk_tiles"], d["dp_waves"]) == (3584, 1776, 3552, 32, 24)
+    assert (d["grid"], d["sk_iters_per_cta"], d["sk_iters_rem"]) == (74, 32 * 128 // 74, 32 * 128 % 74)
+    d, _ = plan(8192, 28672, 8192, tile_m=256)     # asked for by the caller: plain 256 x 256 tiles
+    assert (d["wide_units"], d["sk_tiles"]) == (0, 3584 % 74 + 74)
+    d, _ = plan(8192, 28416, 8192)                 # 111 tile columns: odd, no pairing
+    assert d["wide_units"] == 0
+    rnd = random.Random(5)
+    for _ in range(25):
+        M, N, K = rnd.randint(200, 3000), rnd.randint(2000, 12000), rnd.randint(64, 2048)
+        pairs = rnd.choice([3, 10, 74])
+        d, info = plan(M, N, K, pairs=pairs)
+        tiles_m, tiles_n = d["tiles_m"], d["tiles_n"]
+        assert d["total_tiles"] == tiles_m * tiles_n == d["sk_tiles"] + d["dp_tiles"]
+        seen = {}
+        U = d["wide_units"]
+        if U:
+            assert tiles_n % 2 == 0 and U % d["grid"] == 0 and d["dp_tiles"] == 2 * U
+            for u in range(U):      # the first U units of the rasterised tiles_m x tiles_n/2 grid
+                tm, tnw = oracle.tile_coords(u, tiles_m, tiles_n // 2, d["group_m"])
+                for h in (0, 1):
+                    seen[(tm, 2 * tnw + h)] = seen.get((tm, 2 * tnw + h), 0) + 1
+            tm, tn = C.c_int(), C.c_int()
+            for t in range(d["sk_tiles"]):
+                assert lib.sk_tile_coords(C.byref(info), t, C.byref(tm), C.byref(tn)) == 0
+                seen[(tm.value, tn.value)] = seen.get((tm.value, tn.value), 0) + 1
+            assert len(seen) == tiles_m * tiles_n and set(seen.values()) == {1}
+            # the Stream-K part splits its iterations evenly over the pairs
+            tot = d["sk_tiles"] * d["iters_per_tile"]
+            assert d["sk_iters_per_cta"] * d["grid"] + d["sk_iters_rem"] == tot
