@@ -436,7 +436,7 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
 // are asked for explicitly with tile_m = 256.
 static bool use_cta_pairs(const sk_problem* prob, int num_sms) {
   if (prob->layout != SK_LAYOUT_NT || (num_sms & 1) != 0) return false;
-  if (prob->tile_m == 256) return prob->tile_n == 0 || prob->tile_n == 256;
+  if (prob->tile_m == 256) return true;   // (tile_n: 0 = 256, or any multiple of 16 from 32; checked by the plan)
   if (prob->tile_m != 0 || prob->tile_n != 0) return false;
   const long long tiles = static_cast<long long>((prob->M + 255) / 256) * ((prob->N + 255) / 256);
   return tiles >= 2LL * (num_sms / 2);
@@ -458,8 +458,7 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   SkPlan plan;
   const bool pairs = prob->schedule != SK_SCHED_CLUSTER && use_cta_pairs(prob, num_sms);
   if (pairs) {
-    sk_problem q = *prob;
-    q.tile_n = 0;   // (tile_m stays: 256 = asked for by the caller, 0 = the library's own choice)
+    sk_problem q = *prob;   // (tile_m: 256 = asked for by the caller, 0 = the library's own choice)
     st = sk_make_sched(&q, 3, num_sms / 2, nullptr, &p.sched, &plan);
   } else {
     st = sk_make_sched(prob, 1, num_sms, nullptr, &p.sched, &plan);
@@ -492,7 +491,10 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);  // layout fixed per device, whatever the grid
   p.trace = sk_trace_buffer();
-  if (pairs) return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
+  if (pairs) {
+    p.bn = plan.bn;
+    return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
+  }
   const int split = p.sched.split;   // SK_SCHED_CLUSTER: CTAs per tile
   // Whole tiles of a row-major C leave through shared memory and TMA stores (not the
   // transposed store of the swapped order, not the cluster schedule's reduction).

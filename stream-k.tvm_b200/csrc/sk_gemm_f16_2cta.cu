@@ -126,7 +126,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
         const int a_row0 = (tr * 2 + rank) * BM;          // this CTA's 128 rows of A
-        const int b_row0 = tc * BN + rank * (BN / 2);     // this CTA's 128 rows of B
+        const int b_row0 = tc * p.bn + rank * (p.bn / 2);   // this CTA's half of the tile's rows of B
         for (int k = seg.k0; k < seg.k1;) {
           const int n = (seg.k1 - k) < KG ? (seg.k1 - k) : KG;
           if (!sk_wait_bar(empty0 + 8u * stage, ph ^ 1u, abort_flag, p, stage, 0)) {
@@ -135,7 +135,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           }
           // Both CTAs' loads complete on the leader's barrier; the leader expects all of them.
           const uint32_t full_leader = full0_leader + 8u * stage;
-          if (rank == 0) mbar_arrive_expect_tx(full0 + 8u * stage, n * 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+          if (rank == 0) mbar_arrive_expect_tx(full0 + 8u * stage, n * 2 * (A_STAGE_BYTES + p.col_tx_bytes));
           for (int j = 0; j < n; ++j) {
             tma_load_2d_pair(sA + (stage * KG + j) * A_STAGE_BYTES, &tmA, full_leader, (k + j) * BK, a_row0);
             tma_load_2d_pair(sB + (stage * KG + j) * B_STAGE_BYTES, &tmB, full_leader, (k + j) * BK, b_row0);
@@ -383,7 +383,8 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   CUtensorMap tmA, tmB;
   int st = sk_make_tmap_f16(&tmA, A, prob->M, prob->K, prob->lda, BK, BM);
   if (st != SK_OK) return st;
-  st = sk_make_tmap_f16(&tmB, B, prob->N, prob->K, prob->ldb, BK, BN / 2);
+  const int bn = p->bn;   // tile columns (sk_make_sched): 256, or narrower when asked for (multiple of 16)
+  st = sk_make_tmap_f16(&tmB, B, prob->N, prob->K, prob->ldb, BK, bn / 2);
   CUtensorMap tmC;
   memset(&tmC, 0, sizeof(tmC));
   p->c_tma = p->c_vec_ok;   // whole tiles leave through shared memory and TMA stores
@@ -393,11 +394,11 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   // Wide units (256 x 512, two column-adjacent tiles sharing every A stage): decided by the host
   // scheduler (sk_make_sched), which leaves their count in wide_base.
   p->wide_units = p->sched.wide_base > 0 ? p->sched.wide_base : 0;
-  p->bn = BN;
-  p->acc_stride = BN;
+  p->acc_stride = BN;           // (the accumulator buffers stay 256 columns apart)
+  p->col_tx_bytes = (bn / 2) * BK * 2;   // bytes of this CTA's half of a B stage
   p->tmem_cols = TMEM_COLS;
   p->stages = STAGES;
-  p->idesc = umma_idesc_f16(2 * BM, BN, 0);
+  p->idesc = umma_idesc_f16(2 * BM, bn, 0);
 
   static bool attr_set[64] = {false};
   int dev = 0;

@@ -224,6 +224,28 @@ def test_fp16_cluster_needs_room_for_two_ctas_per_tile():
         sk.streamk_fp16_nt(A.to(DEV), B.to(DEV), schedule="cluster")
 
 
+@pytest.mark.parametrize("shape", [(256, 1024, 512), (300, 520, 1000), (512, 768, 1032), (200, 2000, 264)])
+def test_fp16_cta_pairs_with_narrow_tiles(shape):
+    """The CTA-pair kernel (tile_m = 256) with tile widths other than 256: every schedule and
+    fixup, ragged edges, small grids."""
+    M, N, K = shape
+    A, B = _rand16(M, N, K, seed=M + N)
+    ref = oracle.gemm_ref(A, B, "nt")
+    Ad, Bd = A.to(DEV), B.to(DEV)
+    for tile_n in (32, 64, 96, 160, 192, 256):
+        for schedule in ("dp", "streamk", "hybrid"):
+            for fixup in FIXUPS:
+                _check(sk.streamk_fp16_nt(Ad, Bd, tile_m=256, tile_n=tile_n, schedule=schedule, fixup=fixup), ref, TOL16)
+        _check(sk.streamk_fp16_nt(Ad, Bd, tile_m=256, tile_n=tile_n, schedule="streamk", num_sms=6), ref, TOL16)
+    with pytest.raises(Exception):
+        sk.streamk_fp16_nt(Ad, Bd, tile_m=256, tile_n=72)
+    # what auto makes of more than one 128-row tile row with many columns: pairs, fitted width
+    A2, B2 = _rand16(256, 11008, 256, seed=9)
+    info = sk.schedule_info(256, 11008, 256)
+    assert (info["tile_m"], info["tile_n"], info["total_tiles"]) == (256, 160, 69)
+    _check(sk.streamk_fp16_nt(A2.to(DEV), B2.to(DEV)), oracle.gemm_ref(A2, B2, "nt"), TOL16)
+
+
 def test_fp16_config3_sample_of_the_sweep():
     # the full 24-shape sweep is the benchmark's job; parity on its extremes here
     for case in (0, 7, 22):

@@ -161,8 +161,12 @@ def test_auto_schedule_resolution(lib):
     assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["total_tiles"]) == ("dp", 16, 80, 138)
     d = plan(16, 12288, 4096, kind=2)  # (W4A16 weights come in blocks of 128 rows)
     assert (d["swap_ab"], d["tile_n"], d["total_tiles"]) == (1, 128, 96)
-    d = plan(256, 12288, 4096)        # tile width fitted to 74 columns per tile row
-    assert names[d["schedule"]] == "dp" and d["tile_n"] == 176 and d["total_tiles"] <= 148
+    d = plan(256, 12288, 4096)        # CTA pairs, 256-row tiles, width fitted to the 74 pairs
+    assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["total_tiles"], d["grid"]) == ("dp", 256, 192, 64, 64)
+    d = plan(512, 4096, 4096)         # two tile rows of 256: 37 pairs per row
+    assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["total_tiles"]) == ("dp", 256, 128, 64)
+    d = plan(100, 12288, 4096)        # one 128-row tile row: single CTAs, 128-wide tiles kept
+    assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["total_tiles"]) == ("dp", 128, 128, 96)
     d = plan(128, 4096, 4096)         # 32 tiles: clusters of 4 on 128 x 128 tiles
     assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["cluster"]) == ("cluster", 128, 128, 4)
     d = plan(128, 9000, 4096)         # 71 tiles: clusters of 2
