@@ -69,7 +69,9 @@ typedef struct sk_problem {
   int32_t tile_m;             /* 0 = choose; 128 = M feeds the UMMA M dimension;
                                  16..256 (multiple of 16) = operands swapped: the
                                  weights feed the UMMA M dimension and the tile
-                                 spans tile_m rows of C (for short M)          */
+                                 spans tile_m rows of C (for short M).  fp16 NT,
+                                 256: the CTA-pair kernel (256-row tiles, tile_n a
+                                 multiple of 16 from 32, default 256)           */
   int32_t tile_n;             /* 0 = choose; columns of C per tile: a multiple of 16 up
                                  to 256 (W4A16: 128).  Operands swapped: weight rows
                                  per tile, 128, or for fp16 NT a multiple of 8 from
