@@ -289,10 +289,23 @@ __device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtens
     // the store issued from this buffer two groups ago must have read it
     if (lane == 0) tma_store_wait_read<1>();
     __syncwarp();
+    // both 32-column reads of the group in flight before the one wait
+    uint32_t raw[2][32];
+    tmem_ld_32x32(t_addr + g * 64, raw[0]);
+    tmem_ld_32x32(t_addr + g * 64 + 32, raw[1]);
+    tmem_ld_wait();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float v[32];
-      sk_load_acc(t_addr + g * 64 + h * 32, b_off, v);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[h][j]);
+      if (b_off != 0) {   // second accumulator of a kernel with two MMA issuers
+        uint32_t r2[32];
+        tmem_ld_32x32(t_addr + b_off + g * 64 + h * 32, r2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(r2[j]);
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
