@@ -417,11 +417,12 @@ def main() -> None:
     B_h = torch.empty(B.shape, dtype=B.dtype).pin_memory(); B_h.copy_(B)
     C_h = torch.empty(C.shape, dtype=C.dtype).pin_memory()
 
+    # the library's host-buffer entry point: B and C move in column slabs, copies in, GEMMs and
+    # copies out overlapping on three streams (every byte still crosses PCIe inside the timed region)
+    e2e_slabs = max(2, 16 // world)
+
     def e2e_step():
-        A.copy_(A_h, non_blocking=True)
-        B.copy_(B_h, non_blocking=True)
-        step()
-        C_h.copy_(C, non_blocking=True)
+        sk.streamk_fp16_nt_host(A_h, B_h, C_h, slabs=e2e_slabs, schedule=args.schedule, fixup=args.fixup)
 
     e2e_step()
     barrier()
@@ -432,6 +433,8 @@ def main() -> None:
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
     e2e_value = flops_total * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    torch.cuda.synchronize()
+    e2e_check = float((C_h[rows.cpu()].float().to(dev) - ref).abs().max() / ref.abs().max())
     h2d = (A_h.numel() + B_h.numel()) * 2 * world
     d2h = C_h.numel() * 2 * world
 
@@ -502,7 +505,8 @@ def main() -> None:
         "per_gpu_tflops": value / world,
         "roofline": roofline, "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                "call": f"streamk_fp16_nt_host, {e2e_slabs} column slabs per GPU", "check_rel_err": e2e_check},
         "gpu_launches": args.steps, "clocks": clocks, "check_rel_err": check,
         "cublas_fp16_tflops_same_operands": cublas_tflops,
     }

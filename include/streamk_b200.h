@@ -223,6 +223,13 @@ int sk_dequant_q4(const void* packed, int N, int K, void* W, int ldw, void* stre
 int sk_gemm_w4a16(const sk_problem* p, const void* A, const void* packed, void* C,
                   void* ws, size_t ws_bytes, void* stream);
 
+/* Pitched copy, stream-ordered (cudaMemcpy2DAsync, direction inferred from the pointers):
+ * `rows` rows of `width_bytes` bytes, row pitches in bytes.  Used by the Python layer's
+ * host-buffer entry point to move column slabs of a row-major host matrix at DMA speed.
+ * No counterpart in the reference (its scripts keep everything on the device).            */
+int sk_memcpy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                      size_t width_bytes, size_t rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

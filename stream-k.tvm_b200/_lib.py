@@ -61,6 +61,7 @@ SIGNATURES = {
                                   C.POINTER(C.c_int64)]),
     "sk_tile_coords": (C.c_int, [C.POINTER(SkScheduleInfo), C.c_int, C.POINTER(C.c_int),
                                  C.POINTER(C.c_int)]),
+    "sk_memcpy2d_async": (C.c_int, [_P, C.c_size_t, _P, C.c_size_t, C.c_size_t, C.c_size_t, _P]),
     "sk_workspace_bytes": (C.c_size_t, [C.c_int]),
     "sk_workspace_init": (C.c_int, [_P, C.c_size_t, _P]),
     "sk_poll_status": (C.c_int, [_P, C.POINTER(SkStatus), _P]),

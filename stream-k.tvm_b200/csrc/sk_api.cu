@@ -399,3 +399,13 @@ extern "C" int sk_poll_status(const void* ws, sk_status* host_out, void* stream)
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }
+
+extern "C" int sk_memcpy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                 size_t width_bytes, size_t rows, void* stream) {
+  if (!dst || !src || width_bytes == 0 || rows == 0) return SK_ERR_ARG;
+  if (dst_pitch < width_bytes || src_pitch < width_bytes) return SK_ERR_ARG;
+  cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault,
+                                    static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
+  return SK_OK;
+}

@@ -19,7 +19,7 @@ import torch
 from . import _lib as L
 
 __all__ = [
-    "streamk_fp32", "streamk_fp16_nn", "streamk_fp16_nt", "streamk_fp16_atomic",
+    "streamk_fp32", "streamk_fp16_nn", "streamk_fp16_nt", "streamk_fp16_nt_host", "streamk_fp16_atomic",
     "streamk_fp16_block_reduce", "ladder_prepack", "streamk_fp16_ladder",
     "streamk_fp16_ladder_block_reduce", "q4_prepack", "dequant_w4",
     "streamk_fp16_ladder_block_reduce_q4", "schedule_info", "check_status",
@@ -267,6 +267,93 @@ def streamk_fp16_nt(A, B, *, fixup="block_reduce", schedule="auto", **kw):
     Keyword options: see _options().
     """
     return _gemm_f16(A, B, "nt", fixup, schedule, kw)
+
+
+class _HostPipe:
+    """Device staging buffers, streams and events of streamk_fp16_nt_host for one shape."""
+
+    def __init__(self, M, N, K, slab, device):
+        self.key = (M, N, K, slab)
+        self.A = torch.empty(M, K, dtype=torch.float16, device=device)
+        self.B = [torch.empty(slab, K, dtype=torch.float16, device=device) for _ in range(2)]
+        self.C = [torch.empty(M, slab, dtype=torch.float16, device=device) for _ in range(2)]
+        self.s_in, self.s_mm, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
+
+
+_host_pipes: dict[tuple, _HostPipe] = {}
+
+
+def streamk_fp16_nt_host(A_host, B_host, out_host=None, *, slabs: int = 8, device=None,
+                         fixup="block_reduce", schedule="auto", **kw):
+    """C = A @ B.T for operands and result in (pinned) HOST memory: A [M,K], B [N,K] fp16 CPU
+    tensors, result [M,N] fp16 CPU tensor (out_host, or a new pinned tensor).
+
+    B and C move in `slabs` column slabs through double-buffered device staging: the
+    host-to-device copy of slab i+1, the GEMM of slab i and the device-to-host copy of slab i-1
+    run on three streams at once, so a step costs about the larger of the two PCIe directions
+    instead of their sum plus the GEMM.  The calling stream waits for the result; the host has
+    to synchronise that stream (or the device) before reading out_host.  Each slab is one call of
+    streamk_fp16_nt (same keyword options)."""
+    for name, t in (("A_host", A_host), ("B_host", B_host)):
+        if not isinstance(t, torch.Tensor) or t.is_cuda or t.dtype != torch.float16 or t.dim() != 2:
+            raise TypeError(f"{name} must be a 2-D fp16 CPU tensor")
+    M, K = A_host.shape
+    N = B_host.shape[0]
+    if B_host.shape[1] != K:
+        raise ValueError("A_host [M,K] and B_host [N,K] disagree on K")
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    slabs = max(1, min(int(slabs), N))
+    slab = -(-N // slabs)
+    slab = (slab + 15) // 16 * 16          # whole 16-column groups: aligned rows in the staging tiles
+    slabs = -(-N // slab)
+    if out_host is None:
+        out_host = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    if out_host.shape != (M, N) or out_host.dtype != torch.float16 or out_host.is_cuda or out_host.stride(1) != 1:
+        raise ValueError("out_host must be a row-major fp16 CPU tensor of shape [M, N]")
+    if not (A_host.is_contiguous() and B_host.is_contiguous()):
+        raise ValueError("A_host and B_host must be contiguous")
+    key = (device.index, M, N, K, slab)
+    pipe = _host_pipes.get(key)
+    if pipe is None:
+        pipe = _host_pipes[key] = _HostPipe(M, N, K, slab, device)
+    cur = torch.cuda.current_stream(device)
+    for st in (pipe.s_in, pipe.s_mm, pipe.s_out):
+        st.wait_stream(cur)                 # staging buffers of a previous call are free again
+    with torch.cuda.stream(pipe.s_in):
+        pipe.A.copy_(A_host, non_blocking=True)
+    mm_done = [None, None]                  # per staging buffer: GEMM that last read B / wrote C
+    out_done = [None, None]                 # per staging buffer: copy-out that last read C
+    for i in range(slabs):
+        b = i & 1
+        n0, n1 = i * slab, min(N, (i + 1) * slab)
+        w = n1 - n0
+        with torch.cuda.stream(pipe.s_in):
+            if mm_done[b] is not None:
+                pipe.s_in.wait_event(mm_done[b])
+            pipe.B[b][:w].copy_(B_host[n0:n1], non_blocking=True)
+            loaded = torch.cuda.Event()
+            loaded.record(pipe.s_in)
+        with torch.cuda.stream(pipe.s_mm):
+            pipe.s_mm.wait_event(loaded)
+            if out_done[b] is not None:
+                pipe.s_mm.wait_event(out_done[b])
+            Cb = pipe.C[b] if w == slab else pipe.C[b][:, :w]
+            _gemm_f16(pipe.A, pipe.B[b][:w], "nt", fixup, schedule, dict(kw, out=Cb))
+            mm_done[b] = torch.cuda.Event()
+            mm_done[b].record(pipe.s_mm)
+        with torch.cuda.stream(pipe.s_out):
+            pipe.s_out.wait_event(mm_done[b])
+            # a pitched DMA straight into the column slab of the row-major host matrix (a strided
+            # Tensor.copy_ would go through a staging buffer and a CPU-side scatter)
+            L.check(L.load().sk_memcpy2d_async(
+                out_host.data_ptr() + n0 * 2, out_host.stride(0) * 2, Cb.data_ptr(), Cb.stride(0) * 2,
+                w * 2, M, int(pipe.s_out.cuda_stream)), "sk_memcpy2d_async")
+            out_done[b] = torch.cuda.Event()
+            out_done[b].record(pipe.s_out)
+    cur.wait_stream(pipe.s_out)
+    cur.wait_stream(pipe.s_mm)
+    cur.wait_stream(pipe.s_in)
+    return out_host
 
 
 def streamk_fp16_nn(A, B, *, fixup="block_reduce", schedule="auto", **kw):

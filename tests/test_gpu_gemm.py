@@ -367,3 +367,22 @@ def test_w4a16_config4_extremes():
         ref = oracle.w4a16_ref(c["A"], c["q"], c["scales"], c["zeros"])
         P = sk.q4_prepack(c["qweight"].to(DEV), c["scales"].to(DEV), c["zeros"].to(DEV))
         _check(sk.streamk_fp16_ladder_block_reduce_q4(c["A"].to(DEV), P), ref, TOL16)
+
+
+@pytest.mark.parametrize("shape,slabs", [((300, 1000, 520), 3), ((64, 4096, 256), 8), ((256, 777, 128), 5), ((16, 100, 64), 1)])
+def test_fp16_nt_host_pipeline(shape, slabs):
+    """Host operands in, host result out, B and C moving in column slabs over three streams."""
+    M, N, K = shape
+    A, B = _rand16(M, N, K, seed=N)
+    ref = oracle.gemm_ref(A, B, "nt")
+    A_h, B_h = A.pin_memory(), B.pin_memory()
+    out = sk.streamk_fp16_nt_host(A_h, B_h, slabs=slabs)
+    torch.cuda.synchronize()
+    _check(out, ref, TOL16)
+    out2 = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    for _ in range(3):                                    # staging buffers are reused across calls
+        assert sk.streamk_fp16_nt_host(A_h, B_h, out2, slabs=slabs) is out2
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
+    with pytest.raises(TypeError):
+        sk.streamk_fp16_nt_host(A.to(DEV), B_h)
