@@ -419,7 +419,7 @@ def main() -> None:
 
     # the library's host-buffer entry point: B and C move in column slabs, copies in, GEMMs and
     # copies out overlapping on three streams (every byte still crosses PCIe inside the timed region)
-    e2e_slabs = max(2, 16 // world)
+    e2e_slabs = max(2, 8 // world)
 
     def e2e_step():
         sk.streamk_fp16_nt_host(A_h, B_h, C_h, slabs=e2e_slabs, schedule=args.schedule, fixup=args.fixup)
