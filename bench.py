@@ -453,6 +453,42 @@ def main() -> None:
         barrier()
         gather_ms = max_over_ranks(e0.elapsed_time(e1)) / 5
 
+    # ---- the same product with the all-gather fused into the epilogue (peer stores) ----
+    fused = None
+    if world > 1:
+        res, err = None, ""
+        try:
+            res = sk.GatheredResult(M5, N5)
+        except Exception as e:   # all ranks must agree before anybody enters a collective call
+            err = f"{type(e).__name__}: {e}"
+        bad = torch.tensor([0.0 if res is not None else 1.0], device=dev)
+        dist.all_reduce(bad)
+        if bad.item() == 0:
+            for _ in range(2):
+                sk.streamk_fp16_nt_gather(A, B, res, schedule=args.schedule, fixup=args.fixup)
+            barrier()
+            e0.record()
+            for _ in range(5):
+                sk.streamk_fp16_nt_gather(A, B, res, schedule=args.schedule, fixup=args.fixup)
+            e1.record()
+            barrier()
+            fused_ms = max_over_ranks(e0.elapsed_time(e1)) / 5
+            sk.check_status()
+            # every block of the gathered matrix against what NCCL delivered (same kernels, same bits
+            # with the block-reduce fixup; the atomic fixup's summation order is free)
+            same = all(torch.equal(res.full[:, r * n_slab:(r + 1) * n_slab], parts[r]) for r in range(world))
+            worst = max(float((res.full[:, r * n_slab:(r + 1) * n_slab].float() - parts[r].float()).abs().max())
+                        for r in range(world))
+            agree = torch.tensor([1.0 if same else 0.0, -worst], device=dev)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            fused = {"gemm_fused_allgather_ms": fused_ms, "bitwise_equal_to_nccl_gather": bool(agree[0].item() == 1.0),
+                     "max_abs_diff": float(-agree[1].item()),
+                     "bytes_pushed_per_gpu": M5 * n_slab * 2 * (world - 1)}
+        else:
+            fused = {"error": err or "another rank could not map the shared matrices"}
+        if res is not None:
+            res.close()
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -512,6 +548,8 @@ def main() -> None:
     }
     if gather_ms is not None:
         out["gemm_plus_allgather_ms"] = gather_ms
+    if fused is not None:
+        out["fused_allgather"] = fused
     if args.sweep and world == 1:
         run_sweep(args.sweep, peaks)
         out["sweep_file"] = args.sweep

@@ -198,6 +198,36 @@ int sk_gemm_f32_noalloc(const sk_problem* p, const float* A, const float* B, flo
 int sk_gemm_f16(const sk_problem* p, const void* A, const void* B, void* C,
                 void* ws, size_t ws_bytes, void* stream);
 
+/* sk_gemm_f16 fused with the all-gather of an N-sharded product (the reference is a
+ * single-GPU study; this is the column-sharded configuration's collective).  Every GPU of
+ * a group holds the full result matrix [M, N_total] and computes one column block of it.
+ * C addresses element (0, first column of this GPU's block) of the local matrix and
+ * peers[i] the same element of peer i's matrix (peer-mapped device memory, e.g. from
+ * sk_peer_open; same ldc everywhere).  The kernel's epilogue writes every finished tile
+ * to C and to all peers in the order given (plain peer stores and TMA stores without
+ * multicast, no device-side wait on another GPU), so the transfer overlaps the mainloop
+ * tile by tile.  The call is stream-ordered like sk_gemm_f16; the gathered matrix is
+ * complete on a GPU once ALL GPUs' kernels have finished: the caller places a host or
+ * NCCL barrier after the call before reading foreign blocks, and one before the next call
+ * overwrites them.  Needs the CTA-pair kernel (NT layout, tile_m = 256 or a problem large
+ * enough that the library picks it: SK_ERR_SHAPE otherwise), C and peers 16-byte aligned,
+ * ldc a multiple of 8, n_peers <= SK_MAX_PEERS.  n_peers == 0 is sk_gemm_f16.           */
+enum { SK_MAX_PEERS = 7 };
+int sk_gemm_f16_gather(const sk_problem* p, const void* A, const void* B, void* C,
+                       void* const* peers, int n_peers, void* ws, size_t ws_bytes, void* stream);
+
+/* Device memory other processes of this machine can map (CUDA IPC), for the matrices
+ * sk_gemm_f16_gather writes into.  sk_peer_alloc: cudaMalloc + export; `handle` receives
+ * SK_PEER_HANDLE_BYTES opaque bytes to send to the other processes (any channel).
+ * sk_peer_open maps a handle received from another process (peer access is enabled as
+ * needed) and returns a device pointer valid in this process; sk_peer_close unmaps it;
+ * sk_peer_free releases an allocation of sk_peer_alloc (after every peer closed it).    */
+enum { SK_PEER_HANDLE_BYTES = 64 };
+int sk_peer_alloc(size_t bytes, void** ptr, void* handle);
+int sk_peer_open(const void* handle, void** ptr);
+int sk_peer_close(void* ptr);
+int sk_peer_free(void* ptr);
+
 /* Bytes of the pre-laid-out image of an fp16 weight B[N,K]. */
 size_t sk_ladder_bytes(int N, int K);
 /* One-time re-layout of B[N,K] (row-major fp16, ldb elements) into the image

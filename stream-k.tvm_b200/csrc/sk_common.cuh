@@ -104,6 +104,16 @@ struct SkParams {
   unsigned long long* trace;  // debugging: 16 timestamps per CTA, or null
 };
 
+// Fused all-gather (sk_gemm_f16_gather): every finished piece of C is also written, at the same
+// row and column, into the result matrices of up to SK_MAX_PEERS other GPUs (peer-mapped
+// memory; plain stores and non-multicast TMA stores).  c[i] addresses the same element of peer
+// i's matrix as the kernel's C argument does of the local one; tm[i] is the tensor map over it.
+struct alignas(64) SkPeers {
+  CUtensorMap tm[SK_MAX_PEERS];
+  __half* c[SK_MAX_PEERS];
+  int n;
+};
+
 // Debugging aid: record %globaltimer at a numbered point of this CTA's life.
 __device__ __forceinline__ void sk_trace(const SkParams& p, int slot) {
   if (p.trace) p.trace[blockIdx.x * 16 + slot] = skptx::globaltimer_ns();

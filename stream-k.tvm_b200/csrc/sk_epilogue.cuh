@@ -48,8 +48,8 @@ __device__ __forceinline__ bool sk_wait_bar(uint32_t bar, uint32_t parity, volat
 }
 
 // nv (<= 32) fp32 values of tile row `grow`, columns gcol0.. -> fp16 C
-__device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkParams& p, int grow,
-                                               int gcol0, int nv, const float (&v)[32]) {
+__device__ __forceinline__ void sk_store_chunk1(__half* __restrict__ C, const SkParams& p, int grow,
+                                                int gcol0, int nv, const float (&v)[32]) {
   if (p.transposed) {
     __half* dst = C + static_cast<size_t>(gcol0) * p.ldc + grow;
 #pragma unroll
@@ -79,9 +79,19 @@ __device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkP
   }
 }
 
+// ... and, in the fused all-gather, to the same place of every peer GPU's matrix.  `peers` is a
+// compile-time null in every kernel but the gathering one, where the loop disappears.
+__device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkParams& p, int grow,
+                                               int gcol0, int nv, const float (&v)[32],
+                                               const SkPeers* peers = nullptr) {
+  sk_store_chunk1(C, p, grow, gcol0, nv, v);
+  if (peers != nullptr)
+    for (int i = 0; i < peers->n; ++i) sk_store_chunk1(peers->c[i], p, grow, gcol0, nv, v);
+}
+
 // One float4 of the slot layout (row, columns gcol..gcol+3) -> fp16 C
-__device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
-                                          const float4& x) {
+__device__ __forceinline__ void sk_store4_1(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
+                                            const float4& x) {
   const float v[4] = {x.x, x.y, x.z, x.w};
   if (p.transposed) {
 #pragma unroll
@@ -104,6 +114,13 @@ __device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams
   }
 }
 
+__device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
+                                          const float4& x, const SkPeers* peers = nullptr) {
+  sk_store4_1(C, p, grow, gcol, x);
+  if (peers != nullptr)
+    for (int i = 0; i < peers->n; ++i) sk_store4_1(peers->c[i], p, grow, gcol, x);
+}
+
 struct SkPending {
   int tile;    // -1 = none
   int first, last;
@@ -117,7 +134,7 @@ template <int U, int V>
 __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __restrict__ C,
                                                    int first, int last, int rank, int r0,
                                                    int c0, int rows_valid, int begin, int end,
-                                                   int tid, int nthreads) {
+                                                   int tid, int nthreads, const SkPeers* peers) {
   for (int base = begin + tid; base < end; base += U * nthreads) {
     float4 acc[U];
     bool on[U];
@@ -157,14 +174,14 @@ __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int idx = base + u * nthreads;
-      if (on[u]) sk_store4(C, p, r0 + (idx & (SK_BM - 1)), c0 + (idx >> 7) * 4, acc[u]);
+      if (on[u]) sk_store4(C, p, r0 + (idx & (SK_BM - 1)), c0 + (idx >> 7) * 4, acc[u], peers);
     }
   }
 }
 
 __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __restrict__ C,
                                                 const SkPending& pd, int pid, int rank, int tid,
-                                                int nthreads) {
+                                                int nthreads, const SkPeers* peers) {
   const SkSched& s = p.sched;
   const int first = pd.first, last = pd.last;
   const int n = last - first + 1;
@@ -180,10 +197,10 @@ __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __res
   const int begin = static_cast<int>(static_cast<long long>(j) * L / n);
   const int end = static_cast<int>(static_cast<long long>(j + 1) * L / n);
   // The summation order (0 + p_first + p_first+1 + ...) is the same in every variant.
-  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
+  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
+  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
+  else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
 }
 
 // Deferred block-reduce of the (at most two) split tiles this CTA took part in (see the
@@ -191,7 +208,7 @@ __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __res
 // pend[0] is the tile the CTA started, pend[1] the tile it continued; ok[] is scratch.
 __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __restrict__ C, int pid,
                                                   int rank, const SkPending* pend,
-                                                  volatile uint32_t* ok) {
+                                                  volatile uint32_t* ok, const SkPeers* peers = nullptr) {
   using namespace skptx;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   if (pend[0].tile < 0 && pend[1].tile < 0) return;   // uniform over the CTA
@@ -216,7 +233,7 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
   // 2. reduce this CTA's slice of each tile
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    if (pend[t].tile >= 0 && ok[t] != 0u) sk_reduce_items(p, C, pend[t], pid, rank, tid, nthreads);
+    if (pend[t].tile >= 0 && ok[t] != 0u) sk_reduce_items(p, C, pend[t], pid, rank, tid, nthreads, peers);
     if (tid == 0) sk_trace(p, 9 + t);
   }
   // 3. everybody has read what it needs; the last contributor to get here re-arms the flags
@@ -281,7 +298,8 @@ constexpr int SK_CSTAGE_BYTES = 4 * 2 * 4096;
 // handled (a multiple of 64; the rest of the tile goes through sk_store_chunk).
 __device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtensorMap* tmC, uint32_t cstage,
                                                  int warp_slot, int lane, uint32_t t_addr, uint32_t b_off,
-                                                 int grow0, int gcol0, int valid_cols, uint32_t& groups) {
+                                                 int grow0, int gcol0, int valid_cols, uint32_t& groups,
+                                                 const SkPeers* peers = nullptr) {
   using namespace skptx;
   const int full = valid_cols >> 6;
   for (int g = 0; g < full; ++g, ++groups) {
@@ -324,6 +342,8 @@ __device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtens
     __syncwarp();
     if (lane == 0) {
       tma_store_2d(tmC, buf, gcol0 + g * 64, grow0);
+      if (peers != nullptr)   // the same box into every peer's matrix, in the same bulk group
+        for (int i = 0; i < peers->n; ++i) tma_store_2d(&peers->tm[i], buf, gcol0 + g * 64, grow0);
       tma_store_commit();
     }
   }
@@ -338,7 +358,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
                                                  volatile uint32_t* abort_flag,
                                                  SkPending* pend_out,
                                                  const CUtensorMap* tmC = nullptr, uint32_t cstage = 0,
-                                                 uint32_t* nseg_out = nullptr) {
+                                                 uint32_t* nseg_out = nullptr, const SkPeers* peers = nullptr) {
   using namespace skptx;
   constexpr int BM = SK_BM;
   constexpr int EPI_THREADS = SK_EPI_THREADS;
@@ -394,7 +414,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     int c_first = 0;   // first 32-column chunk that still has to go through the register path
     if (whole && p.c_tma && cstage != 0 && warp_ok && !dead)
       c_first = sk_store_tile_tma(p, tmC, cstage, (warp - 2) & 3, lane, t_addr, two ? p.acc_b_off : 0,
-                                  r0 + q * 32, c0, valid_cols, tma_groups) >> 5;
+                                  r0 + q * 32, c0, valid_cols, tma_groups, peers) >> 5;
     if (warp_ok && !dead) {
       for (int c = c_first; c < nchunks; ++c) {
         float v[32];
@@ -403,7 +423,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
         int nv = valid_cols - c * 32;
         if (nv > 32) nv = 32;
         if (whole) {
-          sk_store_chunk(C, p, grow, c0 + c * 32, nv, v);
+          sk_store_chunk(C, p, grow, c0 + c * 32, nv, v, peers);
         } else if (atomic) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -459,7 +479,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
             const int i = idx + u * EPI_THREADS;
             if (i < L && (i & (BM - 1)) < rows_valid) {
               __stcg(slot4 + i, zero);
-              sk_store4(C, p, r0 + (i & (BM - 1)), c0 + (i >> 7) * 4, x[u]);
+              sk_store4(C, p, r0 + (i & (BM - 1)), c0 + (i >> 7) * 4, x[u], peers);
             }
           }
         }

@@ -430,7 +430,7 @@ void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_sta
 }
 
 int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, void* C, SkParams* p,
-                       void* stream);
+                       void* const* peer_c, int n_peers, void* stream);
 
 // CTA pairs pay off once the problem fills every pair with several 256 x 256 tiles; they
 // are asked for explicitly with tile_m = 256.
@@ -442,8 +442,8 @@ static bool use_cta_pairs(const sk_problem* prob, int num_sms) {
   return tiles >= 2LL * (num_sms / 2);
 }
 
-extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B, void* C, void* ws,
-                           size_t ws_bytes, void* stream) {
+static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* C, void* const* peer_c,
+                    int n_peers, void* ws, size_t ws_bytes, void* stream) {
   if (!prob || !A || !B || !C) return SK_ERR_ARG;
   if (prob->layout < SK_LAYOUT_NN || prob->layout > SK_LAYOUT_LADDER) return SK_ERR_ARG;
   if (prob->fixup != SK_FIXUP_ATOMIC && prob->fixup != SK_FIXUP_BLOCK_REDUCE) return SK_ERR_ARG;
@@ -493,8 +493,9 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
   p.trace = sk_trace_buffer();
   if (pairs) {
     p.bn = plan.bn;
-    return sk_launch_f16_2cta(prob, A, B, C, &p, stream);
+    return sk_launch_f16_2cta(prob, A, B, C, &p, peer_c, n_peers, stream);
   }
+  if (n_peers > 0) return SK_ERR_SHAPE;   // the fused all-gather lives in the CTA-pair kernel
   const int split = p.sched.split;   // SK_SCHED_CLUSTER: CTAs per tile
   // Whole tiles of a row-major C leave through shared memory and TMA stores (not the
   // transposed store of the swapped order, not the cluster schedule's reduction).
@@ -596,4 +597,16 @@ extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B,
                   tmRow, tmCol, tmC, Ch, p);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
+}
+
+extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B, void* C, void* ws,
+                           size_t ws_bytes, void* stream) {
+  return gemm_f16(prob, A, B, C, nullptr, 0, ws, ws_bytes, stream);
+}
+
+extern "C" int sk_gemm_f16_gather(const sk_problem* prob, const void* A, const void* B, void* C,
+                                  void* const* peers, int n_peers, void* ws, size_t ws_bytes,
+                                  void* stream) {
+  if (n_peers < 0 || n_peers > SK_MAX_PEERS || (n_peers > 0 && !peers)) return SK_ERR_ARG;
+  return gemm_f16(prob, A, B, C, peers, n_peers, ws, ws_bytes, stream);
 }

@@ -53,9 +53,14 @@ struct Ctrl {
 };
 static_assert(sizeof(Ctrl) <= CTRL_BYTES, "Ctrl must fit its reserved space");
 
+// PEERS: the fused all-gather (sk_gemm_f16_gather): the epilogue also writes every piece of C
+// into the peer GPUs' matrices named by `peer_set`.
+template <bool PEERS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                        const __grid_constant__ CUtensorMap tmC, __half* __restrict__ C, const SkParams p) {
+                        const __grid_constant__ CUtensorMap tmC, __half* __restrict__ C, const SkParams p,
+                        const __grid_constant__ SkPeers peer_set) {
+  const SkPeers* peers = PEERS ? &peer_set : nullptr;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -96,6 +101,8 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     fence_proxy_async_smem();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    if (PEERS)
+      for (int i = 0; i < peer_set.n; ++i) prefetch_tensormap(&peer_set.tm[i]);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(&ctrl->tmem_base), TMEM_COLS);
@@ -305,7 +312,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const uint32_t tmem_empty0 = mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0);
     uint32_t nseg = 0;
     sk_epilogue_loop(p, C, unit, rank, warp, lane, tmem_base, tmem_full0, tmem_empty0, &ctrl->bcast,
-                     abort_flag, ctrl->pend, &tmC, cstage, &nseg);
+                     abort_flag, ctrl->pend, &tmC, cstage, &nseg, peers);
     if (p.wide_units > 0) {
       // ---- wide units: the two halves are two whole tiles in the two accumulator buffers
       const int q = warp & 3;
@@ -333,13 +340,13 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             int c_first = 0;
             if (cstage != 0)
               c_first = sk_store_tile_tma(p, &tmC, cstage, (warp - 2) & 3, lane, t_addr, 0, r0 + q * 32, c0,
-                                          valid_cols, groups) >> 5;
+                                          valid_cols, groups, peers) >> 5;
             for (int c = c_first; c < ((valid_cols + 31) >> 5); ++c) {
               float v[32];
               sk_load_acc(t_addr + c * 32, 0, v);
               int nv = valid_cols - c * 32;
               if (nv > 32) nv = 32;
-              if (row_ok) sk_store_chunk(C, p, r0 + row, c0 + c * 32, nv, v);
+              if (row_ok) sk_store_chunk(C, p, r0 + row, c0 + c * 32, nv, v, peers);
             }
           }
           tc_fence_before();
@@ -354,7 +361,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   // ------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  sk_reduce_pending(p, C, unit, rank, ctrl->pend, ctrl->ok);
+  sk_reduce_pending(p, C, unit, rank, ctrl->pend, ctrl->ok, peers);
   // Neither CTA may leave while its partner can still signal its barriers or read its
   // shared memory.
   __syncthreads();
@@ -377,9 +384,9 @@ int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
                      uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
 
 // Launch with CTA pairs.  `units` persistent pairs; p->sched must have been built for
-// 256-row tiles and `units` schedulable units.
+// 256-row tiles and `units` schedulable units.  n_peers > 0: the fused all-gather.
 int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, void* C, SkParams* p,
-                       void* stream) {
+                       void* const* peer_c, int n_peers, void* stream) {
   CUtensorMap tmA, tmB;
   int st = sk_make_tmap_f16(&tmA, A, prob->M, prob->K, prob->lda, BK, BM);
   if (st != SK_OK) return st;
@@ -390,6 +397,20 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   p->c_tma = p->c_vec_ok;   // whole tiles leave through shared memory and TMA stores
   if (st == SK_OK && p->c_tma) st = sk_make_tmap_f16(&tmC, C, prob->M, prob->N, prob->ldc, 64, 32);
   if (st != SK_OK) return st;
+  SkPeers peer_set;
+  memset(&peer_set, 0, sizeof(peer_set));
+  if (n_peers > 0) {
+    if (n_peers > SK_MAX_PEERS || !peer_c) return SK_ERR_ARG;
+    if (!p->c_vec_ok) return SK_ERR_ALIGN;
+    peer_set.n = n_peers;
+    for (int i = 0; i < n_peers; ++i) {
+      if (!peer_c[i]) return SK_ERR_ARG;
+      if ((reinterpret_cast<uintptr_t>(peer_c[i]) & 15u) != 0) return SK_ERR_ALIGN;
+      peer_set.c[i] = static_cast<__half*>(peer_c[i]);
+      st = sk_make_tmap_f16(&peer_set.tm[i], peer_c[i], prob->M, prob->N, prob->ldc, 64, 32);
+      if (st != SK_OK) return st;
+    }
+  }
   p->unit_ctas = 2;
   // Wide units (256 x 512, two column-adjacent tiles sharing every A stage): decided by the host
   // scheduler (sk_make_sched), which leaves their count in wide_base.
@@ -404,14 +425,22 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel,
+    cudaError_t e = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SMEM_BYTES);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     attr_set[dev & 63] = true;
   }
-  cudaError_t e = sk_launch(sk_gemm_f16_2cta_kernel, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
-                            static_cast<cudaStream_t>(stream), 2, (prob->flags & SK_FLAG_PDL) != 0, tmA, tmB,
-                            tmC, static_cast<__half*>(C), *p);
+  const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
+  cudaError_t e =
+      n_peers > 0 ? sk_launch(sk_gemm_f16_2cta_kernel<true>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
+                              static_cast<cudaStream_t>(stream), 2, pdl, tmA, tmB, tmC,
+                              static_cast<__half*>(C), *p, peer_set)
+                  : sk_launch(sk_gemm_f16_2cta_kernel<false>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
+                              static_cast<cudaStream_t>(stream), 2, pdl, tmA, tmB, tmC,
+                              static_cast<__half*>(C), *p, peer_set);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

@@ -1,0 +1,157 @@
+"""Column-sharded product with the all-gather fused into the GEMM's epilogue.
+
+The sharded configuration splits B[N, K] by rows over the GPUs of a process group (one
+process per GPU); GPU g computes the column block C[:, g*N/G : (g+1)*N/G].  The plain way
+to give every GPU the whole C is an NCCL all-gather after the GEMM.  Here every GPU holds
+the full matrix in memory that its peers have mapped (CUDA IPC, `sk_peer_*` of the C ABI),
+and the kernel's epilogue writes each finished tile into the local matrix and into every
+peer's (`sk_gemm_f16_gather`), so the transfer runs under the mainloop, tile by tile.  No
+kernel waits on another GPU; the ranks meet in two stream-ordered NCCL all-reduces of one
+element, one before the kernel (nobody still reads the matrix that is about to be
+overwritten) and one after it (every rank's stores have landed).
+
+The reference is a single-GPU study and has no counterpart of this file.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import ops as _ops
+
+__all__ = ["column_block", "peer_order", "GatheredResult", "streamk_fp16_nt_gather"]
+
+MAX_PEERS = 7   # SK_MAX_PEERS
+
+
+def column_block(rank: int, world: int, n_total: int) -> tuple[int, int]:
+    """(first column, width) of rank's block; blocks are equal and 16-byte aligned."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of {world}")
+    if n_total % world != 0 or (n_total // world) % 8 != 0:
+        raise ValueError(f"N = {n_total} does not split into {world} column blocks of a multiple of 8")
+    w = n_total // world
+    return rank * w, w
+
+
+def peer_order(rank: int, world: int) -> list[int]:
+    """The order in which a rank writes to its peers: rank+1, rank+2, ... (mod world), so that
+    at any moment the ranks address different destinations."""
+    return [(rank + i) % world for i in range(1, world)]
+
+
+class _DeviceBytes:
+    """A raw device allocation as something torch.as_tensor understands."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class GatheredResult:
+    """The full fp16 result [M, N_total] on this GPU, mapped into every process of `group`.
+
+    `full` is the local matrix (a torch tensor over the library's allocation), `block` the
+    view of this rank's own columns.  Collective: every rank of the group constructs it (and
+    closes it) at the same point of the program.
+    """
+
+    def __init__(self, M: int, n_total: int, group=None, device=None):
+        if not dist.is_initialized():
+            raise RuntimeError("GatheredResult needs an initialised torch.distributed process group")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world - 1 > MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS + 1} ranks")
+        self.device = (torch.device("cuda", torch.cuda.current_device()) if device is None
+                       else torch.device(device))
+        self.M, self.n_total = int(M), int(n_total)
+        self.col0, self.width = column_block(self.rank, self.world, self.n_total)
+        lib = L.load()
+        nbytes = self.M * self.n_total * 2
+        self._own = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            L.check(lib.sk_peer_alloc(nbytes, C.byref(self._own), handle), "sk_peer_alloc")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self._peer_base = {}
+            for r in peer_order(self.rank, self.world):
+                p = C.c_void_p()
+                L.check(lib.sk_peer_open(handles[r], C.byref(p)), "sk_peer_open")
+                self._peer_base[r] = p.value
+            self.full = torch.as_tensor(_DeviceBytes(self._own.value, nbytes), device=self.device) \
+                .view(torch.float16).view(self.M, self.n_total)
+            if self.full.data_ptr() != self._own.value:
+                raise RuntimeError("the tensor over the shared allocation is a copy, not a view")
+            self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.block = self.full[:, self.col0:self.col0 + self.width]
+        off = self.col0 * 2
+        self._peer_ptrs = (C.c_void_p * max(1, self.world - 1))(
+            *[self._peer_base[r] + off for r in peer_order(self.rank, self.world)])
+        self._open = True
+
+    def meet(self) -> None:
+        """Stream-ordered rendezvous of the group (an all-reduce of one element)."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def close(self) -> None:
+        if not self._open:
+            return
+        self._open = False
+        lib = L.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)          # nobody still writes into a peer
+            for p in self._peer_base.values():
+                lib.sk_peer_close(p)
+            self.full = self.block = None
+            dist.barrier(group=self.group)          # every mapping is gone before the memory is
+            lib.sk_peer_free(self._own)
+
+
+def streamk_fp16_nt_gather(A: torch.Tensor, B_block: torch.Tensor, result: GatheredResult, *,
+                           fixup: str = "block_reduce", schedule: str = "auto", **kw) -> torch.Tensor:
+    """result.full = A @ B.T for B = the ranks' B_block stacked by rows: each rank computes its
+    column block with the CTA-pair Stream-K kernel, whose epilogue writes every tile into all
+    ranks' matrices.  A [M, K] fp16 (the same on every rank), B_block [N_total / world, K] fp16.
+    Returns result.full, complete on every rank once the stream reaches the point after this
+    call.  Options as for streamk_fp16_nt (tile_m: None or 256, the CTA-pair kernel).
+    """
+    o = _ops._options(kw)
+    _ops._check_matrix("A", A, torch.float16)
+    _ops._check_matrix("B_block", B_block, torch.float16)
+    M, K = A.shape
+    if (M, B_block.shape[0]) != (result.M, result.width) or B_block.shape[1] != K:
+        raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} B_block {tuple(B_block.shape)} "
+                         f"result {result.M} x {result.width} of {result.n_total}")
+    if o["out"] is not None:
+        raise TypeError("the result lives in `result`; `out` is not accepted")
+    if o["tile_m"] not in (None, 256):
+        raise ValueError("the fused gather runs on the CTA-pair kernel: tile_m must be 256")
+    if o["tile_m"] is None:
+        # Large blocks: the library's own choice is the CTA-pair kernel (with its 256 x 512
+        # units); smaller ones are steered to it.
+        sms = int(o["num_sms"] or torch.cuda.get_device_properties(A.device).multi_processor_count)
+        tiles = ((M + 255) // 256) * ((result.width + 255) // 256)
+        if tiles < 2 * (sms // 2):
+            o["tile_m"] = 256
+    if o["tile_m"] == 256 and schedule == "auto":
+        schedule = "hybrid"   # (the automatic choice would weigh kernels that cannot gather)
+    A = _ops._aligned16(_ops._rowmajor(_ops._pad_k8(A, 1)))
+    Bt = _ops._aligned16(_ops._rowmajor(_ops._pad_k8(B_block, 1)))
+    prob = _ops._problem(M, result.width, A.shape[1], A.stride(0), Bt.stride(0), result.n_total, "nt",
+                         schedule, fixup, o)
+    with torch.cuda.device(A.device):
+        ws = _ops._workspace(A.device)
+        result.meet()   # the peers are done with the previous contents
+        L.check(L.load().sk_gemm_f16_gather(C.byref(prob), A.data_ptr(), Bt.data_ptr(),
+                                            result.block.data_ptr(), result._peer_ptrs, result.world - 1,
+                                            ws.buf.data_ptr(), ws.nbytes, _ops._stream_ptr(A.device)),
+                "sk_gemm_f16_gather")
+        result.meet()   # every rank's kernel, hence every store into this GPU, has finished
+    return result.full

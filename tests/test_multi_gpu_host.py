@@ -44,6 +44,16 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         C_full = torch.cat(parts, 1)
         ref = oracle.gemm_ref(A, torch.cat(slabs, 0), "nt")
         assert torch.equal(C_full, ref)
+        # the fused gather's host logic: equal aligned column blocks, each rank writing to its
+        # peers in an order of its own (no two ranks address the same destination at once)
+        col0, width = sk.column_block(rank, world, N)
+        assert (col0, width) == (rank * N // world, N // world)
+        assert torch.equal(C_full[:, col0:col0 + width], C_slab)
+        orders = [None] * world
+        dist.all_gather_object(orders, sk.peer_order(rank, world))
+        for step in range(world - 1):
+            assert sorted(o[step] for o in orders) == list(range(world))
+        assert all(r not in orders[r] for r in range(world))
         # max-over-ranks timing reduction used by the benchmark
         t = torch.tensor([float(rank + 1)], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -65,3 +75,16 @@ def test_bench_operand_slabs_are_world_size_independent():
     assert bench.N5 % 8 == 0 and bench.BASE_SLAB * 8 == bench.N5
     for world in (1, 2, 4, 8):
         assert (bench.N5 // world) % 256 == 0       # whole 256-column tiles per GPU
+
+
+def test_gather_layout_rules():
+    sys.path.insert(0, ROOT)
+    import streamk_b200 as sk
+    assert sk.column_block(3, 8, 28672) == (3 * 3584, 3584)
+    assert sk.peer_order(0, 1) == [] and sk.peer_order(6, 8) == [7, 0, 1, 2, 3, 4, 5]
+    with pytest.raises(ValueError):
+        sk.column_block(0, 3, 28672)        # does not divide
+    with pytest.raises(ValueError):
+        sk.column_block(0, 2, 24)           # blocks of 12 columns: not 16-byte aligned
+    with pytest.raises(ValueError):
+        sk.column_block(2, 2, 1024)
