@@ -90,8 +90,8 @@ __device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkP
 }
 
 // One float4 of the slot layout (row, columns gcol..gcol+3) -> fp16 C
-__device__ __forceinline__ void sk_store4_1(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
-                                            const float4& x) {
+__device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
+                                          const float4& x) {
   const float v[4] = {x.x, x.y, x.z, x.w};
   if (p.transposed) {
 #pragma unroll
@@ -114,11 +114,35 @@ __device__ __forceinline__ void sk_store4_1(__half* __restrict__ C, const SkPara
   }
 }
 
-__device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
-                                          const float4& x, const SkPeers* peers = nullptr) {
-  sk_store4_1(C, p, grow, gcol, x);
-  if (peers != nullptr)
-    for (int i = 0; i < peers->n; ++i) sk_store4_1(peers->c[i], p, grow, gcol, x);
+// Fused all-gather, split tiles: the reducers store with a row stride (consecutive threads take
+// consecutive rows of one 4-column group: whole lines of the fp32 partials in, 8 bytes per row
+// out), which the local L2 absorbs but NVLink does not.  So they store locally only, and this
+// copies what they stored from the local matrix to every peer in contiguous runs: one row per
+// warp and pass, 8 bytes per lane.  Items are the reducers' (item = 128 * column group + row) of
+// this CTA's 128 rows starting at r0; [begin, end) is the range the calling threads reduced.
+__device__ __forceinline__ void sk_copy_items_to_peers(const __half* C, const SkParams& p,
+                                                       const SkPeers* peers, int r0, int c0,
+                                                       int rows_valid, int begin, int end, int warp,
+                                                       int nwarps, int lane) {
+  for (int r = warp; r < rows_valid; r += nwarps) {
+    if (end - 1 - r < 0) continue;
+    const int qlo = begin - r > 0 ? (begin - r + SK_BM - 1) >> 7 : 0;
+    const int qhi = (end - 1 - r) >> 7;
+    const size_t row_off = static_cast<size_t>(r0 + r) * p.ldc + c0;
+    for (int q = qlo + lane; q <= qhi; q += 32) {
+      const size_t off = row_off + static_cast<size_t>(q) * 4;
+      if (c0 + q * 4 + 4 <= p.cols) {
+        const uint2 v = __ldcg(reinterpret_cast<const uint2*>(C + off));
+        for (int i = 0; i < peers->n; ++i) *reinterpret_cast<uint2*>(peers->c[i] + off) = v;
+      } else {
+        for (int e = 0; e < 4; ++e)
+          if (c0 + q * 4 + e < p.cols) {
+            const __half v = C[off + e];
+            for (int i = 0; i < peers->n; ++i) peers->c[i][off + e] = v;
+          }
+      }
+    }
+  }
 }
 
 struct SkPending {
@@ -134,7 +158,7 @@ template <int U, int V>
 __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __restrict__ C,
                                                    int first, int last, int rank, int r0,
                                                    int c0, int rows_valid, int begin, int end,
-                                                   int tid, int nthreads, const SkPeers* peers) {
+                                                   int tid, int nthreads) {
   for (int base = begin + tid; base < end; base += U * nthreads) {
     float4 acc[U];
     bool on[U];
@@ -174,7 +198,7 @@ __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int idx = base + u * nthreads;
-      if (on[u]) sk_store4(C, p, r0 + (idx & (SK_BM - 1)), c0 + (idx >> 7) * 4, acc[u], peers);
+      if (on[u]) sk_store4(C, p, r0 + (idx & (SK_BM - 1)), c0 + (idx >> 7) * 4, acc[u]);
     }
   }
 }
@@ -197,10 +221,14 @@ __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __res
   const int begin = static_cast<int>(static_cast<long long>(j) * L / n);
   const int end = static_cast<int>(static_cast<long long>(j + 1) * L / n);
   // The summation order (0 + p_first + p_first+1 + ...) is the same in every variant.
-  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
-  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
-  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
-  else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads, peers);
+  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  if (peers != nullptr) {   // (called by every thread of the CTA, see sk_reduce_pending)
+    __syncthreads();
+    sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, begin, end, tid >> 5, nthreads >> 5, tid & 31);
+  }
 }
 
 // Deferred block-reduce of the (at most two) split tiles this CTA took part in (see the
@@ -479,9 +507,13 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
             const int i = idx + u * EPI_THREADS;
             if (i < L && (i & (BM - 1)) < rows_valid) {
               __stcg(slot4 + i, zero);
-              sk_store4(C, p, r0 + (i & (BM - 1)), c0 + (i >> 7) * 4, x[u], peers);
+              sk_store4(C, p, r0 + (i & (BM - 1)), c0 + (i >> 7) * 4, x[u]);
             }
           }
+        }
+        if (peers != nullptr) {
+          named_bar_sync(EPI_BAR_ID, EPI_THREADS);
+          sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, 0, L, (warp - 2) & 3, 4, lane);
         }
         if (etid == 0) p.ws.counters[first_id] = 0u;
       }
