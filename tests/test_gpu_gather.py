@@ -71,19 +71,29 @@ def test_gather_writes_every_peer_like_the_plain_product(shape):
 
 
 def test_gather_with_wide_units_and_seven_peers():
-    M, N, K = 1024, 10240, 256
+    """The library's own tiling of a large block.  Few peers and a deep K: the 256 x 512 units
+    stay (the transfer hides under the mainloop).  Many peers and a shallow K: plain 256 x 256
+    tiles, so that the transfer starts earlier.  Either way every copy carries the bits of the
+    unfused product with the same tiling."""
     g = torch.Generator(device=DEV).manual_seed(11)
-    A = torch.randn(M, K, generator=g, device=DEV).half()
-    B = (torch.randn(N, K, generator=g, device=DEV) / K ** 0.5).half()
-    info = sk.schedule_info(M, N, K, kind="f16_pairs", schedule="hybrid", num_sms=74)
-    assert info["wide_units"] > 0
-    plain = sk.streamk_fp16_nt(A, B, fixup="block_reduce")
-    mats = [torch.zeros(M, N, dtype=torch.float16, device=DEV) for _ in range(8)]
-    st = _call_gather(A, B, mats[0], mats[1:], 0, "auto", "block_reduce", tile_m=0)
-    assert st == 0, L.load().sk_status_string(st)
-    sk.check_status()
-    for m in mats:
-        assert torch.equal(m, plain)
+    for K, n_peers, wide in ((2304, 1, True), (256, 7, False)):
+        M, N = 1024, 10240
+        A = torch.randn(M, K, generator=g, device=DEV).half()
+        B = (torch.randn(N, K, generator=g, device=DEV) / K ** 0.5).half()
+        info = sk.schedule_info(M, N, K, kind="f16_pairs", schedule="hybrid", num_sms=74)
+        assert info["wide_units"] > 0
+        if wide:
+            plain = sk.streamk_fp16_nt(A, B, fixup="block_reduce")
+        else:
+            plain = sk.streamk_fp16_nt(A, B, tile_m=256, schedule="hybrid", fixup="block_reduce")
+        ref = torch.matmul(A.float(), B.float().t())
+        assert float((plain.float() - ref).abs().max()) <= 1e-2 * float(ref.abs().max())
+        mats = [torch.zeros(M, N, dtype=torch.float16, device=DEV) for _ in range(n_peers + 1)]
+        st = _call_gather(A, B, mats[0], mats[1:], 0, "auto", "block_reduce", tile_m=0)
+        assert st == 0, L.load().sk_status_string(st)
+        sk.check_status()
+        for m in mats:
+            assert torch.equal(m, plain)
 
 
 def test_gather_argument_checks():
