@@ -74,16 +74,36 @@ class GatheredResult:
         lib = L.load()
         nbytes = self.M * self.n_total * 2
         self._own = C.c_void_p()
+        self._peer_base = {}
         handle = C.create_string_buffer(64)
         with torch.cuda.device(self.device):
-            L.check(lib.sk_peer_alloc(nbytes, C.byref(self._own), handle), "sk_peer_alloc")
-            handles = [None] * self.world
-            dist.all_gather_object(handles, handle.raw, group=group)
-            self._peer_base = {}
-            for r in peer_order(self.rank, self.world):
-                p = C.c_void_p()
-                L.check(lib.sk_peer_open(handles[r], C.byref(p)), "sk_peer_open")
-                self._peer_base[r] = p.value
+            # Every rank takes part in both exchanges whatever happened to it before, so that a
+            # failure on one rank (no memory, no peer access) raises on all of them instead of
+            # leaving the others waiting in a collective call.
+            err = ""
+            try:
+                L.check(lib.sk_peer_alloc(nbytes, C.byref(self._own), handle), "sk_peer_alloc")
+            except Exception as e:
+                err = f"rank {self.rank}: {e}"
+            said = [None] * self.world
+            dist.all_gather_object(said, (err, handle.raw), group=group)
+            if not any(e for e, _ in said):
+                try:
+                    for r in peer_order(self.rank, self.world):
+                        p = C.c_void_p()
+                        L.check(lib.sk_peer_open(said[r][1], C.byref(p)), "sk_peer_open")
+                        self._peer_base[r] = p.value
+                except Exception as e:
+                    err = f"rank {self.rank}: {e}"
+            errs = [None] * self.world
+            dist.all_gather_object(errs, err or next((e for e, _ in said if e), ""), group=group)
+            if any(errs):
+                for p in self._peer_base.values():
+                    lib.sk_peer_close(p)
+                dist.barrier(group=group)      # mappings first, then the memory they map
+                if self._own.value:
+                    lib.sk_peer_free(self._own)
+                raise RuntimeError("GatheredResult: " + "; ".join(sorted({e for e in errs if e})))
             self.full = torch.as_tensor(_DeviceBytes(self._own.value, nbytes), device=self.device) \
                 .view(torch.float16).view(self.M, self.n_total)
             if self.full.data_ptr() != self._own.value:
