@@ -451,6 +451,16 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   int st = sk_resolve_grid(prob, &num_sms, &dev_sms);
   if (st != SK_OK) return st;
   sk_problem resolved = *prob;   // SK_SCHED_AUTO -> a concrete schedule and tile
+  // Fused all-gather with more bytes to push than the links can take during the mainloop (about
+  // 600 GB/s out of a GPU against 1.3 PFLOP/s): plain 256 x 256 tiles instead of the 256 x 512
+  // units, whose first results (and with them the transfer) would start twice as late, and
+  // whole tiles only, because a split tile reaches the peers at the very end of the kernel.
+  // Measured on 8 GPUs, 8192 x 3584 x 8192 per GPU: 869 us with the units, 810 with hybrid
+  // 256 x 256 tiles, 780 data-parallel.
+  if (n_peers > 0 && resolved.tile_m == 0 && 2167LL * n_peers > prob->K) {
+    resolved.tile_m = 256;
+    if (resolved.schedule == SK_SCHED_AUTO) resolved.schedule = SK_SCHED_DP;
+  }
   sk_resolve_auto(&resolved, 1, num_sms);
   prob = &resolved;
   SkParams p;
@@ -459,11 +469,6 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   const bool pairs = prob->schedule != SK_SCHED_CLUSTER && use_cta_pairs(prob, num_sms);
   if (pairs) {
     sk_problem q = *prob;   // (tile_m: 256 = asked for by the caller, 0 = the library's own choice)
-    // Fused all-gather with more bytes to push than the links can take during the mainloop (about
-    // 600 GB/s out of a GPU against 1.3 PFLOP/s): plain 256 x 256 tiles instead of the 256 x 512
-    // units, whose first results (and with them the transfer) would start twice as late.
-    // Measured on 8 GPUs, 8192 x 3584 x 8192 per GPU: 808 against 869 us.
-    if (n_peers > 0 && q.tile_m == 0 && 2167LL * n_peers > prob->K) q.tile_m = 256;
     st = sk_make_sched(&q, 3, num_sms / 2, nullptr, &p.sched, &plan);
   } else {
     st = sk_make_sched(prob, 1, num_sms, nullptr, &p.sched, &plan);

@@ -73,7 +73,7 @@ def test_gather_writes_every_peer_like_the_plain_product(shape):
 def test_gather_with_wide_units_and_seven_peers():
     """The library's own tiling of a large block.  Few peers and a deep K: the 256 x 512 units
     stay (the transfer hides under the mainloop).  Many peers and a shallow K: plain 256 x 256
-    tiles, so that the transfer starts earlier.  Either way every copy carries the bits of the
+    tiles, data-parallel, so that the transfer starts earlier and nothing is left for the end.  Either way every copy carries the bits of the
     unfused product with the same tiling."""
     g = torch.Generator(device=DEV).manual_seed(11)
     for K, n_peers, wide in ((2304, 1, True), (256, 7, False)):
@@ -85,7 +85,7 @@ def test_gather_with_wide_units_and_seven_peers():
         if wide:
             plain = sk.streamk_fp16_nt(A, B, fixup="block_reduce")
         else:
-            plain = sk.streamk_fp16_nt(A, B, tile_m=256, schedule="hybrid", fixup="block_reduce")
+            plain = sk.streamk_fp16_nt(A, B, tile_m=256, schedule="dp", fixup="block_reduce")
         ref = torch.matmul(A.float(), B.float().t())
         assert float((plain.float() - ref).abs().max()) <= 1e-2 * float(ref.abs().max())
         mats = [torch.zeros(M, N, dtype=torch.float16, device=DEV) for _ in range(n_peers + 1)]
