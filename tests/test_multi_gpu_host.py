@@ -54,6 +54,11 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         for step in range(world - 1):
             assert sorted(o[step] for o in orders) == list(range(world))
         assert all(r not in orders[r] for r in range(world))
+        # no GPU here: the shared result matrices cannot be made, and every rank says so (none
+        # is left waiting in a collective call for a rank that gave up)
+        if not torch.cuda.is_available():
+            with pytest.raises(Exception):
+                sk.GatheredResult(M, N, device="cuda:0")
         # max-over-ranks timing reduction used by the benchmark
         t = torch.tensor([float(rank + 1)], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
