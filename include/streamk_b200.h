@@ -79,9 +79,10 @@ typedef struct sk_problem {
   int32_t num_sms;            /* 0 = all SMs of the device; else grid size    */
   int32_t group_m;            /* 0 = choose; tile rasterisation group height  */
   int32_t fixup_timeout_us;   /* 0 = default (2 s); bound of every device wait */
-  int32_t test_drop_flag_cta; /* -1 = off. Test only: this CTA never publishes
-                                 its block-reduce flag, so its tile owner runs
-                                 into the bounded wait and reports a timeout. */
+  int32_t test_drop_flag_cta; /* 0 (or negative) = off, so a zero-initialised struct is
+                                 an ordinary problem.  Test only: n > 0 makes CTA n - 1
+                                 never publish its block-reduce flag, so its tile owner
+                                 runs into the bounded wait and reports a timeout. */
   int32_t flags;              /* SK_FLAG_* bits                                */
 } sk_problem;
 
@@ -134,15 +135,19 @@ typedef struct sk_status {
 /* ---- library / device --------------------------------------------------- */
 const char* sk_version(void);
 const char* sk_status_string(int status);
-/* cudaError_t of the most recent SK_ERR_LAUNCH on this thread. */
+/* Cause of the most recent SK_ERR_LAUNCH on this thread: > 0 a cudaError_t of the runtime,
+ * < 0 the negated CUresult of a driver call (tensor-map encoding). */
 int sk_last_cuda_error(void);
 int sk_query(int device, sk_device_info* out);
 
-/* Debugging aid, no counterpart in the reference: while `buf` (device memory, 128 bytes per
- * SM) is set, tensor-core launches record %globaltimer stamps per CTA (16 slots of 8 bytes):
- * 0 entry, 1 set-up done, 2 first TMA issued, 3 first stage consumed, 4 last MMA issued,
- * 5 first accumulator ready, 6 epilogue done, 7 exit, 8 fixup flags seen, 9 / 10 first /
- * second split tile reduced, 11 flags re-armed.  NULL switches it off.                    */
+/* Debugging aid, no counterpart in the reference.  Works only in a library compiled with
+ * -DSK_TRACE (the build recipe's STREAMK_B200_TRACE=1); the ordinary build carries no tracing
+ * code in its kernels and this call then accepts NULL only (SK_ERR_ARG otherwise).  While
+ * `buf` (device memory, 128 bytes per SM) is set, tensor-core launches record %globaltimer
+ * stamps per CTA (16 slots of 8 bytes): 0 entry, 1 set-up done, 2 first TMA issued, 3 first
+ * stage consumed, 4 last MMA issued, 5 first accumulator ready, 6 epilogue done, 7 exit,
+ * 8 fixup flags seen, 9 / 10 first / second split tile reduced, 11 flags re-armed.  One
+ * pointer per process: set it while no launch is in flight.  NULL switches it off.       */
 int sk_debug_set_trace(void* buf);
 
 /* ---- scheduler (host only, no GPU needed) ------------------------------- */
@@ -186,7 +191,11 @@ int sk_gemm_f32(const sk_problem* p, const float* A, const float* B, float* C,
  * first call outside stream capture.  All calls on a device share the one array: calls
  * that can overlap on the GPU (different streams, different host threads) race and must
  * be serialised by the caller.  host_status may be NULL; otherwise the device status
- * word is copied into it asynchronously (valid once the stream is synchronised).       */
+ * word is copied into it asynchronously (valid once the stream is synchronised): pass
+ * pinned host memory -- with pageable memory the copy makes the call wait for the kernel,
+ * and it cannot be recorded into a stream capture -- or NULL and read the status some
+ * other way.  The per-device address look-up is remembered for the life of the process;
+ * a process that resets a device (cudaDeviceReset) must not call this on it afterwards. */
 int sk_gemm_f32_noalloc(const sk_problem* p, const float* A, const float* B, float* C,
                         sk_status* host_status, void* stream);
 

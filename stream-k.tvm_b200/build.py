@@ -2,6 +2,10 @@
 
 The library is a plain C-ABI shared object (no torch, no pybind): nvcc only.
 Objects are rebuilt when a source or header is newer than the object.
+
+STREAMK_B200_TRACE=1 builds a second library, lib/libstreamk_b200_trace.so, compiled with
+-DSK_TRACE: its kernels record per-CTA timestamps while sk_debug_set_trace() names a buffer.
+The ordinary library carries no tracing code.
 """
 from __future__ import annotations
 
@@ -16,11 +20,16 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(HERE, "build")
 LIBNAME = "libstreamk_b200.so"
+TRACE_LIBNAME = "libstreamk_b200_trace.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
+def trace_build() -> bool:
+    return os.environ.get("STREAMK_B200_TRACE") == "1"
+
+
 def lib_path() -> str:
-    return os.path.join(LIBDIR, LIBNAME)
+    return os.path.join(LIBDIR, TRACE_LIBNAME if trace_build() else LIBNAME)
 
 
 def _nvcc() -> str:
@@ -49,16 +58,19 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile (if needed) and return the path of the shared library."""
+    objdir = OBJDIR + ("_trace" if trace_build() else "")
     os.makedirs(LIBDIR, exist_ok=True)
-    os.makedirs(OBJDIR, exist_ok=True)
+    os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
     headers = _headers()
     common = [nvcc, "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS, "-Xcompiler", "-fPIC",
               "-Xptxas", "-v"]
+    if trace_build():
+        common.append("-DSK_TRACE")
     jobs = []
     objs = []
     for src in _sources():
-        obj = os.path.join(OBJDIR, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src, *headers]):
             jobs.append((src, obj))

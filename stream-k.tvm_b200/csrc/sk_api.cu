@@ -1,6 +1,8 @@
 // Library-level C ABI: version, device query, host scheduler, workspace.
 #include <string.h>
 
+#include <atomic>
+
 #include "sk_common.cuh"
 
 static thread_local int g_last_cuda_error = 0;
@@ -10,16 +12,28 @@ int sk_set_cuda_error(cudaError_t e) {
   return SK_ERR_LAUNCH;
 }
 
-static unsigned long long* g_trace = nullptr;
-unsigned long long* sk_trace_buffer() { return g_trace; }
+// A CUresult of the driver API (tensor-map encoding) is kept negated, so that
+// sk_last_cuda_error tells the two apart: > 0 cudaError_t, < 0 -CUresult.
+int sk_set_driver_error(int cu_result) {
+  g_last_cuda_error = -cu_result;
+  return SK_ERR_LAUNCH;
+}
 
-// Debugging aid (not part of the reference surface): later launches of the tensor-core
-// kernels record up to sixteen %globaltimer stamps per CTA into `buf` (device memory, 128
-// bytes per SM); pass NULL to switch it off.
+// Debugging aid (not part of the reference surface), present only in a library built with
+// -DSK_TRACE: later launches of the tensor-core kernels record up to sixteen %globaltimer
+// stamps per CTA into `buf` (device memory, 128 bytes per SM); NULL switches it off.  One
+// pointer for the process: a test-only switch, to be set while no launch is in flight.
+#ifdef SK_TRACE
+static std::atomic<unsigned long long*> g_trace{nullptr};
+unsigned long long* sk_trace_buffer() { return g_trace.load(std::memory_order_acquire); }
 extern "C" int sk_debug_set_trace(void* buf) {
-  g_trace = static_cast<unsigned long long*>(buf);
+  g_trace.store(static_cast<unsigned long long*>(buf), std::memory_order_release);
   return SK_OK;
 }
+#else
+unsigned long long* sk_trace_buffer() { return nullptr; }
+extern "C" int sk_debug_set_trace(void* buf) { return buf ? SK_ERR_ARG : SK_OK; }
+#endif
 
 extern "C" const char* sk_version(void) { return "streamk_b200 0.1 (sm_100a)"; }
 
@@ -57,21 +71,21 @@ extern "C" int sk_query(int device, sk_device_info* out) {
 
 // SM count of the current device (cached per device) and the grid bound asked for.
 int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out) {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];   // zero-initialised; racing first calls store the same value
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   if (dev < 0 || dev >= 64) return SK_ERR_ARG;
-  if (cached[dev] == 0) {
-    int sms = 0, major = 0;
+  int sms = cached[dev].load(std::memory_order_relaxed);
+  if (sms == 0) {
+    int major = 0;
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     if (major != 10) return SK_ERR_ARCH;
-    cached[dev] = sms;
+    cached[dev].store(sms, std::memory_order_relaxed);
   }
-  int sms = cached[dev];
   *device_sms_out = sms;
   if (p->num_sms > 0) {
     if (p->num_sms > sms) return SK_ERR_LIMIT;  // co-residency of all CTAs is required
@@ -324,16 +338,46 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
   return SK_OK;
 }
 
+// CTA pairs pay off once the problem fills every pair with several 256 x 256 tiles; they
+// are asked for explicitly with tile_m = 256.
+static bool use_cta_pairs(const sk_problem* prob, int num_sms) {
+  if (prob->layout != SK_LAYOUT_NT || (num_sms & 1) != 0) return false;
+  if (prob->schedule == SK_SCHED_CLUSTER) return false;
+  if (prob->tile_m == 256) return true;   // (tile_n: 0 = 256, or any multiple of 16 from 32; checked by the plan)
+  if (prob->tile_m != 0 || prob->tile_n != 0) return false;
+  const long long tiles = static_cast<long long>((prob->M + 255) / 256) * ((prob->N + 255) / 256);
+  return tiles >= 2LL * (num_sms / 2);
+}
+
+void sk_f16_dispatch(const sk_problem* in, int num_sms, int n_peers, sk_problem* out, int* kernel_kind,
+                     int* units) {
+  *out = *in;
+  // Fused all-gather with more bytes to push than the links can take during the mainloop (about
+  // 600 GB/s out of a GPU against 1.3 PFLOP/s): plain 256 x 256 tiles instead of the 256 x 512
+  // units, whose first results (and with them the transfer) would start twice as late, and
+  // whole tiles only, because a split tile reaches the peers at the very end of the kernel.
+  // Measured on 8 GPUs, 8192 x 3584 x 8192 per GPU: 869 us with the units, 810 with hybrid
+  // 256 x 256 tiles, 780 data-parallel.
+  if (n_peers > 0 && out->tile_m == 0 && 2167LL * n_peers > in->K) {
+    out->tile_m = 256;
+    if (out->schedule == SK_SCHED_AUTO) out->schedule = SK_SCHED_DP;
+  }
+  sk_resolve_auto(out, 1, num_sms);
+  const bool pairs = use_cta_pairs(out, num_sms);
+  *kernel_kind = pairs ? 3 : 1;
+  *units = pairs ? num_sms / 2 : num_sms;
+}
+
 extern "C" int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms,
                            sk_schedule_info* out) {
   if (!out || !p) return SK_ERR_ARG;
   if (kernel_kind < 0 || kernel_kind > 3) return SK_ERR_ARG;
   sk_problem q = *p;
-  sk_resolve_auto(&q, kernel_kind, num_sms);
-  // (auto may have chosen the CTA-pair kernel: its schedule runs over pairs)
-  if (kernel_kind == 1 && p->schedule == SK_SCHED_AUTO && p->tile_m == 0 && q.tile_m == 256) {
-    kernel_kind = 3;
-    num_sms /= 2;
+  if (kernel_kind == 1) {
+    // exactly what sk_gemm_f16 would run: the pair kernel's schedule runs over pairs
+    sk_f16_dispatch(p, num_sms, 0, &q, &kernel_kind, &num_sms);
+  } else {
+    sk_resolve_auto(&q, kernel_kind, num_sms);
   }
   const int st = sk_make_sched(&q, kernel_kind, num_sms, out, nullptr, nullptr);
   if (st == SK_OK) out->schedule = q.schedule;

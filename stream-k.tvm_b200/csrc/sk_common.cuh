@@ -96,7 +96,8 @@ struct SkParams {
   SkSched sched;
   int fixup;               // SK_FIXUP_*
   int c_vec_ok;            // C rows can take 16-byte stores
-  int drop_flag_cta;       // test hook, -1 = off
+  int drop_flag_cta;       // test hook (sk_problem.test_drop_flag_cta - 1): this CTA never publishes
+                           //    its block-reduce flag; negative = off
   unsigned long long timeout_ns;
   SkWorkspace ws;
   const void* row_img;     // SK_LOAD_IMAGE sources
@@ -114,9 +115,14 @@ struct alignas(64) SkPeers {
   int n;
 };
 
-// Debugging aid: record %globaltimer at a numbered point of this CTA's life.
+// Debugging aid, compiled in only with -DSK_TRACE (the shipped library carries none of it):
+// record %globaltimer at a numbered point of this CTA's life.
 __device__ __forceinline__ void sk_trace(const SkParams& p, int slot) {
+#ifdef SK_TRACE
   if (p.trace) p.trace[blockIdx.x * 16 + slot] = skptx::globaltimer_ns();
+#else
+  (void)p; (void)slot;
+#endif
 }
 
 // First reporter wins; later errors keep the first record.
@@ -150,12 +156,40 @@ struct SkPlan {
   int bm;            // tile extent along kernel-space rows (128 unless fitted, see SkParams::bm)
 };
 int sk_set_cuda_error(cudaError_t e);
+int sk_set_driver_error(int cu_result);   // a CUresult of the driver API; reported negated
 int sk_resolve_grid(const sk_problem* p, int* num_sms_out, int* device_sms_out);
 // kernel_kind 0: fp32 SIMT (64x64x16 tiles); 1: fp16 UMMA; 2: W4A16 UMMA.
 int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
                   SkSched* s, SkPlan* plan);
 unsigned long long* sk_trace_buffer();
 void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms);
+// What the fp16 entry point runs for a problem: SK_SCHED_AUTO resolved, the fused gather's
+// link-bound rule applied (n_peers > 0), and the kernel chosen: *kernel_kind = 1 (single-CTA
+// tiles, *units = num_sms) or 3 (CTA pairs, *units = num_sms / 2).  The one decision shared by
+// sk_gemm_f16 / sk_gemm_f16_gather and the inspection call sk_schedule(kind 1).
+void sk_f16_dispatch(const sk_problem* in, int num_sms, int n_peers, sk_problem* out, int* kernel_kind,
+                     int* units);
+
+// Per-device one-time set-up (kernel attributes): `fn` runs once per device ordinal per process,
+// under a lock, and again only if it failed.  A device reset (cudaDeviceReset) does not clear
+// the record: a process that resets a device must not use this library on it afterwards.
+#include <mutex>
+struct SkPerDeviceOnce {
+  std::mutex m;
+  bool done[64] = {false};
+  template <typename F>
+  cudaError_t run(F fn) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(m);
+    if (done[dev]) return cudaSuccess;
+    e = fn();
+    if (e == cudaSuccess) done[dev] = true;
+    return e;
+  }
+};
 
 // One launch path for the tensor-core kernels: optional cluster dimension (SK_SCHED_CLUSTER, CTA
 // pairs) and optional programmatic stream serialisation (SK_FLAG_PDL).

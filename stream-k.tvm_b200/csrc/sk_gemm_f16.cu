@@ -404,10 +404,7 @@ int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim, gstride,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    sk_set_cuda_error(cudaErrorInvalidValue);
-    return SK_ERR_LAUNCH;
-  }
+  if (r != CUDA_SUCCESS) return sk_set_driver_error(static_cast<int>(r));
   return SK_OK;
 }
 
@@ -432,16 +429,6 @@ void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_sta
 int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, void* C, SkParams* p,
                        void* const* peer_c, int n_peers, void* stream);
 
-// CTA pairs pay off once the problem fills every pair with several 256 x 256 tiles; they
-// are asked for explicitly with tile_m = 256.
-static bool use_cta_pairs(const sk_problem* prob, int num_sms) {
-  if (prob->layout != SK_LAYOUT_NT || (num_sms & 1) != 0) return false;
-  if (prob->tile_m == 256) return true;   // (tile_n: 0 = 256, or any multiple of 16 from 32; checked by the plan)
-  if (prob->tile_m != 0 || prob->tile_n != 0) return false;
-  const long long tiles = static_cast<long long>((prob->M + 255) / 256) * ((prob->N + 255) / 256);
-  return tiles >= 2LL * (num_sms / 2);
-}
-
 static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* C, void* const* peer_c,
                     int n_peers, void* ws, size_t ws_bytes, void* stream) {
   if (!prob || !A || !B || !C) return SK_ERR_ARG;
@@ -450,29 +437,16 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   int num_sms = 0, dev_sms = 0;
   int st = sk_resolve_grid(prob, &num_sms, &dev_sms);
   if (st != SK_OK) return st;
-  sk_problem resolved = *prob;   // SK_SCHED_AUTO -> a concrete schedule and tile
-  // Fused all-gather with more bytes to push than the links can take during the mainloop (about
-  // 600 GB/s out of a GPU against 1.3 PFLOP/s): plain 256 x 256 tiles instead of the 256 x 512
-  // units, whose first results (and with them the transfer) would start twice as late, and
-  // whole tiles only, because a split tile reaches the peers at the very end of the kernel.
-  // Measured on 8 GPUs, 8192 x 3584 x 8192 per GPU: 869 us with the units, 810 with hybrid
-  // 256 x 256 tiles, 780 data-parallel.
-  if (n_peers > 0 && resolved.tile_m == 0 && 2167LL * n_peers > prob->K) {
-    resolved.tile_m = 256;
-    if (resolved.schedule == SK_SCHED_AUTO) resolved.schedule = SK_SCHED_DP;
-  }
-  sk_resolve_auto(&resolved, 1, num_sms);
+  sk_problem resolved;   // SK_SCHED_AUTO -> a concrete schedule and tile, and the kernel to run
+  int kind = 1, units = num_sms;
+  sk_f16_dispatch(prob, num_sms, n_peers, &resolved, &kind, &units);
   prob = &resolved;
   SkParams p;
   memset(&p, 0, sizeof(p));
   SkPlan plan;
-  const bool pairs = prob->schedule != SK_SCHED_CLUSTER && use_cta_pairs(prob, num_sms);
-  if (pairs) {
-    sk_problem q = *prob;   // (tile_m: 256 = asked for by the caller, 0 = the library's own choice)
-    st = sk_make_sched(&q, 3, num_sms / 2, nullptr, &p.sched, &plan);
-  } else {
-    st = sk_make_sched(prob, 1, num_sms, nullptr, &p.sched, &plan);
-  }
+  const bool pairs = kind == 3;
+  // (pairs: tile_m 256 = asked for by the caller, 0 = the library's own choice)
+  st = sk_make_sched(prob, kind, units, nullptr, &p.sched, &plan);
   if (st != SK_OK) return st;
   const int layout = prob->layout;
   const int M = prob->M, N = prob->N, K = prob->K;
@@ -496,7 +470,7 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   p.bm = plan.bm;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
-  p.drop_flag_cta = prob->test_drop_flag_cta;
+  p.drop_flag_cta = prob->test_drop_flag_cta - 1;
   p.timeout_ns = (prob->fixup_timeout_us > 0 ? static_cast<unsigned long long>(prob->fixup_timeout_us)
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);  // layout fixed per device, whatever the grid
@@ -574,25 +548,22 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   }
   const int smem_bytes =
       p.stages * p.kgroup * (ROW_STAGE_BYTES + p.col_stage_bytes) + 1024 + CTRL_BYTES + recv_bytes;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaSuccess;
+  static SkPerDeviceOnce attrs;
+  cudaError_t e = attrs.run([]() {
+    cudaError_t r = cudaSuccess;
     const void* kernels[4] = {
         reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_EPI_ATOMIC>),
         reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_EPI_BLOCK_REDUCE>),
         reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_EPI_WHOLE>),
         reinterpret_cast<const void*>(sk_gemm_f16_kernel<SK_MODE_CLUSTER>)};
-    for (int i = 0; i < 4 && e == cudaSuccess; ++i)
-      e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
-    if (e != cudaSuccess) return sk_set_cuda_error(e);
-    attr_set[dev & 63] = true;
-  }
+    for (int i = 0; i < 4 && r == cudaSuccess; ++i)
+      r = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    return r;
+  });
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
   const cudaStream_t cs = static_cast<cudaStream_t>(stream);
   __half* Ch = static_cast<__half*>(C);
   const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
-  cudaError_t e;
   if (split)
     e = sk_launch(sk_gemm_f16_kernel<SK_MODE_CLUSTER>, p.sched.grid, NUM_THREADS, smem_bytes, cs, split, pdl,
                   tmRow, tmCol, tmC, Ch, p);

@@ -421,21 +421,18 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   p->stages = STAGES;
   p->idesc = umma_idesc_f16(2 * BM, bn, 0);
 
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<false>,
+  static SkPerDeviceOnce attrs;
+  cudaError_t e = attrs.run([]() {
+    cudaError_t r = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (r == cudaSuccess)
+      r = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                SMEM_BYTES);
-    if (e != cudaSuccess) return sk_set_cuda_error(e);
-    attr_set[dev & 63] = true;
-  }
+    return r;
+  });
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
   const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
-  cudaError_t e =
-      n_peers > 0 ? sk_launch(sk_gemm_f16_2cta_kernel<true>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
+  e = n_peers > 0 ? sk_launch(sk_gemm_f16_2cta_kernel<true>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
                               static_cast<cudaStream_t>(stream), 2, pdl, tmA, tmB, tmC,
                               static_cast<__half*>(C), *p, peer_set)
                   : sk_launch(sk_gemm_f16_2cta_kernel<false>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,

@@ -204,7 +204,7 @@ extern "C" int sk_gemm_f32(const sk_problem* prob, const float* A, const float* 
   p.M = prob->M; p.N = prob->N; p.K = prob->K;
   p.lda = prob->lda; p.ldb = prob->ldb; p.ldc = prob->ldc;
   p.fixup = prob->fixup;
-  p.drop_flag_cta = prob->test_drop_flag_cta;
+  p.drop_flag_cta = prob->test_drop_flag_cta - 1;
   p.timeout_ns = (prob->fixup_timeout_us > 0 ? static_cast<unsigned long long>(prob->fixup_timeout_us)
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);  // layout fixed per device, whatever the grid
@@ -310,7 +310,7 @@ extern "C" int sk_gemm_f32_noalloc(const sk_problem* prob, const float* A, const
   p.M = q.M; p.N = q.N; p.K = q.K;
   p.lda = q.lda; p.ldb = q.ldb; p.ldc = q.ldc;
   p.fixup = q.fixup;
-  p.drop_flag_cta = q.test_drop_flag_cta;
+  p.drop_flag_cta = q.test_drop_flag_cta - 1;
   p.timeout_ns = (q.fixup_timeout_us > 0 ? static_cast<unsigned long long>(q.fixup_timeout_us)
                                          : 2000000ULL) * 1000ULL;
   p.ws = w;

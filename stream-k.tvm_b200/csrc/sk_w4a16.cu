@@ -599,7 +599,7 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   p.bm = BM;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
-  p.drop_flag_cta = prob->test_drop_flag_cta;
+  p.drop_flag_cta = prob->test_drop_flag_cta - 1;
   p.timeout_ns = (prob->fixup_timeout_us > 0 ? static_cast<unsigned long long>(prob->fixup_timeout_us)
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);
@@ -643,25 +643,22 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   // the staging area of the cluster exchange lives in the rings
   if (split && bs * W_STAGE_BYTES + ls * load_stage < recv_bytes) return SK_ERR_SHAPE;
   const int smem_bytes = bs * W_STAGE_BYTES + ls * load_stage + 1024 + CTRL_BYTES + recv_bytes;
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaSuccess;
+  static SkPerDeviceOnce attrs;
+  cudaError_t e = attrs.run([]() {
+    cudaError_t r = cudaSuccess;
     const void* kernels[4] = {
         reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_EPI_ATOMIC>),
         reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_EPI_BLOCK_REDUCE>),
         reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_EPI_WHOLE>),
         reinterpret_cast<const void*>(sk_gemm_w4a16_kernel<SK_MODE_CLUSTER>)};
-    for (int i = 0; i < 4 && e == cudaSuccess; ++i)
-      e = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
-    if (e != cudaSuccess) return sk_set_cuda_error(e);
-    attr_set[dev & 63] = true;
-  }
+    for (int i = 0; i < 4 && r == cudaSuccess; ++i)
+      r = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    return r;
+  });
+  if (e != cudaSuccess) return sk_set_cuda_error(e);
   const cudaStream_t cs = static_cast<cudaStream_t>(stream);
   __half* Ch = static_cast<__half*>(C);
   const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
-  cudaError_t e;
   if (split)
     e = sk_launch(sk_gemm_w4a16_kernel<SK_MODE_CLUSTER>, p.sched.grid, NUM_THREADS, smem_bytes, cs, split, pdl,
                   tmA, qb, sz, Ch, p);

@@ -56,7 +56,9 @@ class GatheredResult:
 
     `full` is the local matrix (a torch tensor over the library's allocation), `block` the
     view of this rank's own columns.  Collective: every rank of the group constructs it (and
-    closes it) at the same point of the program.
+    closes it) at the same point of the program.  Usable as a context manager; leaving the
+    block closes it, also on an exception -- but close() is itself collective, so ranks that
+    may fail independently must first agree on the outcome (all_agree) and leave together.
     """
 
     def __init__(self, M: int, n_total: int, group=None, device=None):
@@ -114,6 +116,21 @@ class GatheredResult:
         self._peer_ptrs = (C.c_void_p * max(1, self.world - 1))(
             *[self._peer_base[r] + off for r in peer_order(self.rank, self.world)])
         self._open = True
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        self.close()
+        return False
+
+    def all_agree(self, ok: bool) -> bool:
+        """Collective AND of a per-rank flag (an all-reduce MIN, synchronising): ranks use it at
+        fixed points to decide together whether to go on, so that a failure on one rank never
+        leaves the others inside a collective that will not be matched."""
+        t = torch.tensor([1.0 if ok else 0.0], device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(t.item() == 1.0)
 
     def meet(self) -> None:
         """Stream-ordered rendezvous of the group (an all-reduce of one element)."""

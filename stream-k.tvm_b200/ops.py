@@ -23,7 +23,7 @@ __all__ = [
     "streamk_fp16_block_reduce", "ladder_prepack", "streamk_fp16_ladder",
     "streamk_fp16_ladder_block_reduce", "q4_prepack", "dequant_w4",
     "streamk_fp16_ladder_block_reduce_q4", "schedule_info", "check_status",
-    "reset_workspace", "device_info", "LadderWeight", "PackedQ4", "StreamKError", "SCHEDULES", "FIXUPS",
+    "reset_workspace", "release_cached_memory", "cached_memory_bytes", "device_info", "LadderWeight", "PackedQ4", "StreamKError", "SCHEDULES", "FIXUPS",
 ]
 
 StreamKError = L.StreamKError
@@ -46,6 +46,10 @@ class _Workspace:
                 "sk_workspace_init")
 
 
+# Device memory this module keeps between calls: one workspace (sk_workspace_bytes, about
+# 57 MB on 148 SMs) per (device, stream) that ever launched a GEMM, and the staging buffers of
+# streamk_fp16_nt_host per (device, shape, slab).  cached_memory_bytes() reports them,
+# release_cached_memory() drops them.
 _workspaces: dict[tuple[int, int], _Workspace] = {}
 
 
@@ -72,6 +76,23 @@ def reset_workspace(device=None) -> None:
     with torch.cuda.device(device):
         L.check(L.load().sk_workspace_init(ws.buf.data_ptr(), ws.nbytes, _stream_ptr(device)),
                 "sk_workspace_init")
+
+
+def cached_memory_bytes() -> int:
+    """Device bytes held by the cached workspaces and host-pipeline staging buffers."""
+    n = sum(ws.nbytes for ws in _workspaces.values())
+    for pipe in _host_pipes.values():
+        n += pipe.nbytes
+    return n
+
+
+def release_cached_memory() -> None:
+    """Drop every cached workspace and staging buffer (all devices).  Synchronises the devices
+    first, so nothing in flight still uses them; the next call allocates afresh."""
+    for dev in {k[0] for k in _workspaces} | {k[0] for k in _host_pipes}:
+        torch.cuda.synchronize(dev)
+    _workspaces.clear()
+    _host_pipes.clear()
 
 
 def check_status(device=None) -> None:
@@ -108,14 +129,11 @@ def _options(kw: dict) -> dict:
                      rasterisation), out (result buffer), timeout_us (bound of every device
                      wait), pdl (True: programmatic dependent launch, the kernel's start-up may
                      overlap the tail of the previous kernel of the stream; fp16 / W4A16),
-                     _drop_flag_cta (test hook)."""
+                     _drop_flag_cta (test hook: index of a CTA that withholds its flag)."""
     unknown = set(kw) - set(_OPTION_KEYS)
     if unknown:
         raise TypeError(f"unexpected keyword argument(s): {sorted(unknown)}")
-    o = {k: kw.get(k) for k in _OPTION_KEYS}
-    if o["_drop_flag_cta"] is None:
-        o["_drop_flag_cta"] = -1
-    return o
+    return {k: kw.get(k) for k in _OPTION_KEYS}
 
 
 def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkProblem:
@@ -128,7 +146,8 @@ def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkPr
                        tile_m=int(o["tile_m"] or 0), tile_n=int(o["tile_n"] or 0),
                        num_sms=int(o["num_sms"] or 0), group_m=int(o["group_m"] or 0),
                        fixup_timeout_us=int(o["timeout_us"] or 0),
-                       test_drop_flag_cta=int(o["_drop_flag_cta"]),
+                       # (the C field is 0 = off, n = CTA n - 1)
+                       test_drop_flag_cta=0 if o["_drop_flag_cta"] is None else int(o["_drop_flag_cta"]) + 1,
                        flags=L.SK_FLAG_PDL if o["pdl"] else 0)
 
 
@@ -278,9 +297,12 @@ class _HostPipe:
         self.B = [torch.empty(slab, K, dtype=torch.float16, device=device) for _ in range(2)]
         self.C = [torch.empty(M, slab, dtype=torch.float16, device=device) for _ in range(2)]
         self.s_in, self.s_mm, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
+        self.nbytes = 2 * (M * K + 2 * slab * K + 2 * M * slab)
+        self.busy = None     # event recorded at the end of the last call that used these buffers
 
 
 _host_pipes: dict[tuple, _HostPipe] = {}
+_HOST_PIPES_MAX = 4     # staging sets kept; the least recently used one is dropped beyond that
 
 
 def streamk_fp16_nt_host(A_host, B_host, out_host=None, *, slabs: int = 8, device=None,
@@ -313,12 +335,21 @@ def streamk_fp16_nt_host(A_host, B_host, out_host=None, *, slabs: int = 8, devic
     if not (A_host.is_contiguous() and B_host.is_contiguous()):
         raise ValueError("A_host and B_host must be contiguous")
     key = (device.index, M, N, K, slab)
-    pipe = _host_pipes.get(key)
+    pipe = _host_pipes.pop(key, None)
     if pipe is None:
-        pipe = _host_pipes[key] = _HostPipe(M, N, K, slab, device)
+        while len(_host_pipes) >= _HOST_PIPES_MAX:
+            old = _host_pipes.pop(next(iter(_host_pipes)))
+            if old.busy is not None:
+                old.busy.synchronize()      # its last call may still be running
+        pipe = _HostPipe(M, N, K, slab, device)
+    _host_pipes[key] = pipe                 # (most recently used last)
     cur = torch.cuda.current_stream(device)
     for st in (pipe.s_in, pipe.s_mm, pipe.s_out):
-        st.wait_stream(cur)                 # staging buffers of a previous call are free again
+        st.wait_stream(cur)
+        # The staging buffers are free again only when the previous call that used them has
+        # finished, whichever stream that call was made from.
+        if pipe.busy is not None:
+            st.wait_event(pipe.busy)
     with torch.cuda.stream(pipe.s_in):
         pipe.A.copy_(A_host, non_blocking=True)
     mm_done = [None, None]                  # per staging buffer: GEMM that last read B / wrote C
@@ -353,6 +384,8 @@ def streamk_fp16_nt_host(A_host, B_host, out_host=None, *, slabs: int = 8, devic
     cur.wait_stream(pipe.s_out)
     cur.wait_stream(pipe.s_mm)
     cur.wait_stream(pipe.s_in)
+    pipe.busy = torch.cuda.Event()
+    pipe.busy.record(cur)
     return out_host
 
 

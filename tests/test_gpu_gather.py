@@ -32,7 +32,7 @@ def _call_gather(A, B, full, peers_full, col0, schedule, fixup, tile_m=256, tile
     N = B.shape[0]
     prob = L.SkProblem(M=M, N=N, K=K, lda=A.stride(0), ldb=B.stride(0), ldc=full.stride(0),
                        layout=L.LAYOUTS["nt"], schedule=L.SCHEDULES[schedule], fixup=L.FIXUPS[fixup],
-                       tile_m=tile_m, tile_n=tile_n, num_sms=num_sms, test_drop_flag_cta=-1)
+                       tile_m=tile_m, tile_n=tile_n, num_sms=num_sms)
     ptrs = (C.c_void_p * max(1, len(peers_full)))(*[p[:, col0:].data_ptr() for p in peers_full])
     ws = _ops._workspace(DEV)
     st = lib.sk_gemm_f16_gather(C.byref(prob), A.data_ptr(), B.data_ptr(), full[:, col0:].data_ptr(), ptrs,
@@ -120,13 +120,19 @@ def _free_port() -> int:
 
 
 def _rank_main(rank: int, world: int, port: int, out_dir: str):
+    """One rank of the multi-GPU test.  A failed check on one rank must not strand the others
+    in a collective: every iteration ends with an agreed verdict (all_agree), all ranks leave
+    the loop together, and the process group has a short timeout as a last resort."""
+    import datetime
+    import traceback
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
     try:
         M, K, n_total = 512, 384, 1024 * world
         g = torch.Generator().manual_seed(77)
@@ -135,26 +141,38 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
         ref = oracle.gemm_ref(A, Bfull, "nt")
         col0, width = sk.column_block(rank, world, n_total)
         Ad, Bd = A.to(dev), Bfull[col0:col0 + width].to(dev)
-        res = sk.GatheredResult(M, n_total)
-        try:
+        failure = ""
+        with sk.GatheredResult(M, n_total) as res:
             for it, (schedule, fixup) in enumerate((("hybrid", "block_reduce"), ("streamk", "atomic"),
                                                     ("dp", "block_reduce"))):
-                res.full.fill_(float(it))          # stale contents the call must replace everywhere
-                out = sk.streamk_fp16_nt_gather(Ad, Bd, res, schedule=schedule, fixup=fixup)
-                torch.cuda.synchronize(dev)
-                sk.check_status(dev)
-                assert oracle.rel_err(out.cpu(), ref) <= 1e-2, (rank, schedule, fixup)
-                own = sk.streamk_fp16_nt(Ad, Bd, tile_m=256, schedule=schedule, fixup=fixup)
-                if fixup == "block_reduce":
-                    assert torch.equal(out[:, col0:col0 + width], own)
-                # every rank ends up with the same bits
-                mine = out.contiguous()
+                try:
+                    res.full.fill_(float(it))          # stale contents the call must replace everywhere
+                    out = sk.streamk_fp16_nt_gather(Ad, Bd, res, schedule=schedule, fixup=fixup)
+                    torch.cuda.synchronize(dev)
+                    mine = out.contiguous()
+                except Exception:
+                    failure = traceback.format_exc()
+                    mine = torch.zeros(M, n_total, dtype=torch.float16, device=dev)
+                # (the collectives below are reached by every rank whatever happened above)
                 parts = [torch.empty_like(mine) for _ in range(world)]
                 dist.all_gather(parts, mine)
-                assert all(torch.equal(p, mine) for p in parts)
-        finally:
-            res.close()
-        open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
+                if not failure:
+                    try:
+                        sk.check_status(dev)
+                        assert oracle.rel_err(out.cpu(), ref) <= 1e-2, (rank, schedule, fixup)
+                        own = sk.streamk_fp16_nt(Ad, Bd, tile_m=256, schedule=schedule, fixup=fixup)
+                        if fixup == "block_reduce":
+                            assert torch.equal(out[:, col0:col0 + width], own)
+                        # every rank ends up with the same bits
+                        assert all(torch.equal(p, mine) for p in parts)
+                    except Exception:
+                        failure = traceback.format_exc()
+                if not res.all_agree(not failure):
+                    break
+        if failure:
+            open(os.path.join(out_dir, f"fail{rank}"), "w").write(failure)
+        else:
+            open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
 
@@ -164,4 +182,6 @@ def test_gather_across_gpus(tmp_path):
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 8)
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    fails = [open(tmp_path / f"fail{r}").read() for r in range(world) if os.path.exists(tmp_path / f"fail{r}")]
+    assert not fails, "\n".join(fails)
     assert all(os.path.exists(tmp_path / f"ok{r}") for r in range(world))

@@ -10,8 +10,7 @@ import oracle
 def _sched(lib, M, N, K, kind, schedule, P, tile_n=0, group_m=0):
     from streamk_b200 import _lib as L
     prob = L.SkProblem(M=M, N=N, K=K, lda=K, ldb=K, ldc=N, layout=1, schedule=L.SCHEDULES[schedule],
-                       fixup=0, tile_n=tile_n, num_sms=0, group_m=group_m, fixup_timeout_us=0,
-                       test_drop_flag_cta=-1)
+                       fixup=0, tile_n=tile_n, num_sms=0, group_m=group_m, fixup_timeout_us=0)
     info = L.SkScheduleInfo()
     st = lib.sk_schedule(C.byref(prob), kind, P, C.byref(info))
     assert st == 0, st
@@ -261,3 +260,29 @@ def test_pair_kernel_wide_units(lib):
             # the Stream-K part splits its iterations evenly over the pairs
             tot = d["sk_tiles"] * d["iters_per_tile"]
             assert d["sk_iters_per_cta"] * d["grid"] + d["sk_iters_rem"] == tot
+
+
+def test_inspection_call_reports_what_the_fp16_entry_point_runs(lib):
+    """sk_schedule(kind 1, auto) and sk_gemm_f16 share one decision (sk_f16_dispatch): for a
+    large NT problem the entry point runs the CTA-pair kernel (256 x 256 tiles, 74 pairs,
+    256 x 512 units), and the inspection call must say so, not describe 128-row tiles."""
+    from streamk_b200 import _lib as L
+    info = L.SkScheduleInfo()
+    prob = L.SkProblem(M=8192, N=3584, K=8192, lda=8192, ldb=8192, ldc=3584, layout=1,
+                       schedule=L.SCHEDULES["auto"])
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    d = info.as_dict()
+    assert (d["tile_m"], d["tile_n"], d["grid"]) == (256, 256, 74)
+    assert d["wide_units"] == 222 and d["sk_tiles"] == 4 and d["schedule"] == L.SCHEDULES["hybrid"]
+    # the same problem in the NN layout has no pair kernel: single-CTA tiles on every SM
+    prob.layout = 0
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    assert (info.tile_m, info.grid, info.wide_units) == (128, 148, 0)
+    # an odd SM count cannot pair up either
+    prob.layout = 1
+    assert lib.sk_schedule(C.byref(prob), 1, 147, C.byref(info)) == 0
+    assert (info.tile_m, info.grid) == (128, 147)
+    # a zero-initialised problem with only the shape filled in is a valid question
+    z = L.SkProblem()
+    z.M, z.N, z.K = 384, 384, 8192
+    assert lib.sk_schedule(C.byref(z), 1, 148, C.byref(info)) == 0 and info.total_tiles > 0

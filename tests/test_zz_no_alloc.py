@@ -18,8 +18,7 @@ TOL32 = 1e-4   # the fp32 bar of the other GPU tests
 
 def _problem(L, M, N, K, fixup, num_sms):
     return L.SkProblem(M=M, N=N, K=K, lda=K, ldb=N, ldc=N, layout=L.LAYOUTS["nn"],
-                       schedule=L.SCHEDULES["streamk"], fixup=L.FIXUPS[fixup], num_sms=num_sms,
-                       test_drop_flag_cta=-1)
+                       schedule=L.SCHEDULES["streamk"], fixup=L.FIXUPS[fixup], num_sms=num_sms)
 
 
 @pytest.mark.parametrize("fixup", ["atomic", "block_reduce"])
