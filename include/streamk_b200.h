@@ -87,14 +87,17 @@ typedef struct sk_problem {
 } sk_problem;
 
 /* sk_problem.flags */
-enum { SK_FLAG_PDL = 1 /* fp16 / W4A16 entry points: launch with programmatic stream
+enum { SK_FLAG_PDL = 1, /* fp16 / W4A16 entry points: launch with programmatic stream
                           serialisation.  The kernel's start-up (mbarrier set-up, tensor-memory
                           allocation, scheduling arithmetic) may then overlap the tail of the
                           kernel before it in the stream if that kernel lets its dependents go
                           early (these kernels do, at entry); nothing touches global memory
                           before the preceding kernel has completed (griddepcontrol.wait), so
                           results and stream order are unchanged.  Worth 1-2 us per launch in a
-                          chain of small GEMMs.                                            */ };
+                          chain of small GEMMs.                                            */
+       SK_FLAG_NO_TABLE = 2 /* SK_SCHED_AUTO: resolve by the built-in rules only, without
+                          consulting the table of tuned shapes (what the offline tuner itself
+                          uses to time the rules' choice).                                 */ };
 
 /* Host scheduler result: the integers of streamk_fp16.py:83-113 plus the
  * derived per-CTA split, exposed so callers and tests can inspect them.     */
@@ -151,9 +154,14 @@ int sk_query(int device, sk_device_info* out);
 int sk_debug_set_trace(void* buf);
 
 /* ---- scheduler (host only, no GPU needed) ------------------------------- */
-/* kernel_kind: 0 = fp32 SIMT tiles (64x64x16), 1 = fp16 UMMA tiles, 2 = W4A16 UMMA
- * tiles (tile_m x tile_n x 64).  Mirrors streamk_fp16.py:83-113 for SK_SCHED_HYBRID. */
+/* kernel_kind: 0 = fp32 SIMT tiles (64x64x16), 1 = what sk_gemm_f16 runs for the problem
+ * (single-CTA UMMA tiles, or the CTA-pair kernel over num_sms / 2 pairs: the info then
+ * describes 256-row tiles), 2 = W4A16 UMMA tiles (tile_m x tile_n x 64), 3 = the CTA-pair
+ * kernel with num_sms pairs.  Mirrors streamk_fp16.py:83-113 for SK_SCHED_HYBRID. */
 int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* out);
+/* The same question for sk_gemm_f16_gather with n_peers peers (a link-bound gather makes the
+ * library drop the 256 x 512 units and, if the schedule was left to it, run data-parallel). */
+int sk_schedule_gather(const sk_problem* p, int n_peers, int num_sms, sk_schedule_info* out);
 /* Iteration interval [begin,end) of CTA `cta` (streamk_fp16.py:176-181). */
 int sk_cta_interval(const sk_schedule_info* s, int cta, int64_t* begin, int64_t* end);
 /* Tile id -> (tile row, tile column) under the grouped rasterisation. */

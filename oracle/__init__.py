@@ -26,3 +26,22 @@ Parity status
 from .gemm_ref import gemm_ref, unpack_u4, pack_u4_int32, dequant_ref, w4a16_ref, rel_err  # noqa: F401
 from .sched_ref import reference_schedule, cta_segments, cluster_segments, coverage, tile_coords  # noqa: F401
 from .inputs import make_case, CONFIGS  # noqa: F401
+
+
+def load_triton_ref():
+    """The reference's own Triton Stream-K kernel (oracle/_ref/triton_streamk.py, generated from a
+    reference checkout by oracle/make_triton_ref.py), or None when the file or triton is absent.
+    A GPU comparator for tests/ and bench.py's sweep; importing it compiles nothing yet."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "triton_streamk.py")
+    if not os.path.exists(path):
+        return None
+    try:
+        import triton  # noqa: F401
+    except Exception:
+        return None
+    spec = importlib.util.spec_from_file_location("oracle_ref_triton_streamk", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod

@@ -19,6 +19,7 @@ LAYOUTS = {"nn": 0, "nt": 1, "ladder": 2}
 SCHEDULES = {"streamk": 0, "hybrid": 1, "hybrid_dp_first": 2, "dp": 3, "auto": 4, "cluster": 5}
 FIXUPS = {"atomic": 0, "block_reduce": 1}
 SK_FLAG_PDL = 1
+SK_FLAG_NO_TABLE = 2
 
 
 class SkProblem(C.Structure):
@@ -57,6 +58,7 @@ SIGNATURES = {
     "sk_query": (C.c_int, [C.c_int, C.POINTER(SkDeviceInfo)]),
     "sk_debug_set_trace": (C.c_int, [_P]),
     "sk_schedule": (C.c_int, [C.POINTER(SkProblem), C.c_int, C.c_int, C.POINTER(SkScheduleInfo)]),
+    "sk_schedule_gather": (C.c_int, [C.POINTER(SkProblem), C.c_int, C.c_int, C.POINTER(SkScheduleInfo)]),
     "sk_cta_interval": (C.c_int, [C.POINTER(SkScheduleInfo), C.c_int, C.POINTER(C.c_int64),
                                   C.POINTER(C.c_int64)]),
     "sk_tile_coords": (C.c_int, [C.POINTER(SkScheduleInfo), C.c_int, C.POINTER(C.c_int),

@@ -155,11 +155,34 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
 //    most SMs busy, run them data-parallel with the tile width fitted to the SM count;
 //  * otherwise every SM has to stream (a single SM ingests only ~110 GB/s): Stream-K;
 //  * large problems: the reference's hybrid split.
+// Shapes for which the offline tuner (`python bench.py --tune FILE`, which times the candidates
+// and rejects any whose result is out of tolerance) found something better than the rules
+// below.  Consulted first, for exact (kind, M, N, K, SM count) matches with open tile sizes.
+namespace {
+struct SkTuned { int kind, M, N, K, sms, schedule, tile_m, tile_n; };
+const SkTuned kTuned[] = {
+#include "sk_tuned_table.inc"
+    {-1, 0, 0, 0, 0, 0, 0, 0}};
+}  // namespace
+
 void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
   if (q->schedule != SK_SCHED_AUTO) return;
   q->schedule = SK_SCHED_HYBRID;
   if (kernel_kind == 0 || kernel_kind == 3) return;
   const bool tiles_open = q->tile_m == 0 && q->tile_n == 0;
+  if (tiles_open && (q->flags & SK_FLAG_NO_TABLE) == 0) {
+    for (const SkTuned* t = kTuned; t->kind >= 0; ++t) {
+      if (t->kind != kernel_kind || t->M != q->M || t->N != q->N || t->K != q->K || t->sms != num_sms) continue;
+      sk_problem c = *q;
+      c.schedule = t->schedule; c.tile_m = t->tile_m; c.tile_n = t->tile_n;
+      // (a row that no longer plans -- the kernels changed since it was written -- is ignored)
+      const bool pairs = kernel_kind == 1 && t->tile_m == 256;
+      if (sk_make_sched(&c, pairs ? 3 : kernel_kind, pairs ? num_sms / 2 : num_sms, nullptr, nullptr, nullptr) == SK_OK) {
+        *q = c;
+        return;
+      }
+    }
+  }
   const long long t256 = static_cast<long long>((q->M + 255) / 256) * ((q->N + 255) / 256);
   if (t256 >= num_sms) return;                       // large: hybrid (CTA pairs when eligible)
   if ((kernel_kind == 1 || kernel_kind == 2) && (q->K + 63) / 64 >= 8) {
@@ -368,20 +391,30 @@ void sk_f16_dispatch(const sk_problem* in, int num_sms, int n_peers, sk_problem*
   *units = pairs ? num_sms / 2 : num_sms;
 }
 
-extern "C" int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms,
-                           sk_schedule_info* out) {
+static int schedule_for(const sk_problem* p, int kernel_kind, int num_sms, int n_peers,
+                        sk_schedule_info* out) {
   if (!out || !p) return SK_ERR_ARG;
   if (kernel_kind < 0 || kernel_kind > 3) return SK_ERR_ARG;
   sk_problem q = *p;
   if (kernel_kind == 1) {
     // exactly what sk_gemm_f16 would run: the pair kernel's schedule runs over pairs
-    sk_f16_dispatch(p, num_sms, 0, &q, &kernel_kind, &num_sms);
+    sk_f16_dispatch(p, num_sms, n_peers, &q, &kernel_kind, &num_sms);
   } else {
     sk_resolve_auto(&q, kernel_kind, num_sms);
   }
   const int st = sk_make_sched(&q, kernel_kind, num_sms, out, nullptr, nullptr);
   if (st == SK_OK) out->schedule = q.schedule;
   return st;
+}
+
+extern "C" int sk_schedule(const sk_problem* p, int kernel_kind, int num_sms,
+                           sk_schedule_info* out) {
+  return schedule_for(p, kernel_kind, num_sms, 0, out);
+}
+
+extern "C" int sk_schedule_gather(const sk_problem* p, int n_peers, int num_sms, sk_schedule_info* out) {
+  if (n_peers < 0 || n_peers > SK_MAX_PEERS) return SK_ERR_ARG;
+  return schedule_for(p, 1, num_sms, n_peers, out);
 }
 
 // Kernel-space schedule (rows = the 128-wide UMMA M side) from the logical description.

@@ -23,12 +23,13 @@ __all__ = [
     "streamk_fp16_block_reduce", "ladder_prepack", "streamk_fp16_ladder",
     "streamk_fp16_ladder_block_reduce", "q4_prepack", "dequant_w4",
     "streamk_fp16_ladder_block_reduce_q4", "schedule_info", "check_status",
-    "reset_workspace", "release_cached_memory", "cached_memory_bytes", "device_info", "LadderWeight", "PackedQ4", "StreamKError", "SCHEDULES", "FIXUPS",
+    "SCHEDULE_NAMES", "reset_workspace", "release_cached_memory", "cached_memory_bytes", "device_info", "LadderWeight", "PackedQ4", "StreamKError", "SCHEDULES", "FIXUPS",
 ]
 
 StreamKError = L.StreamKError
 SCHEDULES = L.SCHEDULES   # name -> SK_SCHED_* value
 FIXUPS = L.FIXUPS
+SCHEDULE_NAMES = {v: k for k, v in L.SCHEDULES.items()}   # SK_SCHED_* value -> name
 GROUP_SIZE = 128
 
 
@@ -119,7 +120,8 @@ def device_info(device: int = 0) -> dict:
 
 
 # --------------------------------------------------------------------------- helpers
-_OPTION_KEYS = ("tile_m", "tile_n", "num_sms", "group_m", "out", "timeout_us", "pdl", "_drop_flag_cta")
+_OPTION_KEYS = ("tile_m", "tile_n", "num_sms", "group_m", "out", "timeout_us", "pdl", "no_table",
+                "_drop_flag_cta")
 
 
 def _options(kw: dict) -> dict:
@@ -129,6 +131,8 @@ def _options(kw: dict) -> dict:
                      rasterisation), out (result buffer), timeout_us (bound of every device
                      wait), pdl (True: programmatic dependent launch, the kernel's start-up may
                      overlap the tail of the previous kernel of the stream; fp16 / W4A16),
+                     no_table (True: schedule "auto" by the built-in rules only, ignoring the table
+                     of tuned shapes),
                      _drop_flag_cta (test hook: index of a CTA that withholds its flag)."""
     unknown = set(kw) - set(_OPTION_KEYS)
     if unknown:
@@ -148,19 +152,25 @@ def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkPr
                        fixup_timeout_us=int(o["timeout_us"] or 0),
                        # (the C field is 0 = off, n = CTA n - 1)
                        test_drop_flag_cta=0 if o["_drop_flag_cta"] is None else int(o["_drop_flag_cta"]) + 1,
-                       flags=L.SK_FLAG_PDL if o["pdl"] else 0)
+                       flags=(L.SK_FLAG_PDL if o["pdl"] else 0) | (L.SK_FLAG_NO_TABLE if o["no_table"] else 0))
 
 
 def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "auto",
-                  num_sms: int = 148, **kw) -> dict:
+                  num_sms: int = 148, gather_peers: int = 0, **kw) -> dict:
     """Host scheduler integers (streamk_fp16.py:83-113) and the tile plan for a problem;
-    needs no GPU.  kind: "f32", "f16", "w4a16", or "f16_pairs" (the CTA-pair kernel the fp16 NT
-    entry point picks for large problems; num_sms is then the number of pairs)."""
+    needs no GPU.  kind: "f32", "f16" (what the fp16 NT entry point runs: single-CTA tiles, or
+    for large problems the CTA-pair kernel, described over num_sms / 2 pairs), "w4a16", or
+    "f16_pairs" (the CTA-pair kernel with num_sms pairs).  gather_peers > 0: the plan of the
+    fused all-gather call with that many peers."""
     o = _options(kw)
     prob = _problem(M, N, K, K, K, N, "nt", schedule, "atomic", o)
     info = L.SkScheduleInfo()
     kinds = {"f32": 0, "f16": 1, "w4a16": 2, "f16_pairs": 3}
-    L.check(L.load().sk_schedule(C.byref(prob), kinds[kind], num_sms, C.byref(info)), "sk_schedule")
+    if gather_peers:
+        L.check(L.load().sk_schedule_gather(C.byref(prob), gather_peers, num_sms, C.byref(info)),
+                "sk_schedule_gather")
+    else:
+        L.check(L.load().sk_schedule(C.byref(prob), kinds[kind], num_sms, C.byref(info)), "sk_schedule")
     return info.as_dict()
 
 
@@ -306,9 +316,15 @@ _HOST_PIPES_MAX = 4     # staging sets kept; the least recently used one is drop
 
 
 def streamk_fp16_nt_host(A_host, B_host, out_host=None, *, slabs: int = 8, device=None,
-                         fixup="block_reduce", schedule="auto", **kw):
+                         fixup="block_reduce", schedule="auto", group=None, **kw):
     """C = A @ B.T for operands and result in (pinned) HOST memory: A [M,K], B [N,K] fp16 CPU
     tensors, result [M,N] fp16 CPU tensor (out_host, or a new pinned tensor).
+
+    Column-sharded use (one process per GPU, `group` = a torch.distributed NCCL group of G
+    ranks, B_host / out_host = this rank's column block): A_host is then only this rank's
+    1/G of A's rows, [M/G, K]; every rank copies its part from the host and the parts are
+    all-gathered into each GPU's memory over NVLink (NCCL, ahead of the first slab's GEMM), so
+    that A crosses PCIe once for the whole group instead of once per GPU.
 
     B and C move in `slabs` column slabs through double-buffered device staging: the
     host-to-device copy of slab i+1, the GEMM of slab i and the device-to-host copy of slab i-1
@@ -319,7 +335,12 @@ def streamk_fp16_nt_host(A_host, B_host, out_host=None, *, slabs: int = 8, devic
     for name, t in (("A_host", A_host), ("B_host", B_host)):
         if not isinstance(t, torch.Tensor) or t.is_cuda or t.dtype != torch.float16 or t.dim() != 2:
             raise TypeError(f"{name} must be a 2-D fp16 CPU tensor")
-    M, K = A_host.shape
+    Mpart, K = A_host.shape
+    world = 1
+    if group is not None:
+        import torch.distributed as dist
+        world = dist.get_world_size(group)
+    M = Mpart * world
     N = B_host.shape[0]
     if B_host.shape[1] != K:
         raise ValueError("A_host [M,K] and B_host [N,K] disagree on K")
@@ -351,7 +372,14 @@ def streamk_fp16_nt_host(A_host, B_host, out_host=None, *, slabs: int = 8, devic
         if pipe.busy is not None:
             st.wait_event(pipe.busy)
     with torch.cuda.stream(pipe.s_in):
-        pipe.A.copy_(A_host, non_blocking=True)
+        if world == 1:
+            pipe.A.copy_(A_host, non_blocking=True)
+        else:
+            rank = dist.get_rank(group)
+            pipe.A[rank * Mpart:(rank + 1) * Mpart].copy_(A_host, non_blocking=True)
+            # row blocks are contiguous: the gather lands in place (NCCL kernel on the copy-in
+            # stream; no peer pointer is handed to a GEMM kernel as an operand)
+            dist.all_gather_into_tensor(pipe.A, pipe.A[rank * Mpart:(rank + 1) * Mpart], group=group)
     mm_done = [None, None]                  # per staging buffer: GEMM that last read B / wrote C
     out_done = [None, None]                 # per staging buffer: copy-out that last read C
     for i in range(slabs):
