@@ -116,6 +116,21 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
   }
   int tm = p->tile_m, tn = p->tile_n;
   if (tm < 0 || tn < 0) return SK_ERR_ARG;
+  if (kernel_kind == 2) {
+    // W4A16: the weights always feed the UMMA M dimension (their dequantised form is the
+    // tensor-memory A operand): 128 weight rows per tile, tile_m = 16 .. 128 rows of C.  Left
+    // open, M is cut into equal tiles of at most 128 rows.
+    if (tn != 0 && tn != 128) return SK_ERR_ARG;
+    if (tm == 0) {
+      // (the cluster schedule's exchange buffers leave room for tiles of at most 112 rows)
+      const int cap = p->schedule == SK_SCHED_CLUSTER ? 112 : 128;
+      const int parts = (p->M + cap - 1) / cap;
+      tm = ((p->M + parts - 1) / parts + 15) & ~15;
+    }
+    if (tm < 16 || tm > 128 || (tm & 15) != 0) return SK_ERR_ARG;
+    plan->swap = 1; plan->bn = tm; plan->bm = 128; plan->rows = p->N; plan->cols = p->M;
+    return SK_OK;
+  }
   bool swap;
   if (tm == 0 && tn == 0) swap = p->M <= 64;
   else if (tm != 0 && tm != 128) swap = true;
@@ -133,18 +148,13 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
     return SK_OK;
   }
   if (tn == 0) {
-    if (kernel_kind == 2) {
-      tn = 128;
-    } else {
-      // Wide tiles halve shared-memory traffic per flop; use them once there is
-      // enough work to fill every SM twice over, else favour granularity.
-      const long long t256 = static_cast<long long>((p->M + 127) / 128) * ((p->N + 255) / 256);
-      tn = (t256 >= 2LL * num_sms) ? 256 : 128;
-    }
+    // Wide tiles halve shared-memory traffic per flop; use them once there is
+    // enough work to fill every SM twice over, else favour granularity.
+    const long long t256 = static_cast<long long>((p->M + 127) / 128) * ((p->N + 255) / 256);
+    tn = (t256 >= 2LL * num_sms) ? 256 : 128;
   }
-  // fp16: any multiple of 16 up to 256 (NN and ladder weights come in 128-row units: checked
-  // by the caller); W4A16 dequantises 128 weight rows per stage.
-  if (kernel_kind == 2 ? tn != 128 : (tn < 16 || tn > 256 || (tn & 15) != 0)) return SK_ERR_ARG;
+  // any multiple of 16 up to 256 (NN and ladder weights come in 128-row units: checked by the caller)
+  if (tn < 16 || tn > 256 || (tn & 15) != 0) return SK_ERR_ARG;
   plan->swap = 0; plan->bn = tn; plan->bm = 128; plan->rows = p->M; plan->cols = p->N;
   return SK_OK;
 }
@@ -185,13 +195,15 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
   }
   const long long t256 = static_cast<long long>((q->M + 255) / 256) * ((q->N + 255) / 256);
   if (t256 >= num_sms) return;                       // large: hybrid (CTA pairs when eligible)
-  if ((kernel_kind == 1 || kernel_kind == 2) && (q->K + 63) / 64 >= 8) {
+  // (W4A16 beyond 112 rows: the cluster schedule would need two narrower tiles per 128 weight
+  // rows, i.e. dequantise every weight twice; Stream-K on whole-height tiles instead)
+  if ((kernel_kind == 1 || (kernel_kind == 2 && (q->M <= 112 || !tiles_open))) && (q->K + 63) / 64 >= 8) {
     // Few tiles and a deep K: split every tile over the CTAs of a cluster.  Measured 15-25 %
     // ahead of Stream-K with either workspace fixup wherever it applies (at most half as many
     // tiles as SMs): the partials never leave the SMs and no flag is polled.
     sk_problem c = *q;
     c.schedule = SK_SCHED_CLUSTER;
-    if (tiles_open && c.M > 64) { c.tile_m = 128; c.tile_n = 128; }
+    if (tiles_open && c.M > 64 && kernel_kind == 1) { c.tile_m = 128; c.tile_n = 128; }
     if (sk_make_sched(&c, kernel_kind, num_sms, nullptr, nullptr, nullptr) == SK_OK) {
       *q = c;
       return;
@@ -248,7 +260,7 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
     }
   }
   q->schedule = SK_SCHED_STREAMK;
-  if (tiles_open) { q->tile_m = 128; q->tile_n = 128; }
+  if (tiles_open && kernel_kind == 1) { q->tile_m = 128; q->tile_n = 128; }
 }
 
 int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule_info* info,
@@ -291,7 +303,8 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
     // the largest portable cluster that still gives every tile its own cluster in one wave
     if (kernel_kind != 1 && kernel_kind != 2) return SK_ERR_ARG;
     if (2 * total > P) return SK_ERR_SHAPE;
-    if (plan.bn > 192) return SK_ERR_SHAPE;   // exchange buffers of wider tiles do not fit beside the ring
+    // exchange buffers of wider tiles do not fit beside the ring
+    if (plan.bn > (kernel_kind == 2 ? 112 : 192)) return SK_ERR_SHAPE;
     split = 2;
     while (split < 8 && 2 * split * total <= P) split *= 2;
     grid = total * split;

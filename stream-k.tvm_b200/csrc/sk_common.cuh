@@ -79,6 +79,7 @@ struct SkParams {
   int prefetch_steps;      // K steps whose boxes the producers ask L2 for before the pipeline is up
   int c_tma;               // 1: whole tiles leave through shared memory and TMA stores (tensor map of C given)
   int wide_units;          // CTA-pair kernel: 256 x 512 units walked whole after the schedule's tiles
+  int wide_lag;            //    K steps the second half of a unit stays behind the first
   int kpair;               // 1: a stage is the K steps of one scale group (W4A16): two, or one at an odd
                            //    start / the end of a segment; 0: kgroup K steps per stage
   int acc_b_off;           // > 0: two MMA-issuing threads take alternate stages of a segment, the second

@@ -203,6 +203,9 @@ __device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __
   }
 }
 
+// LIGHT: half as many loads in flight per thread, for kernels with many threads and few
+// registers each (the W4A16 kernel: 736 threads, 80 registers).
+template <bool LIGHT = false>
 __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __restrict__ C,
                                                 const SkPending& pd, int pid, int rank, int tid,
                                                 int nthreads, const SkPeers* peers) {
@@ -221,10 +224,16 @@ __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __res
   const int begin = static_cast<int>(static_cast<long long>(j) * L / n);
   const int end = static_cast<int>(static_cast<long long>(j + 1) * L / n);
   // The summation order (0 + p_first + p_first+1 + ...) is the same in every variant.
-  if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  if constexpr (LIGHT) {
+    if (n <= 2)      sk_reduce_items_uv<4, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+    else if (n <= 4) sk_reduce_items_uv<2, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+    else             sk_reduce_items_uv<1, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  } else {
+    if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+    else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+    else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+    else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
+  }
   if (peers != nullptr) {   // (called by every thread of the CTA, see sk_reduce_pending)
     __syncthreads();
     sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, begin, end, tid >> 5, nthreads >> 5, tid & 31);
@@ -234,6 +243,7 @@ __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __res
 // Deferred block-reduce of the (at most two) split tiles this CTA took part in (see the
 // header comment).  Called by EVERY thread of the CTA after all roles have finished;
 // pend[0] is the tile the CTA started, pend[1] the tile it continued; ok[] is scratch.
+template <bool LIGHT = false>
 __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __restrict__ C, int pid,
                                                   int rank, const SkPending* pend,
                                                   volatile uint32_t* ok, const SkPeers* peers = nullptr) {
@@ -261,7 +271,7 @@ __device__ __forceinline__ void sk_reduce_pending(const SkParams& p, __half* __r
   // 2. reduce this CTA's slice of each tile
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    if (pend[t].tile >= 0 && ok[t] != 0u) sk_reduce_items(p, C, pend[t], pid, rank, tid, nthreads, peers);
+    if (pend[t].tile >= 0 && ok[t] != 0u) sk_reduce_items<LIGHT>(p, C, pend[t], pid, rank, tid, nthreads, peers);
     if (tid == 0) sk_trace(p, 9 + t);
   }
   // 3. everybody has read what it needs; the last contributor to get here re-arms the flags
@@ -316,24 +326,29 @@ __device__ __forceinline__ void sk_load_acc(uint32_t taddr, uint32_t b_off, floa
 constexpr int SK_EPI_ANY = -1, SK_EPI_ATOMIC = SK_FIXUP_ATOMIC, SK_EPI_BLOCK_REDUCE = SK_FIXUP_BLOCK_REDUCE,
               SK_EPI_WHOLE = 2;
 
-// Staging area of the TMA-store path: per epilogue warp two buffers of 32 rows x 128 bytes
-// (64 fp16 columns, 128-byte swizzle), 1024-byte aligned.
+// Staging area of the TMA-store path: per epilogue warp buffers of 32 rows x 128 bytes (64
+// fp16 columns, 128-byte swizzle), 1024-byte aligned; 32 KB in all: two buffers each for four
+// epilogue warps, one each for eight.
 constexpr int SK_CSTAGE_BYTES = 4 * 2 * 4096;
 
 // Whole tile, 64 columns at a time: accumulator -> fp16 -> swizzled staging buffer -> one TMA
 // store of a 64 x 32 box per warp (full 128-byte lines, issued asynchronously), instead of
-// sixteen-byte stores to 32 different rows per instruction.  Returns the number of columns
-// handled (a multiple of 64; the rest of the tile goes through sk_store_chunk).
+// sixteen-byte stores to 32 different rows per instruction.  This warp takes the 64-column
+// groups g_first, g_first + g_step, ... (the warps that share a TMEM lane quadrant split the
+// columns).  NBUF: staging buffers per warp.  Returns the number of columns the warps handle
+// together (a multiple of 64; the rest of the tile goes through sk_store_chunk).
+template <int NBUF = 2>
 __device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtensorMap* tmC, uint32_t cstage,
                                                  int warp_slot, int lane, uint32_t t_addr, uint32_t b_off,
                                                  int grow0, int gcol0, int valid_cols, uint32_t& groups,
-                                                 const SkPeers* peers = nullptr) {
+                                                 const SkPeers* peers = nullptr, int g_first = 0,
+                                                 int g_step = 1) {
   using namespace skptx;
   const int full = valid_cols >> 6;
-  for (int g = 0; g < full; ++g, ++groups) {
-    const uint32_t buf = cstage + static_cast<uint32_t>(warp_slot * 2 + (groups & 1u)) * 4096u;
-    // the store issued from this buffer two groups ago must have read it
-    if (lane == 0) tma_store_wait_read<1>();
+  for (int g = g_first; g < full; g += g_step, ++groups) {
+    const uint32_t buf = cstage + static_cast<uint32_t>(warp_slot * NBUF + (NBUF == 2 ? (groups & 1u) : 0u)) * 4096u;
+    // the store issued from this buffer NBUF groups ago must have read it
+    if (lane == 0) tma_store_wait_read<NBUF - 1>();
     __syncwarp();
     // both 32-column reads of the group in flight before the one wait
     uint32_t raw[2][32];
@@ -378,7 +393,10 @@ __device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtens
   return full * 64;
 }
 
-template <int MODE = SK_EPI_ANY>
+// EPI_WARPS: 4 (warps 2..5) or 8 (warps 2..9).  TMEM lets a warp read only the lane quadrant
+// `warp & 3`, so with eight warps two share each quadrant and split a tile's columns: warp w
+// takes the 64-column groups (and 32-column chunks) of parity (w - 2) / 4.
+template <int MODE = SK_EPI_ANY, int EPI_WARPS = 4>
 __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __restrict__ C, int pid,
                                                  int rank, int warp, int lane, uint32_t tmem_base,
                                                  uint32_t tmem_full_bar, uint32_t tmem_empty_bar,
@@ -389,12 +407,15 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
                                                  uint32_t* nseg_out = nullptr, const SkPeers* peers = nullptr) {
   using namespace skptx;
   constexpr int BM = SK_BM;
-  constexpr int EPI_THREADS = SK_EPI_THREADS;
+  constexpr int EPI_THREADS = 32 * EPI_WARPS;
   constexpr int EPI_BAR_ID = SK_EPI_BAR_ID;
+  constexpr int NSUB = EPI_WARPS / 4;       // warps per TMEM lane quadrant
+  constexpr int NBUF = EPI_WARPS == 4 ? 2 : 1;   // staging buffers per warp (sk_store_tile_tma)
   const SkSched& s = p.sched;
   const int q = warp & 3;            // TMEM lane quadrant this warp may read
   const int row = q * 32 + lane;     // row inside the tile
-  const int etid = ((warp - 2) & 3) * 32 + lane;
+  const int sub = (warp - 2) >> 2;   // which of the quadrant's warps this is
+  const int etid = (warp - 2) * 32 + lane;
   SkCursor cur;
   sk_cursor_init(s, pid, cur);
   SkSeg seg;
@@ -441,10 +462,10 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
     const bool two = sk_second_acc_used(p, seg.k0, seg.k1);
     int c_first = 0;   // first 32-column chunk that still has to go through the register path
     if (whole && p.c_tma && cstage != 0 && warp_ok && !dead)
-      c_first = sk_store_tile_tma(p, tmC, cstage, (warp - 2) & 3, lane, t_addr, two ? p.acc_b_off : 0,
-                                  r0 + q * 32, c0, valid_cols, tma_groups, peers) >> 5;
+      c_first = sk_store_tile_tma<NBUF>(p, tmC, cstage, warp - 2, lane, t_addr, two ? p.acc_b_off : 0,
+                                        r0 + q * 32, c0, valid_cols, tma_groups, peers, sub, NSUB) >> 5;
     if (warp_ok && !dead) {
-      for (int c = c_first; c < nchunks; ++c) {
+      for (int c = c_first + sub; c < nchunks; c += NSUB) {
         float v[32];
         sk_load_acc(t_addr + c * 32, two ? p.acc_b_off : 0, v);
         if (!row_ok) continue;
@@ -513,7 +534,7 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
         }
         if (peers != nullptr) {
           named_bar_sync(EPI_BAR_ID, EPI_THREADS);
-          sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, 0, L, (warp - 2) & 3, 4, lane);
+          sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, 0, L, warp - 2, EPI_WARPS, lane);
         }
         if (etid == 0) p.ws.counters[first_id] = 0u;
       }

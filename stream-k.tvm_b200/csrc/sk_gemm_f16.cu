@@ -114,7 +114,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   if (warp == 2) {
     if (lane < STAGES) {
       mbar_init(smem_u32(&ctrl->full[lane]), 1);
-      mbar_init(smem_u32(&ctrl->empty[lane]), 1);
+      mbar_init(smem_u32(&ctrl->empty[lane]), p.acc_b_off ? 2 : 1);   // MMA commit (+ the other issuer's "seen it")
     } else if (lane < STAGES + 2) {
       const int i = lane - STAGES;
       mbar_init(smem_u32(&ctrl->tmem_full[i]), p.acc_b_off ? 2 : 1);   // one arrival per MMA issuer
@@ -283,6 +283,10 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
             break;
           }
           if (dual && (si & 1u) != me) {   // the other issuer's stage
+            // The slot must not be refilled before BOTH issuers have seen this use of it: a
+            // lagging issuer that found the barrier two phases on would read that as "not yet"
+            // and wait for a use that may never come.  So the skipping issuer arrives as well.
+            mbar_arrive(empty0 + 8u * stage);
             k += n;
             if (++stage == STAGES) { stage = 0; ph ^= 1u; }
             continue;

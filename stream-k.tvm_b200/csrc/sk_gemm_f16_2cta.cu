@@ -9,8 +9,13 @@
 // pulls 2/3 of the bytes the single-CTA kernel does, so the same shared-memory budget
 // covers 1.5x the load latency.  No load is multicast: each CTA fetches what it needs.
 //
-// Roles per CTA as in sk_gemm_f16.cu; the MMA warp of the second CTA only takes part in
-// the tensor-memory allocation.
+// Roles per CTA as in sk_gemm_f16.cu, but with eight epilogue warps (two per TMEM lane quadrant,
+// splitting a tile's columns): draining a 128 x 256 accumulator is a latency chain per warp
+// (TMEM load, convert, staging store, proxy fence, TMA store), and with tensor memory full of
+// accumulators every microsecond of drain at a unit boundary is a microsecond without MMAs.
+// The MMA warp of the second CTA only takes part in the tensor-memory allocation.
+#include <stdlib.h>
+
 #include "sk_common.cuh"
 #include "sk_epilogue.cuh"
 
@@ -25,7 +30,8 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;         // 16 KB
 constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;   // 16 KB: this CTA's half of the B tile
 constexpr int KG = 2;                  // K steps that share a pipeline stage (one barrier round trip)
 constexpr int STAGES = 3;              // 3 x 2 x 32 KB = 192 KB
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;   // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
 constexpr int TMEM_COLS = 512;
 constexpr int PIPE_BYTES = STAGES * KG * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int CTRL_BYTES = 512;
@@ -44,7 +50,7 @@ struct Ctrl {
   uint64_t fullw[WSTAGES];    // the same pair for the wide ring
   uint64_t emptyw[WSTAGES];
   uint64_t tmem_full[2];      // one per CTA, multicast commit
-  uint64_t tmem_empty[2];     // used in the leader CTA: 8 arrivals (4 epilogue warps x 2 CTAs)
+  uint64_t tmem_empty[2];     // used in the leader CTA: one arrival per epilogue warp of both CTAs
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t bcast;
@@ -91,7 +97,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctrl->tmem_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[i]), 8);
+      mbar_init(smem_u32(&ctrl->tmem_empty[i]), 2 * EPI_WARPS);
     }
     ctrl->abort = 0u;
     ctrl->bcast = 0u;
@@ -250,15 +256,18 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           // The epilogue drains the first half's buffer, then the second's.  The first half
           // starts as soon as its buffer is free and may run up to WSTAGES - 1 K steps ahead of
           // the second (the stages stay held until the second half has read them too), so the
-          // second buffer's drain overlaps the start of this unit.
+          // second buffer's drain overlaps the start of this unit.  Once the second half may
+          // run it catches up to within `lag` K steps (a held stage is a stage the producer
+          // cannot refill) and stays that far behind: the first half then finishes `lag` steps
+          // early, hands its accumulator to the epilogue at once, and its drain runs under the
+          // second half's last MMAs instead of after them.
           const int I = s.iters_per_tile;
+          const int lag = p.wide_lag;
           int k0 = 0, k1 = 0;          // next K step of the first / second half
           int ws1 = ws;                // stage of K step k1 (ws is the stage of k0)
           bool h1_ready = false;
           while (ok && k1 < I) {
-            // (once the second half may run it first catches up: a held stage is a stage the
-            // producer cannot refill)
-            if (k0 < I && (h1_ready ? k0 == k1 : k0 - k1 < WSTAGES - 1)) {
+            if (k0 < I && (h1_ready ? k0 - k1 <= lag : k0 - k1 < WSTAGES - 1)) {
               if (!sk_wait_bar(fullw0 + 8u * ws, wph, abort_flag, p, 40 + ws, 1)) {
                 ok = false;
                 break;
@@ -272,6 +281,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                                  (k0 | kk) ? 1u : 0u);
               ++k0;
               if (++ws == WSTAGES) { ws = 0; wph ^= 1u; }
+              if (k0 == I) umma_commit_pair(smem_u32(&ctrl->tmem_full[buf0]));   // first half complete
             }
             if (!h1_ready) {
               if (mbar_try_wait(empty1, empty1_ph, 0u)) {
@@ -285,7 +295,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
               }
               if (h1_ready) tc_fence_after();
             }
-            if (h1_ready && k1 < k0) {
+            if (h1_ready && k1 < k0 && (k0 - k1 > lag || k0 == I)) {
               const uint32_t a_lo = w_lo0 + ws1 * (W_STAGE_BYTES >> 4);
               const uint32_t b_lo = a_lo + ((A_STAGE_BYTES + B_STAGE_BYTES) >> 4);
 #pragma unroll
@@ -298,7 +308,6 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             }
           }
           if (!ok) break;
-          umma_commit_pair(smem_u32(&ctrl->tmem_full[buf0]));
           umma_commit_pair(smem_u32(&ctrl->tmem_full[buf1]));
           nseg += 2;
         }
@@ -311,11 +320,12 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const uint32_t tmem_full0 = smem_u32(&ctrl->tmem_full[0]);
     const uint32_t tmem_empty0 = mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0);
     uint32_t nseg = 0;
-    sk_epilogue_loop(p, C, unit, rank, warp, lane, tmem_base, tmem_full0, tmem_empty0, &ctrl->bcast,
-                     abort_flag, ctrl->pend, &tmC, cstage, &nseg, peers);
+    sk_epilogue_loop<SK_EPI_ANY, EPI_WARPS>(p, C, unit, rank, warp, lane, tmem_base, tmem_full0, tmem_empty0,
+                                            &ctrl->bcast, abort_flag, ctrl->pend, &tmC, cstage, &nseg, peers);
     if (p.wide_units > 0) {
       // ---- wide units: the two halves are two whole tiles in the two accumulator buffers
       const int q = warp & 3;
+      const int sub = (warp - 2) >> 2;   // the quadrant's two warps take alternate column groups
       const int row = q * 32 + lane;
       uint32_t groups = 0;
       bool dead = false;
@@ -339,9 +349,9 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           if (warp_ok && !dead && valid_cols > 0) {
             int c_first = 0;
             if (cstage != 0)
-              c_first = sk_store_tile_tma(p, &tmC, cstage, (warp - 2) & 3, lane, t_addr, 0, r0 + q * 32, c0,
-                                          valid_cols, groups, peers) >> 5;
-            for (int c = c_first; c < ((valid_cols + 31) >> 5); ++c) {
+              c_first = sk_store_tile_tma<1>(p, &tmC, cstage, warp - 2, lane, t_addr, 0, r0 + q * 32, c0,
+                                             valid_cols, groups, peers, sub, EPI_WARPS / 4) >> 5;
+            for (int c = c_first + sub; c < ((valid_cols + 31) >> 5); c += EPI_WARPS / 4) {
               float v[32];
               sk_load_acc(t_addr + c * 32, 0, v);
               int nv = valid_cols - c * 32;
@@ -420,6 +430,9 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   p->tmem_cols = TMEM_COLS;
   p->stages = STAGES;
   p->idesc = umma_idesc_f16(2 * BM, bn, 0);
+  // K steps the second half of a 256 x 512 unit stays behind the first (see the MMA issuer)
+  p->wide_lag = 1;
+  if (const char* e = getenv("SK_WIDE_LAG")) p->wide_lag = atoi(e) < WSTAGES - 1 ? atoi(e) : WSTAGES - 2;
 
   static SkPerDeviceOnce attrs;
   cudaError_t e = attrs.run([]() {

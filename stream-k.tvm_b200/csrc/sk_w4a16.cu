@@ -2,9 +2,9 @@
 // uint4 q, per-group (128 along K) uint4 zero-point z and fp16 scale s.
 //
 // Stands in for the TL kernel of streamk_fp16_ladder_block_reduce_q4.py:143-522
-// (int8-packed weight tile in shared memory, decode_i4u_to_f16 in registers, then
-// mma.sync) and for its CPU weight preparation (LadderPermutate + LOP3Permutate,
-// …q4.py:568-595).  The reference applies no scale or zero-point; with s = 1,
+// (int8-packed weight tile in shared memory, decode_i4u_to_f16 in registers immediately
+// ahead of the mma, …q4.py:255-294) and for its CPU weight preparation (LadderPermutate +
+// LOP3Permutate, …q4.py:568-595).  The reference applies no scale or zero-point; with s = 1,
 // z = 0 this kernel computes the same C = A . unpack_u4(qB)^T.
 //
 // Packed image (sk_prepack_q4):
@@ -15,11 +15,23 @@
 //                  the fp16 pair (e(2i), e(2i+1)) in one lop3;
 //   group blocks   [n_block][group] = 128 fp16 scales + 128 uint8 zero-points (384 B).
 //
-// CTA roles (448 threads): warp 0 producer (TMA activation tile + bulk copies of the
-// packed blocks), warp 1 MMA issuer, warps 2..5 epilogue, warps 6..13 dequantise the
-// packed block into the 128-byte-swizzled fp16 stage the UMMA descriptor reads.  For short
-// M the operands are swapped: the dequantised weights feed the UMMA M dimension and the
-// activation tile (M rounded up to 16 rows) the N dimension.
+// Data path.  The weights ALWAYS feed the UMMA M dimension (128 weight rows per tile) and the
+// activations the N dimension (a tile spans tile_m = 16 .. 128 rows of C; C is stored
+// transposed).  That makes the weights the UMMA's A operand, which may live in tensor memory:
+// a dequantise thread owns one weight row (TMEM lane), turns its packed words into halves in
+// registers and writes them straight to tensor memory (tcgen05.st); the MMA issuer reads them
+// from there (tcgen05.mma with the A operand in TMEM).  The dequantised weights never pass
+// through shared memory: no swizzled stores, no generic-to-async proxy fence, and the shared
+// memory holds nothing but the load ring (activation tile + packed block + group block per
+// stage), which can therefore be deep.
+//
+// CTA roles (736 threads): warp 0 producer (TMA activation tile + bulk copies of the packed
+// blocks), warp 1 MMA issuer, warps 2..5 epilogue, warps 6..21 dequantise in four groups of
+// four (one warp per TMEM lane quadrant; group g takes stages g, g+4, ... whole), warp 22
+// second MMA issuer (narrow tiles).  A stage is one scale group (128 of K, two K steps).
+// Tensor memory (512 columns): [0, 256) the dequantised-weight ring, four slots of 64 columns
+// (slot g belongs to group g); [256, 512) the accumulators (two buffers, each one or, with two
+// issuers, two accumulators).
 #include "sk_common.cuh"
 #include "sk_epilogue.cuh"
 
@@ -31,25 +43,25 @@ constexpr int BM = SK_BM;
 constexpr int BK = 64;
 constexpr int Q_BLOCK_BYTES = 128 * BK / 2;    // 4096: packed nibbles of 128 weight rows x 64 K
 constexpr int SZ_BLOCK_BYTES = 128 * 2 + 128;  // 384: fp16 scales + uint8 zero-points of a group
-constexpr int W_SLAB_BYTES = 128 * BK * 2;     // 16384: dequantised fp16 tile of one K step
 constexpr int KG = 2;                          // K steps per stage = one scale group (128 along K)
-constexpr int W_STAGE_BYTES = KG * W_SLAB_BYTES;
-constexpr int MAX_LS = 12;                     // load stages (activation tile + packed block)
-constexpr int MAX_BS = 8;                      // dequantised weight stages (ring depth chosen per launch)
-constexpr int DQ_WARPS = 8;
-constexpr int DQ_GROUPS = 4;                   // groups of DQ_WARPS / DQ_GROUPS warps, one stage each at a time
-constexpr int DQ_GROUP_WARPS = DQ_WARPS / DQ_GROUPS;
+constexpr int MAX_LS = 16;                     // load stages (activation tile + packed block)
+constexpr int DQ_GROUPS = 4;                   // dequantise groups = slots of the TMEM weight ring
+constexpr int DQ_GROUP_WARPS = 4;              // one warp per TMEM lane quadrant
+constexpr int DQ_WARPS = DQ_GROUPS * DQ_GROUP_WARPS;
 constexpr int DQ_THREADS = DQ_WARPS * 32;
-constexpr int NUM_THREADS = 64 + SK_EPI_THREADS + DQ_THREADS + 32;   // + warp 14, the second MMA issuer
+constexpr int NUM_THREADS = 64 + SK_EPI_THREADS + DQ_THREADS + 32;   // + warp 22, the second MMA issuer
 constexpr int MMA_B_WARP = 6 + DQ_WARPS;
+constexpr int W_SLOT_COLS = KG * 32;           // TMEM columns of one dequantised stage (128 K halves, two per column)
+constexpr int W_RING_COLS = DQ_GROUPS * W_SLOT_COLS;   // 256
+constexpr int TMEM_COLS = 512;
 constexpr int CTRL_BYTES = 512;
 constexpr int SMEM_LIMIT = 232448;
 
 struct Ctrl {
   uint64_t load_full[MAX_LS];
   uint64_t load_empty[MAX_LS];
-  uint64_t w_full[MAX_BS];
-  uint64_t w_empty[MAX_BS];
+  uint64_t w_full[DQ_GROUPS];
+  uint64_t w_empty[DQ_GROUPS];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t recv_full;      // SK_SCHED_CLUSTER: the partial tiles of the other CTAs have arrived
@@ -84,9 +96,10 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, __half2 zmagic, __half
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-// Shared memory: [BS dequantised weight stages][LS activation stages][LS packed blocks]
-// [LS group blocks][Ctrl]; BS and LS are chosen per launch.  p.col_stage_bytes holds the activation stage size in both
-// operand orders (128 rows normally, bn rows when the operands are swapped).
+// Shared memory: [LS activation stages][LS packed blocks][LS group blocks][Ctrl][cluster
+// receive buffer]; LS (a multiple of DQ_GROUPS, so that a load slot always belongs to the same
+// dequantise group) is chosen per launch.  p.row_tx_bytes holds the bytes of one K step's
+// activation tile (bn rows x 128 B).
 // MODE as in the fp16 kernel: SK_EPI_ATOMIC, SK_EPI_BLOCK_REDUCE, SK_EPI_WHOLE (data-parallel
 // schedule, no fixup code) or SK_MODE_CLUSTER; one instantiation each.
 constexpr int SK_MODE_CLUSTER = 3;
@@ -100,14 +113,11 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
   const int LS = p.stages;
-  const int BS = p.w_stages;
   const int a_tile_bytes = p.row_tx_bytes;         // activation tile bytes of one K step
   const int a_stage_bytes = KG * a_tile_bytes;
-  const int off_a = BS * W_STAGE_BYTES;
-  const int off_q = off_a + LS * a_stage_bytes;
+  const int off_q = LS * a_stage_bytes;
   const int off_sz = off_q + LS * KG * Q_BLOCK_BYTES;
-  const uint32_t sW = base;
-  const uint32_t sA = base + off_a;
+  const uint32_t sA = base;
   const uint32_t sQ = base + off_q;
   const uint32_t sSZ = base + off_sz;
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + off_sz + LS * SZ_BLOCK_BYTES);
@@ -119,46 +129,49 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const SkSched& s = p.sched;
   const int kblocks = s.iters_per_tile;  // K / 64
   const int groups = kblocks >> 1;       // K / 128
-  const bool swapped = p.transposed != 0;
   if (threadIdx.x == 0) {
     sk_trace(p, 0);
     griddep_launch_dependents();   // the next kernel of the stream may begin its own start-up
   }
   // Split-K inside a cluster (sk_epilogue.cuh): receive buffer behind the control block,
-  // staging area in the rings, which are idle by then.
+  // staging area in the load ring, which is idle by then.
   constexpr bool clustered = MODE == SK_MODE_CLUSTER;
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
-  if (threadIdx.x == 0) {
-    if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
-    for (int i = 0; i < LS; ++i) {
-      mbar_init(smem_u32(&ctrl->load_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->load_empty[i]), DQ_GROUP_WARPS + 1);  // the stage's dequant warps + MMA commit
-    }
-    for (int i = 0; i < BS; ++i) {
-      mbar_init(smem_u32(&ctrl->w_full[i]), DQ_GROUP_WARPS);   // one arrival per dequant warp of the stage's group
-      mbar_init(smem_u32(&ctrl->w_empty[i]), 1);
-    }
-    for (int i = 0; i < 2; ++i) {
+  if (warp == 2) {
+    // an epilogue warp (idle until the first tile is done) sets the barriers up, one per lane
+    if (lane < LS) {
+      mbar_init(smem_u32(&ctrl->load_full[lane]), 1);
+      // the stage's dequant warps + the MMA commit (+ the other issuer's "seen it", see below)
+      mbar_init(smem_u32(&ctrl->load_empty[lane]), DQ_GROUP_WARPS + 1 + (p.acc_b_off ? 1 : 0));
+    } else if (lane < LS + DQ_GROUPS) {
+      const int i = lane - LS;
+      mbar_init(smem_u32(&ctrl->w_full[i]), DQ_GROUP_WARPS);   // one arrival per dequant warp of the group
+      mbar_init(smem_u32(&ctrl->w_empty[i]), p.acc_b_off ? 2 : 1);   // MMA commit (+ the other issuer)
+    } else if (lane < LS + DQ_GROUPS + 2) {
+      const int i = lane - LS - DQ_GROUPS;
       mbar_init(smem_u32(&ctrl->tmem_full[i]), p.acc_b_off ? 2 : 1);   // one arrival per MMA issuer
       mbar_init(smem_u32(&ctrl->tmem_empty[i]), 4);
+    } else if (lane == LS + DQ_GROUPS + 2) {
+      if (clustered) mbar_init(smem_u32(&ctrl->recv_full), 5);   // 4 epilogue warps + the byte count
+      ctrl->abort = 0u;
+      ctrl->bcast = 0u;
+      ctrl->pend[0].tile = -1;
+      ctrl->pend[1].tile = -1;
     }
-    ctrl->abort = 0u;
-    ctrl->bcast = 0u;
-    ctrl->pend[0].tile = -1;
-    ctrl->pend[1].tile = -1;
     fence_mbar_init();
     fence_proxy_async_smem();
-    prefetch_tensormap(&tmA);
-    if (clustered)
+    __syncwarp();
+    if (clustered && lane == LS + DQ_GROUPS + 2)
       mbar_arrive_expect_tx(smem_u32(&ctrl->recv_full),
                             static_cast<uint32_t>((s.split - 1) * p.cl_per) * SK_CL_QUAD_BYTES);
   }
+  if (threadIdx.x == 0) prefetch_tensormap(&tmA);
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), p.tmem_cols);
+    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
-  if (threadIdx.x == 64) {
+  if (threadIdx.x == 96) {
     // While the barriers are being set up (and, with SK_FLAG_PDL, while the previous kernel of
     // the stream is still running) an idle thread asks L2 for the packed weights of the first
     // stages (a hint; L2 is the coherence point, so nothing can go stale).
@@ -168,10 +181,9 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     if (sk_next(s, pid, c0, g0)) {
       int tr, tc;
       sk_tile_mn(s, g0.tile, tr, tc);
-      const int nblk = swapped ? tr : tc;
       int n = g0.k1 - g0.k0;
-      if (n > 8) n = 8;
-      bulk_prefetch_l2(qblocks + (static_cast<size_t>(nblk) * kblocks + g0.k0) * Q_BLOCK_BYTES,
+      if (n > 12) n = 12;
+      bulk_prefetch_l2(qblocks + (static_cast<size_t>(tr) * kblocks + g0.k0) * Q_BLOCK_BYTES,
                        static_cast<uint32_t>(n) * Q_BLOCK_BYTES);
     }
   }
@@ -179,6 +191,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+  const uint32_t tmem_acc = tmem_base + W_RING_COLS;   // accumulators behind the weight ring
   if (threadIdx.x == 0) sk_trace(p, 1);
   // global memory is the previous kernel's until it has completed (no-op without SK_FLAG_PDL)
   griddep_wait();
@@ -197,8 +210,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       while (ok && sk_next(s, pid, cur, seg)) {
         int tr, tc;
         sk_tile_mn(s, seg.tile, tr, tc);
-        const int nblk = swapped ? tr : tc;                  // 128-row block of the weight
-        const int a_row0 = swapped ? tc * p.bn : tr * BM;    // first activation row of the tile
+        const int a_row0 = tc * p.bn;    // first activation row of the tile; tr = 128-row block of the weight
         for (int k = seg.k0; k < seg.k1;) {
           // A stage carries the K steps of one scale group (two, unless the segment starts
           // or ends inside the group): one barrier round trip, one packed copy, one group block.
@@ -209,19 +221,20 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
             break;
           }
           mbar_arrive_expect_tx(full, n * (a_tile_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES);
-          for (int j = 0; j < n; ++j)
-            tma_load_2d(sA + ls * a_stage_bytes + j * a_tile_bytes, &tmA, full, (k + j) * BK, a_row0);
           bulk_load_1d(sQ + ls * KG * Q_BLOCK_BYTES,
-                       qblocks + (static_cast<size_t>(nblk) * kblocks + k) * Q_BLOCK_BYTES,
+                       qblocks + (static_cast<size_t>(tr) * kblocks + k) * Q_BLOCK_BYTES,
                        n * Q_BLOCK_BYTES, full);
           bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
-                       szblocks + (static_cast<size_t>(nblk) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
+                       szblocks + (static_cast<size_t>(tr) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
                        SZ_BLOCK_BYTES, full);
+          for (int j = 0; j < n; ++j)
+            tma_load_2d(sA + ls * a_stage_bytes + j * a_tile_bytes, &tmA, full, (k + j) * BK, a_row0);
           k += n;
           if (++ls == LS) {
             ls = 0; lph ^= 1u;
-            // ring full for the first time; this thread initialised the mbarriers the other
-            // CTAs will signal, so its arrival releases
+            // ring full for the first time: a good moment for this thread's share of the
+            // cluster's start-up barrier.  Its arrival releases: it has met (at the CTA barrier
+            // above) the thread that initialised the mbarrier the other CTAs will signal.
             if (clustered && !arrived) { cluster_arrive(); arrived = true; }
           }
           if (!traced) { sk_trace(p, 2); traced = true; }
@@ -233,8 +246,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     }
   } else if (warp == 1 || warp == MMA_B_WARP) {
     // ------------------------------------------------------------- MMA issuers
-    // Issuing a UMMA costs its thread about 50 ns, and with eight per stage this thread was
-    // the mainloop's limit.  With room in tensor memory for two accumulators per buffer
+    // Issuing a UMMA costs its thread tens of nanoseconds whatever the tile width, and a stage
+    // is eight of them.  With room in tensor memory for two accumulators per buffer
     // (p.acc_b_off), a second thread takes every other stage of a segment and accumulates on
     // its own; the epilogue adds the two.
     const uint32_t me = warp == 1 ? 0u : 1u;
@@ -243,12 +256,12 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
-      int ls = 0, bs = 0;
-      uint32_t lph = 0, bph = 0, nseg = 0;
+      int ls = 0, g = 0;
+      uint32_t lph = 0, wph = 0, nseg = 0;
       bool ok = true;
       bool arrived = false;
       const uint64_t desc_hi = umma_desc_sw128_hi(16, 1024);
-      const uint32_t act_lo0 = umma_desc_lo(sA), wgt_lo0 = umma_desc_lo(sW);
+      const uint32_t act_lo0 = umma_desc_lo(sA);
       const uint32_t act_tile16 = static_cast<uint32_t>(a_tile_bytes) >> 4;
       const uint32_t idesc = p.idesc;
       while (ok && sk_next(s, pid, cur, seg)) {
@@ -257,14 +270,19 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
         if (!sk_wait_bar(smem_u32(&ctrl->tmem_empty[buf]), acc_ph ^ 1u, abort_flag, p, 16 + buf, 1))
           break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * p.acc_stride + me * p.acc_b_off;
+        const uint32_t d_tmem = tmem_acc + buf * p.acc_stride + me * p.acc_b_off;
         uint32_t accumulate = 0u;   // this thread's first UMMA of the segment overwrites its accumulator
         uint32_t si = 0;            // stage number inside the segment
         for (int k = seg.k0; k < seg.k1; ++si) {
           const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
-          // (both issuers watch every stage's barriers complete, in order: see the dequant warps)
+          // Both issuers watch every stage's barriers complete, in order: a parity wait only
+          // tells a phase from its neighbours, so a thread that skipped the other's stages could
+          // take a slot's previous use for the one it waits for.  For the same reason a slot
+          // must not be reused before BOTH have seen its current use (else a lagging issuer
+          // could find the barrier two phases on, which looks like "not yet"): the issuer that
+          // skips a stage arrives on the slot's release barriers too.
           if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 32 + ls, 1) ||
-              !sk_wait_bar(smem_u32(&ctrl->w_full[bs]), bph, abort_flag, p, 48 + bs, 1)) {
+              !sk_wait_bar(smem_u32(&ctrl->w_full[g]), wph, abort_flag, p, 48 + g, 1)) {
             ok = false;
             break;
           }
@@ -272,23 +290,24 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
             tc_fence_after();
             if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
             for (int j = 0; j < n; ++j) {
-              const uint32_t act = act_lo0 + (ls * KG + j) * act_tile16;
-              const uint32_t wgt = wgt_lo0 + (bs * KG + j) * (W_SLAB_BYTES >> 4);
-              const uint32_t a_lo = swapped ? wgt : act;   // UMMA M side
-              const uint32_t b_lo = swapped ? act : wgt;   // UMMA N side
+              const uint32_t b_lo = act_lo0 + (ls * KG + j) * act_tile16;          // activations: UMMA N side
+              const uint32_t a_t = tmem_base + g * W_SLOT_COLS + j * 32;            // weights: A operand in TMEM
 #pragma unroll
               for (int kk = 0; kk < BK / 16; ++kk) {
-                umma_f16_ss(d_tmem, desc_hi | (a_lo + kk * 2), desc_hi | (b_lo + kk * 2), idesc, accumulate);
+                umma_f16_ts(d_tmem, a_t + kk * 8, desc_hi | (b_lo + kk * 2), idesc, accumulate);
                 accumulate = 1u;
               }
             }
             umma_commit(smem_u32(&ctrl->load_empty[ls]));
-            umma_commit(smem_u32(&ctrl->w_empty[bs]));
+            umma_commit(smem_u32(&ctrl->w_empty[g]));
             if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
+          } else {
+            mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
+            mbar_arrive(smem_u32(&ctrl->w_empty[g]));
           }
           k += n;
           if (++ls == LS) { ls = 0; lph ^= 1u; }
-          if (++bs == BS) { bs = 0; bph ^= 1u; }
+          if (++g == DQ_GROUPS) { g = 0; wph ^= 1u; }
         }
         if (!ok) break;
         // (a thread that issued nothing in this segment has nothing to wait for)
@@ -304,92 +323,79 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   } else if (warp < 6) {
     // ------------------------------------------------------------- epilogue
     if constexpr (clustered)   // (takes part in the cluster's start-up barrier on its own)
-      sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_base,
-                      smem_u32(&ctrl->tmem_full[0]), sW, recv_base, smem_u32(&ctrl->recv_full),
+      sk_cluster_send(p, static_cast<int>(cluster_ctarank()), warp, lane, tmem_acc,
+                      smem_u32(&ctrl->tmem_full[0]), sA, recv_base, smem_u32(&ctrl->recv_full),
                       abort_flag, sk_cta_begin(s, pid) % s.iters_per_tile,
                       sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
     else
-      sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_base, smem_u32(&ctrl->tmem_full[0]),
+      sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_acc, smem_u32(&ctrl->tmem_full[0]),
                              smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   } else {
     // ------------------------------------------------------------- dequantise
-    // The eight warps form four groups of two, and group g takes stages g, g+4, g+8, ... whole.
-    // A stage costs a group far more in fixed latencies (two barrier waits, the loads of the
-    // packed words, scales and zero-points, the proxy fence, the arrivals) than in arithmetic,
-    // so what counts is how many stages are in flight at once, not how many threads share one:
-    // with every warp working on every stage, as a first version did, the stage rate was one
-    // warp's latency chain (0.8 us per stage, whatever was removed from it).
-    // Thread t of a group handles the 16-byte units u = t, t+64, t+128, t+192 of a K step:
-    // unit u = weight row u & 127, K half u >> 7 (32 values = 4 packed words).
+    // Group g (four warps, one per TMEM lane quadrant) takes stages g, g + 4, ... whole; a
+    // thread owns weight row `row` of the tile: the packed words of its row in, 64 halves of
+    // K per K step out, into the TMEM lane of that row.  Load slots (LS is a multiple of four)
+    // and TMEM slots are thus always used by the same group, which sees every phase of their
+    // barriers in order.  What a stage costs a group is mostly issue slots (about 250
+    // instructions per thread), so four groups keep all four schedulers busy while the waits
+    // of one are covered by the arithmetic of the others.
     const int dw = warp - 6;
-    const int grp = dw >> 1;
-    const int t = (dw & 1) * 32 + lane;
+    const int grp = dw >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * W_SLOT_COLS;
     SkCursor cur;
     sk_cursor_init(s, pid, cur);
     SkSeg seg;
-    int ls = 0, bs = 0;
-    uint32_t lph = 0, bph = 0;
-    uint32_t sidx = 0;   // running stage number
+    int ls = grp;                 // load slot of this group's next stage
+    uint32_t lph = 0, wph = 0;
+    uint32_t sidx = 0;            // running stage number
     bool dead = false;
     if (clustered) cluster_arrive_relaxed();
     while (sk_next(s, pid, cur, seg)) {
       for (int k = seg.k0; k < seg.k1;) {
         const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
-        // Every warp watches every stage's barriers complete, in order, also those of the
-        // stages it does not work on: a parity wait only tells a phase from its neighbours, and
-        // a group that skipped phases could take a slot's previous use for the awaited one
-        // (its stages are four apart, the rings may be shorter).  Both barriers of a foreign
-        // stage complete before those of the group's own next stage, so this costs no time.
-        if (!dead) {
-          if (!sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 64 + ls, 3) ||
-              !sk_wait_bar(smem_u32(&ctrl->w_empty[bs]), bph ^ 1u, abort_flag, p, 80 + bs, 3))
-            dead = true;
-        }
         if ((sidx & (DQ_GROUPS - 1)) == static_cast<uint32_t>(grp)) {
           if (!dead) {
+            // (warp-uniform outcome: the tensor-memory stores below are warp-wide instructions)
+            const bool got = sk_wait_bar(smem_u32(&ctrl->load_full[ls]), lph, abort_flag, p, 64 + ls, 3) &&
+                             sk_wait_bar(smem_u32(&ctrl->w_empty[grp]), wph ^ 1u, abort_flag, p, 80 + grp, 3);
+            if (!__all_sync(0xffffffffu, got)) dead = true;
+          }
+          if (!dead) {
+            tc_fence_after();     // the MMAs that read this slot's previous contents have retired
             const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
-            // rows t and t + 64
-            __half2 s2[2], zmagic[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int r = t + 64 * e;
-              const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
-              const uint32_t z = sz[256 + r];
-              s2[e] = __half2half2(sc);
-              const uint32_t zm = 0x64006400u | z | (z << 16);
-              zmagic[e] = *reinterpret_cast<const __half2*>(&zm);
-            }
+            const __half sc = *reinterpret_cast<const __half*>(sz + row * 2);
+            const uint32_t z = sz[256 + row];
+            const __half2 s2 = __half2half2(sc);
+            const uint32_t zm = 0x64006400u | z | (z << 16);
+            const __half2 zmagic = *reinterpret_cast<const __half2*>(&zm);
             for (int j = 0; j < n; ++j) {
-              const uint8_t* q = smem + off_q + (ls * KG + j) * Q_BLOCK_BYTES;
-              uint8_t* slab = smem + (bs * KG + j) * W_SLAB_BYTES;
-              uint4 w[4];
+              const uint8_t* q = smem + off_q + (ls * KG + j) * Q_BLOCK_BYTES + row * 16;
+              const uint4 w0 = *reinterpret_cast<const uint4*>(q);          // K 0..31 of the step
+              const uint4 w1 = *reinterpret_cast<const uint4*>(q + 2048);   // K 32..63
+              const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+              uint32_t v[32];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint4*>(q + (t + 64 * i) * 16);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int u = t + 64 * i;
-                const int r = u & 127, h = u >> 7, e = i & 1;
-                uint8_t* wrow = slab + r * 128;
-                const int sw = r & 7;
-                const uint32_t words[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                  *reinterpret_cast<uint4*>(wrow + (((h * 4 + c) ^ sw) << 4)) =
-                      dequant_word(words[c], zmagic[e], s2[e]);
+              for (int c = 0; c < 8; ++c) {
+                const uint4 o = dequant_word(words[c], zmagic, s2);
+                v[4 * c + 0] = o.x; v[4 * c + 1] = o.y; v[4 * c + 2] = o.z; v[4 * c + 3] = o.w;
               }
+              tmem_st_32x32(t_row + j * 32, v);
             }
-            fence_proxy_async_smem();  // generic-proxy stores -> visible to the UMMA reads
+            tmem_st_wait();
+            tc_fence_before();    // the stores are ordered before the arrival the MMA issuer acquires
           }
           __syncwarp();
           if (lane == 0) {
-            mbar_arrive(smem_u32(&ctrl->w_full[bs]));
+            mbar_arrive(smem_u32(&ctrl->w_full[grp]));
             mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
           }
+          wph ^= 1u;
+          ls += DQ_GROUPS;
+          if (ls >= LS) { ls -= LS; lph ^= 1u; }
         }
         ++sidx;
         k += n;
-        if (++ls == LS) { ls = 0; lph ^= 1u; }
-        if (++bs == BS) { bs = 0; bph ^= 1u; }
       }
     }
   }
@@ -417,7 +423,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     }
     tc_fence_after();
     __syncwarp();
-    tmem_dealloc(tmem_base, p.tmem_cols);
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if constexpr (clustered) {
     if (reduce_ok)
@@ -426,7 +432,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   } else {
     // Block-reduce fixup: every thread of the CTA now helps to reduce this CTA's slices of
     // the split tiles it took part in.
-    if constexpr (MODE == SK_EPI_BLOCK_REDUCE) sk_reduce_pending(p, C, pid, 0, ctrl->pend, ctrl->ok);
+    if constexpr (MODE == SK_EPI_BLOCK_REDUCE) sk_reduce_pending<true>(p, C, pid, 0, ctrl->pend, ctrl->ok);
   }
   if (threadIdx.x == 32) sk_trace(p, 7);
 }
@@ -522,8 +528,6 @@ inline int q4_nblocks(int N) { return (N + 255) / 256 * 2; }
 
 int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                      uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
-void sk_fill_tile_params(SkParams* p, int bn, int stage_fixed_bytes, int max_stages,
-                         int reserved_bytes, bool two_issuers);
 
 extern "C" size_t sk_q4_bytes(int N, int K) {
   if (N <= 0 || K <= 0 || (K % 128) != 0) return 0;
@@ -604,45 +608,46 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
                                              : 2000000ULL) * 1000ULL;
   p.ws = sk_ws_carve(ws, dev_sms);
   p.trace = sk_trace_buffer();
-  // The activation tile has 128 rows normally, bn rows when the operands are swapped.
-  const int a_rows = plan.swap ? plan.bn : BM;
-  const int a_stage_bytes = a_rows * BK * 2;
-  // (two MMA issuers pay off for the narrow UMMAs of the swapped order only: measured)
-  sk_fill_tile_params(&p, plan.bn, 0, 1, 0, plan.swap != 0);   // TMEM layout only; stages set below
+  if (!plan.swap || plan.bm != BM || plan.bn > 128) return SK_ERR_ARG;   // (make_plan: always swapped, tile_m <= 128)
+  // The activation tile feeds the UMMA N side: bn = tile_m rows of A per K step.
+  const int a_tile_bytes = plan.bn * BK * 2;
+  // Tensor memory: [0, 256) the dequantised-weight ring, [256, 512) two accumulator buffers.
+  // Narrow tiles (<= 64 columns) leave room for two accumulators per buffer, one per MMA
+  // issuer (issuing a UMMA costs its thread about the same whatever the width).
+  p.bn = plan.bn;
+  const int acc_cols = (plan.bn + 31) & ~31;
+  const bool dual = acc_cols <= 64;
+  p.acc_b_off = dual ? acc_cols : 0;
+  p.acc_stride = dual ? 2 * acc_cols : acc_cols;
+  p.tmem_cols = TMEM_COLS;
   p.kpair = 1;
-  // Two rings share the shared memory: load stages (activation tile + packed block) and
-  // dequantised weight stages.  The chain dequantise -> MMA -> release runs once per K step
-  // and takes over a microsecond end to end, so the weight ring has to be deep as well: take
-  // the deepest weight ring that still leaves at least as many load stages.
   const int split = p.sched.split;   // SK_SCHED_CLUSTER: CTAs per tile
   const int recv_bytes = split ? sk_cluster_recv_bytes(plan.bn, split) : 0;
   p.cl_per = split ? sk_cluster_quads_per_cta(plan.bn, split) : 1;
   p.cl_per_div = sk_div_make(p.cl_per);
+  // Shared memory is all load ring: activation tiles + packed block + group block per stage,
+  // in a multiple of DQ_GROUPS stages (a slot then always belongs to the same dequantise group).
   const int budget = SMEM_LIMIT - 1024 - CTRL_BYTES - recv_bytes;
-  const int load_stage = KG * (a_stage_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES;
-  int ls = 0, bs = 2;
-  for (int b = 4; b >= 2; --b) {
-    const int l = (budget - b * W_STAGE_BYTES) / load_stage;
-    if (l >= b || b == 2) { bs = b; ls = l; break; }
-  }
-  if (ls > 8) ls = 8;
-  if (ls < 2) return SK_ERR_SHAPE;
+  const int load_stage = KG * (a_tile_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES;
+  int ls = budget / load_stage / DQ_GROUPS * DQ_GROUPS;
+  if (ls > MAX_LS) ls = MAX_LS;
+  if (ls < DQ_GROUPS) return SK_ERR_SHAPE;
   p.stages = ls;
-  p.w_stages = bs;
-  p.row_tx_bytes = a_stage_bytes;
-  p.col_stage_bytes = a_stage_bytes;
+  p.w_stages = DQ_GROUPS;
+  p.row_tx_bytes = a_tile_bytes;
+  p.col_stage_bytes = a_tile_bytes;
   p.idesc = umma_idesc_f16(BM, plan.bn, 0);
 
   CUtensorMap tmA;
-  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, a_rows);
+  st = sk_make_tmap_f16(&tmA, A, M, K, prob->lda, BK, plan.bn);
   if (st != SK_OK) return st;
   const int nb = q4_nblocks(N), kb = K / 64;
   const uint8_t* qb = static_cast<const uint8_t*>(packed);
   const uint8_t* sz = qb + static_cast<size_t>(nb) * kb * Q_BLOCK_BYTES;
 
-  // the staging area of the cluster exchange lives in the rings
-  if (split && bs * W_STAGE_BYTES + ls * load_stage < recv_bytes) return SK_ERR_SHAPE;
-  const int smem_bytes = bs * W_STAGE_BYTES + ls * load_stage + 1024 + CTRL_BYTES + recv_bytes;
+  // the staging area of the cluster exchange lives in the load ring
+  if (split && ls * load_stage < recv_bytes) return SK_ERR_SHAPE;
+  const int smem_bytes = ls * load_stage + 1024 + CTRL_BYTES + recv_bytes;
   static SkPerDeviceOnce attrs;
   cudaError_t e = attrs.run([]() {
     cudaError_t r = cudaSuccess;
