@@ -126,6 +126,16 @@ __device__ __forceinline__ void sk_trace(const SkParams& p, int slot) {
 #endif
 }
 
+// The same with the SM's cycle counter (finer than %globaltimer's quarter microsecond), for
+// intervals inside one CTA.
+__device__ __forceinline__ void sk_trace_clk(const SkParams& p, int slot) {
+#ifdef SK_TRACE
+  if (p.trace) p.trace[blockIdx.x * 16 + slot] = static_cast<unsigned long long>(clock64());
+#else
+  (void)p; (void)slot;
+#endif
+}
+
 // First reporter wins; later errors keep the first record.
 __device__ __forceinline__ void sk_report(uint32_t* status, uint32_t code, uint32_t d0, uint32_t d1) {
   if (atomicCAS(status, 0u, code) == 0u) {

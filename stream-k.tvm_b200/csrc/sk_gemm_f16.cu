@@ -89,7 +89,16 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * G * (ROW_STAGE_BYTES + p.col_stage_bytes));
   volatile uint32_t* abort_flag = &ctrl->abort;
 
-  const int warp = threadIdx.x >> 5;
+  // The single-thread roles (producers, MMA issuers) are run by their whole warp, with only the
+  // TMA / tcgen05 / mbarrier instructions behind an elected lane (skptx::elect_one): the code
+  // then is warp-uniform for the compiler, operands sit in uniform registers, and issuing one of
+  // those instructions costs the warp about half of what it costs a lone lane inside a divergent
+  // `if (lane == 0)` region (measured on the W4A16 kernel: 125 -> 65 cycles per UMMA).  The
+  // warp index is therefore computed in the form the compiler knows to be uniform.  The cluster
+  // instantiation keeps the plain form and single-lane loops: with the uniform form the W4A16
+  // kernel's cluster start-up barrier never completed (cause not found by reading).
+  constexpr bool clustered = MODE == SK_MODE_CLUSTER;
+  const int warp = clustered ? static_cast<int>(threadIdx.x >> 5) : uniform_warp_idx();
   const int lane = threadIdx.x & 31;
   const int pid = blockIdx.x;
   const SkSched& s = p.sched;
@@ -98,7 +107,6 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     griddep_launch_dependents();   // the next kernel of the stream may begin its own start-up
   }
   // Split-K inside a cluster: the partial tiles meet in a receive buffer behind the control block.
-  constexpr bool clustered = MODE == SK_MODE_CLUSTER;
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
   // Start-up.  The time from kernel entry to the first load is pure latency on every small
@@ -139,7 +147,8 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
   SkSeg seg;
   bool have = false;
   int tr = 0, tc = 0;
-  if (lane == 0 && (warp == 0 || warp == 1 || warp == 6 || warp == 7)) {
+  const bool solo = clustered ? lane == 0 : true;   // which lanes of a single-thread role's warp run its loop
+  if (solo && (warp == 0 || warp == 1 || warp == 6 || warp == 7)) {
     sk_cursor_init(s, pid, cur);
     have = sk_next(s, pid, cur, seg);
     if (have) sk_tile_mn(s, seg.tile, tr, tc);
@@ -182,7 +191,8 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     // that, not bandwidth, bounds the K-step rate.  So two threads in two warps share the
     // work: warp 0 loads the row operand (and announces the stage's byte count), warp 6 the
     // column operand.  Both wait on the same "stage free" barrier.
-    if (lane == 0) {
+    if (solo) {
+      const bool leader = clustered ? true : elect_one();
       const bool is_row = warp == 0;
       bool traced = false;
       bool arrived = false;
@@ -210,11 +220,13 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
             ok = false;
             break;
           }
-          if (is_row) mbar_arrive_expect_tx(full, n * tx);
-          for (int j = 0; j < n; ++j) {
-            const uint32_t dst = dst0 + (stage * G + j) * stage_bytes;
-            if (loader == SK_LOAD_TMA_K) tma_load_2d(dst, tm, full, (k + j) * BK, first_row);
-            else load_operand(loader, dst, tm, img, full, first_row, k + j, tile_rows, s.iters_per_tile);
+          if (leader) {
+            if (is_row) mbar_arrive_expect_tx(full, n * tx);
+            for (int j = 0; j < n; ++j) {
+              const uint32_t dst = dst0 + (stage * G + j) * stage_bytes;
+              if (loader == SK_LOAD_TMA_K) tma_load_2d(dst, tm, full, (k + j) * BK, first_row);
+              else load_operand(loader, dst, tm, img, full, first_row, k + j, tile_rows, s.iters_per_tile);
+            }
           }
           k += n;
           if (++stage == STAGES) {
@@ -227,7 +239,7 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
               arrived = true;
             }
           }
-          if (is_row && !traced) { sk_trace(p, 2); traced = true; }
+          if (leader && is_row && !traced) { sk_trace(p, 2); traced = true; }
         }
       }
       if (clustered && !arrived) {
@@ -243,7 +255,8 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
     // buffer (p.acc_b_off), a second thread in a warp of another scheduler takes every other
     // stage of a segment and accumulates on its own; the epilogue adds the two.
     const uint32_t me = warp == 1 ? 0u : 1u;
-    if (lane == 0 && (me == 0u || p.acc_b_off != 0)) {
+    if (solo && (me == 0u || p.acc_b_off != 0)) {
+      const bool leader = clustered ? true : elect_one();
       const bool dual = p.acc_b_off != 0;
       int stage = 0;
       uint32_t ph = 0;
@@ -286,36 +299,39 @@ sk_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmRow, const __grid_const
             // The slot must not be refilled before BOTH issuers have seen this use of it: a
             // lagging issuer that found the barrier two phases on would read that as "not yet"
             // and wait for a use that may never come.  So the skipping issuer arrives as well.
-            mbar_arrive(empty0 + 8u * stage);
+            if (leader) mbar_arrive(empty0 + 8u * stage);
             k += n;
             if (++stage == STAGES) { stage = 0; ph ^= 1u; }
             continue;
           }
           tc_fence_after();
-          if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
+          if (leader && nseg == 0 && k == seg.k0) sk_trace(p, 3);
           for (int j = 0; j < n; ++j) {
             const uint32_t a_lo = row_lo0 + (stage * G + j) * (ROW_STAGE_BYTES >> 4);
             const uint32_t b_lo = col_lo0 + (stage * G + j) * col_stage16;
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk) {
-              umma_f16_ss(d_tmem, row_hi | (a_lo + kk * row_kstep16), col_hi | (b_lo + kk * col_kstep16),
-                          idesc, accumulate);
+              if (leader)
+                umma_f16_ss(d_tmem, row_hi | (a_lo + kk * row_kstep16), col_hi | (b_lo + kk * col_kstep16),
+                            idesc, accumulate);
               accumulate = 1u;
             }
           }
-          umma_commit(empty0 + 8u * stage);  // frees the stage when the MMAs retire
+          if (leader) umma_commit(empty0 + 8u * stage);  // frees the stage when the MMAs retire
           k += n;
           if (++stage == STAGES) { stage = 0; ph ^= 1u; }
           // start-up barrier of the cluster: while the pipeline is still filling
           if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
         }
         if (!ok) break;
-        // (a thread that issued nothing in this segment has nothing to wait for)
-        if (accumulate) umma_commit(smem_u32(&ctrl->tmem_full[buf]));
-        else mbar_arrive(smem_u32(&ctrl->tmem_full[buf]));
+        // (an issuer that issued nothing in this segment has nothing to wait for)
+        if (leader) {
+          if (accumulate) umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+          else mbar_arrive(smem_u32(&ctrl->tmem_full[buf]));
+        }
         ++nseg;
       }
-      if (me == 0u) sk_trace(p, 4);
+      if (leader && me == 0u) sk_trace(p, 4);
       if (clustered && !arrived) cluster_arrive_relaxed();
     } else if (clustered) {
       cluster_arrive_relaxed();

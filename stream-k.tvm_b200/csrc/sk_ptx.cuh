@@ -25,6 +25,27 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
+// One lane of a converged warp (the same one every time it is asked).  Code that the whole
+// warp runs with only the tcgen05 / mbarrier instructions behind this predicate stays
+// warp-uniform for the compiler: addresses and descriptors live in uniform registers instead
+// of being moved there one by one ahead of every instruction, as they are inside a divergent
+// `if (lane == 0)` region.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok));
+  return ok != 0;
+}
+// The warp's index, as a value the compiler knows to be the same in every lane.
+__device__ __forceinline__ int uniform_warp_idx() {
+  return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -123,7 +123,13 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + off_sz + LS * SZ_BLOCK_BYTES);
   volatile uint32_t* abort_flag = &ctrl->abort;
 
-  const int warp = threadIdx.x >> 5;
+  // Outside the cluster schedule the warp index is computed so that the compiler knows it to
+  // be warp-uniform (role branches then do not count as divergent, see elect_one).  The cluster
+  // kernel keeps the plain form and single-lane issue loops: with the uniform form its
+  // barrier.cluster start-up barrier never completed (hung, cause not found by reading; the
+  // plain form is the one that has always run).
+  constexpr bool clustered = MODE == SK_MODE_CLUSTER;
+  const int warp = clustered ? static_cast<int>(threadIdx.x >> 5) : uniform_warp_idx();
   const int lane = threadIdx.x & 31;
   const int pid = blockIdx.x;
   const SkSched& s = p.sched;
@@ -135,7 +141,6 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   }
   // Split-K inside a cluster (sk_epilogue.cuh): receive buffer behind the control block,
   // staging area in the load ring, which is idle by then.
-  constexpr bool clustered = MODE == SK_MODE_CLUSTER;
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
   if (warp == 2) {
@@ -250,16 +255,26 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     // is eight of them.  With room in tensor memory for two accumulators per buffer
     // (p.acc_b_off), a second thread takes every other stage of a segment and accumulates on
     // its own; the epilogue adds the two.
+    // The whole warp walks the schedule and waits on the barriers; one elected lane issues the
+    // tcgen05 instructions and barrier arrivals (see elect_one).
     const uint32_t me = warp == 1 ? 0u : 1u;
-    if (lane == 0 && (me == 0u || p.acc_b_off != 0)) {
+    bool in_loop = me == 0u || p.acc_b_off != 0;
+    bool leader;
+    if constexpr (clustered) {
+      leader = lane == 0;
+      in_loop = in_loop && leader;
+    } else {
+      leader = in_loop && elect_one();
+    }
+    if (in_loop) {
       const bool dual = p.acc_b_off != 0;
+      bool arrived = false;    // this thread's share of the cluster's start-up barrier
       SkCursor cur;
       sk_cursor_init(s, pid, cur);
       SkSeg seg;
       int ls = 0, g = 0;
       uint32_t lph = 0, wph = 0, nseg = 0;
       bool ok = true;
-      bool arrived = false;
       const uint64_t desc_hi = umma_desc_sw128_hi(16, 1024);
       const uint32_t act_lo0 = umma_desc_lo(sA);
       const uint32_t act_tile16 = static_cast<uint32_t>(a_tile_bytes) >> 4;
@@ -286,36 +301,42 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
             ok = false;
             break;
           }
+          if (leader && me == 0u && nseg == 0 && si >= 8 && si < 10) sk_trace_clk(p, 12 + 2 * (si - 8));   // barriers seen
           if (!dual || (si & 1u) == me) {
             tc_fence_after();
-            if (nseg == 0 && k == seg.k0) sk_trace(p, 3);
+            if (leader && nseg == 0 && k == seg.k0) sk_trace(p, 3);
             for (int j = 0; j < n; ++j) {
               const uint32_t b_lo = act_lo0 + (ls * KG + j) * act_tile16;          // activations: UMMA N side
               const uint32_t a_t = tmem_base + g * W_SLOT_COLS + j * 32;            // weights: A operand in TMEM
 #pragma unroll
               for (int kk = 0; kk < BK / 16; ++kk) {
-                umma_f16_ts(d_tmem, a_t + kk * 8, desc_hi | (b_lo + kk * 2), idesc, accumulate);
+                if (leader) umma_f16_ts(d_tmem, a_t + kk * 8, desc_hi | (b_lo + kk * 2), idesc, accumulate);
                 accumulate = 1u;
               }
             }
-            umma_commit(smem_u32(&ctrl->load_empty[ls]));
-            umma_commit(smem_u32(&ctrl->w_empty[g]));
+            if (leader) {
+              umma_commit(smem_u32(&ctrl->load_empty[ls]));
+              umma_commit(smem_u32(&ctrl->w_empty[g]));
+            }
             if (clustered && !arrived) { cluster_arrive_relaxed(); arrived = true; }
-          } else {
+          } else if (leader) {
             mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
             mbar_arrive(smem_u32(&ctrl->w_empty[g]));
           }
+          if (leader && me == 0u && nseg == 0 && si >= 8 && si < 10) sk_trace_clk(p, 13 + 2 * (si - 8));   // issued / skipped
           k += n;
           if (++ls == LS) { ls = 0; lph ^= 1u; }
           if (++g == DQ_GROUPS) { g = 0; wph ^= 1u; }
         }
         if (!ok) break;
-        // (a thread that issued nothing in this segment has nothing to wait for)
-        if (accumulate) umma_commit(smem_u32(&ctrl->tmem_full[buf]));
-        else mbar_arrive(smem_u32(&ctrl->tmem_full[buf]));
+        // (an issuer that issued nothing in this segment has nothing to wait for)
+        if (leader) {
+          if (accumulate) umma_commit(smem_u32(&ctrl->tmem_full[buf]));
+          else mbar_arrive(smem_u32(&ctrl->tmem_full[buf]));
+        }
         ++nseg;
       }
-      if (me == 0u) sk_trace(p, 4);
+      if (leader && me == 0u) sk_trace(p, 4);
       if (clustered && !arrived) cluster_arrive_relaxed();
     } else if (clustered) {
       cluster_arrive_relaxed();
@@ -350,6 +371,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     uint32_t lph = 0, wph = 0;
     uint32_t sidx = 0;            // running stage number
     bool dead = false;
+    const bool tracer = grp == 0 && (warp & 3) == 0 && lane == 0;
+    int own = 0;                  // stages this group has done (tracing only)
     if (clustered) cluster_arrive_relaxed();
     while (sk_next(s, pid, cur, seg)) {
       for (int k = seg.k0; k < seg.k1;) {
@@ -361,6 +384,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
                              sk_wait_bar(smem_u32(&ctrl->w_empty[grp]), wph ^ 1u, abort_flag, p, 80 + grp, 3);
             if (!__all_sync(0xffffffffu, got)) dead = true;
           }
+          if (tracer && own >= 2 && own < 4) sk_trace_clk(p, 8 + 2 * (own - 2));    // stage start (waits done)
           if (!dead) {
             tc_fence_after();     // the MMAs that read this slot's previous contents have retired
             const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
@@ -390,6 +414,8 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
             mbar_arrive(smem_u32(&ctrl->w_full[grp]));
             mbar_arrive(smem_u32(&ctrl->load_empty[ls]));
           }
+          if (tracer && own >= 2 && own < 4) sk_trace_clk(p, 9 + 2 * (own - 2));    // stage handed over
+          ++own;
           wph ^= 1u;
           ls += DQ_GROUPS;
           if (ls >= LS) { ls -= LS; lph ^= 1u; }
