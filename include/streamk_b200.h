@@ -95,6 +95,14 @@ enum { SK_FLAG_PDL = 1, /* fp16 / W4A16 entry points: launch with programmatic s
                           before the preceding kernel has completed (griddepcontrol.wait), so
                           results and stream order are unchanged.  Worth 1-2 us per launch in a
                           chain of small GEMMs.                                            */
+       SK_FLAG_BF16 = 4, /* sk_gemm_f16 / sk_gemm_f16_gather / sk_prepack_ladder images: A, B and C hold
+                          bfloat16 instead of fp16 (same layouts, same kernels: the UMMA reads the
+                          operands as bf16, accumulates in fp32, and the epilogue rounds to bf16).
+                          No counterpart in the reference (fp16 only); its README's dtype TODO.  */
+       /* sk_gemm_w4a16: group size of the packed image's scales / zero-points along K (two-bit
+          field; the default, 0, is 128).  Must match what sk_prepack_q4_ex was given.         */
+       SK_FLAG_Q4_GROUP_32 = 0x100, SK_FLAG_Q4_GROUP_64 = 0x200, SK_FLAG_Q4_PER_CHANNEL = 0x300,
+       SK_FLAG_Q4_GROUP_MASK = 0x300,
        SK_FLAG_NO_TABLE = 2 /* SK_SCHED_AUTO: resolve by the built-in rules only, without
                           consulting the table of tuned shapes (what the offline tuner itself
                           uses to time the rules' choice).                                 */ };
@@ -266,6 +274,16 @@ int sk_prepack_q4(const void* qweight, const void* scales, const void* zeros, in
                   void* out, size_t out_bytes, void* stream);
 /* W[N,K] fp16 = dequantised image (bit-exact (q - z) * s with fp16 rounding). */
 int sk_dequant_q4(const void* packed, int N, int K, void* W, int ldw, void* stream);
+/* Further quantisation formats (the reference stops at plain uint4 and lists the rest as open
+ * work, README.md:20-21).  group_size: 32, 64, 128, or 0 / K for one group per weight row
+ * (per-channel scales); scales / zeros are then [N, K / group_size] (or [N, 1]).  is_signed: the
+ * nibbles are two's-complement int4 and the format is symmetric, W = q * s (zeros must be NULL);
+ * stored as q + 8 with zero-point 8, which is the same arithmetic exactly.  The GEMM is told
+ * the group size through SK_FLAG_Q4_GROUP_* in sk_problem.flags.                            */
+size_t sk_q4_bytes_ex(int N, int K, int group_size);
+int sk_prepack_q4_ex(const void* qweight, const void* scales, const void* zeros, int N, int K,
+                     int group_size, int is_signed, void* out, size_t out_bytes, void* stream);
+int sk_dequant_q4_ex(const void* packed, int N, int K, int group_size, void* W, int ldw, void* stream);
 /* Replaces tl_mod(A, QLB, C) of streamk_fp16_ladder_block_reduce_q4.py:143-599. */
 int sk_gemm_w4a16(const sk_problem* p, const void* A, const void* packed, void* C,
                   void* ws, size_t ws_bytes, void* stream);

@@ -20,6 +20,8 @@ SCHEDULES = {"streamk": 0, "hybrid": 1, "hybrid_dp_first": 2, "dp": 3, "auto": 4
 FIXUPS = {"atomic": 0, "block_reduce": 1}
 SK_FLAG_PDL = 1
 SK_FLAG_NO_TABLE = 2
+SK_FLAG_BF16 = 4
+SK_FLAG_Q4_GROUP = {128: 0, 32: 0x100, 64: 0x200, 0: 0x300}   # group size -> sk_problem.flags bits (0 = per-channel)
 
 
 class SkProblem(C.Structure):
@@ -81,6 +83,9 @@ SIGNATURES = {
     "sk_q4_bytes": (C.c_size_t, [C.c_int, C.c_int]),
     "sk_prepack_q4": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, _P, C.c_size_t, _P]),
     "sk_dequant_q4": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, _P]),
+    "sk_q4_bytes_ex": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "sk_prepack_q4_ex": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_size_t, _P]),
+    "sk_dequant_q4_ex": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int, _P]),
     "sk_gemm_w4a16": (C.c_int, [C.POINTER(SkProblem), _P, _P, _P, _P, C.c_size_t, _P]),
 }
 

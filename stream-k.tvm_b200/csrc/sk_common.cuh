@@ -88,6 +88,7 @@ struct SkParams {
   int stages;              // shared-memory pipeline depth
   int kgroup;              // K steps (of 64) that travel together through one pipeline stage
   int w_stages;            // W4A16: depth of the dequantised-weight ring
+  int q_gshift, q_groups;  // W4A16: group block of a 32-wide half step = index >> q_gshift; blocks per row
   int col_stage_bytes;     // bn * 128
   int row_tx_bytes, col_tx_bytes;   // bytes the loads of one stage deliver per operand
   int row_loader, col_loader;       // SK_LOAD_*
@@ -97,6 +98,7 @@ struct SkParams {
   SkSched sched;
   int fixup;               // SK_FIXUP_*
   int c_vec_ok;            // C rows can take 16-byte stores
+  int out_bf16;            // 1: operands and result are bfloat16 (SK_FLAG_BF16), else fp16
   int drop_flag_cta;       // test hook (sk_problem.test_drop_flag_cta - 1): this CTA never publishes
                            //    its block-reduce flag; negative = off
   unsigned long long timeout_ns;

@@ -47,35 +47,44 @@ __device__ __forceinline__ bool sk_wait_bar(uint32_t bar, uint32_t parity, volat
   }
 }
 
-// nv (<= 32) fp32 values of tile row `grow`, columns gcol0.. -> fp16 C
+// fp32 -> the 16-bit result type: fp16, or bfloat16 when the problem carries SK_FLAG_BF16
+// (p.out_bf16).  C is addressed as 16-bit words either way.
+__device__ __forceinline__ uint32_t sk_pack2(float a, float b, int bf16) {
+  uint32_t r;
+  if (bf16) asm("cvt.rn.bf16x2.f32 %0, %2, %1;" : "=r"(r) : "f"(a), "f"(b));   // (first source -> upper half)
+  else      asm("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ __half sk_cvt1(float a, int bf16) {
+  const uint32_t r = sk_pack2(a, 0.f, bf16);
+  return __ushort_as_half(static_cast<unsigned short>(r & 0xFFFFu));
+}
+
+// nv (<= 32) fp32 values of tile row `grow`, columns gcol0.. -> 16-bit C
 __device__ __forceinline__ void sk_store_chunk1(__half* __restrict__ C, const SkParams& p, int grow,
                                                 int gcol0, int nv, const float (&v)[32]) {
   if (p.transposed) {
     __half* dst = C + static_cast<size_t>(gcol0) * p.ldc + grow;
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (j < nv) dst[static_cast<size_t>(j) * p.ldc] = __float2half_rn(v[j]);
+      if (j < nv) dst[static_cast<size_t>(j) * p.ldc] = sk_cvt1(v[j], p.out_bf16);
     return;
   }
   __half* dst = C + static_cast<size_t>(grow) * p.ldc + gcol0;
   if (p.c_vec_ok && nv == 32) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
-      __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
-      __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
-      __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
       uint4 u;
-      u.x = *reinterpret_cast<uint32_t*>(&h0);
-      u.y = *reinterpret_cast<uint32_t*>(&h1);
-      u.z = *reinterpret_cast<uint32_t*>(&h2);
-      u.w = *reinterpret_cast<uint32_t*>(&h3);
+      u.x = sk_pack2(v[8 * j + 0], v[8 * j + 1], p.out_bf16);
+      u.y = sk_pack2(v[8 * j + 2], v[8 * j + 3], p.out_bf16);
+      u.z = sk_pack2(v[8 * j + 4], v[8 * j + 5], p.out_bf16);
+      u.w = sk_pack2(v[8 * j + 6], v[8 * j + 7], p.out_bf16);
       *reinterpret_cast<uint4*>(dst + 8 * j) = u;
     }
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (j < nv) dst[j] = __float2half_rn(v[j]);
+      if (j < nv) dst[j] = sk_cvt1(v[j], p.out_bf16);
   }
 }
 
@@ -96,20 +105,18 @@ __device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams
   if (p.transposed) {
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-      if (gcol + e < p.cols) C[static_cast<size_t>(gcol + e) * p.ldc + grow] = __float2half_rn(v[e]);
+      if (gcol + e < p.cols) C[static_cast<size_t>(gcol + e) * p.ldc + grow] = sk_cvt1(v[e], p.out_bf16);
   } else {
     __half* dst = C + static_cast<size_t>(grow) * p.ldc + gcol;
     if (p.c_vec_ok && gcol + 4 <= p.cols) {
-      __half2 h0 = __floats2half2_rn(v[0], v[1]);
-      __half2 h1 = __floats2half2_rn(v[2], v[3]);
       uint2 u;
-      u.x = *reinterpret_cast<uint32_t*>(&h0);
-      u.y = *reinterpret_cast<uint32_t*>(&h1);
+      u.x = sk_pack2(v[0], v[1], p.out_bf16);
+      u.y = sk_pack2(v[2], v[3], p.out_bf16);
       *reinterpret_cast<uint2*>(dst) = u;
     } else {
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        if (gcol + e < p.cols) dst[e] = __float2half_rn(v[e]);
+        if (gcol + e < p.cols) dst[e] = sk_cvt1(v[e], p.out_bf16);
     }
   }
 }
@@ -369,15 +376,13 @@ __device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtens
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        __half2 h0 = __floats2half2_rn(v[8 * j + 0], v[8 * j + 1]);
-        __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
-        __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
-        __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
+        const uint32_t h0 = sk_pack2(v[8 * j + 0], v[8 * j + 1], p.out_bf16);
+        const uint32_t h1 = sk_pack2(v[8 * j + 2], v[8 * j + 3], p.out_bf16);
+        const uint32_t h2 = sk_pack2(v[8 * j + 4], v[8 * j + 5], p.out_bf16);
+        const uint32_t h3 = sk_pack2(v[8 * j + 6], v[8 * j + 7], p.out_bf16);
         const uint32_t chunk = static_cast<uint32_t>(h * 4 + j);   // 16-byte chunk of the 128-byte row
         const uint32_t a = buf + static_cast<uint32_t>(lane) * 128u + ((chunk ^ (static_cast<uint32_t>(lane) & 7u)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a),
-                     "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
-                     "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3))
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(h0), "r"(h1), "r"(h2), "r"(h3)
                      : "memory");
       }
     }

@@ -490,6 +490,7 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   p.bm = plan.bm;
   p.fixup = prob->fixup;
   p.c_vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (prob->ldc & 7) == 0) ? 1 : 0;
+  p.out_bf16 = (prob->flags & SK_FLAG_BF16) ? 1 : 0;
   p.drop_flag_cta = prob->test_drop_flag_cta - 1;
   p.timeout_ns = (prob->fixup_timeout_us > 0 ? static_cast<unsigned long long>(prob->fixup_timeout_us)
                                              : 2000000ULL) * 1000ULL;
@@ -555,7 +556,7 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   }
   p.row_tx_bytes = plan.bm * BK * 2;   // the TMA box of the M-side operand has plan.bm rows
   p.col_tx_bytes = p.col_stage_bytes;
-  p.idesc = umma_idesc_f16(BM, plan.bn, 0) |
+  p.idesc = umma_idesc_f16(BM, plan.bn, 0, p.out_bf16) |
             (p.row_loader == SK_LOAD_TMA_MN ? (1u << 15) : 0u) |
             (p.col_loader == SK_LOAD_TMA_MN ? (1u << 16) : 0u);
 

@@ -429,7 +429,7 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   p->col_tx_bytes = (bn / 2) * BK * 2;   // bytes of this CTA's half of a B stage
   p->tmem_cols = TMEM_COLS;
   p->stages = STAGES;
-  p->idesc = umma_idesc_f16(2 * BM, bn, 0);
+  p->idesc = umma_idesc_f16(2 * BM, bn, 0, p->out_bf16);
   // K steps the second half of a 256 x 512 unit stays behind the first (see the MMA issuer)
   p->wide_lag = 1;
   if (const char* e = getenv("SK_WIDE_LAG")) p->wide_lag = atoi(e) < WSTAGES - 1 ? atoi(e) : WSTAGES - 2;

@@ -295,13 +295,13 @@ __device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) {
   return (smem_addr & 0x3FFFFu) >> 4;
 }
 
-// Instruction descriptor for kind::f16, fp16 A/B, fp32 D.
-//   [4,6) D format 1=f32   [7,10) A format 0=f16   [10,13) B format 0=f16
+// Instruction descriptor for kind::f16, fp16 (or bfloat16) A/B, fp32 D.
+//   [4,6) D format 1=f32   [7,10) A format 0=f16, 1=bf16   [10,13) B format 0=f16, 1=bf16
 //   [15] A major (0=K)     [16] B major (0=K, 1=MN)
 //   [17,23) N>>3           [24,29) M>>4
-__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, int b_mn_major) {
-  return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) |
-         (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n, int b_mn_major, int bf16 = 0) {
+  return (1u << 4) | (static_cast<uint32_t>(bf16 ? 1 : 0) << 7) | (static_cast<uint32_t>(bf16 ? 1 : 0) << 10) |
+         (0u << 15) | (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 

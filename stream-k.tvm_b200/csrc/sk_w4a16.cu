@@ -43,6 +43,7 @@ constexpr int BM = SK_BM;
 constexpr int BK = 64;
 constexpr int Q_BLOCK_BYTES = 128 * BK / 2;    // 4096: packed nibbles of 128 weight rows x 64 K
 constexpr int SZ_BLOCK_BYTES = 128 * 2 + 128;  // 384: fp16 scales + uint8 zero-points of a group
+constexpr int SZ_SLOT_BYTES = 4 * SZ_BLOCK_BYTES;   // a stage (128 of K) spans at most four groups (group size 32)
 constexpr int KG = 2;                          // K steps per stage = one scale group (128 along K)
 constexpr int MAX_LS = 16;                     // load stages (activation tile + packed block)
 constexpr int DQ_GROUPS = 4;                   // dequantise groups = slots of the TMEM weight ring
@@ -120,7 +121,11 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const uint32_t sA = base;
   const uint32_t sQ = base + off_q;
   const uint32_t sSZ = base + off_sz;
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + off_sz + LS * SZ_BLOCK_BYTES);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + off_sz + LS * SZ_SLOT_BYTES);
+  // Group g of a row covers K halves [g << (5 + gshift), ...): gshift 0 / 1 / 2 for group sizes
+  // 32 / 64 / 128, 30 for one group per row (per-channel scales).  Group blocks of a row block
+  // are consecutive in the image (q_groups of them).
+  const int gshift = p.q_gshift;
   volatile uint32_t* abort_flag = &ctrl->abort;
 
   // Outside the cluster schedule the warp index is computed so that the compiler knows it to
@@ -134,7 +139,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   const int pid = blockIdx.x;
   const SkSched& s = p.sched;
   const int kblocks = s.iters_per_tile;  // K / 64
-  const int groups = kblocks >> 1;       // K / 128
+  const int groups = p.q_groups;         // group blocks per 128-row block: K / group size, or 1
   if (threadIdx.x == 0) {
     sk_trace(p, 0);
     griddep_launch_dependents();   // the next kernel of the stream may begin its own start-up
@@ -225,13 +230,15 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(full, n * (a_tile_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES);
+          // the group blocks the stage's K range touches: one (group size 128 or per-channel) up to four
+          const int g0 = (2 * k) >> gshift, g1 = (2 * (k + n) - 1) >> gshift;
+          const int sz_bytes = (g1 - g0 + 1) * SZ_BLOCK_BYTES;
+          mbar_arrive_expect_tx(full, n * (a_tile_bytes + Q_BLOCK_BYTES) + sz_bytes);
           bulk_load_1d(sQ + ls * KG * Q_BLOCK_BYTES,
                        qblocks + (static_cast<size_t>(tr) * kblocks + k) * Q_BLOCK_BYTES,
                        n * Q_BLOCK_BYTES, full);
-          bulk_load_1d(sSZ + ls * SZ_BLOCK_BYTES,
-                       szblocks + (static_cast<size_t>(tr) * groups + (k >> 1)) * SZ_BLOCK_BYTES,
-                       SZ_BLOCK_BYTES, full);
+          bulk_load_1d(sSZ + ls * SZ_SLOT_BYTES,
+                       szblocks + (static_cast<size_t>(tr) * groups + g0) * SZ_BLOCK_BYTES, sz_bytes, full);
           for (int j = 0; j < n; ++j)
             tma_load_2d(sA + ls * a_stage_bytes + j * a_tile_bytes, &tmA, full, (k + j) * BK, a_row0);
           k += n;
@@ -387,12 +394,10 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           if (tracer && own >= 2 && own < 4) sk_trace_clk(p, 8 + 2 * (own - 2));    // stage start (waits done)
           if (!dead) {
             tc_fence_after();     // the MMAs that read this slot's previous contents have retired
-            const uint8_t* sz = smem + off_sz + ls * SZ_BLOCK_BYTES;
-            const __half sc = *reinterpret_cast<const __half*>(sz + row * 2);
-            const uint32_t z = sz[256 + row];
-            const __half2 s2 = __half2half2(sc);
-            const uint32_t zm = 0x64006400u | z | (z << 16);
-            const __half2 zmagic = *reinterpret_cast<const __half2*>(&zm);
+            const uint8_t* sz = smem + off_sz + ls * SZ_SLOT_BYTES;
+            const int g0 = (2 * k) >> gshift;    // first group block of the stage (slot-relative index 0)
+            __half2 s2, zmagic;
+            int cur_blk = -1;
             for (int j = 0; j < n; ++j) {
               const uint8_t* q = smem + off_q + (ls * KG + j) * Q_BLOCK_BYTES + row * 16;
               const uint4 w0 = *reinterpret_cast<const uint4*>(q);          // K 0..31 of the step
@@ -400,9 +405,22 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
               const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
               uint32_t v[32];
 #pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                const uint4 o = dequant_word(words[c], zmagic, s2);
-                v[4 * c + 0] = o.x; v[4 * c + 1] = o.y; v[4 * c + 2] = o.z; v[4 * c + 3] = o.w;
+              for (int h = 0; h < 2; ++h) {
+                const int blk = ((2 * (k + j) + h) >> gshift) - g0;   // group of this 32-wide half step
+                if (blk != cur_blk) {   // (group size 128: once per stage)
+                  cur_blk = blk;
+                  const uint8_t* b = sz + blk * SZ_BLOCK_BYTES;
+                  const __half sc = *reinterpret_cast<const __half*>(b + row * 2);
+                  const uint32_t z = b[256 + row];
+                  s2 = __half2half2(sc);
+                  const uint32_t zm = 0x64006400u | z | (z << 16);
+                  zmagic = *reinterpret_cast<const __half2*>(&zm);
+                }
+#pragma unroll
+                for (int c = 4 * h; c < 4 * h + 4; ++c) {
+                  const uint4 o = dequant_word(words[c], zmagic, s2);
+                  v[4 * c + 0] = o.x; v[4 * c + 1] = o.y; v[4 * c + 2] = o.z; v[4 * c + 3] = o.w;
+                }
               }
               tmem_st_32x32(t_row + j * 32, v);
             }
@@ -465,12 +483,13 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
 
 // ---------------------------------------------------------------- prepack / dequant
 // One thread per output word.  Source nibble e of an 8-element group sits at bits 4e.
+// groups: group blocks per row (K / group size, or 1); is_signed: the nibbles are two's-complement
+// int4, stored here as q + 8 with zero-point 8 (the same (q - z) * s arithmetic, exactly).
 __global__ void prepack_q4_kernel(const uint32_t* __restrict__ qw, const __half* __restrict__ scales,
                                   const uint8_t* __restrict__ zeros, int N, int K,
                                   uint32_t* __restrict__ qout, uint8_t* __restrict__ szout,
-                                  int nblocks, int kblocks) {
+                                  int nblocks, int kblocks, int groups, int is_signed) {
   const int kwords = K / 8;
-  const int groups = K / 128;
   const size_t total_words = static_cast<size_t>(nblocks) * kblocks * 1024;
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total_words;
@@ -485,7 +504,8 @@ __global__ void prepack_q4_kernel(const uint32_t* __restrict__ qw, const __half*
     const int n = nb * 128 + r;
     uint32_t out = 0u;
     if (n < N) {
-      const uint32_t w = qw[static_cast<size_t>(n) * kwords + kb * 8 + h * 4 + j];
+      uint32_t w = qw[static_cast<size_t>(n) * kwords + kb * 8 + h * 4 + j];
+      if (is_signed) w ^= 0x88888888u;   // two's complement -> offset binary, every nibble
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         out |= ((w >> (8 * t)) & 0xFu) << (4 * t);            // even elements 0,2,4,6
@@ -506,7 +526,7 @@ __global__ void prepack_q4_kernel(const uint32_t* __restrict__ qw, const __half*
     uint8_t z = 0;
     if (n < N) {
       sc = scales ? scales[static_cast<size_t>(n) * groups + g] : __float2half(1.f);
-      z = zeros ? static_cast<uint8_t>(zeros[static_cast<size_t>(n) * groups + g] & 0xF) : 0;
+      z = is_signed ? 8 : zeros ? static_cast<uint8_t>(zeros[static_cast<size_t>(n) * groups + g] & 0xF) : 0;
     }
     uint8_t* dst = szout + gblk * SZ_BLOCK_BYTES;
     *reinterpret_cast<__half*>(dst + r * 2) = sc;
@@ -517,8 +537,7 @@ __global__ void prepack_q4_kernel(const uint32_t* __restrict__ qw, const __half*
 // One thread per packed word -> eight halves of W[n, k..k+7].
 __global__ void dequant_q4_kernel(const uint32_t* __restrict__ qblocks,
                                   const uint8_t* __restrict__ szblocks, int N, int K,
-                                  __half* __restrict__ W, int ldw, int kblocks) {
-  const int groups = K / 128;
+                                  __half* __restrict__ W, int ldw, int kblocks, int groups, int gshift) {
   const size_t nb_used = (static_cast<size_t>(N) + 127) / 128;
   const size_t total_words = nb_used * kblocks * 1024;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total_words;
@@ -532,7 +551,7 @@ __global__ void dequant_q4_kernel(const uint32_t* __restrict__ qblocks,
     const int kb = static_cast<int>(blk - static_cast<size_t>(nb) * kblocks);
     const int n = nb * 128 + r;
     if (n >= N) continue;
-    const uint8_t* sz = szblocks + (static_cast<size_t>(nb) * groups + (kb >> 1)) * SZ_BLOCK_BYTES;
+    const uint8_t* sz = szblocks + (static_cast<size_t>(nb) * groups + ((2 * kb + h) >> gshift)) * SZ_BLOCK_BYTES;
     const __half sc = *reinterpret_cast<const __half*>(sz + r * 2);
     const uint32_t z = sz[256 + r];
     const uint32_t zm = 0x64006400u | z | (z << 16);
@@ -555,17 +574,35 @@ inline int q4_nblocks(int N) { return (N + 255) / 256 * 2; }
 int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                      uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
 
-extern "C" size_t sk_q4_bytes(int N, int K) {
-  if (N <= 0 || K <= 0 || (K % 128) != 0) return 0;
-  const size_t nb = q4_nblocks(N);
-  return nb * (K / 64) * Q_BLOCK_BYTES + nb * (K / 128) * SZ_BLOCK_BYTES;
+// group_size 32, 64, 128, or K / 0 (one group per row: per-channel scales) -> gshift, groups per row
+static bool q4_group(int K, int group_size, int* gshift, int* groups) {
+  if (group_size == 0 || (group_size == K && K > 128)) { *gshift = 30; *groups = 1; return true; }
+  if (group_size == 32) *gshift = 0;
+  else if (group_size == 64) *gshift = 1;
+  else if (group_size == 128) *gshift = 2;
+  else return false;
+  *groups = K / group_size;
+  return true;
 }
 
-extern "C" int sk_prepack_q4(const void* qweight, const void* scales, const void* zeros, int N,
-                             int K, void* out, size_t out_bytes, void* stream) {
+extern "C" size_t sk_q4_bytes_ex(int N, int K, int group_size) {
+  int gshift, groups;
+  if (N <= 0 || K <= 0 || (K % 128) != 0 || !q4_group(K, group_size, &gshift, &groups)) return 0;
+  const size_t nb = q4_nblocks(N);
+  return nb * (K / 64) * Q_BLOCK_BYTES + nb * groups * SZ_BLOCK_BYTES;
+}
+
+extern "C" size_t sk_q4_bytes(int N, int K) { return sk_q4_bytes_ex(N, K, 128); }
+
+extern "C" int sk_prepack_q4_ex(const void* qweight, const void* scales, const void* zeros, int N,
+                                int K, int group_size, int is_signed, void* out, size_t out_bytes,
+                                void* stream) {
   if (!qweight || !out) return SK_ERR_ARG;
+  int gshift, groups;
   if (N <= 0 || K <= 0 || (K % 128) != 0) return SK_ERR_SHAPE;
-  if (out_bytes < sk_q4_bytes(N, K)) return SK_ERR_WORKSPACE;
+  if (!q4_group(K, group_size, &gshift, &groups)) return SK_ERR_ARG;
+  if (is_signed && zeros) return SK_ERR_ARG;     // signed int4 is symmetric: W = q * s
+  if (out_bytes < sk_q4_bytes_ex(N, K, group_size)) return SK_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(out) & 15u) || (reinterpret_cast<uintptr_t>(qweight) & 3u))
     return SK_ERR_ALIGN;
   const int nb = q4_nblocks(N), kb = K / 64;
@@ -575,15 +612,28 @@ extern "C" int sk_prepack_q4(const void* qweight, const void* scales, const void
   const int grid = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   prepack_q4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint32_t*>(qweight), static_cast<const __half*>(scales),
-      static_cast<const uint8_t*>(zeros), N, K, reinterpret_cast<uint32_t*>(o), sz, nb, kb);
+      static_cast<const uint8_t*>(zeros), N, K, reinterpret_cast<uint32_t*>(o), sz, nb, kb, groups,
+      is_signed ? 1 : 0);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }
 
+extern "C" int sk_prepack_q4(const void* qweight, const void* scales, const void* zeros, int N,
+                             int K, void* out, size_t out_bytes, void* stream) {
+  return sk_prepack_q4_ex(qweight, scales, zeros, N, K, 128, 0, out, out_bytes, stream);
+}
+
 extern "C" int sk_dequant_q4(const void* packed, int N, int K, void* W, int ldw, void* stream) {
+  return sk_dequant_q4_ex(packed, N, K, 128, W, ldw, stream);
+}
+
+extern "C" int sk_dequant_q4_ex(const void* packed, int N, int K, int group_size, void* W, int ldw,
+                                void* stream) {
   if (!packed || !W) return SK_ERR_ARG;
+  int gshift, groups;
   if (N <= 0 || K <= 0 || (K % 128) != 0 || ldw < K) return SK_ERR_SHAPE;
+  if (!q4_group(K, group_size, &gshift, &groups)) return SK_ERR_ARG;
   if (reinterpret_cast<uintptr_t>(packed) & 15u) return SK_ERR_ALIGN;
   const int nb = q4_nblocks(N), kb = K / 64;
   const uint8_t* o = static_cast<const uint8_t*>(packed);
@@ -591,7 +641,7 @@ extern "C" int sk_dequant_q4(const void* packed, int N, int K, void* W, int ldw,
   const size_t total = (static_cast<size_t>(N) + 127) / 128 * kb * 1024;
   const int grid = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   dequant_q4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint32_t*>(o), sz, N, K, static_cast<__half*>(W), ldw, kb);
+      reinterpret_cast<const uint32_t*>(o), sz, N, K, static_cast<__half*>(W), ldw, kb, groups, gshift);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
@@ -610,6 +660,11 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   const int M = prob->M, N = prob->N, K = prob->K;
   if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0) return SK_ERR_SHAPE;
   if (prob->lda < K || prob->ldc < N) return SK_ERR_SHAPE;
+  const int gcode = prob->flags & SK_FLAG_Q4_GROUP_MASK;
+  const int group_size = gcode == SK_FLAG_Q4_GROUP_32 ? 32 : gcode == SK_FLAG_Q4_GROUP_64 ? 64
+                       : gcode == SK_FLAG_Q4_PER_CHANNEL ? 0 : 128;
+  int gshift = 2, groups = K / 128;
+  if (!q4_group(K, group_size, &gshift, &groups)) return SK_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(packed) & 15u))
     return SK_ERR_ALIGN;
   if ((prob->lda & 7) != 0 || (reinterpret_cast<uintptr_t>(C) & 1u) != 0) return SK_ERR_ALIGN;
@@ -654,7 +709,9 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   // Shared memory is all load ring: activation tiles + packed block + group block per stage,
   // in a multiple of DQ_GROUPS stages (a slot then always belongs to the same dequantise group).
   const int budget = SMEM_LIMIT - 1024 - CTRL_BYTES - recv_bytes;
-  const int load_stage = KG * (a_tile_bytes + Q_BLOCK_BYTES) + SZ_BLOCK_BYTES;
+  const int load_stage = KG * (a_tile_bytes + Q_BLOCK_BYTES) + SZ_SLOT_BYTES;
+  p.q_gshift = gshift;
+  p.q_groups = groups;
   int ls = budget / load_stage / DQ_GROUPS * DQ_GROUPS;
   if (ls > MAX_LS) ls = MAX_LS;
   if (ls < DQ_GROUPS) return SK_ERR_SHAPE;

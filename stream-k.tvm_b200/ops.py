@@ -121,7 +121,7 @@ def device_info(device: int = 0) -> dict:
 
 # --------------------------------------------------------------------------- helpers
 _OPTION_KEYS = ("tile_m", "tile_n", "num_sms", "group_m", "out", "timeout_us", "pdl", "no_table",
-                "_drop_flag_cta")
+                "_drop_flag_cta", "_bf16")
 
 
 def _options(kw: dict) -> dict:
@@ -152,7 +152,8 @@ def _problem(M, N, K, lda, ldb, ldc, layout, schedule, fixup, o: dict) -> L.SkPr
                        fixup_timeout_us=int(o["timeout_us"] or 0),
                        # (the C field is 0 = off, n = CTA n - 1)
                        test_drop_flag_cta=0 if o["_drop_flag_cta"] is None else int(o["_drop_flag_cta"]) + 1,
-                       flags=(L.SK_FLAG_PDL if o["pdl"] else 0) | (L.SK_FLAG_NO_TABLE if o["no_table"] else 0))
+                       flags=(L.SK_FLAG_PDL if o["pdl"] else 0) | (L.SK_FLAG_NO_TABLE if o["no_table"] else 0)
+                             | (L.SK_FLAG_BF16 if o["_bf16"] else 0))
 
 
 def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = "auto",
@@ -174,10 +175,15 @@ def schedule_info(M: int, N: int, K: int, *, kind: str = "f16", schedule: str = 
     return info.as_dict()
 
 
-def _check_matrix(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
+HALF_TYPES = (torch.float16, torch.bfloat16)
+
+
+def _check_matrix(name: str, t: torch.Tensor, dtype) -> None:
+    """dtype: one torch dtype, or a tuple of acceptable ones."""
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
-    if t.dtype != dtype:
+    ok = t.dtype in dtype if isinstance(dtype, tuple) else t.dtype == dtype
+    if not ok:
         raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
     if t.dim() != 2:
         raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
@@ -250,19 +256,24 @@ def streamk_fp32(A: torch.Tensor, B: torch.Tensor, *, fixup: str = "atomic",
 
 # --------------------------------------------------------------------------- fp16
 def _gemm_f16(A, B, layout, fixup, schedule, kw):
+    """fp16 operands, or bfloat16 ones (both operands alike; the result has their type)."""
     o = _options(kw)
-    _check_matrix("A", A, torch.float16)
+    _check_matrix("A", A, HALF_TYPES)
+    dtype = A.dtype
+    o["_bf16"] = dtype == torch.bfloat16
     M, K = A.shape
     if layout == "ladder":
         if not isinstance(B, LadderWeight):
             raise TypeError("B must come from ladder_prepack()")
         if B.K != K:
             raise ValueError(f"Incompatible dimensions: A {tuple(A.shape)} weight K={B.K}")
+        if B.dtype != dtype:
+            raise TypeError(f"A is {dtype} but the weight image was packed from {B.dtype}")
         N = B.N
         Bt, ldb = B.data, 0
         A = _aligned16(_rowmajor(_pad_k8(A, 1)))
     else:
-        _check_matrix("B", B, torch.float16)
+        _check_matrix("B", B, dtype)
         if layout == "nt":
             N, Kb = B.shape
         else:
@@ -276,7 +287,7 @@ def _gemm_f16(A, B, layout, fixup, schedule, kw):
             # NN: rows of B are K; the N pitch must be a multiple of 8 halves
             Bt = _aligned16(_rowmajor(_pad_k8(B, 0)))
         ldb = Bt.stride(0)
-    Cout = _out(o["out"], M, N, torch.float16, A.device)
+    Cout = _out(o["out"], M, N, dtype, A.device)
     prob = _problem(M, N, A.shape[1], A.stride(0), ldb, Cout.stride(0), layout, schedule, fixup, o)
     with torch.cuda.device(A.device):
         ws = _workspace(A.device)
@@ -288,6 +299,8 @@ def _gemm_f16(A, B, layout, fixup, schedule, kw):
 
 def streamk_fp16_nt(A, B, *, fixup="block_reduce", schedule="auto", **kw):
     """C = A @ B.T, fp16 in, fp32 accumulate, fp16 out.  A [M,K], B [N,K].
+    (bfloat16 tensors are accepted as well, here and in the NN and ladder forms: same kernels,
+    bf16 operands, fp32 accumulation, bf16 result; the reference is fp16 only.)
 
     Mirrors `tl_matmul_streamk(M, N, K, streamk_tiles, "float16", "float16", ...)` +
     `tl_mod(A, B, C)` of streamk_fp16.py:116-387 and streamk_fp16_nt.py:57-192.
@@ -441,6 +454,7 @@ class LadderWeight:
     data: torch.Tensor
     N: int
     K: int
+    dtype: torch.dtype = torch.float16
 
 
 def ladder_prepack(B: torch.Tensor) -> LadderWeight:
@@ -448,7 +462,7 @@ def ladder_prepack(B: torch.Tensor) -> LadderWeight:
 
     Replaces `bitblas.ops.LadderPermutate(...)(B.cpu())` (streamk_fp16_ladder.py:468-477);
     runs on the GPU."""
-    _check_matrix("B", B, torch.float16)
+    _check_matrix("B", B, HALF_TYPES)
     B = _rowmajor(B)
     N, K = B.shape
     lib = L.load()
@@ -457,7 +471,7 @@ def ladder_prepack(B: torch.Tensor) -> LadderWeight:
     with torch.cuda.device(B.device):
         L.check(lib.sk_prepack_ladder(B.data_ptr(), N, K, B.stride(0), out.data_ptr(), nbytes,
                                       _stream_ptr(B.device)), "sk_prepack_ladder")
-    return LadderWeight(out, N, K)
+    return LadderWeight(out, N, K, B.dtype)
 
 
 def streamk_fp16_ladder(A, LB: LadderWeight, *, fixup="block_reduce", schedule="auto", **kw):
@@ -477,20 +491,24 @@ class PackedQ4:
     data: torch.Tensor
     N: int
     K: int
+    group_size: int = GROUP_SIZE     # 32, 64, 128, or 0 = one group per weight row (per-channel)
+    signed: bool = False
 
 
 def q4_prepack(qweight: torch.Tensor, scales: torch.Tensor | None = None,
-               zeros: torch.Tensor | None = None, group_size: int = GROUP_SIZE) -> PackedQ4:
-    """Pack uint4 weights for the W4A16 mainloop.
+               zeros: torch.Tensor | None = None, group_size: int = GROUP_SIZE,
+               signed: bool = False) -> PackedQ4:
+    """Pack 4-bit weights for the W4A16 mainloop.
 
     qweight: int32 [N, K/8] (nibble j of word w = element 8w+j) or int8/uint8 [N, K/2]
     (low nibble = even k, the reference's storage, …_q4.py:28-30,545-554).
-    scales: fp16 [N, K/128] or None (=1).  zeros: uint8 [N, K/128] in 0..15 or None (=0).
-    With scales=None, zeros=None the GEMM reproduces the reference's `A @ unpack(qB).T`.
-    Replaces LadderPermutate + LOP3Permutate on the CPU (…_q4.py:568-595).
+    scales: fp16 [N, K/group_size] or None (=1).  zeros: uint8 [N, K/group_size] in 0..15 or None
+    (=0).  With scales=None, zeros=None the GEMM reproduces the reference's `A @ unpack(qB).T`.
+    group_size: 128 (the benchmark's), 64, 32, or 0 / K for per-channel scales ([N, 1]).
+    signed: the nibbles are two's-complement int4 (-8..7), W = q * s (no zero-points).
+    Replaces LadderPermutate + LOP3Permutate on the CPU (…_q4.py:568-595); formats beyond plain
+    uint4 have no counterpart in the reference.
     """
-    if group_size != GROUP_SIZE:
-        raise ValueError("group_size must be 128")
     if not qweight.is_cuda:
         raise ValueError("qweight must be a CUDA tensor (this library has no CPU path)")
     if qweight.dtype in (torch.int8, torch.uint8):
@@ -503,8 +521,14 @@ def q4_prepack(qweight: torch.Tensor, scales: torch.Tensor | None = None,
         raise TypeError("qweight must be int32 [N,K/8] or int8/uint8 [N,K/2]")
     if K % GROUP_SIZE:
         raise ValueError("K must be a multiple of 128")
+    if group_size == K and K > 128:
+        group_size = 0
+    if group_size not in (0, 32, 64, 128):
+        raise ValueError("group_size must be 32, 64, 128, or 0 / K (per-channel)")
+    if signed and zeros is not None:
+        raise ValueError("signed int4 is symmetric (W = q * s): zeros must be None")
     qweight = qweight.contiguous()
-    G = K // GROUP_SIZE
+    G = K // group_size if group_size else 1
     sp = zp = None
     if scales is not None:
         if scales.shape != (N, G) or scales.dtype != torch.float16:
@@ -515,20 +539,20 @@ def q4_prepack(qweight: torch.Tensor, scales: torch.Tensor | None = None,
             raise ValueError(f"zeros must be uint8 [{N},{G}]")
         zeros = zeros.contiguous(); zp = zeros.data_ptr()
     lib = L.load()
-    nbytes = int(lib.sk_q4_bytes(N, K))
+    nbytes = int(lib.sk_q4_bytes_ex(N, K, group_size))
     out = torch.empty(nbytes, dtype=torch.uint8, device=qweight.device)
     with torch.cuda.device(qweight.device):
-        L.check(lib.sk_prepack_q4(qweight.data_ptr(), sp, zp, N, K, out.data_ptr(), nbytes,
-                                  _stream_ptr(qweight.device)), "sk_prepack_q4")
-    return PackedQ4(out, N, K)
+        L.check(lib.sk_prepack_q4_ex(qweight.data_ptr(), sp, zp, N, K, group_size, 1 if signed else 0,
+                                     out.data_ptr(), nbytes, _stream_ptr(qweight.device)), "sk_prepack_q4_ex")
+    return PackedQ4(out, N, K, group_size, bool(signed))
 
 
 def dequant_w4(QLB: PackedQ4) -> torch.Tensor:
     """W [N,K] fp16 = (q - z) * s, bit-exact with the fp16 expression evaluated on the CPU."""
     W = torch.empty((QLB.N, QLB.K), dtype=torch.float16, device=QLB.data.device)
     with torch.cuda.device(W.device):
-        L.check(L.load().sk_dequant_q4(QLB.data.data_ptr(), QLB.N, QLB.K, W.data_ptr(),
-                                       W.stride(0), _stream_ptr(W.device)), "sk_dequant_q4")
+        L.check(L.load().sk_dequant_q4_ex(QLB.data.data_ptr(), QLB.N, QLB.K, QLB.group_size, W.data_ptr(),
+                                          W.stride(0), _stream_ptr(W.device)), "sk_dequant_q4_ex")
     return W
 
 
@@ -547,6 +571,7 @@ def streamk_fp16_ladder_block_reduce_q4(A, QLB: PackedQ4, *, fixup="block_reduce
     A = _aligned16(_rowmajor(A))
     Cout = _out(o["out"], M, QLB.N, torch.float16, A.device)
     prob = _problem(M, QLB.N, K, A.stride(0), 0, Cout.stride(0), "nt", schedule, fixup, o)
+    prob.flags |= L.SK_FLAG_Q4_GROUP[QLB.group_size]
     with torch.cuda.device(A.device):
         ws = _workspace(A.device)
         L.check(L.load().sk_gemm_w4a16(C.byref(prob), A.data_ptr(), QLB.data.data_ptr(),
