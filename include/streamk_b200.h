@@ -241,6 +241,26 @@ enum { SK_MAX_PEERS = 7 };
 int sk_gemm_f16_gather(const sk_problem* p, const void* A, const void* B, void* C,
                        void* const* peers, int n_peers, void* ws, size_t ws_bytes, void* stream);
 
+/* sk_gemm_f16 for a K-SHARDED product, fused with the reduce-scatter of the partial sums (the
+ * other collective of a tensor-parallel linear layer; no counterpart in the single-GPU
+ * reference).  GPU g of G holds A[:, K_g] and B[:, K_g] and computes the partial product
+ * P_g = A_g . B_g^T over the full [M, N]; GPU j is to end up with columns [j N/G, (j+1) N/G) of
+ * the sum.  The kernel's epilogue writes every tile of P_g, as fp32, straight into dst[j], the
+ * receive slot that the owner j of the tile's column block keeps for this sender: row-major
+ * [M, N/G] fp32, pitch N/G, 16-byte aligned, local or peer-mapped memory (sk_peer_open).  Plain
+ * TMA stores without multicast, no device-side wait on another GPU: the transfer runs under the
+ * mainloop tile by tile.  Once every GPU's kernel has finished (a host or NCCL barrier placed by
+ * the caller), each owner adds its G slots in ascending sender order with sk_reduce_partials --
+ * a fixed order, so the result is bitwise reproducible.  Runs the CTA-pair kernel with whole
+ * tiles (NT layout, even SM count, N/G a multiple of the tile width: tile_n, default 256, and
+ * of 4; SK_ERR_SHAPE otherwise); prob->ldc and prob->schedule are ignored, n_blocks <= 8.     */
+int sk_gemm_f16_scatter(const sk_problem* p, const void* A, const void* B, void* const* dst, int n_blocks,
+                        void* ws, size_t ws_bytes, void* stream);
+/* C[M, Nb] (fp16, or bf16 with SK_FLAG_BF16 in flags; pitch ldc, a multiple of 4) = the sum, in
+ * ascending order, of n_parts fp32 matrices [M, Nb] stored back to back at `parts`.          */
+int sk_reduce_partials(const void* parts, int n_parts, int M, int Nb, void* C, int ldc, int flags,
+                       void* stream);
+
 /* Device memory other processes of this machine can map (CUDA IPC), for the matrices
  * sk_gemm_f16_gather writes into.  sk_peer_alloc: cudaMalloc + export; `handle` receives
  * SK_PEER_HANDLE_BYTES opaque bytes to send to the other processes (any channel).

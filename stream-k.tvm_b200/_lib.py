@@ -74,6 +74,8 @@ SIGNATURES = {
     "sk_gemm_f16": (C.c_int, [C.POINTER(SkProblem), _P, _P, _P, _P, C.c_size_t, _P]),
     "sk_gemm_f16_gather": (C.c_int, [C.POINTER(SkProblem), _P, _P, _P, C.POINTER(_P), C.c_int, _P,
                                      C.c_size_t, _P]),
+    "sk_gemm_f16_scatter": (C.c_int, [C.POINTER(SkProblem), _P, _P, C.POINTER(_P), C.c_int, _P, C.c_size_t, _P]),
+    "sk_reduce_partials": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P]),
     "sk_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(_P), _P]),
     "sk_peer_open": (C.c_int, [_P, C.POINTER(_P)]),
     "sk_peer_close": (C.c_int, [_P]),

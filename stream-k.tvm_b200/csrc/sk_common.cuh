@@ -112,10 +112,16 @@ struct SkParams {
 // row and column, into the result matrices of up to SK_MAX_PEERS other GPUs (peer-mapped
 // memory; plain stores and non-multicast TMA stores).  c[i] addresses the same element of peer
 // i's matrix as the kernel's C argument does of the local one; tm[i] is the tensor map over it.
+//
+// The same block serves the fused reduce-scatter (sk_gemm_f16_scatter): there n is the number of
+// column blocks of block_cols columns each, c[j] / tm[j] the fp32 receive slot of block j's owner
+// (row-major [M, block_cols], pitch block_cols), and every tile goes to exactly one of them.
+constexpr int SK_MAX_TARGETS = 8;
 struct alignas(64) SkPeers {
-  CUtensorMap tm[SK_MAX_PEERS];
-  __half* c[SK_MAX_PEERS];
+  CUtensorMap tm[SK_MAX_TARGETS];
+  void* c[SK_MAX_TARGETS];
   int n;
+  int block_cols;
 };
 
 // Debugging aid, compiled in only with -DSK_TRACE (the shipped library carries none of it):

@@ -95,7 +95,7 @@ __device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkP
                                                const SkPeers* peers = nullptr) {
   sk_store_chunk1(C, p, grow, gcol0, nv, v);
   if (peers != nullptr)
-    for (int i = 0; i < peers->n; ++i) sk_store_chunk1(peers->c[i], p, grow, gcol0, nv, v);
+    for (int i = 0; i < peers->n; ++i) sk_store_chunk1(static_cast<__half*>(peers->c[i]), p, grow, gcol0, nv, v);
 }
 
 // One float4 of the slot layout (row, columns gcol..gcol+3) -> fp16 C
@@ -140,12 +140,12 @@ __device__ __forceinline__ void sk_copy_items_to_peers(const __half* C, const Sk
       const size_t off = row_off + static_cast<size_t>(q) * 4;
       if (c0 + q * 4 + 4 <= p.cols) {
         const uint2 v = __ldcg(reinterpret_cast<const uint2*>(C + off));
-        for (int i = 0; i < peers->n; ++i) *reinterpret_cast<uint2*>(peers->c[i] + off) = v;
+        for (int i = 0; i < peers->n; ++i) *reinterpret_cast<uint2*>(static_cast<__half*>(peers->c[i]) + off) = v;
       } else {
         for (int e = 0; e < 4; ++e)
           if (c0 + q * 4 + e < p.cols) {
             const __half v = C[off + e];
-            for (int i = 0; i < peers->n; ++i) peers->c[i][off + e] = v;
+            for (int i = 0; i < peers->n; ++i) static_cast<__half*>(peers->c[i])[off + e] = v;
           }
       }
     }
@@ -401,6 +401,39 @@ __device__ __forceinline__ int sk_store_tile_tma(const SkParams& p, const CUtens
 // EPI_WARPS: 4 (warps 2..5) or 8 (warps 2..9).  TMEM lets a warp read only the lane quadrant
 // `warp & 3`, so with eight warps two share each quadrant and split a tile's columns: warp w
 // takes the 64-column groups (and 32-column chunks) of parity (w - 2) / 4.
+// Fused reduce-scatter: a whole tile leaves as fp32, 32 columns at a time: accumulator ->
+// swizzled staging buffer (32 rows x 128 bytes) -> one TMA store of a 32 x 32 fp32 box into the
+// receive slot `tm` of the tile's column block (x0 = the tile's first column inside that block).
+// Ragged edges are clipped by the tensor map, so there is no register path.  One staging buffer
+// per warp; this warp takes the groups g_first, g_first + g_step, ...
+__device__ __forceinline__ void sk_store_tile_tma_f32(const CUtensorMap* tm, uint32_t cstage, int warp_slot,
+                                                      int lane, uint32_t t_addr, int grow0, int x0,
+                                                      int valid_cols, int g_first, int g_step) {
+  using namespace skptx;
+  const int ngroups = (valid_cols + 31) >> 5;
+  const uint32_t buf = cstage + static_cast<uint32_t>(warp_slot) * 4096u;
+  for (int g = g_first; g < ngroups; g += g_step) {
+    if (lane == 0) tma_store_wait_read<0>();   // the previous store from this buffer has read it
+    __syncwarp();
+    uint32_t raw[32];
+    tmem_ld_32x32(t_addr + g * 32, raw);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t a = buf + static_cast<uint32_t>(lane) * 128u + ((static_cast<uint32_t>(j) ^ (static_cast<uint32_t>(lane) & 7u)) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(raw[4 * j]), "r"(raw[4 * j + 1]),
+                   "r"(raw[4 * j + 2]), "r"(raw[4 * j + 3])
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm, buf, x0 + g * 32, grow0);
+      tma_store_commit();
+    }
+  }
+}
+
 template <int MODE = SK_EPI_ANY, int EPI_WARPS = 4>
 __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __restrict__ C, int pid,
                                                  int rank, int warp, int lane, uint32_t tmem_base,

@@ -459,7 +459,17 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   if (st != SK_OK) return st;
   sk_problem resolved;   // SK_SCHED_AUTO -> a concrete schedule and tile, and the kernel to run
   int kind = 1, units = num_sms;
-  sk_f16_dispatch(prob, num_sms, n_peers, &resolved, &kind, &units);
+  sk_problem asked = *prob;
+  if (n_peers < 0) {
+    // fused reduce-scatter: the CTA-pair kernel, whole tiles (nothing of the partial product
+    // stays on this GPU to fix up), C unused
+    if (asked.tile_m != 0 && asked.tile_m != 256) return SK_ERR_ARG;
+    asked.tile_m = 256;
+    asked.schedule = SK_SCHED_DP;
+    asked.ldc = asked.N;
+  }
+  sk_f16_dispatch(&asked, num_sms, n_peers > 0 ? n_peers : 0, &resolved, &kind, &units);
+  if (n_peers < 0 && kind != 3) return SK_ERR_SHAPE;
   prob = &resolved;
   SkParams p;
   memset(&p, 0, sizeof(p));
@@ -604,6 +614,12 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
 extern "C" int sk_gemm_f16(const sk_problem* prob, const void* A, const void* B, void* C, void* ws,
                            size_t ws_bytes, void* stream) {
   return gemm_f16(prob, A, B, C, nullptr, 0, ws, ws_bytes, stream);
+}
+
+extern "C" int sk_gemm_f16_scatter(const sk_problem* prob, const void* A, const void* B, void* const* dst,
+                                   int n_blocks, void* ws, size_t ws_bytes, void* stream) {
+  if (n_blocks < 1 || n_blocks > SK_MAX_TARGETS || !dst || !dst[0]) return SK_ERR_ARG;
+  return gemm_f16(prob, A, B, dst[0], dst, -n_blocks, ws, ws_bytes, stream);
 }
 
 extern "C" int sk_gemm_f16_gather(const sk_problem* prob, const void* A, const void* B, void* C,

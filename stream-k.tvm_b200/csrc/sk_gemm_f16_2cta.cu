@@ -59,13 +59,19 @@ struct Ctrl {
 };
 static_assert(sizeof(Ctrl) <= CTRL_BYTES, "Ctrl must fit its reserved space");
 
-// PEERS: the fused all-gather (sk_gemm_f16_gather): the epilogue also writes every piece of C
-// into the peer GPUs' matrices named by `peer_set`.
-template <bool PEERS>
+// OUT_GATHER: the fused all-gather (sk_gemm_f16_gather): the epilogue also writes every piece of
+// C into the peer GPUs' matrices named by `peer_set`.  OUT_SCATTER: the fused reduce-scatter
+// (sk_gemm_f16_scatter): the product is a partial sum over this GPU's share of K; every tile
+// (whole tiles only: the data-parallel schedule) leaves as fp32 into the receive slot of the
+// GPU that owns its column block, and nothing is written to C.
+constexpr int OUT_PLAIN = 0, OUT_GATHER = 1, OUT_SCATTER = 2;
+
+template <int OUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmC, __half* __restrict__ C, const SkParams p,
                         const __grid_constant__ SkPeers peer_set) {
+  constexpr bool PEERS = OUT == OUT_GATHER;
   const SkPeers* peers = PEERS ? &peer_set : nullptr;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -107,7 +113,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     fence_proxy_async_smem();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
-    if (PEERS)
+    if (OUT != OUT_PLAIN)
       for (int i = 0; i < peer_set.n; ++i) prefetch_tensormap(&peer_set.tm[i]);
   }
   if (warp == 1) {
@@ -320,9 +326,42 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const uint32_t tmem_full0 = smem_u32(&ctrl->tmem_full[0]);
     const uint32_t tmem_empty0 = mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0);
     uint32_t nseg = 0;
+    if constexpr (OUT == OUT_SCATTER) {
+      // ---- fused reduce-scatter: whole tiles, fp32, each to the owner of its column block
+      const int q = warp & 3, sub = (warp - 2) >> 2;
+      const uint32_t stage = smem_u32(ctrl) + 1024u;
+      SkCursor cur;
+      sk_cursor_init(s, unit, cur);
+      SkSeg seg;
+      bool dead = false;
+      while (sk_next(s, unit, cur, seg)) {
+        const uint32_t buf = nseg & 1u;
+        if (!dead) {
+          const bool got = sk_wait_bar(tmem_full0 + 8u * buf, (nseg >> 1) & 1u, abort_flag, p, 24 + buf, 2);
+          if (!__all_sync(0xffffffffu, got)) dead = true;
+        }
+        ++nseg;
+        tc_fence_after();
+        int tr, tc;
+        sk_tile_mn(s, seg.tile, tr, tc);
+        const int r0 = (tr * 2 + rank) * BM + q * 32, c0 = tc * p.bn;
+        int valid_cols = p.cols - c0;
+        if (valid_cols > p.bn) valid_cols = p.bn;
+        const int blk = c0 / peer_set.block_cols;     // (tiles never straddle blocks: checked by the launcher)
+        if (!dead && r0 < p.rows)
+          sk_store_tile_tma_f32(&peer_set.tm[blk], stage, warp - 2, lane,
+                                tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16), r0,
+                                c0 - blk * peer_set.block_cols, valid_cols, sub, EPI_WARPS / 4);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(tmem_empty0 + 8u * buf);
+      }
+      if (lane == 0) tma_store_wait_read<0>();
+    } else {
     sk_epilogue_loop<SK_EPI_ANY, EPI_WARPS>(p, C, unit, rank, warp, lane, tmem_base, tmem_full0, tmem_empty0,
                                             &ctrl->bcast, abort_flag, ctrl->pend, &tmC, cstage, &nseg, peers);
-    if (p.wide_units > 0) {
+    }
+    if (OUT != OUT_SCATTER && p.wide_units > 0) {
       // ---- wide units: the two halves are two whole tiles in the two accumulator buffers
       const int q = warp & 3;
       const int sub = (warp - 2) >> 2;   // the quadrant's two warps take alternate column groups
@@ -371,7 +410,7 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   // ------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  sk_reduce_pending(p, C, unit, rank, ctrl->pend, ctrl->ok, peers);
+  if constexpr (OUT != OUT_SCATTER) sk_reduce_pending(p, C, unit, rank, ctrl->pend, ctrl->ok, peers);
   // Neither CTA may leave while its partner can still signal its barriers or read its
   // shared memory.
   __syncthreads();
@@ -393,10 +432,35 @@ sk_gemm_f16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 int sk_make_tmap_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                      uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows);
 
+// fp32 row-major [rows, cols] tensor map with a 32 x 32 box (128-byte rows), 128-byte swizzle.
+static int make_tmap_f32_store(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld) {
+  typedef CUresult (*Fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                         const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                         CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Fn enc = []() -> Fn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    return q == cudaDriverEntryPointSuccess ? reinterpret_cast<Fn>(f) : nullptr;
+  }();
+  if (!enc) return SK_ERR_LAUNCH;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {ld * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SK_OK : sk_set_driver_error(static_cast<int>(r));
+}
+
 // Launch with CTA pairs.  `units` persistent pairs; p->sched must have been built for
-// 256-row tiles and `units` schedulable units.  n_peers > 0: the fused all-gather.
+// 256-row tiles and `units` schedulable units.  n_peers > 0: the fused all-gather; n_peers < 0:
+// the fused reduce-scatter with -n_peers column blocks, peer_c[j] the fp32 receive slot of block j.
 int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, void* C, SkParams* p,
                        void* const* peer_c, int n_peers, void* stream) {
+  const int n_blocks = n_peers < 0 ? -n_peers : 0;
+  if (n_blocks) n_peers = 0;
   CUtensorMap tmA, tmB;
   int st = sk_make_tmap_f16(&tmA, A, prob->M, prob->K, prob->lda, BK, BM);
   if (st != SK_OK) return st;
@@ -405,10 +469,27 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
   CUtensorMap tmC;
   memset(&tmC, 0, sizeof(tmC));
   p->c_tma = p->c_vec_ok;   // whole tiles leave through shared memory and TMA stores
+  if (n_blocks) p->c_tma = 0;
   if (st == SK_OK && p->c_tma) st = sk_make_tmap_f16(&tmC, C, prob->M, prob->N, prob->ldc, 64, 32);
   if (st != SK_OK) return st;
   SkPeers peer_set;
   memset(&peer_set, 0, sizeof(peer_set));
+  if (n_blocks) {
+    if (n_blocks > SK_MAX_TARGETS || !peer_c) return SK_ERR_ARG;
+    if (prob->N % n_blocks != 0) return SK_ERR_SHAPE;
+    const int bc = prob->N / n_blocks;
+    // whole tiles only, none straddling two blocks; fp32 rows 16-byte aligned
+    if (prob->schedule != SK_SCHED_DP || (bc % bn) != 0 || (bc & 3) != 0) return SK_ERR_SHAPE;
+    peer_set.n = n_blocks;
+    peer_set.block_cols = bc;
+    for (int j = 0; j < n_blocks; ++j) {
+      if (!peer_c[j]) return SK_ERR_ARG;
+      if ((reinterpret_cast<uintptr_t>(peer_c[j]) & 15u) != 0) return SK_ERR_ALIGN;
+      peer_set.c[j] = peer_c[j];
+      st = make_tmap_f32_store(&peer_set.tm[j], peer_c[j], prob->M, bc, bc);
+      if (st != SK_OK) return st;
+    }
+  }
   if (n_peers > 0) {
     if (n_peers > SK_MAX_PEERS || !peer_c) return SK_ERR_ARG;
     if (!p->c_vec_ok) return SK_ERR_ALIGN;
@@ -416,7 +497,7 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
     for (int i = 0; i < n_peers; ++i) {
       if (!peer_c[i]) return SK_ERR_ARG;
       if ((reinterpret_cast<uintptr_t>(peer_c[i]) & 15u) != 0) return SK_ERR_ALIGN;
-      peer_set.c[i] = static_cast<__half*>(peer_c[i]);
+      peer_set.c[i] = peer_c[i];
       st = sk_make_tmap_f16(&peer_set.tm[i], peer_c[i], prob->M, prob->N, prob->ldc, 64, 32);
       if (st != SK_OK) return st;
     }
@@ -436,21 +517,29 @@ int sk_launch_f16_2cta(const sk_problem* prob, const void* A, const void* B, voi
 
   static SkPerDeviceOnce attrs;
   cudaError_t e = attrs.run([]() {
-    cudaError_t r = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<false>,
+    cudaError_t r = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<OUT_PLAIN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (r == cudaSuccess)
-      r = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      r = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<OUT_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SMEM_BYTES);
+    if (r == cudaSuccess)
+      r = cudaFuncSetAttribute(sk_gemm_f16_2cta_kernel<OUT_SCATTER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                SMEM_BYTES);
     return r;
   });
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
-  e = n_peers > 0 ? sk_launch(sk_gemm_f16_2cta_kernel<true>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
-                              static_cast<cudaStream_t>(stream), 2, pdl, tmA, tmB, tmC,
-                              static_cast<__half*>(C), *p, peer_set)
-                  : sk_launch(sk_gemm_f16_2cta_kernel<false>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES,
-                              static_cast<cudaStream_t>(stream), 2, pdl, tmA, tmB, tmC,
-                              static_cast<__half*>(C), *p, peer_set);
+  const cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  __half* Ch = static_cast<__half*>(C);
+  if (n_blocks)
+    e = sk_launch(sk_gemm_f16_2cta_kernel<OUT_SCATTER>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES, cs, 2, pdl,
+                  tmA, tmB, tmC, Ch, *p, peer_set);
+  else if (n_peers > 0)
+    e = sk_launch(sk_gemm_f16_2cta_kernel<OUT_GATHER>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES, cs, 2, pdl,
+                  tmA, tmB, tmC, Ch, *p, peer_set);
+  else
+    e = sk_launch(sk_gemm_f16_2cta_kernel<OUT_PLAIN>, p->sched.grid * 2, NUM_THREADS, SMEM_BYTES, cs, 2, pdl,
+                  tmA, tmB, tmC, Ch, *p, peer_set);
   if (e != cudaSuccess) return sk_set_cuda_error(e);
   return SK_OK;
 }

@@ -22,7 +22,8 @@ import torch.distributed as dist
 from . import _lib as L
 from . import ops as _ops
 
-__all__ = ["column_block", "peer_order", "GatheredResult", "streamk_fp16_nt_gather"]
+__all__ = ["column_block", "peer_order", "GatheredResult", "streamk_fp16_nt_gather", "ScatteredResult",
+           "streamk_fp16_nt_reduce_scatter"]
 
 MAX_PEERS = 7   # SK_MAX_PEERS
 
@@ -51,30 +52,21 @@ class _DeviceBytes:
                                          "version": 3, "strides": None}
 
 
-class GatheredResult:
-    """The full fp16 result [M, N_total] on this GPU, mapped into every process of `group`.
+class _SharedAllocation:
+    """One device allocation per rank, mapped into every process of `group` (CUDA IPC through
+    the C ABI's sk_peer_*).  Collective: every rank constructs and closes it at the same point of
+    the program; a failure on one rank raises on all of them."""
 
-    `full` is the local matrix (a torch tensor over the library's allocation), `block` the
-    view of this rank's own columns.  Collective: every rank of the group constructs it (and
-    closes it) at the same point of the program.  Usable as a context manager; leaving the
-    block closes it, also on an exception -- but close() is itself collective, so ranks that
-    may fail independently must first agree on the outcome (all_agree) and leave together.
-    """
-
-    def __init__(self, M: int, n_total: int, group=None, device=None):
+    def __init__(self, nbytes: int, what: str, group=None, device=None):
         if not dist.is_initialized():
-            raise RuntimeError("GatheredResult needs an initialised torch.distributed process group")
+            raise RuntimeError(f"{what} needs an initialised torch.distributed process group")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
-        if self.world - 1 > MAX_PEERS:
-            raise ValueError(f"at most {MAX_PEERS + 1} ranks")
         self.device = (torch.device("cuda", torch.cuda.current_device()) if device is None
                        else torch.device(device))
-        self.M, self.n_total = int(M), int(n_total)
-        self.col0, self.width = column_block(self.rank, self.world, self.n_total)
+        self.nbytes = int(nbytes)
         lib = L.load()
-        nbytes = self.M * self.n_total * 2
         self._own = C.c_void_p()
         self._peer_base = {}
         handle = C.create_string_buffer(64)
@@ -84,7 +76,7 @@ class GatheredResult:
             # leaving the others waiting in a collective call.
             err = ""
             try:
-                L.check(lib.sk_peer_alloc(nbytes, C.byref(self._own), handle), "sk_peer_alloc")
+                L.check(lib.sk_peer_alloc(self.nbytes, C.byref(self._own), handle), "sk_peer_alloc")
             except Exception as e:
                 err = f"rank {self.rank}: {e}"
             said = [None] * self.world
@@ -105,17 +97,16 @@ class GatheredResult:
                 dist.barrier(group=group)      # mappings first, then the memory they map
                 if self._own.value:
                     lib.sk_peer_free(self._own)
-                raise RuntimeError("GatheredResult: " + "; ".join(sorted({e for e in errs if e})))
-            self.full = torch.as_tensor(_DeviceBytes(self._own.value, nbytes), device=self.device) \
-                .view(torch.float16).view(self.M, self.n_total)
-            if self.full.data_ptr() != self._own.value:
+                raise RuntimeError(f"{what}: " + "; ".join(sorted({e for e in errs if e})))
+            self.bytes = torch.as_tensor(_DeviceBytes(self._own.value, self.nbytes), device=self.device)
+            if self.bytes.data_ptr() != self._own.value:
                 raise RuntimeError("the tensor over the shared allocation is a copy, not a view")
             self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
-        self.block = self.full[:, self.col0:self.col0 + self.width]
-        off = self.col0 * 2
-        self._peer_ptrs = (C.c_void_p * max(1, self.world - 1))(
-            *[self._peer_base[r] + off for r in peer_order(self.rank, self.world)])
         self._open = True
+
+    def base_of(self, r: int) -> int:
+        """Address, in this process, of rank r's allocation."""
+        return self._own.value if r == self.rank else self._peer_base[r]
 
     def __enter__(self):
         return self
@@ -136,6 +127,9 @@ class GatheredResult:
         """Stream-ordered rendezvous of the group (an all-reduce of one element)."""
         dist.all_reduce(self._token, group=self.group)
 
+    def _drop_views(self) -> None:
+        self.bytes = None
+
     def close(self) -> None:
         if not self._open:
             return
@@ -146,9 +140,63 @@ class GatheredResult:
             dist.barrier(group=self.group)          # nobody still writes into a peer
             for p in self._peer_base.values():
                 lib.sk_peer_close(p)
-            self.full = self.block = None
+            self._drop_views()
             dist.barrier(group=self.group)          # every mapping is gone before the memory is
             lib.sk_peer_free(self._own)
+
+
+class GatheredResult(_SharedAllocation):
+    """The full fp16 result [M, N_total] on this GPU, mapped into every process of `group`.
+
+    `full` is the local matrix (a torch tensor over the library's allocation), `block` the
+    view of this rank's own columns.  Collective: every rank of the group constructs it (and
+    closes it) at the same point of the program.  Usable as a context manager; leaving the
+    block closes it, also on an exception -- but close() is itself collective, so ranks that
+    may fail independently must first agree on the outcome (all_agree) and leave together.
+    """
+
+    def __init__(self, M: int, n_total: int, group=None, device=None):
+        if dist.is_initialized() and dist.get_world_size(group) - 1 > MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS + 1} ranks")
+        self.M, self.n_total = int(M), int(n_total)
+        if dist.is_initialized():
+            self.col0, self.width = column_block(dist.get_rank(group), dist.get_world_size(group), self.n_total)
+        super().__init__(self.M * self.n_total * 2, "GatheredResult", group, device)
+        self.full = self.bytes.view(torch.float16).view(self.M, self.n_total)
+        self.block = self.full[:, self.col0:self.col0 + self.width]
+        off = self.col0 * 2
+        self._peer_ptrs = (C.c_void_p * max(1, self.world - 1))(
+            *[self._peer_base[r] + off for r in peer_order(self.rank, self.world)])
+
+    def _drop_views(self) -> None:
+        self.full = self.block = self.bytes = None
+
+
+class ScatteredResult(_SharedAllocation):
+    """Receive side of the fused reduce-scatter: this rank's fp32 slots [world, M, N_total / world]
+    (slot g = the partial sum sender g computed for this rank's column block), mapped into every
+    process of `group`, and the 16-bit result block [M, N_total / world] the slots are reduced
+    into.  Collective like GatheredResult."""
+
+    def __init__(self, M: int, n_total: int, group=None, device=None, dtype=torch.float16):
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise TypeError("dtype must be float16 or bfloat16")
+        self.M, self.n_total, self.dtype = int(M), int(n_total), dtype
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if world > 8:
+            raise ValueError("at most 8 ranks")
+        if self.n_total % world or (self.n_total // world) % 32:
+            raise ValueError(f"N = {n_total} does not split into {world} column blocks of a multiple of 32")
+        self.width = self.n_total // world
+        super().__init__(world * self.M * self.width * 4, "ScatteredResult", group, device)
+        self.parts = self.bytes.view(torch.float32).view(self.world, self.M, self.width)
+        self.block = torch.empty(self.M, self.width, dtype=dtype, device=self.device)
+        slot = self.M * self.width * 4
+        # where THIS rank's partial of column block j goes: slot `rank` of rank j's buffer
+        self._dst = (C.c_void_p * self.world)(*[self.base_of(j) + self.rank * slot for j in range(self.world)])
+
+    def _drop_views(self) -> None:
+        self.parts = self.bytes = None
 
 
 def streamk_fp16_nt_gather(A: torch.Tensor, B_block: torch.Tensor, result: GatheredResult, *,
@@ -192,3 +240,44 @@ def streamk_fp16_nt_gather(A: torch.Tensor, B_block: torch.Tensor, result: Gathe
                 "sk_gemm_f16_gather")
         result.meet()   # every rank's kernel, hence every store into this GPU, has finished
     return result.full
+
+
+def streamk_fp16_nt_reduce_scatter(A_shard: torch.Tensor, B_shard: torch.Tensor, result: ScatteredResult, *,
+                                   tile_n: int | None = None, **kw) -> torch.Tensor:
+    """result.block = columns [rank N/G, (rank+1) N/G) of A @ B.T for A = the ranks' A_shard side by
+    side along K and B likewise: A_shard [M, K/G], B_shard [N, K/G] (fp16, or bf16 to match
+    `result`).  Each rank multiplies its K shard over the full [M, N] with the CTA-pair kernel,
+    whose epilogue writes every fp32 partial tile straight into the owning rank's receive slot
+    (peer stores under the mainloop); after a stream-ordered rendezvous each rank adds its slots in
+    rank order (bitwise reproducible) and rounds once.  Returns result.block, valid once the
+    stream reaches the point after this call.  tile_n: tile width (a divisor of N/G, multiple of
+    32; default 256, narrower for small blocks)."""
+    o = _ops._options(kw)
+    _ops._check_matrix("A_shard", A_shard, result.dtype)
+    _ops._check_matrix("B_shard", B_shard, result.dtype)
+    M, K = A_shard.shape
+    if (M, B_shard.shape[0]) != (result.M, result.n_total) or B_shard.shape[1] != K:
+        raise ValueError(f"Incompatible dimensions: A_shard {tuple(A_shard.shape)} B_shard {tuple(B_shard.shape)} "
+                         f"result {result.M} x {result.n_total}")
+    if o["out"] is not None:
+        raise TypeError("the result lives in `result`; `out` is not accepted")
+    if tile_n is None:
+        tile_n = next(t for t in (256, 128, 64, 32) if result.width % t == 0)
+    o["tile_n"] = tile_n
+    o["_bf16"] = result.dtype == torch.bfloat16
+    A = _ops._aligned16(_ops._rowmajor(_ops._pad_k8(A_shard, 1)))
+    Bt = _ops._aligned16(_ops._rowmajor(_ops._pad_k8(B_shard, 1)))
+    prob = _ops._problem(M, result.n_total, A.shape[1], A.stride(0), Bt.stride(0), result.n_total, "nt", "dp",
+                         "block_reduce", o)
+    lib = L.load()
+    with torch.cuda.device(A.device):
+        ws = _ops._workspace(A.device)
+        stream = _ops._stream_ptr(A.device)
+        result.meet()   # every rank has reduced (read) the previous contents of its slots
+        L.check(lib.sk_gemm_f16_scatter(C.byref(prob), A.data_ptr(), Bt.data_ptr(), result._dst, result.world,
+                                        ws.buf.data_ptr(), ws.nbytes, stream), "sk_gemm_f16_scatter")
+        result.meet()   # every rank's kernel, hence every store into this GPU's slots, has finished
+        L.check(lib.sk_reduce_partials(result.parts.data_ptr(), result.world, M, result.width,
+                                       result.block.data_ptr(), result.block.stride(0),
+                                       L.SK_FLAG_BF16 if o["_bf16"] else 0, stream), "sk_reduce_partials")
+    return result.block
