@@ -52,7 +52,7 @@ CPU_SAMPLE_ROWS = 256
 NOMINAL_TFLOPS = 2250.0
 NOMINAL_HBM_GBS = 8000.0
 TOL16, TOL32 = 1e-2, 1e-4
-PREHEAT = 30                   # untimed launches ahead of the warm-up steps (clock ramp of an idle GPU)
+PREHEAT = 10                   # untimed launches ahead of the warm-up steps (clock ramp of an idle GPU)
 METRIC = "Stream-K fp16 GEMM TFLOP/s"
 
 
@@ -576,12 +576,25 @@ def run_tune(path: str, peaks: dict) -> None:
         return c
 
     def candidates_q4(M, N, K):
-        c = [dict(schedule="streamk"), dict(schedule="hybrid"), dict(schedule="dp")]
-        try:
-            if sk.schedule_info(M, N, K, kind="w4a16", schedule="cluster", no_table=True)["cluster"] > 0:
-                c.append(dict(schedule="cluster"))
-        except sk.StreamKError:
-            pass
+        c = [dict(schedule="streamk"), dict(schedule="hybrid"), dict(schedule="dp"),
+             dict(schedule="streamk", fixup="atomic")]
+        # narrower tiles along M: more tiles (more CTAs streaming, cluster split-K within reach) for
+        # the price of dequantising every weight once per tile column
+        widths = sorted({w for w in (16, 32, 48, 64, 96, 112) if w < ((M + 15) // 16 * 16) and M > 16})
+        for tm in [None] + widths:
+            for sched in ("streamk", "dp", "cluster"):
+                kw = dict(schedule=sched) if tm is None else dict(schedule=sched, tile_m=tm)
+                if kw in c:
+                    continue
+                try:
+                    info = sk.schedule_info(M, N, K, kind="w4a16", no_table=True, **kw)
+                except sk.StreamKError:
+                    continue
+                if sched == "cluster" and info["cluster"] == 0:
+                    continue
+                if sched == "dp" and info["total_tiles"] > 2 * sms:
+                    continue
+                c.append(kw)
         return c
 
     def tune(case, kind, cands):
@@ -595,6 +608,10 @@ def run_tune(path: str, peaks: dict) -> None:
                 fn(0)
                 sk.check_status()
             except sk.StreamKError:
+                try:
+                    sk.reset_workspace()
+                except sk.StreamKError:
+                    pass
                 continue
             if oracle.rel_err(case.out, case.ref) > TOL16:      # the check the reference's tuner skips
                 rejected += 1
@@ -606,7 +623,7 @@ def run_tune(path: str, peaks: dict) -> None:
                "best_us": round(best_us, 2), "best": best, "rejected": rejected}
         report.append(row)
         print(json.dumps(row), file=sys.stderr, flush=True)
-        if best is not None and best_us < 0.97 * base:
+        if best is not None and best_us < 0.97 * base and best.get("fixup") is None:
             entries.append((1 if kind == "f16" else 2, case.M, case.N, case.K, sms, sk.SCHEDULES[best["schedule"]],
                             int(best.get("tile_m") or 0), int(best.get("tile_n") or 0)))
 

@@ -44,7 +44,7 @@ def _sources() -> list[str]:
 
 
 def _headers() -> list[str]:
-    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     hs.append(os.path.join(HERE, "..", "include", "streamk_b200.h"))
     return hs
 

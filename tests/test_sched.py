@@ -286,3 +286,35 @@ def test_inspection_call_reports_what_the_fp16_entry_point_runs(lib):
     z = L.SkProblem()
     z.M, z.N, z.K = 384, 384, 8192
     assert lib.sk_schedule(C.byref(z), 1, 148, C.byref(info)) == 0 and info.total_tiles > 0
+
+
+def test_tuned_table_is_consulted_first(lib):
+    """SK_SCHED_AUTO looks a shape up in the table the offline tuner wrote (csrc/sk_tuned_table.inc)
+    before applying its rules; SK_FLAG_NO_TABLE gives the rules alone.  Rows are read from the
+    file, so the test follows whatever the last tuner run installed."""
+    import os
+    import re
+    from streamk_b200 import _lib as L
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "stream-k.tvm_b200",
+                        "csrc", "sk_tuned_table.inc")
+    rows = [tuple(int(x) for x in m.groups()) for m in
+            re.finditer(r"^\{(\d+), (\d+), (\d+), (\d+), (\d+), (\d+), (\d+), (\d+)\},", open(path).read(), re.M)]
+    info = L.SkScheduleInfo()
+    for kind, M, N, K, sms, schedule, tile_m, tile_n in rows:
+        prob = L.SkProblem(M=M, N=N, K=K, lda=K, ldb=K, ldc=N, layout=1, schedule=L.SCHEDULES["auto"])
+        assert lib.sk_schedule(C.byref(prob), kind, sms, C.byref(info)) == 0
+        assert info.schedule == schedule
+        if tile_m:
+            assert info.tile_m == tile_m
+        if tile_n:
+            assert info.tile_n == tile_n
+        # another SM count, or the flag: the rules answer (they may agree, but must not fail)
+        prob.flags = L.SK_FLAG_NO_TABLE
+        assert lib.sk_schedule(C.byref(prob), kind, sms, C.byref(info)) == 0
+    # a shape that is not in the table is untouched by it
+    prob = L.SkProblem(M=123, N=4567, K=896, lda=896, ldb=896, ldc=4567, layout=1, schedule=L.SCHEDULES["auto"])
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    a = info.as_dict()
+    prob.flags = L.SK_FLAG_NO_TABLE
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
+    assert info.as_dict() == a
