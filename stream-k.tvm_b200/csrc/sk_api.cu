@@ -180,7 +180,8 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
   q->schedule = SK_SCHED_HYBRID;
   if (kernel_kind == 0 || kernel_kind == 3) return;
   const bool tiles_open = q->tile_m == 0 && q->tile_n == 0;
-  if (tiles_open && (q->flags & SK_FLAG_NO_TABLE) == 0) {
+  // (the tuner times the NT entry point; NN and ladder weights come in 128-row units and keep the rules)
+  if (tiles_open && (q->flags & SK_FLAG_NO_TABLE) == 0 && (kernel_kind != 1 || q->layout == SK_LAYOUT_NT)) {
     for (const SkTuned* t = kTuned; t->kind >= 0; ++t) {
       if (t->kind != kernel_kind || t->M != q->M || t->N != q->N || t->K != q->K || t->sms != num_sms) continue;
       sk_problem c = *q;

@@ -107,3 +107,14 @@ def test_zero_initialised_problem_means_no_test_hook():
     assert st == 0
     sk.check_status()                          # no SK_ERR_FIXUP_TIMEOUT
     assert oracle.rel_err(out, oracle.gemm_ref(A.cpu(), B.cpu(), "nt")) <= TOL16
+
+
+def test_tabled_shapes_in_the_other_layouts():
+    """The tuned table holds choices for the NT entry point; the NN and ladder entry points (whose
+    weights come in 128-row units) must not inherit tile widths they cannot run."""
+    c = oracle.make_case(3, 20)                      # 256 x 4096 x 4096: in the table with 64-wide tiles
+    ref = oracle.gemm_ref(c["A"], c["B"], "nt")
+    A, B = c["A"].to(DEV), c["B"].to(DEV)
+    _check(sk.streamk_fp16_nn(A, B.t().contiguous()), ref, "nn")
+    _check(sk.streamk_fp16_ladder(A, sk.ladder_prepack(B)), ref, "ladder")
+    _check(sk.streamk_fp16_nt(A, B, no_table=True), ref, "nt, rules only")
