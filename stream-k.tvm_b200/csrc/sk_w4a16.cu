@@ -148,8 +148,14 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
   // staging area in the load ring, which is idle by then.
   const uint32_t recv_base = smem_u32(ctrl) + CTRL_BYTES;
 
+  // Start-up.  Kernel entry -> first load is pure latency on every problem this kernel sees,
+  // so the work is spread: an epilogue warp (idle until the first tile is done) sets the
+  // barriers up, one per lane, while the producer warp works out its first segment and asks L2
+  // for that segment's first packed blocks; the producer then waits for nothing but the
+  // barriers (named barrier BAR_PRODUCER), and the tensor-memory allocation runs beside the
+  // first loads, awaited by everybody else (BAR_CONSUMERS).
+  constexpr int BAR_PRODUCER = 2, BAR_CONSUMERS = 3;
   if (warp == 2) {
-    // an epilogue warp (idle until the first tile is done) sets the barriers up, one per lane
     if (lane < LS) {
       mbar_init(smem_u32(&ctrl->load_full[lane]), 1);
       // the stage's dequant warps + the MMA commit (+ the other issuer's "seen it", see below)
@@ -172,35 +178,46 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
     fence_mbar_init();
     fence_proxy_async_smem();
     __syncwarp();
+    named_bar_arrive(BAR_PRODUCER, 64);       // the producer warp waits on it
     if (clustered && lane == LS + DQ_GROUPS + 2)
       mbar_arrive_expect_tx(smem_u32(&ctrl->recv_full),
                             static_cast<uint32_t>((s.split - 1) * p.cl_per) * SK_CL_QUAD_BYTES);
   }
-  if (threadIdx.x == 0) prefetch_tensormap(&tmA);
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
-    tmem_relinquish();
-  }
-  if (threadIdx.x == 96) {
-    // While the barriers are being set up (and, with SK_FLAG_PDL, while the previous kernel of
-    // the stream is still running) an idle thread asks L2 for the packed weights of the first
-    // stages (a hint; L2 is the coherence point, so nothing can go stale).
-    SkCursor c0;
-    sk_cursor_init(s, pid, c0);
-    SkSeg g0;
-    if (sk_next(s, pid, c0, g0)) {
-      int tr, tc;
-      sk_tile_mn(s, g0.tile, tr, tc);
-      int n = g0.k1 - g0.k0;
-      if (n > 12) n = 12;
-      bulk_prefetch_l2(qblocks + (static_cast<size_t>(tr) * kblocks + g0.k0) * Q_BLOCK_BYTES,
-                       static_cast<uint32_t>(n) * Q_BLOCK_BYTES);
+  // The producer's first segment, and the L2 hint for its first packed blocks (L2 is the
+  // coherence point, so nothing can go stale; with SK_FLAG_PDL this runs while the previous
+  // kernel of the stream is still going).
+  const bool solo = clustered ? lane == 0 : true;   // which lanes of the producer warp run its loop
+  SkCursor pcur;
+  SkSeg pseg;
+  bool phave = false;
+  int ptr = 0, ptc = 0;
+  if (warp == 0 && solo) {
+    sk_cursor_init(s, pid, pcur);
+    phave = sk_next(s, pid, pcur, pseg);
+    if (phave) {
+      sk_tile_mn(s, pseg.tile, ptr, ptc);
+      if (lane == 0) {
+        prefetch_tensormap(&tmA);
+        int n = pseg.k1 - pseg.k0;
+        if (n > 12) n = 12;
+        bulk_prefetch_l2(qblocks + (static_cast<size_t>(ptr) * kblocks + pseg.k0) * Q_BLOCK_BYTES,
+                         static_cast<uint32_t>(n) * Q_BLOCK_BYTES);
+      }
     }
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+  uint32_t tmem_base = 0;
+  if (warp == 0) {
+    named_bar_sync(BAR_PRODUCER, 64);
+  } else {
+    if (warp == 1) {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    named_bar_sync(BAR_CONSUMERS, NUM_THREADS - 32);
+    tc_fence_after();
+    tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+  }
   const uint32_t tmem_acc = tmem_base + W_RING_COLS;   // accumulators behind the weight ring
   if (threadIdx.x == 0) sk_trace(p, 1);
   // global memory is the previous kernel's until it has completed (no-op without SK_FLAG_PDL)
@@ -208,23 +225,24 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer
-    if (lane == 0) {
+    // (whole warp, one elected lane issues: see the warp index above; single lane in the cluster kernel)
+    if (solo) {
+      const bool leader = clustered ? true : elect_one();
       bool traced = false;
       bool arrived = false;   // this thread's share of the cluster's start-up barrier
-      SkCursor cur;
-      sk_cursor_init(s, pid, cur);
-      SkSeg seg;
+      bool first_seg = true;
       int ls = 0;
       uint32_t lph = 0;
       bool ok = true;
-      while (ok && sk_next(s, pid, cur, seg)) {
-        int tr, tc;
-        sk_tile_mn(s, seg.tile, tr, tc);
-        const int a_row0 = tc * p.bn;    // first activation row of the tile; tr = 128-row block of the weight
-        for (int k = seg.k0; k < seg.k1;) {
+      for (; ok && phave; phave = sk_next(s, pid, pcur, pseg)) {
+        if (!first_seg) sk_tile_mn(s, pseg.tile, ptr, ptc);   // (the first segment's are known already)
+        first_seg = false;
+        const int tr = ptr;
+        const int a_row0 = ptc * p.bn;    // first activation row of the tile; tr = 128-row block of the weight
+        for (int k = pseg.k0; k < pseg.k1;) {
           // A stage carries the K steps of one scale group (two, unless the segment starts
           // or ends inside the group): one barrier round trip, one packed copy, one group block.
-          const int n = ((k & 1) || k + 1 >= seg.k1) ? 1 : 2;
+          const int n = ((k & 1) || k + 1 >= pseg.k1) ? 1 : 2;
           const uint32_t full = smem_u32(&ctrl->load_full[ls]);
           if (!sk_wait_bar(smem_u32(&ctrl->load_empty[ls]), lph ^ 1u, abort_flag, p, ls, 0)) {
             ok = false;
@@ -233,23 +251,25 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
           // the group blocks the stage's K range touches: one (group size 128 or per-channel) up to four
           const int g0 = (2 * k) >> gshift, g1 = (2 * (k + n) - 1) >> gshift;
           const int sz_bytes = (g1 - g0 + 1) * SZ_BLOCK_BYTES;
-          mbar_arrive_expect_tx(full, n * (a_tile_bytes + Q_BLOCK_BYTES) + sz_bytes);
-          bulk_load_1d(sQ + ls * KG * Q_BLOCK_BYTES,
-                       qblocks + (static_cast<size_t>(tr) * kblocks + k) * Q_BLOCK_BYTES,
-                       n * Q_BLOCK_BYTES, full);
-          bulk_load_1d(sSZ + ls * SZ_SLOT_BYTES,
-                       szblocks + (static_cast<size_t>(tr) * groups + g0) * SZ_BLOCK_BYTES, sz_bytes, full);
-          for (int j = 0; j < n; ++j)
-            tma_load_2d(sA + ls * a_stage_bytes + j * a_tile_bytes, &tmA, full, (k + j) * BK, a_row0);
+          if (leader) {
+            mbar_arrive_expect_tx(full, n * (a_tile_bytes + Q_BLOCK_BYTES) + sz_bytes);
+            bulk_load_1d(sQ + ls * KG * Q_BLOCK_BYTES,
+                         qblocks + (static_cast<size_t>(tr) * kblocks + k) * Q_BLOCK_BYTES,
+                         n * Q_BLOCK_BYTES, full);
+            bulk_load_1d(sSZ + ls * SZ_SLOT_BYTES,
+                         szblocks + (static_cast<size_t>(tr) * groups + g0) * SZ_BLOCK_BYTES, sz_bytes, full);
+            for (int j = 0; j < n; ++j)
+              tma_load_2d(sA + ls * a_stage_bytes + j * a_tile_bytes, &tmA, full, (k + j) * BK, a_row0);
+          }
           k += n;
           if (++ls == LS) {
             ls = 0; lph ^= 1u;
             // ring full for the first time: a good moment for this thread's share of the
-            // cluster's start-up barrier.  Its arrival releases: it has met (at the CTA barrier
-            // above) the thread that initialised the mbarrier the other CTAs will signal.
+            // cluster's start-up barrier.  Its arrival releases: it has met (at the named
+            // barrier above) the warp that initialised the mbarrier the other CTAs will signal.
             if (clustered && !arrived) { cluster_arrive(); arrived = true; }
           }
-          if (!traced) { sk_trace(p, 2); traced = true; }
+          if (leader && !traced) { sk_trace(p, 2); traced = true; }
         }
       }
       if (clustered && !arrived) cluster_arrive();
