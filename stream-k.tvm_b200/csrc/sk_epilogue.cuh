@@ -60,20 +60,21 @@ __device__ __forceinline__ __half sk_cvt1(float a, int bf16) {
   return __ushort_as_half(static_cast<unsigned short>(r & 0xFFFFu));
 }
 
-// nv (<= 32) fp32 values of tile row `grow`, columns gcol0.. -> 16-bit C
-__device__ __forceinline__ void sk_store_chunk1(__half* __restrict__ C, const SkParams& p, int grow,
-                                                int gcol0, int nv, const float (&v)[32]) {
+// nv (<= NC) fp32 values of tile row `grow`, columns gcol0.. -> 16-bit C  (NC = 16 or 32)
+template <int NC>
+__device__ __forceinline__ void sk_store_cols(__half* __restrict__ C, const SkParams& p, int grow,
+                                              int gcol0, int nv, const float (&v)[NC]) {
   if (p.transposed) {
     __half* dst = C + static_cast<size_t>(gcol0) * p.ldc + grow;
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
+    for (int j = 0; j < NC; ++j)
       if (j < nv) dst[static_cast<size_t>(j) * p.ldc] = sk_cvt1(v[j], p.out_bf16);
     return;
   }
   __half* dst = C + static_cast<size_t>(grow) * p.ldc + gcol0;
-  if (p.c_vec_ok && nv == 32) {
+  if (p.c_vec_ok && nv == NC) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < NC / 8; ++j) {
       uint4 u;
       u.x = sk_pack2(v[8 * j + 0], v[8 * j + 1], p.out_bf16);
       u.y = sk_pack2(v[8 * j + 2], v[8 * j + 3], p.out_bf16);
@@ -83,22 +84,16 @@ __device__ __forceinline__ void sk_store_chunk1(__half* __restrict__ C, const Sk
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
+    for (int j = 0; j < NC; ++j)
       if (j < nv) dst[j] = sk_cvt1(v[j], p.out_bf16);
   }
 }
-
-// ... and, in the fused all-gather, to the same place of every peer GPU's matrix.  `peers` is a
-// compile-time null in every kernel but the gathering one, where the loop disappears.
-__device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkParams& p, int grow,
-                                               int gcol0, int nv, const float (&v)[32],
-                                               const SkPeers* peers = nullptr) {
-  sk_store_chunk1(C, p, grow, gcol0, nv, v);
-  if (peers != nullptr)
-    for (int i = 0; i < peers->n; ++i) sk_store_chunk1(static_cast<__half*>(peers->c[i]), p, grow, gcol0, nv, v);
+__device__ __forceinline__ void sk_store_chunk1(__half* __restrict__ C, const SkParams& p, int grow,
+                                                int gcol0, int nv, const float (&v)[32]) {
+  sk_store_cols<32>(C, p, grow, gcol0, nv, v);
 }
 
-// One float4 of the slot layout (row, columns gcol..gcol+3) -> fp16 C
+// Four columns (gcol..gcol+3) of tile row `grow` -> 16-bit C
 __device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams& p, int grow, int gcol,
                                           const float4& x) {
   const float v[4] = {x.x, x.y, x.z, x.w};
@@ -121,20 +116,32 @@ __device__ __forceinline__ void sk_store4(__half* __restrict__ C, const SkParams
   }
 }
 
+// ... and, in the fused all-gather, to the same place of every peer GPU's matrix.  `peers` is a
+// compile-time null in every kernel but the gathering one, where the loop disappears.
+__device__ __forceinline__ void sk_store_chunk(__half* __restrict__ C, const SkParams& p, int grow,
+                                               int gcol0, int nv, const float (&v)[32],
+                                               const SkPeers* peers = nullptr) {
+  sk_store_chunk1(C, p, grow, gcol0, nv, v);
+  if (peers != nullptr)
+    for (int i = 0; i < peers->n; ++i) sk_store_chunk1(static_cast<__half*>(peers->c[i]), p, grow, gcol0, nv, v);
+}
+
 // Fused all-gather, split tiles: the reducers store with a row stride (consecutive threads take
-// consecutive rows of one 4-column group: whole lines of the fp32 partials in, 8 bytes per row
-// out), which the local L2 absorbs but NVLink does not.  So they store locally only, and this
-// copies what they stored from the local matrix to every peer in contiguous runs: one row per
-// warp and pass, 8 bytes per lane.  Items are the reducers' (item = 128 * column group + row) of
-// this CTA's 128 rows starting at r0; [begin, end) is the range the calling threads reduced.
+// consecutive rows: whole lines of the fp32 partials in, one 32- or 64-byte run per row out),
+// which the local L2 absorbs but NVLink does not.  So they store locally only, and this copies
+// what they stored from the local matrix to every peer in contiguous runs: one row per warp and
+// pass, 8 bytes per lane.  Items are the reducers' (item = 128 * chunk + row, a chunk = QC quads
+// of four columns) of this CTA's 128 rows starting at r0; [begin, end) is the range the calling
+// threads reduced.
 __device__ __forceinline__ void sk_copy_items_to_peers(const __half* C, const SkParams& p,
                                                        const SkPeers* peers, int r0, int c0,
-                                                       int rows_valid, int begin, int end, int warp,
-                                                       int nwarps, int lane) {
+                                                       int rows_valid, int quads_valid, int qc, int begin, int end,
+                                                       int warp, int nwarps, int lane) {
   for (int r = warp; r < rows_valid; r += nwarps) {
     if (end - 1 - r < 0) continue;
-    const int qlo = begin - r > 0 ? (begin - r + SK_BM - 1) >> 7 : 0;
-    const int qhi = (end - 1 - r) >> 7;
+    const int qlo = (begin - r > 0 ? (begin - r + SK_BM - 1) >> 7 : 0) * qc;
+    int qhi = ((end - 1 - r) >> 7) * qc + qc - 1;
+    if (qhi > quads_valid - 1) qhi = quads_valid - 1;
     const size_t row_off = static_cast<size_t>(r0 + r) * p.ldc + c0;
     for (int q = qlo + lane; q <= qhi; q += 32) {
       const size_t off = row_off + static_cast<size_t>(q) * 4;
@@ -157,65 +164,64 @@ struct SkPending {
   int first, last;
 };
 
-// Sum one slice of a split tile over all of its partials, in ascending CTA order, and
-// store it.  The loop is bound by L2 latency, not by arithmetic, so a thread keeps U items
-// x V contributors = 16 loads in flight: a deep split (many contributors, few items per
-// thread) fetches all contributors of an item at once, a shallow one many items at once.
-template <int U, int V>
-__device__ __forceinline__ void sk_reduce_items_uv(const SkParams& p, __half* __restrict__ C,
-                                                   int first, int last, int rank, int r0,
-                                                   int c0, int rows_valid, int begin, int end,
+// Sum one slice of a split tile over all of its partials, in ascending CTA order, and store
+// it.  An item is one row of one chunk of QC quads (QC * 4 columns): the thread that takes it
+// reads QC float4 per contributor (the slots are laid out [quad][row], so a warp's 32 rows
+// read 512 contiguous bytes per instruction, at offsets that are immediates of one base
+// address) and writes QC * 8 contiguous bytes of C, i.e. whole 32-byte sectors.  V contributors
+// are fetched at once: QC * V loads in flight per thread; the loop is bound by L2 latency, not
+// by arithmetic.  The code is kept small on purpose: it runs once per launch, from cold
+// instruction caches.
+template <int QC, int V>
+__device__ __forceinline__ void sk_reduce_items_qv(const SkParams& p, __half* __restrict__ C,
+                                                   int first, int last, int rank, int r0, int c0,
+                                                   int rows_valid, int valid_cols, int begin, int end,
                                                    int tid, int nthreads) {
-  for (int base = begin + tid; base < end; base += U * nthreads) {
-    float4 acc[U];
-    bool on[U];
+  for (int it = begin + tid; it < end; it += nthreads) {
+    const int row = it & (SK_BM - 1), chunk = it >> 7;
+    if (row >= rows_valid) continue;
+    int nv = valid_cols - chunk * (QC * 4);
+    if (nv > QC * 4) nv = QC * 4;
+    float acc[QC * 4];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int idx = base + u * nthreads;
-      on[u] = idx < end && (idx & (SK_BM - 1)) < rows_valid;
-      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+    for (int e = 0; e < QC * 4; ++e) acc[e] = 0.f;
+    const size_t item0 = static_cast<size_t>(chunk * QC) * SK_BM + row;   // float4 index of the first quad
     for (int cta = first; cta <= last; cta += V) {
-      float4 x[V][U];
+      float4 x[V][QC];
 #pragma unroll
       for (int v = 0; v < V; ++v) {
-        const int c = cta + v;
-        if (c <= last) {
-          // partial of contributor c: the first one's tail slot, everybody else's head slot
-          const float4* src = reinterpret_cast<const float4*>(
-              p.ws.part_slots +
-              static_cast<size_t>(2 * (c * p.unit_ctas + rank) + (c == first ? 1 : 0)) * SK_SLOT_FLOATS);
+        const int c = cta + v <= last ? cta + v : last;   // (a repeated fetch, not added)
+        // partial of contributor c: the first one's tail slot, everybody else's head slot
+        const float4* src = reinterpret_cast<const float4*>(
+                                p.ws.part_slots +
+                                static_cast<size_t>(2 * (c * p.unit_ctas + rank) + (c == first ? 1 : 0)) * SK_SLOT_FLOATS) +
+                            item0;
+        // (quads past the tile's last column hold stale values inside the slot; never stored)
 #pragma unroll
-          for (int u = 0; u < U; ++u)
-            if (on[u]) x[v][u] = __ldcg(src + base + u * nthreads);
-        }
+        for (int q = 0; q < QC; ++q) x[v][q] = __ldcg(src + q * SK_BM);
       }
 #pragma unroll
       for (int v = 0; v < V; ++v) {
         if (cta + v <= last) {
 #pragma unroll
-          for (int u = 0; u < U; ++u)
-            if (on[u]) {
-              acc[u].x += x[v][u].x; acc[u].y += x[v][u].y;
-              acc[u].z += x[v][u].z; acc[u].w += x[v][u].w;
-            }
+          for (int q = 0; q < QC; ++q) {
+            acc[4 * q + 0] += x[v][q].x; acc[4 * q + 1] += x[v][q].y;
+            acc[4 * q + 2] += x[v][q].z; acc[4 * q + 3] += x[v][q].w;
+          }
         }
       }
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int idx = base + u * nthreads;
-      if (on[u]) sk_store4(C, p, r0 + (idx & (SK_BM - 1)), c0 + (idx >> 7) * 4, acc[u]);
-    }
+    sk_store_cols<QC * 4>(C, p, r0 + row, c0 + chunk * (QC * 4), nv, acc);
   }
 }
 
-// LIGHT: half as many loads in flight per thread, for kernels with many threads and few
+// LIGHT: 16-column items and one contributor at a time, for kernels with many threads and few
 // registers each (the W4A16 kernel: 736 threads, 80 registers).
 template <bool LIGHT = false>
 __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __restrict__ C,
                                                 const SkPending& pd, int pid, int rank, int tid,
                                                 int nthreads, const SkPeers* peers) {
+  constexpr int QC = LIGHT ? 4 : 8;
   const SkSched& s = p.sched;
   const int first = pd.first, last = pd.last;
   const int n = last - first + 1;
@@ -226,24 +232,17 @@ __device__ __forceinline__ void sk_reduce_items(const SkParams& p, __half* __res
   if (valid_cols > p.bn) valid_cols = p.bn;
   int rows_valid = p.rows - r0;
   if (rows_valid > p.bm) rows_valid = p.bm;
-  const int L = ((valid_cols + 3) >> 2) * SK_BM;  // float4 items of this CTA's part of the tile
+  const int L = ((valid_cols + QC * 4 - 1) / (QC * 4)) * SK_BM;  // items of this CTA's part of the tile
   const int j = pid - first;
-  const int begin = static_cast<int>(static_cast<long long>(j) * L / n);
-  const int end = static_cast<int>(static_cast<long long>(j + 1) * L / n);
-  // The summation order (0 + p_first + p_first+1 + ...) is the same in every variant.
-  if constexpr (LIGHT) {
-    if (n <= 2)      sk_reduce_items_uv<4, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-    else if (n <= 4) sk_reduce_items_uv<2, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-    else             sk_reduce_items_uv<1, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  } else {
-    if (n <= 2)      sk_reduce_items_uv<8, 2>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-    else if (n <= 4) sk_reduce_items_uv<4, 4>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-    else if (n <= 8) sk_reduce_items_uv<2, 8>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-    else             sk_reduce_items_uv<1, 16>(p, C, first, last, rank, r0, c0, rows_valid, begin, end, tid, nthreads);
-  }
+  const int begin = j * L / n;
+  const int end = (j + 1) * L / n;
+  // The summation order (0 + p_first + p_first+1 + ...) is the same whatever the grouping.
+  sk_reduce_items_qv<QC, LIGHT ? 1 : 2>(p, C, first, last, rank, r0, c0, rows_valid, valid_cols, begin, end, tid,
+                                        nthreads);
   if (peers != nullptr) {   // (called by every thread of the CTA, see sk_reduce_pending)
     __syncthreads();
-    sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, begin, end, tid >> 5, nthreads >> 5, tid & 31);
+    sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, (valid_cols + 3) >> 2, QC, begin, end, tid >> 5,
+                           nthreads >> 5, tid & 31);
   }
 }
 
@@ -434,7 +433,9 @@ __device__ __forceinline__ void sk_store_tile_tma_f32(const CUtensorMap* tm, uin
   }
 }
 
-template <int MODE = SK_EPI_ANY, int EPI_WARPS = 4>
+// FOLD: items the atomic fixup's last arriver fetches per thread and pass (2 = 16 loads in
+// flight; 1 for kernels whose threads have few registers).
+template <int MODE = SK_EPI_ANY, int EPI_WARPS = 4, int FOLD = (EPI_WARPS == 4 ? 2 : 1)>
 __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __restrict__ C, int pid,
                                                  int rank, int warp, int lane, uint32_t tmem_base,
                                                  uint32_t tmem_full_bar, uint32_t tmem_empty_bar,
@@ -550,29 +551,45 @@ __device__ __forceinline__ void sk_epilogue_loop(const SkParams& p, __half* __re
         __threadfence();
         int rows_valid = p.rows - r0;
         if (rows_valid > p.bm) rows_valid = p.bm;
-        const int L = ((valid_cols + 3) >> 2) * BM;
+        const int L = ((valid_cols + 31) >> 5) * BM;   // items: one row of one 32-column chunk
         float4* slot4 = reinterpret_cast<float4*>(acc_slot);
         const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-        constexpr int UF = 12;   // loads in flight per thread: this pass is L2-latency bound
-        for (int idx = etid; idx < L; idx += UF * EPI_THREADS) {
-          float4 x[UF];
+        // FOLD items (row x 32-column chunk) per thread and pass: 8 loads in flight each, the pass is
+        // bound by L2 latency
+        for (int it = etid; it < L; it += FOLD * EPI_THREADS) {
+          float4 x[FOLD][8];
+          float4* src[FOLD];
+          bool on[FOLD];
 #pragma unroll
-          for (int u = 0; u < UF; ++u) {
-            const int i = idx + u * EPI_THREADS;
-            if (i < L && (i & (BM - 1)) < rows_valid) x[u] = __ldcg(slot4 + i);
+          for (int h = 0; h < FOLD; ++h) {
+            const int i = it + h * EPI_THREADS;
+            on[h] = i < L && (i & (BM - 1)) < rows_valid;
+            src[h] = slot4 + static_cast<size_t>((i >> 7) * 8) * BM + (i & (BM - 1));
+            if (on[h]) {
+#pragma unroll
+              for (int qd = 0; qd < 8; ++qd) x[h][qd] = __ldcg(src[h] + qd * BM);
+            }
           }
 #pragma unroll
-          for (int u = 0; u < UF; ++u) {
-            const int i = idx + u * EPI_THREADS;
-            if (i < L && (i & (BM - 1)) < rows_valid) {
-              __stcg(slot4 + i, zero);
-              sk_store4(C, p, r0 + (i & (BM - 1)), c0 + (i >> 7) * 4, x[u]);
+          for (int h = 0; h < FOLD; ++h) {
+            if (!on[h]) continue;
+            const int i = it + h * EPI_THREADS;
+            int nv = valid_cols - (i >> 7) * 32;
+            if (nv > 32) nv = 32;
+            float v[32];
+#pragma unroll
+            for (int qd = 0; qd < 8; ++qd) {
+              __stcg(src[h] + qd * BM, zero);
+              v[4 * qd + 0] = x[h][qd].x; v[4 * qd + 1] = x[h][qd].y;
+              v[4 * qd + 2] = x[h][qd].z; v[4 * qd + 3] = x[h][qd].w;
             }
+            sk_store_cols<32>(C, p, r0 + (i & (BM - 1)), c0 + (i >> 7) * 32, nv, v);
           }
         }
         if (peers != nullptr) {
           named_bar_sync(EPI_BAR_ID, EPI_THREADS);
-          sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, 0, L, warp - 2, EPI_WARPS, lane);
+          sk_copy_items_to_peers(C, p, peers, r0, c0, rows_valid, (valid_cols + 3) >> 2, 8, 0, L, warp - 2,
+                                 EPI_WARPS, lane);
         }
         if (etid == 0) p.ws.counters[first_id] = 0u;
       }

@@ -376,7 +376,7 @@ sk_gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmA, const uint8_t* __r
                       abort_flag, sk_cta_begin(s, pid) % s.iters_per_tile,
                       sk_cta_begin(s, pid + 1) - sk_cta_begin(s, pid));
     else
-      sk_epilogue_loop<MODE>(p, C, pid, 0, warp, lane, tmem_acc, smem_u32(&ctrl->tmem_full[0]),
+      sk_epilogue_loop<MODE, 4, 1>(p, C, pid, 0, warp, lane, tmem_acc, smem_u32(&ctrl->tmem_full[0]),
                              smem_u32(&ctrl->tmem_empty[0]), &ctrl->bcast, abort_flag, ctrl->pend);
   } else {
     // ------------------------------------------------------------- dequantise
