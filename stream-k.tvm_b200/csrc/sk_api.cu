@@ -213,12 +213,14 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
   if (q->M <= 64 && (tiles_open || (q->tile_m != 0 && q->tile_m != 128))) {
     // operands swapped: one tile per 128 weight rows
     const int tiles = (q->N + 127) / 128;
-    // (the W4A16 mainloop's K-step rate is set by its dequantise hand-over, so it always
-    // wants every SM: Stream-K)
-    q->schedule = (kernel_kind == 1 && 2 * tiles >= num_sms) ? SK_SCHED_DP : SK_SCHED_STREAMK;
-    if (q->schedule == SK_SCHED_DP && tiles_open && q->layout == SK_LAYOUT_NT && tiles < num_sms) {
-      // fewer weight rows per tile, so that (nearly) every SM gets a tile of its own: a single
-      // SM ingests only ~110 GB/s, and 86 tiles of 128 rows leave 62 SMs idle
+    // Whole tiles once they occupy half the SMs (measured, both kernels: a split tile's fix-up
+    // costs more than the idle SMs: 16.0 against 17.7 us for W4A16 at 16 x 11008 x 4096),
+    // Stream-K below that.
+    q->schedule = 2 * tiles >= num_sms ? SK_SCHED_DP : SK_SCHED_STREAMK;
+    if (q->schedule == SK_SCHED_DP && kernel_kind == 1 && tiles_open && q->layout == SK_LAYOUT_NT && tiles < num_sms) {
+      // fewer weight rows per tile, so that (nearly) every SM gets a tile of its own: the weight
+      // stream of one SM stays below ~50 GB/s, and 86 tiles of 128 rows leave 62 SMs idle
+      // (measured at 16 x 11008 x 4096: 19.3 us with 138 tiles of 80 rows, 21.5 with 86 of 128)
       const int bm = ((q->N + num_sms - 1) / num_sms + 7) & ~7;
       if (bm >= 64 && bm < 128) {
         q->tile_m = (q->M + 15) & ~15;
@@ -249,11 +251,9 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
     // widest column count per tile row that still gives every tile its own SM
     const int per_row = num_sms / tiles_m;
     int bn = ((q->N + per_row - 1) / per_row + 15) & ~15;
-    // One tile row whose 128-wide tiles already occupy half the SMs: keep them.  Every CTA pulls
-    // its own copy of the activation tile, and with more, narrower tiles that traffic (tiles x
-    // 16 KB per K step) runs into the L2's aggregate bandwidth (~10 TB/s) before the fewer,
-    // wider tiles run into the 110 GB/s a single SM can ingest (measured at 128 x 11008 x 4096:
-    // 24.2 us with 86 tiles of 128 against 26.1 us with 138 tiles of 80).
+    // One tile row whose 128-wide tiles already occupy half the SMs: keep them (measured at
+    // 128 x 11008 x 4096: 23.0 us with 86 tiles of 128, 22.9 with 115 of 96, 25.0 with 138 of
+    // 80; the weight stream as a whole stays near 4 TB/s whatever the number of tiles).
     if (tiles_m == 1 && bn < 128 && 2 * ((q->N + 127) / 128) >= num_sms) bn = 128;
     if (bn >= 80 && bn <= 256 && q->layout == SK_LAYOUT_NT) {
       q->schedule = SK_SCHED_DP; q->tile_m = 128; q->tile_n = bn;
