@@ -163,7 +163,7 @@ static int make_plan(const sk_problem* p, int kernel_kind, int num_sms, SkPlan* 
 // choice that measured best on B200 for this kind of shape.  The rules of thumb behind it:
 //  * a fixup costs a few microseconds of L2 round trips, so when whole tiles alone can keep
 //    most SMs busy, run them data-parallel with the tile width fitted to the SM count;
-//  * otherwise every SM has to stream (a single SM ingests only ~110 GB/s): Stream-K;
+//  * otherwise every SM has to stream (one SM's share of a weight stream stays below ~50 GB/s): Stream-K;
 //  * large problems: the reference's hybrid split.
 // Shapes for which the offline tuner (`python bench.py --tune FILE`, which times the candidates
 // and rejects any whose result is out of tolerance) found something better than the rules
