@@ -46,14 +46,22 @@ enum { SK_SCHED_STREAMK = 0,        /* every tile is Stream-K'd                 
        SK_SCHED_HYBRID_DP_FIRST = 2,/* same tile split, DP waves first, SK remainder last         */
        SK_SCHED_DP = 3,             /* plain data-parallel: one whole tile per CTA per wave       */
        SK_SCHED_AUTO = 4,           /* the library picks schedule (and open tile sizes) by shape  */
-       SK_SCHED_CLUSTER = 5         /* split-K inside a thread-block cluster: every tile is walked
+       SK_SCHED_CLUSTER = 5,        /* split-K inside a thread-block cluster: every tile is walked
                                        by the 2, 4 or 8 CTAs of one cluster (the largest size with
                                        tiles x size <= num_sms), CTA r taking K iterations
                                        [r*I/size, (r+1)*I/size); the partial tiles meet in the
                                        cluster's distributed shared memory and are summed in CTA
                                        order, so no workspace traffic and a bitwise reproducible
                                        result.  fp16 and W4A16 entry points; `fixup` is ignored.  No
-                                       counterpart in the reference.                              */ };
+                                       counterpart in the reference.                              */
+       SK_SCHED_GEMV = 6            /* M <= 4 only (fp16 / bf16 NT and W4A16 entry points): the
+                                       product runs on the CUDA cores as a stream of the weights,
+                                       row groups of 128 x a split of K whose partial sums are added
+                                       in split order by the last CTA of a group to arrive
+                                       (bitwise reproducible; `fixup`, tile_m, tile_n, group_m and
+                                       num_sms < device are ignored, N <= 512 x the SM count).
+                                       What SK_SCHED_AUTO picks at M = 1.  No counterpart in the
+                                       reference, whose kernels are tensor-core tiled at every M. */ };
 
 enum { SK_FIXUP_ATOMIC = 0,        /* fp32 red.global.add into a self-cleaning workspace
                                       (replaces T.atomic_addx2, streamk_fp16.py:248-255)          */

@@ -16,7 +16,7 @@ SK_ERR_ARCH, SK_ERR_ALIGN, SK_ERR_SHAPE, SK_ERR_WORKSPACE, SK_ERR_LAUNCH = 1, 2,
 SK_ERR_FIXUP_TIMEOUT, SK_ERR_PIPE_TIMEOUT, SK_ERR_ARG, SK_ERR_LIMIT = 6, 7, 8, 9
 
 LAYOUTS = {"nn": 0, "nt": 1, "ladder": 2}
-SCHEDULES = {"streamk": 0, "hybrid": 1, "hybrid_dp_first": 2, "dp": 3, "auto": 4, "cluster": 5}
+SCHEDULES = {"streamk": 0, "hybrid": 1, "hybrid_dp_first": 2, "dp": 3, "auto": 4, "cluster": 5, "gemv": 6}
 FIXUPS = {"atomic": 0, "block_reduce": 1}
 SK_FLAG_PDL = 1
 SK_FLAG_NO_TABLE = 2

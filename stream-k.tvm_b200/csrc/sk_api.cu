@@ -194,6 +194,18 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
       }
     }
   }
+  if (tiles_open && q->M <= SK_GEMV_AUTO_M && (kernel_kind == 2 || q->layout == SK_LAYOUT_NT)) {
+    // A single row of activations: the weights stream once through the CUDA cores, without the
+    // tensor-core kernels' fixed costs.  Measured L2-cold at M = 1: W4A16 7.7 / 13.5 / 13.2 us
+    // against 10.5 / 16.0 / 17.1 at 4096 x 4096, 11008 x 4096, 4096 x 11008; fp16 10.3 against
+    // 11.1 at 4096 x 4096 and level elsewhere.  From M = 2 the tensor-core kernels are ahead
+    // (W4A16 17.0 against 16.1 us at 2 x 11008 x 4096, fp16 24.4 against 19.2).
+    SkGemvPlan pl;
+    if (sk_gemv_plan(kernel_kind, q->M, q->N, q->K, num_sms, &pl)) {
+      q->schedule = SK_SCHED_GEMV;
+      return;
+    }
+  }
   const long long t256 = static_cast<long long>((q->M + 255) / 256) * ((q->N + 255) / 256);
   if (t256 >= num_sms) return;                       // large: hybrid (CTA pairs when eligible)
   // (W4A16 beyond 112 rows: the cluster schedule would need two narrower tiles per 128 weight
@@ -268,6 +280,32 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
                   SkSched* s, SkPlan* plan_out) {
   if (!p || num_sms <= 0) return SK_ERR_ARG;
   if (p->M <= 0 || p->N <= 0 || p->K <= 0) return SK_ERR_SHAPE;
+  if (p->schedule == SK_SCHED_GEMV) {
+    // the small-M CUDA-core path has no tiles to schedule: describe its grid
+    if (kernel_kind == 3) kernel_kind = 1;
+    if (kernel_kind == 1 && p->layout != SK_LAYOUT_NT) return SK_ERR_ARG;
+    SkGemvPlan pl;
+    if (!sk_gemv_plan(kernel_kind, p->M, p->N, p->K, num_sms, &pl)) return SK_ERR_SHAPE;
+    if (s) {
+      memset(s, 0, sizeof(*s));
+      s->grid = pl.grid;
+    }
+    if (plan_out) memset(plan_out, 0, sizeof(*plan_out));
+    if (info) {
+      memset(info, 0, sizeof(*info));
+      info->tile_m = p->M; info->tile_n = SK_GEMV_ROWS; info->tile_k = pl.k_per_split;
+      info->tiles_m = 1; info->tiles_n = pl.groups; info->total_tiles = pl.groups;
+      info->iters_per_tile = pl.splits;
+      info->sk_tiles = pl.splits > 1 ? pl.groups : 0;
+      info->dp_tiles = pl.splits > 1 ? 0 : pl.groups;
+      info->grid = pl.grid;
+      info->sk_iters_per_cta = 1;
+      info->dp_waves = pl.splits > 1 ? 0 : 1;
+      info->group_m = 1;
+      info->swap_ab = 1;
+    }
+    return SK_OK;
+  }
   SkPlan plan;
   int st = make_plan(p, kernel_kind, num_sms, &plan);
   if (st != SK_OK) return st;
@@ -382,7 +420,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
 // are asked for explicitly with tile_m = 256.
 static bool use_cta_pairs(const sk_problem* prob, int num_sms) {
   if (prob->layout != SK_LAYOUT_NT || (num_sms & 1) != 0) return false;
-  if (prob->schedule == SK_SCHED_CLUSTER) return false;
+  if (prob->schedule == SK_SCHED_CLUSTER || prob->schedule == SK_SCHED_GEMV) return false;
   if (prob->tile_m == 256) return true;   // (tile_n: 0 = 256, or any multiple of 16 from 32; checked by the plan)
   if (prob->tile_m != 0 || prob->tile_n != 0) return false;
   const long long tiles = static_cast<long long>((prob->M + 255) / 256) * ((prob->N + 255) / 256);
@@ -403,6 +441,8 @@ void sk_f16_dispatch(const sk_problem* in, int num_sms, int n_peers, sk_problem*
     if (out->schedule == SK_SCHED_AUTO) out->schedule = SK_SCHED_DP;
   }
   sk_resolve_auto(out, 1, num_sms);
+  // (the fused multi-GPU epilogues live in the CTA-pair kernel, not in the small-M path)
+  if (n_peers != 0 && in->schedule == SK_SCHED_AUTO && out->schedule == SK_SCHED_GEMV) out->schedule = SK_SCHED_STREAMK;
   const bool pairs = use_cta_pairs(out, num_sms);
   *kernel_kind = pairs ? 3 : 1;
   *units = pairs ? num_sms / 2 : num_sms;

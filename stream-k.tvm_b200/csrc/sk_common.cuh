@@ -124,6 +124,44 @@ struct alignas(64) SkPeers {
   int block_cols;
 };
 
+// ---------------------------------------------------------------------------------------
+// Small-M path (SK_SCHED_GEMV, sk_gemv.cu): how the grid is cut.  A row group is 128 weight
+// rows; K is split so that about four CTAs per SM are in flight, in units of 256 (fp16: one
+// warp-wide 16-byte load per row) or 128 (W4A16: one scale-group stage), at most 2048 per CTA
+// (its activations sit in shared memory as fp32).
+// ---------------------------------------------------------------------------------------
+constexpr int SK_GEMV_MAX_M = 4;      // what the kernels take
+constexpr int SK_GEMV_AUTO_M = 1;     // what SK_SCHED_AUTO sends there (measured: behind the tensor-core kernels from M = 2)
+constexpr int SK_GEMV_ROWS = 128;
+struct SkGemvPlan {
+  int groups, splits, k_per_split, grid;
+};
+inline bool sk_gemv_plan(int kernel_kind, int M, int N, int K, int num_sms, SkGemvPlan* out) {
+  if (M < 1 || M > SK_GEMV_MAX_M || N < 1 || K < 1 || num_sms < 1) return false;
+  if (kernel_kind != 1 && kernel_kind != 2) return false;
+  const int gran = kernel_kind == 1 ? 256 : 128;
+  const long long groups = (static_cast<long long>(N) + SK_GEMV_ROWS - 1) / SK_GEMV_ROWS;
+  if (groups > 4LL * num_sms) return false;       // one counter per group (the workspace has 4 per SM)
+  const int kunits = (K + gran - 1) / gran;
+  const long long per_sm = 4;     // CTAs in flight per SM (more were measured: no gain)
+  long long want = (per_sm * num_sms + groups - 1) / groups;
+  if (want < 1) want = 1;
+  if (want > kunits) want = kunits;
+  int per = (kunits + static_cast<int>(want) - 1) / static_cast<int>(want);   // K units per split
+  if (per * gran > 2048) per = 2048 / gran;
+  const int splits = (kunits + per - 1) / per;
+  out->groups = static_cast<int>(groups);
+  out->splits = splits;
+  out->k_per_split = per * gran;
+  out->grid = static_cast<int>(groups) * splits;
+  return true;
+}
+struct SkWorkspace;
+int sk_launch_gemv_f16(const sk_problem* prob, const void* A, const void* B, void* C, const SkWorkspace& ws,
+                       int num_sms, int dev_sms, void* stream);
+int sk_launch_gemv_q4(const sk_problem* prob, const void* A, const void* qblocks, const void* szblocks, void* C,
+                      int gshift, int q_groups, const SkWorkspace& ws, int num_sms, int dev_sms, void* stream);
+
 // Debugging aid, compiled in only with -DSK_TRACE (the shipped library carries none of it):
 // record %globaltimer at a numbered point of this CTA's life.
 __device__ __forceinline__ void sk_trace(const SkParams& p, int slot) {

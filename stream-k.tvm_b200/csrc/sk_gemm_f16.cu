@@ -491,6 +491,10 @@ static int gemm_f16(const sk_problem* prob, const void* A, const void* B, void* 
   if ((reinterpret_cast<uintptr_t>(C) & 1u) != 0) return SK_ERR_ALIGN;
   if (!ws || ws_bytes < sk_ws_total_bytes(dev_sms)) return SK_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return SK_ERR_ALIGN;
+  if (prob->schedule == SK_SCHED_GEMV) {   // small M: the CUDA-core path (sk_gemv.cu)
+    if (n_peers != 0) return SK_ERR_SHAPE;
+    return sk_launch_gemv_f16(prob, A, B, C, sk_ws_carve(ws, dev_sms), num_sms, dev_sms, stream);
+  }
 
   p.M = M; p.N = N; p.K = K;
   p.lda = prob->lda; p.ldb = prob->ldb; p.ldc = prob->ldc;

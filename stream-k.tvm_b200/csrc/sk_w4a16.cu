@@ -696,6 +696,11 @@ extern "C" int sk_gemm_w4a16(const sk_problem* prob, const void* A, const void* 
   SkPlan plan;
   st = sk_make_sched(prob, 2, num_sms, nullptr, &p.sched, &plan);
   if (st != SK_OK) return st;
+  if (prob->schedule == SK_SCHED_GEMV) {   // small M: the CUDA-core path (sk_gemv.cu)
+    const uint8_t* qb0 = static_cast<const uint8_t*>(packed);
+    return sk_launch_gemv_q4(prob, A, qb0, qb0 + static_cast<size_t>(q4_nblocks(N)) * (K / 64) * Q_BLOCK_BYTES, C,
+                             gshift, groups, sk_ws_carve(ws, dev_sms), num_sms, dev_sms, stream);
+  }
   p.M = M; p.N = N; p.K = K;
   p.lda = prob->lda; p.ldb = 0; p.ldc = prob->ldc;
   p.rows = plan.rows; p.cols = plan.cols;

@@ -147,6 +147,9 @@ def test_fp16_swapped_with_fitted_weight_tiles(M):
     # the library's own choice for many weight rows: data-parallel tiles of fitted height
     A2, B2 = _rand16(M, 11008, 512, seed=7)
     info = sk.schedule_info(M, 11008, 512)
+    if M == 1:      # (a single row goes to the CUDA-core path)
+        assert sk.SCHEDULE_NAMES[info["schedule"]] == "gemv"
+        info = sk.schedule_info(M, 11008, 512, no_table=True, schedule="dp", tile_m=16, tile_n=80)
     assert (info["swap_ab"], info["tile_n"], info["total_tiles"]) == (1, 80, 138)
     _check(sk.streamk_fp16_nt(A2.to(DEV), B2.to(DEV)), oracle.gemm_ref(A2, B2, "nt"), TOL16)
     with pytest.raises(Exception):     # other layouts come in 128-row units

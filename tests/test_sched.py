@@ -174,6 +174,22 @@ def test_auto_schedule_resolution(lib):
     assert (names[d["schedule"]], d["tile_m"], d["tile_n"]) == ("streamk", 128, 128)
     d = plan(8192, 28672, 8192, kind=3)
     assert names[d["schedule"]] == "hybrid" and d["tile_m"] == 256
+    # a single row of activations: the CUDA-core path, row groups of 128 x a split of K
+    d = plan(1, 4096, 4096)
+    assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["tiles_n"], d["iters_per_tile"], d["tile_k"],
+            d["grid"]) == ("gemv", 1, 128, 32, 16, 256, 512)
+    d = plan(1, 11008, 4096, kind=2)
+    assert (names[d["schedule"]], d["tiles_n"], d["iters_per_tile"], d["tile_k"], d["grid"]) == ("gemv", 86, 7, 640, 602)
+    d = plan(2, 4096, 4096)                  # from M = 2 the tensor cores are ahead
+    assert names[d["schedule"]] == "cluster"
+    d = plan(1, 148 * 4 * 128 + 1, 4096)     # more row groups than the workspace has counters: tensor cores
+    assert names[d["schedule"]] != "gemv"
+    # ... which an explicit request may still take up to M = 4
+    prob = L.SkProblem(M=4, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
+    info = L.SkScheduleInfo()
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and info.grid == 602
+    prob = L.SkProblem(M=5, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == L.SK_ERR_SHAPE
     cov = oracle.coverage(plan(300, 5000, 1000))
     assert set(cov.values()) == {1}
 
