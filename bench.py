@@ -552,6 +552,8 @@ def run_tune(path: str, peaks: dict) -> None:
 
     def candidates_f16(M, N, K):
         c = [dict(schedule="streamk"), dict(schedule="hybrid"), dict(schedule="dp")]
+        if M <= 4:
+            c.append(dict(schedule="gemv"))
         if M <= 64:
             tm = (M + 15) // 16 * 16
             for tn in (64, 80, 96, 112, 128):
@@ -578,6 +580,8 @@ def run_tune(path: str, peaks: dict) -> None:
     def candidates_q4(M, N, K):
         c = [dict(schedule="streamk"), dict(schedule="hybrid"), dict(schedule="dp"),
              dict(schedule="streamk", fixup="atomic")]
+        if M <= 4:
+            c.append(dict(schedule="gemv"))
         # narrower tiles along M: more tiles (more CTAs streaming, cluster split-K within reach) for
         # the price of dequantising every weight once per tile column
         widths = sorted({w for w in (16, 32, 48, 64, 96, 112) if w < ((M + 15) // 16 * 16) and M > 16})
