@@ -519,9 +519,12 @@ def run_sweep(path: str, peaks: dict) -> None:
             fn = case.run(sk, schedule=schedule, fixup=fixup, pdl=pdl)
             err = case.check(sk, fn, f"w4a16 {schedule}/{fixup}")
             us = time_rotating(fn, case.copies, case.est)
+            info = sk.schedule_info(case.M, case.N, case.K, kind="w4a16", schedule=schedule)
+            how = f"cluster of {info['cluster']}" if info["cluster"] else fixup
+            label = schedule if schedule != "auto" else f"auto={names[info['schedule']]}"
             record(4, "streamk_fp16_ladder_block_reduce_q4", case.M, case.N, case.K,
-                   f"{'pdl ' if pdl else ''}{schedule}/{fixup}", us, case.flops, case.nbytes,
-                   {"rel_err": float(f"{err:.3e}")})
+                   f"{'pdl ' if pdl else ''}{label}/{how}/tile{info['tile_m']}x{info['tile_n']}", us,
+                   case.flops, case.nbytes, {"rel_err": float(f"{err:.3e}")})
         record(4, "cublas on dequantised fp16 W", case.M, case.N, case.K, "library GEMM, 4x the weight bytes",
                time_rotating(case.cublas(), len(case.Ws), case.est), case.flops, case.nbytes)
 
