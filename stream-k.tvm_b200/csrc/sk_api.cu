@@ -265,7 +265,7 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
     int bn = ((q->N + per_row - 1) / per_row + 15) & ~15;
     // One tile row whose 128-wide tiles already occupy half the SMs: keep them (measured at
     // 128 x 11008 x 4096: 23.0 us with 86 tiles of 128, 22.9 with 115 of 96, 25.0 with 138 of
-    // 80; the weight stream as a whole stays near 4 TB/s whatever the number of tiles).
+    // 80).
     if (tiles_m == 1 && bn < 128 && 2 * ((q->N + 127) / 128) >= num_sms) bn = 128;
     if (bn >= 80 && bn <= 256 && q->layout == SK_LAYOUT_NT) {
       q->schedule = SK_SCHED_DP; q->tile_m = 128; q->tile_n = bn;
