@@ -705,6 +705,8 @@ def run_case(a) -> None:
     for _ in range(a.iters):
         fn()
     torch.cuda.synchronize()
+    if a.timeline:
+        case_timeline(a, kind, M, N, K, kw, dev)
     if a.time:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -722,6 +724,69 @@ def run_case(a) -> None:
     torch.cuda.synchronize()
     sk.check_status()
     print("done")
+
+
+def case_timeline(a, kind, M, N, K, kw, dev) -> None:
+    """--case ... --timeline: per-CTA %globaltimer stamps of ONE launch in the middle of a
+    back-to-back sequence on rotating weight copies (the state the timed runs see; no cache flush:
+    a memset before the launch leaves the L2 full of dirty lines whose write-back slows the
+    kernel under test).  Needs the trace build of the library: run with STREAMK_B200_TRACE=1
+    (`STREAMK_B200_TRACE=1 python stream-k.tvm_b200/build.py` builds it)."""
+    import torch
+    import streamk_b200 as sk
+    from streamk_b200 import _lib as L
+    if os.environ.get("STREAMK_B200_TRACE") != "1":
+        raise SystemExit("--timeline needs STREAMK_B200_TRACE=1 (the trace build of the library)")
+    if kind not in ("f16", "w4a16"):
+        raise SystemExit("--timeline: KIND f16 or w4a16")
+    lib = L.load()
+    l2 = torch.cuda.get_device_properties(0).L2_cache_size
+    g = torch.Generator(device=dev).manual_seed(1)
+    A = torch.randn(M, K, generator=g, device=dev).half()
+    out = torch.empty(M, N, dtype=torch.float16, device=dev)
+    wbytes = 2 * N * K if kind == "f16" else N * K // 2
+    copies = min(max(3, 2 * l2 // wbytes + 2), 40)
+    if kind == "f16":
+        Ws = [(0.02 * torch.randn(N, K, generator=g, device=dev)).half() for _ in range(copies)]
+        fn = lambda i: sk.streamk_fp16_nt(A, Ws[i % copies], out=out, **kw)
+    else:
+        def packed():
+            q = torch.randint(0, 16, (N, K // 8, 8), generator=g, device=dev, dtype=torch.int64)
+            word = sum(q[:, :, j] << (4 * j) for j in range(8))
+            word = torch.where(word >= 2 ** 31, word - 2 ** 32, word).to(torch.int32)
+            z = torch.randint(0, 16, (N, K // 128), generator=g, device=dev, dtype=torch.uint8)
+            s = (0.002 + 0.018 * torch.rand(N, K // 128, generator=g, device=dev)).half()
+            return sk.q4_prepack(word, s, z)
+        Ps = [packed() for _ in range(copies)]
+        kw = {k: v for k, v in kw.items() if k != "group_m"}
+        fn = lambda i: sk.streamk_fp16_ladder_block_reduce_q4(A, Ps[i % copies], out=out, **kw)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    buf = torch.zeros(2 * sms * 16, dtype=torch.int64, device=dev)
+    names = {0: "entry", 1: "barriers up", 2: "first load issued", 3: "first MMA", 4: "last MMA",
+             6: "epilogue done", 7: "exit"}
+    for rep in range(3):
+        for i in range(2 * copies):
+            fn(i)
+        buf.zero_()
+        for i in range(copies):
+            fn(i)
+        L.check(lib.sk_debug_set_trace(buf.data_ptr()), "sk_debug_set_trace")
+        fn(0)
+        lib.sk_debug_set_trace(None)
+        fn(1)
+        torch.cuda.synchronize()
+        t = buf.view(-1, 16).cpu().double()
+        t = t[t[:, 0] > 0]
+        if len(t) == 0:
+            raise SystemExit("no stamps: is this the trace build?")
+        t0 = float(t[:, 0].min())
+        row = {"ctas": int(len(t))}
+        for slot, name in names.items():
+            x = t[:, slot]
+            x = x[x > 1e15]            # (globaltimer values; other slots may hold cycle counts)
+            if len(x):
+                row[name] = [round((float(x.median()) - t0) / 1e3, 2), round((float(x.max()) - t0) / 1e3, 2)]
+        print(json.dumps({"case": a.case, "schedule": a.schedule, "timeline_us_median_max": row}))
 
 
 # ------------------------------------------------------------------------- main arm
@@ -744,6 +809,8 @@ def main() -> None:
     ap.add_argument("--cublas", action="store_true", help="--case: also run torch.matmul on the same operands")
     ap.add_argument("--time", action="store_true", help="--case: print the time per launch of a second batch")
     ap.add_argument("--peers", type=int, default=0)
+    ap.add_argument("--timeline", action="store_true",
+                    help="--case: per-CTA timestamps of one launch in a replayed sequence (trace build)")
     args = ap.parse_args()
     if args.case:
         run_case(args)
