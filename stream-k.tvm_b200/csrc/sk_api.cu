@@ -430,15 +430,17 @@ static bool use_cta_pairs(const sk_problem* prob, int num_sms) {
 void sk_f16_dispatch(const sk_problem* in, int num_sms, int n_peers, sk_problem* out, int* kernel_kind,
                      int* units) {
   *out = *in;
-  // Fused all-gather with more bytes to push than the links can take during the mainloop (about
-  // 600 GB/s out of a GPU against 1.3 PFLOP/s): plain 256 x 256 tiles instead of the 256 x 512
-  // units, whose first results (and with them the transfer) would start twice as late, and
-  // whole tiles only, because a split tile reaches the peers at the very end of the kernel.
-  // Measured on 8 GPUs, 8192 x 3584 x 8192 per GPU: 869 us with the units, 810 with hybrid
-  // 256 x 256 tiles, 780 data-parallel.
-  if (n_peers > 0 && out->tile_m == 0 && 2167LL * n_peers > in->K) {
+  // Fused all-gather: how the bytes to push compare with the mainloop (a GPU's stores reach
+  // its peers at about 600 GB/s, its tensor cores do 1.3 PFLOP/s: 2167 K-steps' worth per peer).
+  // From 60 % of the mainloop on, plain 256 x 256 tiles instead of the 256 x 512 units, whose
+  // first results (and with them the transfer) would start twice as late; measured on 4 GPUs,
+  // 8192 x 7168 x 8192 per GPU: 885 us against 966 with the units (the GEMM alone: 707 against
+  // 655).  Beyond 100 % (the gather is link-bound) whole tiles only as well, because a split
+  // tile reaches the peers at the very end of the kernel; measured on 8 GPUs, 8192 x 3584 x 8192
+  // per GPU: 869 us with the units, 810 with hybrid 256 x 256 tiles, 780 data-parallel.
+  if (n_peers > 0 && out->tile_m == 0 && 5LL * 2167 * n_peers > 3LL * in->K) {
     out->tile_m = 256;
-    if (out->schedule == SK_SCHED_AUTO) out->schedule = SK_SCHED_DP;
+    if (2167LL * n_peers > in->K && out->schedule == SK_SCHED_AUTO) out->schedule = SK_SCHED_DP;
   }
   sk_resolve_auto(out, 1, num_sms);
   // (the fused multi-GPU epilogues live in the CTA-pair kernel, not in the small-M path)

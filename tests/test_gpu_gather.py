@@ -72,18 +72,24 @@ def test_gather_writes_every_peer_like_the_plain_product(shape):
 
 def test_gather_with_wide_units_and_seven_peers():
     """The library's own tiling of a large block.  Few peers and a deep K: the 256 x 512 units
-    stay (the transfer hides under the mainloop).  Many peers and a shallow K: plain 256 x 256
-    tiles, data-parallel, so that the transfer starts earlier and nothing is left for the end.  Either way every copy carries the bits of the
-    unfused product with the same tiling."""
+    stay (the transfer hides under the mainloop).  Bytes to push worth 60 % of the mainloop or
+    more: plain 256 x 256 tiles, so that the transfer starts earlier.  More than the whole
+    mainloop: those tiles data-parallel, so that nothing is left for the end.  Either way every
+    copy carries the bits of the unfused product with the same tiling."""
     g = torch.Generator(device=DEV).manual_seed(11)
-    for K, n_peers, wide in ((2304, 1, True), (256, 7, False)):
+    for K, n_peers, how in ((4096, 1, "units"), (2304, 1, "tiles"), (256, 7, "tiles_dp")):
         M, N = 1024, 10240
         A = torch.randn(M, K, generator=g, device=DEV).half()
         B = (torch.randn(N, K, generator=g, device=DEV) / K ** 0.5).half()
         info = sk.schedule_info(M, N, K, kind="f16_pairs", schedule="hybrid", num_sms=74)
         assert info["wide_units"] > 0
-        if wide:
+        info = sk.schedule_info(M, N, K, gather_peers=n_peers)
+        assert (info["wide_units"] > 0) == (how == "units")
+        assert sk.SCHEDULE_NAMES[info["schedule"]] == ("dp" if how == "tiles_dp" else "hybrid")
+        if how == "units":
             plain = sk.streamk_fp16_nt(A, B, fixup="block_reduce")
+        elif how == "tiles":
+            plain = sk.streamk_fp16_nt(A, B, tile_m=256, schedule="hybrid", fixup="block_reduce")
         else:
             plain = sk.streamk_fp16_nt(A, B, tile_m=256, schedule="dp", fixup="block_reduce")
         ref = torch.matmul(A.float(), B.float().t())
