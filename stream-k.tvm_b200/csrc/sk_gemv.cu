@@ -195,32 +195,83 @@ sk_gemv_f16_kernel(const uint16_t* __restrict__ A, int lda, const uint16_t* __re
 }
 
 // ------------------------------------------------------------------------------------ W4A16
-// Four nibbles of a 16-bit half word as fp32 (q - z), without a conversion instruction: nibble p
-// (bits 4p .. 4p+3) OR-ed into the mantissa of 2^(23 - 4p) reads as 2^(23 - 4p) + q exactly, and
-// adding c[p] = -(2^(23 - 4p) + z) leaves q - z exactly.  (Conversions run at a fraction of the
-// FMA rate and would bound the kernel: this costs one logic and one add per weight.)
-__device__ __forceinline__ void nibbles4(uint32_t w16, const float (&c)[4], float (&f)[4]) {
+// Activations of this CTA's K range as fp16 in shared memory, sA[m][k - k_lo] (zero beyond K),
+// each row multiplied by a power of two that brings its largest magnitude into [32, 64): the
+// inner sums below are taken in fp16 over 16 terms of |q - z| <= 15, which then stay below
+// 16 * 15 * 64 whatever the activations are (an outlier of a few thousand would overflow them
+// otherwise).  inv[m] undoes the factor (exactly) on the fp32 side.
+template <int M>
+__device__ __forceinline__ void stage_activations_scaled(uint16_t* sA, float* s_max /* shared [M][4] */,
+                                                         const uint16_t* A, int lda, int K, int k_lo, int k_len,
+                                                         int tid, float (&inv)[M]) {
+  const int chunks = k_len >> 3;   // 16-byte chunks per row; at most 2 per thread (k_len <= 2048)
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    __half2 mx = __float2half2_rn(0.f);
+    for (int c = tid; c < chunks; c += GEMV_THREADS_Q4) {
+      const int k = k_lo + c * 8;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (k < K) v = *reinterpret_cast<const uint4*>(A + static_cast<size_t>(m) * lda + k);
+      *reinterpret_cast<uint4*>(sA + m * k_len + c * 8) = v;
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) mx = __hmax2(mx, __habs2(h[e]));
+    }
+    float f = fmaxf(__low2float(mx), __high2float(mx));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, o));
+    if (lane == 0) s_max[m * 4 + warp] = f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const float f = fmaxf(fmaxf(s_max[m * 4], s_max[m * 4 + 1]), fmaxf(s_max[m * 4 + 2], s_max[m * 4 + 3]));
+    int e = 132 - static_cast<int>((__float_as_uint(f) >> 23) & 0xFFu);   // 2^e * max in [32, 64)
+    e = e < -11 ? -11 : (e > 14 ? 14 : e);                                 // 2^e is a normal fp16
+    const __half2 up = __float2half2_rn(__uint_as_float(static_cast<uint32_t>(127 + e) << 23));
+    inv[m] = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+    for (int c = tid; c < chunks; c += GEMV_THREADS_Q4) {   // (the chunks this thread wrote)
+      uint4* dst = reinterpret_cast<uint4*>(sA + m * k_len + c * 8);
+      uint4 v = *dst;
+      __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) h[q] = __hmul2(h[q], up);
+      *dst = v;
+    }
+  }
+  __syncthreads();
+}
+
+// The eight nibbles of a packed word as four fp16 pairs (q - z), without a conversion
+// instruction.  The word's low half holds the even K values of its eight and the high half the
+// odd ones, so one mask picks a pair of neighbours: a nibble in bits 0-3 of 0x6400 reads as
+// 1024 + q, in bits 4-7 as 1024 + 16 q; `c0` = 1024 + z, `c1` = -(64 + z): both results exact.
+__device__ __forceinline__ void nibbles8(uint32_t w, __half2 c0, __half2 c1, __half2 (&d)[4]) {
   uint32_t t0, t1, t2, t3;
-  asm("lop3.b32 %0, %1, 0x0000000F, 0x4B000000, 0xEA;" : "=r"(t0) : "r"(w16));
-  asm("lop3.b32 %0, %1, 0x000000F0, 0x49000000, 0xEA;" : "=r"(t1) : "r"(w16));
-  asm("lop3.b32 %0, %1, 0x00000F00, 0x47000000, 0xEA;" : "=r"(t2) : "r"(w16));
-  asm("lop3.b32 %0, %1, 0x0000F000, 0x45000000, 0xEA;" : "=r"(t3) : "r"(w16));
-  f[0] = __uint_as_float(t0) + c[0];
-  f[1] = __uint_as_float(t1) + c[1];
-  f[2] = __uint_as_float(t2) + c[2];
-  f[3] = __uint_as_float(t3) + c[3];
+  const uint32_t w8 = w >> 8;
+  asm("lop3.b32 %0, %1, 0x000F000F, 0x64006400, 0xEA;" : "=r"(t0) : "r"(w));
+  asm("lop3.b32 %0, %1, 0x00F000F0, 0x64006400, 0xEA;" : "=r"(t1) : "r"(w));
+  asm("lop3.b32 %0, %1, 0x000F000F, 0x64006400, 0xEA;" : "=r"(t2) : "r"(w8));
+  asm("lop3.b32 %0, %1, 0x00F000F0, 0x64006400, 0xEA;" : "=r"(t3) : "r"(w8));
+  const __half2 sixteenth = __float2half2_rn(0.0625f);
+  d[0] = __hsub2(*reinterpret_cast<const __half2*>(&t0), c0);              // K values 0, 1
+  d[1] = __hfma2(*reinterpret_cast<const __half2*>(&t1), sixteenth, c1);   //          2, 3
+  d[2] = __hsub2(*reinterpret_cast<const __half2*>(&t2), c0);              //          4, 5
+  d[3] = __hfma2(*reinterpret_cast<const __half2*>(&t3), sixteenth, c1);   //          6, 7
 }
 
 // A thread owns one weight row of the 128-row block; four K blocks (256 of K) per step: eight
-// 16-byte loads per thread in flight.
+// 16-byte loads per thread in flight, the first step's already while the activations are staged.
 template <int M>
 __global__ void __launch_bounds__(GEMV_THREADS_Q4)
 sk_gemv_q4_kernel(const uint16_t* __restrict__ A, int lda, const uint8_t* __restrict__ qblocks,
                   const uint8_t* __restrict__ szblocks, uint16_t* __restrict__ C, int ldc, int N, int K,
                   int kblocks, int kb_per_split, int S, int gshift, int q_groups, float* parts,
                   uint32_t* counters) {
-  extern __shared__ __align__(16) float sA[];   // [M][kb_per_split * 64]
+  extern __shared__ __align__(16) uint16_t sAh[];   // [M][kb_per_split * 64]
   __shared__ float sums[M * SK_GEMV_ROWS];
+  __shared__ float s_max[M * 4];
   __shared__ uint32_t s_last;
   const int tid = threadIdx.x;                // = weight row inside the 128-row block
   const int g = blockIdx.x / S, s = blockIdx.x - g * S;
@@ -228,29 +279,30 @@ sk_gemv_q4_kernel(const uint16_t* __restrict__ A, int lda, const uint8_t* __rest
   int kb_hi = kb_lo + kb_per_split;
   if (kb_hi > kblocks) kb_hi = kblocks;
   const int k_len = kb_per_split * 64;
+  const uint8_t* q = qblocks + (static_cast<size_t>(g) * kblocks + kb_lo) * 4096 + tid * 16;
+  const uint8_t* sz = szblocks + static_cast<size_t>(g) * q_groups * 384;
+  constexpr int UNR = 4;                      // K blocks whose loads travel together
+  uint4 w[UNR][2];
   skptx::griddep_wait();
-  stage_activations<M, false>(sA, A, lda, K, kb_lo * 64, k_len, tid, GEMV_THREADS_Q4);
-  __syncthreads();
-  // C[m][row] = sum over scale groups of s * sum over the group's K of (q - z) * a: the inner sum
-  // in fp32 on exact integers (the weight is not rounded to fp16 on the way, unlike in the
-  // tensor-core kernel, whose operands have to be fp16), the scale once per group.
+#pragma unroll
+  for (int u = 0; u < UNR; ++u) {
+    const int kk = kb_lo + u < kb_hi ? u : 0;   // (past the range: a repeated load, not used)
+    w[u][0] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096);
+    w[u][1] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096 + 2048);
+  }
+  float inv[M];
+  stage_activations_scaled<M>(sAh, s_max, A, lda, K, kb_lo * 64, k_len, tid, inv);
+  // C[m][row] = sum over scale groups of s * sum over the group's K of (q - z) * a.  The inner
+  // sum: exact integers (q - z) times fp16 activations, 16 terms at a time in fp16 (two chains of
+  // eight fused multiply-adds on pairs), then in fp32; the scale once per group.  (The reference
+  // accumulates in fp16 throughout, streamk_fp16_ladder_block_reduce_q4.py:25.)
   float acc[M], part[M];
 #pragma unroll
   for (int m = 0; m < M; ++m) { acc[m] = 0.f; part[m] = 0.f; }
-  const uint8_t* q = qblocks + (static_cast<size_t>(g) * kblocks + kb_lo) * 4096 + tid * 16;
-  const uint8_t* sz = szblocks + static_cast<size_t>(g) * q_groups * 384;
   int cur_blk = -1;
   float scale = 0.f;
-  float cz[4] = {0.f, 0.f, 0.f, 0.f};
-  constexpr int UNR = 4;                      // K blocks whose loads travel together
+  __half2 c0 = __float2half2_rn(1024.f), c1 = __float2half2_rn(-64.f);
   for (int kb = kb_lo; kb < kb_hi; kb += UNR) {
-    uint4 w[UNR][2];
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const int kk = kb + u < kb_hi ? u : 0;   // (past the range: a repeated load, not used)
-      w[u][0] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096);
-      w[u][1] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096 + 2048);
-    }
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
       if (kb + u >= kb_hi) break;
@@ -264,35 +316,47 @@ sk_gemv_q4_kernel(const uint16_t* __restrict__ A, int lda, const uint8_t* __rest
           const uint8_t* b = sz + static_cast<size_t>(blk) * 384;
           scale = __half2float(*reinterpret_cast<const __half*>(b + tid * 2));
           const float z = static_cast<float>(b[256 + tid]);
-          cz[0] = -(8388608.f + z); cz[1] = -(524288.f + z); cz[2] = -(32768.f + z); cz[3] = -(2048.f + z);
+          c0 = __float2half2_rn(1024.f + z);
+          c1 = __float2half2_rn(-(64.f + z));
         }
         const uint32_t words[4] = {w[u][h].x, w[u][h].y, w[u][h].z, w[u][h].w};
-        const float* a0 = sA + ((kb + u - kb_lo) * 64 + h * 32);
+        const uint16_t* a0 = sAh + ((kb + u - kb_lo) * 64 + h * 32);
+        __half2 p0[M], p1[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) { p0[m] = __float2half2_rn(0.f); p1[m] = p0[m]; }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          // word c: K values 8c .. 8c+7; the low half word holds the even ones, the high half the odd
-          float fe[4], fo[4];
-          nibbles4(words[c], cz, fe);
-          nibbles4(words[c] >> 16, cz, fo);
+          __half2 d[4];
+          nibbles8(words[c], c0, c1, d);
 #pragma unroll
           for (int m = 0; m < M; ++m) {
-            const float4* src = reinterpret_cast<const float4*>(a0 + m * k_len + c * 8);
-            const float4 x = src[0], y = src[1];   // (every lane reads the same address)
-            // two chains of four dependent FMAs instead of one of eight
-            float v = part[m], u2 = fe[2] * y.x;
-            v = fmaf(fe[0], x.x, v);  u2 = fmaf(fo[2], y.y, u2);
-            v = fmaf(fo[0], x.y, v);  u2 = fmaf(fe[3], y.z, u2);
-            v = fmaf(fe[1], x.z, v);  u2 = fmaf(fo[3], y.w, u2);
-            v = fmaf(fo[1], x.w, v);
-            part[m] = v + u2;
+            const uint4 x = *reinterpret_cast<const uint4*>(a0 + m * k_len + c * 8);   // (same address in every lane)
+            const __half2* a = reinterpret_cast<const __half2*>(&x);
+            p0[m] = __hfma2(d[0], a[0], p0[m]);
+            p1[m] = __hfma2(d[1], a[1], p1[m]);
+            p0[m] = __hfma2(d[2], a[2], p0[m]);
+            p1[m] = __hfma2(d[3], a[3], p1[m]);
           }
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float2 f = __half22float2(__hadd2(p0[m], p1[m]));
+          part[m] += f.x + f.y;
         }
       }
     }
     q += static_cast<size_t>(UNR) * 4096;
+    if (kb + UNR < kb_hi) {
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const int kk = kb + UNR + u < kb_hi ? u : 0;
+        w[u][0] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096);
+        w[u][1] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096 + 2048);
+      }
+    }
   }
 #pragma unroll
-  for (int m = 0; m < M; ++m) sums[m * SK_GEMV_ROWS + tid] = fmaf(scale, part[m], acc[m]);
+  for (int m = 0; m < M; ++m) sums[m * SK_GEMV_ROWS + tid] = fmaf(scale, part[m], acc[m]) * inv[m];
   skptx::griddep_launch_dependents();
   __syncthreads();
   finish_group<M>(sums, parts, counters, C, ldc, N, g, s, S, 0, tid, GEMV_THREADS_Q4, &s_last);
@@ -344,7 +408,7 @@ int sk_launch_gemv_q4(const sk_problem* prob, const void* A, const void* qblocks
   if ((prob->flags & SK_FLAG_BF16) != 0) return SK_ERR_ARG;
   const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
   const int kblocks = prob->K / 64, kb_per_split = pl.k_per_split / 64;
-  const size_t smem = static_cast<size_t>(prob->M) * pl.k_per_split * sizeof(float);
+  const size_t smem = static_cast<size_t>(prob->M) * pl.k_per_split * sizeof(uint16_t);
   const cudaStream_t cs = static_cast<cudaStream_t>(stream);
   const uint16_t* a = static_cast<const uint16_t*>(A);
   const uint8_t* qb = static_cast<const uint8_t*>(qblocks);
