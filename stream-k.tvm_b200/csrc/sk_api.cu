@@ -194,14 +194,19 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
       }
     }
   }
-  if (tiles_open && q->M <= SK_GEMV_AUTO_M && (kernel_kind == 2 || q->layout == SK_LAYOUT_NT)) {
-    // A single row of activations: the weights stream once through the CUDA cores, without the
-    // tensor-core kernels' fixed costs.  Measured L2-cold at M = 1: W4A16 7.7 / 13.5 / 13.2 us
-    // against 10.5 / 16.0 / 17.1 at 4096 x 4096, 11008 x 4096, 4096 x 11008; fp16 10.3 against
-    // 11.1 at 4096 x 4096 and level elsewhere.  From M = 2 the tensor-core kernels are ahead
-    // (W4A16 17.0 against 16.1 us at 2 x 11008 x 4096, fp16 24.4 against 19.2).
+  const int gemv_kind = sk_gemv_kind(kernel_kind, q->flags);
+  if (tiles_open && q->M <= (gemv_kind == 2 ? SK_GEMV_Q4_MAX_M : SK_GEMV_AUTO_M) &&
+      (kernel_kind == 2 || q->layout == SK_LAYOUT_NT)) {
+    // Few rows of activations: the weights stream once through a kernel without the tensor-core
+    // kernels' fixed costs (tensor-memory allocation, mbarrier rings, a cluster exchange or a
+    // workspace fix-up).  W4A16 with scale groups of 128 and more, whose small-M kernel takes
+    // eight rows for the price of one (measured L2-cold at 4096 x 4096, 11008 x 4096,
+    // 4096 x 11008: M = 1 5.9 / 11.2 / 11.3 us, M = 8 6.2 / 12.0 / 13.0, against 10.6 / 16.1 /
+    // 17.3 for the best tensor-memory kernel at either M): up to M = 8.  fp16 (10.3 against
+    // 11.1 us at 1 x 4096 x 4096, level elsewhere) and W4A16 with smaller groups (CUDA-core
+    // kernels whose time grows with M: behind from M = 2): a single row.
     SkGemvPlan pl;
-    if (sk_gemv_plan(kernel_kind, q->M, q->N, q->K, num_sms, &pl)) {
+    if (sk_gemv_plan(gemv_kind, q->M, q->N, q->K, num_sms, &pl)) {
       q->schedule = SK_SCHED_GEMV;
       return;
     }
@@ -285,7 +290,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
     if (kernel_kind == 3) kernel_kind = 1;
     if (kernel_kind == 1 && p->layout != SK_LAYOUT_NT) return SK_ERR_ARG;
     SkGemvPlan pl;
-    if (!sk_gemv_plan(kernel_kind, p->M, p->N, p->K, num_sms, &pl)) return SK_ERR_SHAPE;
+    if (!sk_gemv_plan(sk_gemv_kind(kernel_kind, p->flags), p->M, p->N, p->K, num_sms, &pl)) return SK_ERR_SHAPE;
     if (s) {
       memset(s, 0, sizeof(*s));
       s->grid = pl.grid;
@@ -293,7 +298,7 @@ int sk_make_sched(const sk_problem* p, int kernel_kind, int num_sms, sk_schedule
     if (plan_out) memset(plan_out, 0, sizeof(*plan_out));
     if (info) {
       memset(info, 0, sizeof(*info));
-      info->tile_m = p->M; info->tile_n = SK_GEMV_ROWS; info->tile_k = pl.k_per_split;
+      info->tile_m = p->M; info->tile_n = pl.rows; info->tile_k = pl.k_per_split;
       info->tiles_m = 1; info->tiles_n = pl.groups; info->total_tiles = pl.groups;
       info->iters_per_tile = pl.splits;
       info->sk_tiles = pl.splits > 1 ? pl.groups : 0;

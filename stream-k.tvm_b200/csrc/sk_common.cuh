@@ -125,21 +125,69 @@ struct alignas(64) SkPeers {
 };
 
 // ---------------------------------------------------------------------------------------
-// Small-M path (SK_SCHED_GEMV, sk_gemv.cu): how the grid is cut.  A row group is 128 weight
-// rows; K is split so that about four CTAs per SM are in flight, in units of 256 (fp16: one
-// warp-wide 16-byte load per row) or 128 (W4A16: one scale-group stage), at most 2048 per CTA
-// (its activations sit in shared memory as fp32).
+// Small-M path (SK_SCHED_GEMV, sk_gemv.cu): how the grid is cut.  kernel_kind 1: fp16 / bf16;
+// 2: W4A16 with scale groups of 128 and more (M <= 8); 3: W4A16 with groups of 32 or 64 (M <= 4).
+//   fp16 / bf16: a row group is 128 weight rows; K is split across CTAs so that about four CTAs
+//     per SM are in flight, in units of 256 (one warp-wide 16-byte load per row), at most 2048
+//     per CTA (its activations sit in shared memory as fp32).
+//   W4A16: a CTA takes 32 weight rows over all of K and cuts K into `slices` of whole steps
+//     (128 of K), one per warp, whose sums meet in shared memory: 16 warps when there is at
+//     most one CTA per SM, else 4 (kind 2) or 8 (kind 3) (measured, 11008 x 4096: kind 2 11.2 us
+//     with 4 warps, 13.7 with 8, 14.5 with 16; kind 3 13.1 / 10.4 / 11.6).  Only a matrix with too
+//     few rows for half of the SMs is also split across CTAs (`splits`), in pieces of at
+//     least 512 of K.  (More rows per CTA with fewer slices each, 64 to 256 rows, were
+//     measured with kind 3: 10-40 % slower.)
 // ---------------------------------------------------------------------------------------
-constexpr int SK_GEMV_MAX_M = 4;      // what the kernels take
-constexpr int SK_GEMV_AUTO_M = 1;     // what SK_SCHED_AUTO sends there (measured: behind the tensor-core kernels from M = 2)
+constexpr int SK_GEMV_MAX_M = 4;      // what the kernels take ...
+constexpr int SK_GEMV_Q4_MAX_M = 8;   // ... W4A16 with scale groups of 128 and more
+constexpr int SK_GEMV_AUTO_M = 1;     // what SK_SCHED_AUTO sends there: fp16 and W4A16 with small groups ...
 constexpr int SK_GEMV_ROWS = 128;
+constexpr int SK_GEMV_Q4_WARPS = 16;  // per CTA, at most
+constexpr int SK_GEMV_Q4_SMEM_MAX = 160 * 1024;
 struct SkGemvPlan {
   int groups, splits, k_per_split, grid;
+  int rows, slices, k_per_slice, threads;   // W4A16; fp16: 128, 1, k_per_split, 256
 };
 inline bool sk_gemv_plan(int kernel_kind, int M, int N, int K, int num_sms, SkGemvPlan* out) {
-  if (M < 1 || M > SK_GEMV_MAX_M || N < 1 || K < 1 || num_sms < 1) return false;
-  if (kernel_kind != 1 && kernel_kind != 2) return false;
-  const int gran = kernel_kind == 1 ? 256 : 128;
+  if (kernel_kind < 1 || kernel_kind > 3) return false;
+  if (M < 1 || M > (kernel_kind == 2 ? SK_GEMV_Q4_MAX_M : SK_GEMV_MAX_M) || N < 1 || K < 1 || num_sms < 1) return false;
+  if (kernel_kind != 1) {
+    const long long groups = (static_cast<long long>(N) + 31) / 32;
+    if (groups > 0x7fffffffLL / 64) return false;
+    const int kblocks = (K + 63) / 64;
+    const int slices0 = groups <= num_sms ? SK_GEMV_Q4_WARPS : (kernel_kind == 2 ? 4 : 8);
+    int splits = 1;
+    if (2 * groups <= num_sms) {
+      splits = static_cast<int>(num_sms / groups);
+      const int cap = kblocks / 8 > 1 ? kblocks / 8 : 1;
+      if (splits > cap) splits = cap;
+    }
+    int kb_split, kb_slice, slices;
+    for (;;) {   // (K blocks in pairs: a step of the kernels is 128 of K)
+      kb_split = ((kblocks + splits - 1) / splits + 1) & ~1;
+      kb_slice = ((kb_split + slices0 - 1) / slices0 + 1) & ~1;
+      slices = (kb_split + kb_slice - 1) / kb_slice;
+      // (kind 3 stages its activations: [slice][M][K of a slice] fp16)
+      const long long smem = kernel_kind == 3 ? static_cast<long long>(slices) * M * kb_slice * 64 * 2 : 0;
+      if (smem <= SK_GEMV_Q4_SMEM_MAX) break;
+      if (splits >= kblocks) return false;
+      splits *= 2;
+      if (splits > kblocks) splits = kblocks;
+    }
+    splits = (kblocks + kb_split - 1) / kb_split;
+    if (splits > 1 && groups > 4LL * num_sms) return false;   // one counter per group (the workspace has 4 per SM)
+    if (groups * splits > 0x7fffffffLL) return false;
+    out->groups = static_cast<int>(groups);
+    out->splits = splits;
+    out->k_per_split = kb_split * 64;
+    out->grid = static_cast<int>(groups) * splits;
+    out->rows = 32;
+    out->slices = slices;
+    out->k_per_slice = kb_slice * 64;
+    out->threads = 32 * slices;
+    return true;
+  }
+  const int gran = 256;
   const long long groups = (static_cast<long long>(N) + SK_GEMV_ROWS - 1) / SK_GEMV_ROWS;
   if (groups > 4LL * num_sms) return false;       // one counter per group (the workspace has 4 per SM)
   const int kunits = (K + gran - 1) / gran;
@@ -154,7 +202,17 @@ inline bool sk_gemv_plan(int kernel_kind, int M, int N, int K, int num_sms, SkGe
   out->splits = splits;
   out->k_per_split = per * gran;
   out->grid = static_cast<int>(groups) * splits;
+  out->rows = SK_GEMV_ROWS;
+  out->slices = 1;
+  out->k_per_slice = per * gran;
+  out->threads = 256;
   return true;
+}
+// The plan kind of an entry point's kernel kind (1: fp16, 2: W4A16) and problem flags.
+inline int sk_gemv_kind(int kernel_kind, int flags) {
+  if (kernel_kind != 2) return 1;
+  const int grp = flags & SK_FLAG_Q4_GROUP_MASK;
+  return (grp == SK_FLAG_Q4_GROUP_32 || grp == SK_FLAG_Q4_GROUP_64) ? 3 : 2;
 }
 struct SkWorkspace;
 int sk_launch_gemv_f16(const sk_problem* prob, const void* A, const void* B, void* C, const SkWorkspace& ws,

@@ -25,7 +25,7 @@
 namespace {
 
 constexpr int GEMV_THREADS_F16 = 256;
-constexpr int GEMV_THREADS_Q4 = 128;
+constexpr int GEMV_THREADS_Q4 = 32 * SK_GEMV_Q4_WARPS;   // at most
 
 __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
   uint4 v;
@@ -79,22 +79,21 @@ __device__ __forceinline__ void stage_activations(float* sA, const uint16_t* A, 
   }
 }
 
-// Partial sums of CTA (g, s) are at parts[((g * S + s) * M + m) * 128 + row]; the last CTA of
-// group g to arrive adds them over s = 0 .. S-1 in that order and stores C[m][g * 128 + row].
-template <int M>
-__device__ __forceinline__ void finish_group(const float* sums /* shared: [M][128] */, float* parts,
+// Partial sums of CTA (g, s) are at parts[((g * S + s) * M + m) * rows + row]; the last CTA of
+// group g to arrive adds them over s = 0 .. S-1 in that order and stores C[m][g * rows + row].
+__device__ __forceinline__ void finish_group(const float* sums /* shared: [M][rows] */, int M, int rows, float* parts,
                                              uint32_t* counters, uint16_t* C, int ldc, int N, int g, int s,
                                              int S, int bf16, int tid, int nthreads, uint32_t* s_last) {
-  const int row0 = g * SK_GEMV_ROWS;
+  const int row0 = g * rows, items = M * rows;
   if (S == 1) {
-    for (int i = tid; i < M * SK_GEMV_ROWS; i += nthreads) {
-      const int m = i >> 7, r = i & 127;
+    for (int i = tid; i < items; i += nthreads) {
+      const int m = i / rows, r = i - m * rows;
       if (row0 + r < N) C[static_cast<size_t>(m) * ldc + row0 + r] = static_cast<uint16_t>(pack_out(sums[i], bf16));
     }
     return;
   }
-  float* mine = parts + static_cast<size_t>(g * S + s) * (M * SK_GEMV_ROWS);
-  for (int i = tid; i < M * SK_GEMV_ROWS; i += nthreads) __stcg(mine + i, sums[i]);
+  float* mine = parts + static_cast<size_t>(g * S + s) * items;
+  for (int i = tid; i < items; i += nthreads) __stcg(mine + i, sums[i]);
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -104,15 +103,15 @@ __device__ __forceinline__ void finish_group(const float* sums /* shared: [M][12
   __syncthreads();
   if (*s_last == 0u) return;
   __threadfence();
-  const float* all = parts + static_cast<size_t>(g * S) * (M * SK_GEMV_ROWS);
-  for (int i = tid; i < M * SK_GEMV_ROWS; i += nthreads) {
-    const int m = i >> 7, r = i & 127;
+  const float* all = parts + static_cast<size_t>(g * S) * items;
+  for (int i = tid; i < items; i += nthreads) {
+    const int m = i / rows, r = i - m * rows;
     float acc = 0.f;
     for (int j0 = 0; j0 < S; j0 += 8) {     // eight loads in flight, added in split order
       float v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        v[u] = __ldcg(all + static_cast<size_t>(j0 + u < S ? j0 + u : S - 1) * (M * SK_GEMV_ROWS) + i);
+        v[u] = __ldcg(all + static_cast<size_t>(j0 + u < S ? j0 + u : S - 1) * items + i);
 #pragma unroll
       for (int u = 0; u < 8; ++u)
         if (j0 + u < S) acc += v[u];
@@ -191,29 +190,26 @@ sk_gemv_f16_kernel(const uint16_t* __restrict__ A, int lda, const uint16_t* __re
   // of this grid that have not started)
   skptx::griddep_launch_dependents();
   __syncthreads();
-  finish_group<M>(sums, parts, counters, C, ldc, N, g, s, S, BF16 ? 1 : 0, tid, GEMV_THREADS_F16, &s_last);
+  finish_group(sums, M, SK_GEMV_ROWS, parts, counters, C, ldc, N, g, s, S, BF16 ? 1 : 0, tid, GEMV_THREADS_F16, &s_last);
 }
 
 // ------------------------------------------------------------------------------------ W4A16
-// Activations of this CTA's K range as fp16 in shared memory, sA[m][k - k_lo] (zero beyond K),
-// each row multiplied by a power of two that brings its largest magnitude into [32, 64): the
-// inner sums below are taken in fp16 over 16 terms of |q - z| <= 15, which then stay below
-// 16 * 15 * 64 whatever the activations are (an outlier of a few thousand would overflow them
-// otherwise).  inv[m] undoes the factor (exactly) on the fp32 side.
+// A warp's slice of the activations as fp16 in its own piece of shared memory, sA[m][k - k_lo],
+// each row multiplied by a power of two that brings the slice's largest magnitude into
+// [32, 64): the inner sums below are taken in fp16 over 16 terms of |q - z| <= 15, which then
+// stay below 16 * 15 * 64 whatever the activations are (an outlier of a few thousand would
+// overflow them otherwise).  inv[m] undoes the factor (exactly) on the fp32 side.  Warp-local:
+// no CTA-wide barrier.
 template <int M>
-__device__ __forceinline__ void stage_activations_scaled(uint16_t* sA, float* s_max /* shared [M][4] */,
-                                                         const uint16_t* A, int lda, int K, int k_lo, int k_len,
-                                                         int tid, float (&inv)[M]) {
-  const int chunks = k_len >> 3;   // 16-byte chunks per row; at most 2 per thread (k_len <= 2048)
-  const int warp = tid >> 5, lane = tid & 31;
+__device__ __forceinline__ void stage_slice_scaled(uint16_t* sA, const uint16_t* A, int lda, int k_lo, int k_len,
+                                                   int k_stride, int lane, float (&inv)[M]) {
+  const int chunks = k_len >> 3;   // 16-byte chunks per row
 #pragma unroll
   for (int m = 0; m < M; ++m) {
     __half2 mx = __float2half2_rn(0.f);
-    for (int c = tid; c < chunks; c += GEMV_THREADS_Q4) {
-      const int k = k_lo + c * 8;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (k < K) v = *reinterpret_cast<const uint4*>(A + static_cast<size_t>(m) * lda + k);
-      *reinterpret_cast<uint4*>(sA + m * k_len + c * 8) = v;
+    for (int c = lane; c < chunks; c += 32) {
+      const uint4 v = *reinterpret_cast<const uint4*>(A + static_cast<size_t>(m) * lda + k_lo + c * 8);
+      *reinterpret_cast<uint4*>(sA + m * k_stride + c * 8) = v;
       const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
       for (int e = 0; e < 4; ++e) mx = __hmax2(mx, __habs2(h[e]));
@@ -221,18 +217,12 @@ __device__ __forceinline__ void stage_activations_scaled(uint16_t* sA, float* s_
     float f = fmaxf(__low2float(mx), __high2float(mx));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, o));
-    if (lane == 0) s_max[m * 4 + warp] = f;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int m = 0; m < M; ++m) {
-    const float f = fmaxf(fmaxf(s_max[m * 4], s_max[m * 4 + 1]), fmaxf(s_max[m * 4 + 2], s_max[m * 4 + 3]));
     int e = 132 - static_cast<int>((__float_as_uint(f) >> 23) & 0xFFu);   // 2^e * max in [32, 64)
     e = e < -11 ? -11 : (e > 14 ? 14 : e);                                 // 2^e is a normal fp16
     const __half2 up = __float2half2_rn(__uint_as_float(static_cast<uint32_t>(127 + e) << 23));
     inv[m] = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-    for (int c = tid; c < chunks; c += GEMV_THREADS_Q4) {   // (the chunks this thread wrote)
-      uint4* dst = reinterpret_cast<uint4*>(sA + m * k_len + c * 8);
+    for (int c = lane; c < chunks; c += 32) {   // (the chunks this lane wrote)
+      uint4* dst = reinterpret_cast<uint4*>(sA + m * k_stride + c * 8);
       uint4 v = *dst;
       __half2* h = reinterpret_cast<__half2*>(&v);
 #pragma unroll
@@ -240,7 +230,7 @@ __device__ __forceinline__ void stage_activations_scaled(uint16_t* sA, float* s_
       *dst = v;
     }
   }
-  __syncthreads();
+  __syncwarp();
 }
 
 // The eight nibbles of a packed word as four fp16 pairs (q - z), without a conversion
@@ -261,105 +251,288 @@ __device__ __forceinline__ void nibbles8(uint32_t w, __half2 c0, __half2 c1, __h
   d[3] = __hfma2(*reinterpret_cast<const __half2*>(&t3), sixteenth, c1);   //          6, 7
 }
 
-// A thread owns one weight row of the 128-row block; four K blocks (256 of K) per step: eight
-// 16-byte loads per thread in flight, the first step's already while the activations are staged.
+constexpr int Q4_UNR = 2;   // K blocks (64 of K each) whose loads travel together: four 16-byte loads per thread
+
+// The packed words of up to Q4_UNR K blocks of this thread's row (`left` = K blocks that remain;
+// past them a repeated load, not used).
+__device__ __forceinline__ void q4_load(uint4 (&w)[Q4_UNR][2], const uint8_t* q, int left) {
+#pragma unroll
+  for (int u = 0; u < Q4_UNR; ++u) {
+    const uint8_t* src = q + static_cast<size_t>(u < left ? u : 0) * 4096;
+    w[u][0] = ld_stream_v4(src);
+    w[u][1] = ld_stream_v4(src + 2048);
+  }
+}
+
+// C[m][row] = sum over scale groups of s * sum over the group's K of (q - z) * a.  The inner sum:
+// exact integers (q - z) times fp16 activations, 16 terms at a time in fp16 (two chains of eight
+// fused multiply-adds on pairs), then in fp32; the scale once per group.  (The reference
+// accumulates in fp16 throughout, streamk_fp16_ladder_block_reduce_q4.py:25.)
+template <int M>
+struct Q4Sum {
+  float acc[M], part[M], scale;
+  __half2 c0, c1;
+  int cur_blk;
+};
+
+// One step: K blocks kb .. kb + Q4_UNR - 1 (below kb_hi) of the thread's row against the
+// activations at `a` (shared memory, rows k_stride apart).  sz: the row's scale of group 0.
+template <int M>
+__device__ __forceinline__ void q4_step(Q4Sum<M>& t, const uint4 (&w)[Q4_UNR][2], int kb, int kb_hi,
+                                        const uint8_t* sz, int rb, int gshift, const uint16_t* a,
+                                        int k_stride) {
+#pragma unroll
+  for (int u = 0; u < Q4_UNR; ++u) {
+    if (kb + u >= kb_hi) break;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int blk = (2 * (kb + u) + h) >> gshift;   // scale group of this 32-wide half step
+      if (blk != t.cur_blk) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) { t.acc[m] = fmaf(t.scale, t.part[m], t.acc[m]); t.part[m] = 0.f; }
+        t.cur_blk = blk;
+        const uint8_t* b = sz + static_cast<size_t>(blk) * 384;
+        t.scale = __half2float(*reinterpret_cast<const __half*>(b));
+        const float z = static_cast<float>(b[256 - rb]);   // (b points rb * 2 into the scales: 256 + rb from their start)
+        t.c0 = __float2half2_rn(1024.f + z);
+        t.c1 = __float2half2_rn(-(64.f + z));
+      }
+      const uint32_t words[4] = {w[u][h].x, w[u][h].y, w[u][h].z, w[u][h].w};
+      const uint16_t* a0 = a + (u * 64 + h * 32);
+      __half2 p0[M], p1[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) { p0[m] = __float2half2_rn(0.f); p1[m] = p0[m]; }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        __half2 d[4];
+        nibbles8(words[c], t.c0, t.c1, d);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const uint4 x = *reinterpret_cast<const uint4*>(a0 + m * k_stride + c * 8);   // (same address in every lane)
+          const __half2* av = reinterpret_cast<const __half2*>(&x);
+          p0[m] = __hfma2(d[0], av[0], p0[m]);
+          p1[m] = __hfma2(d[1], av[1], p1[m]);
+          p0[m] = __hfma2(d[2], av[2], p0[m]);
+          p1[m] = __hfma2(d[3], av[3], p1[m]);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float2 f = __half22float2(__hadd2(p0[m], p1[m]));
+        t.part[m] += f.x + f.y;
+      }
+    }
+  }
+}
+
+// CTA (g, s): 32 weight rows times `slices` pieces of the CTA's K range, one per warp.  A thread
+// owns one weight row over its warp's K slice, two K blocks (128 of K) per step, the next step's
+// loads in flight while it sums (the first step's while the warp stages its activations).  The
+// slices' sums meet in shared memory and are added in slice order.
 template <int M>
 __global__ void __launch_bounds__(GEMV_THREADS_Q4)
 sk_gemv_q4_kernel(const uint16_t* __restrict__ A, int lda, const uint8_t* __restrict__ qblocks,
                   const uint8_t* __restrict__ szblocks, uint16_t* __restrict__ C, int ldc, int N, int K,
-                  int kblocks, int kb_per_split, int S, int gshift, int q_groups, float* parts,
-                  uint32_t* counters) {
-  extern __shared__ __align__(16) uint16_t sAh[];   // [M][kb_per_split * 64]
-  __shared__ float sums[M * SK_GEMV_ROWS];
-  __shared__ float s_max[M * 4];
+                  int kblocks, int kb_per_split, int kb_per_slice, int S, int gshift, int q_groups,
+                  float* parts, uint32_t* counters) {
+  extern __shared__ __align__(16) uint16_t sAh[];   // [warp][M][kb_per_slice * 64]
+  __shared__ float red[M * GEMV_THREADS_Q4];        // [slice][m][row of the CTA]
+  __shared__ float sums[M * 32];
   __shared__ uint32_t s_last;
-  const int tid = threadIdx.x;                // = weight row inside the 128-row block
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nthreads = blockDim.x, slices = nthreads >> 5;
   const int g = blockIdx.x / S, s = blockIdx.x - g * S;
-  const int kb_lo = s * kb_per_split;
-  int kb_hi = kb_lo + kb_per_split;
-  if (kb_hi > kblocks) kb_hi = kblocks;
-  const int k_len = kb_per_split * 64;
-  const uint8_t* q = qblocks + (static_cast<size_t>(g) * kblocks + kb_lo) * 4096 + tid * 16;
-  const uint8_t* sz = szblocks + static_cast<size_t>(g) * q_groups * 384;
-  constexpr int UNR = 4;                      // K blocks whose loads travel together
-  uint4 w[UNR][2];
-  skptx::griddep_wait();
-#pragma unroll
-  for (int u = 0; u < UNR; ++u) {
-    const int kk = kb_lo + u < kb_hi ? u : 0;   // (past the range: a repeated load, not used)
-    w[u][0] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096);
-    w[u][1] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096 + 2048);
-  }
+  const int row = g * 32 + lane;                        // weight row of this thread
+  const int rb = row & 127;                             // ... inside its 128-row block
+  int kb_end = (s + 1) * kb_per_split;
+  if (kb_end > kblocks) kb_end = kblocks;
+  const int kb_lo = s * kb_per_split + warp * kb_per_slice;
+  int kb_hi = kb_lo + kb_per_slice;
+  if (kb_hi > kb_end) kb_hi = kb_end;
+  const int k_slice = kb_per_slice * 64;
+  const uint8_t* q = qblocks + (static_cast<size_t>(row >> 7) * kblocks + kb_lo) * 4096 + rb * 16;
+  const uint8_t* sz = szblocks + static_cast<size_t>(row >> 7) * q_groups * 384;
+  uint16_t* sA = sAh + static_cast<size_t>(warp) * M * k_slice;
   float inv[M];
-  stage_activations_scaled<M>(sAh, s_max, A, lda, K, kb_lo * 64, k_len, tid, inv);
-  // C[m][row] = sum over scale groups of s * sum over the group's K of (q - z) * a.  The inner
-  // sum: exact integers (q - z) times fp16 activations, 16 terms at a time in fp16 (two chains of
-  // eight fused multiply-adds on pairs), then in fp32; the scale once per group.  (The reference
-  // accumulates in fp16 throughout, streamk_fp16_ladder_block_reduce_q4.py:25.)
-  float acc[M], part[M];
+  Q4Sum<M> sum;
 #pragma unroll
-  for (int m = 0; m < M; ++m) { acc[m] = 0.f; part[m] = 0.f; }
-  int cur_blk = -1;
-  float scale = 0.f;
-  __half2 c0 = __float2half2_rn(1024.f), c1 = __float2half2_rn(-64.f);
-  for (int kb = kb_lo; kb < kb_hi; kb += UNR) {
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      if (kb + u >= kb_hi) break;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int blk = (2 * (kb + u) + h) >> gshift;   // scale group of this 32-wide half step
-        if (blk != cur_blk) {
-#pragma unroll
-          for (int m = 0; m < M; ++m) { acc[m] = fmaf(scale, part[m], acc[m]); part[m] = 0.f; }
-          cur_blk = blk;
-          const uint8_t* b = sz + static_cast<size_t>(blk) * 384;
-          scale = __half2float(*reinterpret_cast<const __half*>(b + tid * 2));
-          const float z = static_cast<float>(b[256 + tid]);
-          c0 = __float2half2_rn(1024.f + z);
-          c1 = __float2half2_rn(-(64.f + z));
-        }
-        const uint32_t words[4] = {w[u][h].x, w[u][h].y, w[u][h].z, w[u][h].w};
-        const uint16_t* a0 = sAh + ((kb + u - kb_lo) * 64 + h * 32);
-        __half2 p0[M], p1[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) { p0[m] = __float2half2_rn(0.f); p1[m] = p0[m]; }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          __half2 d[4];
-          nibbles8(words[c], c0, c1, d);
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            const uint4 x = *reinterpret_cast<const uint4*>(a0 + m * k_len + c * 8);   // (same address in every lane)
-            const __half2* a = reinterpret_cast<const __half2*>(&x);
-            p0[m] = __hfma2(d[0], a[0], p0[m]);
-            p1[m] = __hfma2(d[1], a[1], p1[m]);
-            p0[m] = __hfma2(d[2], a[2], p0[m]);
-            p1[m] = __hfma2(d[3], a[3], p1[m]);
-          }
-        }
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          const float2 f = __half22float2(__hadd2(p0[m], p1[m]));
-          part[m] += f.x + f.y;
-        }
-      }
-    }
-    q += static_cast<size_t>(UNR) * 4096;
-    if (kb + UNR < kb_hi) {
-#pragma unroll
-      for (int u = 0; u < UNR; ++u) {
-        const int kk = kb + UNR + u < kb_hi ? u : 0;
-        w[u][0] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096);
-        w[u][1] = ld_stream_v4(q + static_cast<size_t>(kk) * 4096 + 2048);
-      }
+  for (int m = 0; m < M; ++m) { sum.acc[m] = 0.f; sum.part[m] = 0.f; inv[m] = 0.f; }
+  sum.scale = 0.f;
+  sum.cur_blk = -1;
+  sum.c0 = __float2half2_rn(1024.f);
+  sum.c1 = __float2half2_rn(-64.f);
+  skptx::griddep_wait();
+  if (kb_lo < kb_hi) {
+    // Two sets of registers: the loads of one step travel while the other is summed.
+    uint4 w0[Q4_UNR][2], w1[Q4_UNR][2];
+    q4_load(w0, q, kb_hi - kb_lo);
+    stage_slice_scaled<M>(sA, A, lda, kb_lo * 64, (kb_hi - kb_lo) * 64, k_slice, lane, inv);
+    sz += rb * 2;
+    for (int kb = kb_lo; kb < kb_hi; kb += 2 * Q4_UNR) {
+      if (kb + Q4_UNR < kb_hi) q4_load(w1, q + static_cast<size_t>(Q4_UNR) * 4096, kb_hi - kb - Q4_UNR);
+      q4_step<M>(sum, w0, kb, kb_hi, sz, rb, gshift, sA + (kb - kb_lo) * 64, k_slice);
+      if (kb + Q4_UNR >= kb_hi) break;
+      q += static_cast<size_t>(2 * Q4_UNR) * 4096;
+      if (kb + 2 * Q4_UNR < kb_hi) q4_load(w0, q, kb_hi - kb - 2 * Q4_UNR);
+      q4_step<M>(sum, w1, kb + Q4_UNR, kb_hi, sz, rb, gshift, sA + (kb + Q4_UNR - kb_lo) * 64, k_slice);
     }
   }
 #pragma unroll
-  for (int m = 0; m < M; ++m) sums[m * SK_GEMV_ROWS + tid] = fmaf(scale, part[m], acc[m]) * inv[m];
+  for (int m = 0; m < M; ++m) red[(warp * M + m) * 32 + lane] = fmaf(sum.scale, sum.part[m], sum.acc[m]) * inv[m];
   skptx::griddep_launch_dependents();
   __syncthreads();
-  finish_group<M>(sums, parts, counters, C, ldc, N, g, s, S, 0, tid, GEMV_THREADS_Q4, &s_last);
+  for (int i = tid; i < M * 32; i += nthreads) {
+    float v = red[i];                           // slice 0 of (m, row) = i
+    for (int j = 1; j < slices; ++j) v += red[j * M * 32 + i];
+    sums[i] = v;
+  }
+  __syncthreads();
+  finish_group(sums, M, 32, parts, counters, C, ldc, N, g, s, S, 0, tid, nthreads, &s_last);
+}
+
+// --------------------------------------------------------- W4A16, scale groups of 128 and more
+// The same split of the work (32 weight rows per CTA, one K slice per warp), with the products
+// on the tensor cores through register-level mma.sync (m16n8k16, fp32 accumulators): the eight
+// columns of the instruction hold the rows of activations, so up to eight cost what one costs.
+//
+// No instruction is spent on turning nibbles into numbers: a nibble masked in place into bits
+// 0-3 (or 4-7) of an fp16 is the subnormal q * 2^-24 (or 16 q * 2^-24), which the tensor cores
+// multiply exactly; the two nibble positions get accumulators of their own, and a third set
+// takes the activations against a tile of ones (the sum that the zero-point multiplies).  Nothing
+// is staged: the activations come from global memory through L1 in the instruction's operand
+// layout as they are.  Scales and zero-points are applied to the accumulators once per step of
+// 128 along K, which is why the scale group must be a multiple of 128:
+//   C[m][row] += s * (sum q a  -  z * sum a).
+//
+// Lane (g = lane / 4, t = lane % 4) reads the 16 bytes (32 values of K) of piece t of a step
+// (piece = K block t / 2, half t % 2) for weight rows g, g + 8, g + 16, g + 24 of the CTA's 32:
+// rows g, g + 8 are rows g, g + 8 of the first 16-row operand tile, the other two of the second.
+// A packed word holds 8 consecutive K values, the even ones in its low half: the mask
+// 0x000F000F leaves values 0, 1 of the eight as a pair, the same mask after a shift by 8 values
+// 4, 5, and these four are the lane's K slots of one instruction; 0x00F000F0 gives 2, 3 and
+// 6, 7 for the next.  The activations' 16 bytes for the same eight K values hold the pairs
+// (0,1) (2,3) (4,5) (6,7): first and third word for the one, second and fourth for the other.
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_cached_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// What a lane holds of one step: its 16 bytes of four rows, and (lane = row of the CTA) that
+// row's scale and zero-point of the step's group.
+struct Q4mStep {
+  uint4 w[4];
+  uint16_t s;
+  uint8_t z;
+};
+
+// sz_row: this lane's scale of group 0; its zero-point is z_off bytes further.
+__device__ __forceinline__ void q4m_load(Q4mStep& st, const uint8_t* q, const uint8_t* sz_row, int z_off, int blk) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) st.w[j] = ld_stream_v4(q + j * 128);
+  const uint8_t* b = sz_row + static_cast<size_t>(blk) * 384;
+  st.s = *reinterpret_cast<const uint16_t*>(b);
+  st.z = b[z_off];
+}
+
+__global__ void __launch_bounds__(GEMV_THREADS_Q4)
+sk_gemv_q4_mma_kernel(const uint16_t* __restrict__ A, int lda, int M, const uint8_t* __restrict__ qblocks,
+                      const uint8_t* __restrict__ szblocks, uint16_t* __restrict__ C, int ldc, int N, int K,
+                      int kblocks, int kb_per_split, int kb_per_slice, int S, int gshift, int q_groups,
+                      float* parts, uint32_t* counters) {
+  __shared__ float red[SK_GEMV_Q4_MAX_M * GEMV_THREADS_Q4];   // [slice][m][row of the CTA]
+  __shared__ float sums[SK_GEMV_Q4_MAX_M * 32];
+  __shared__ uint32_t s_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g8 = lane >> 2, t = lane & 3;
+  const int nthreads = blockDim.x, slices = nthreads >> 5;
+  const int g = blockIdx.x / S, s = blockIdx.x - g * S;
+  const int row0 = g * 32;                              // first weight row of the CTA
+  const int rb0 = row0 & 127;                           // ... inside its 128-row block
+  int kb_end = (s + 1) * kb_per_split;
+  if (kb_end > kblocks) kb_end = kblocks;
+  const int kb_lo = s * kb_per_split + warp * kb_per_slice;
+  int kb_hi = kb_lo + kb_per_slice;
+  if (kb_hi > kb_end) kb_hi = kb_end;
+  float acc[4][2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { acc[j][0] = 0.f; acc[j][1] = 0.f; }
+  skptx::griddep_wait();
+  if (kb_lo < kb_hi) {   // (K blocks come in pairs: K is a multiple of 128, and so is every slice)
+    const uint8_t* q = qblocks + (static_cast<size_t>(row0 >> 7) * kblocks + kb_lo + (t >> 1)) * 4096 +
+                       (t & 1) * 2048 + (rb0 + g8) * 16;
+    const uint8_t* sz_row = szblocks + static_cast<size_t>(row0 >> 7) * q_groups * 384 + (rb0 + lane) * 2;
+    const int z_off = 256 - (rb0 + lane);   // (the zero-point of row r is 256 + r bytes into the block, its scale 2 r)
+    // the activations this lane feeds: row g of A (column g of the operand; past M: the last row,
+    // into columns that nobody reads), piece t of the step
+    const uint16_t* aB = A + static_cast<size_t>(g8 < M ? g8 : M - 1) * lda + kb_lo * 64 + t * 32;
+    Q4mStep st0, st1;
+    q4m_load(st0, q, sz_row, z_off, (2 * kb_lo) >> gshift);
+    auto step = [&](const Q4mStep& st, const uint16_t* a) {
+      float lo[2][4], hi[2][4], one[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { lo[0][e] = 0.f; lo[1][e] = 0.f; hi[0][e] = 0.f; hi[1][e] = 0.f; one[e] = 0.f; }
+      const uint32_t wj[4][4] = {{st.w[0].x, st.w[0].y, st.w[0].z, st.w[0].w}, {st.w[1].x, st.w[1].y, st.w[1].z, st.w[1].w},
+                                 {st.w[2].x, st.w[2].y, st.w[2].z, st.w[2].w}, {st.w[3].x, st.w[3].y, st.w[3].z, st.w[3].w}};
+      constexpr uint32_t ONES = 0x00010001u;   // 2^-24 twice
+#pragma unroll
+      for (int cw = 0; cw < 4; ++cw) {
+        const uint4 x = ld_cached_v4(a + cw * 8);   // (L1: every CTA of the SM reads the same few KB)
+#pragma unroll
+        for (int T = 0; T < 2; ++T) {
+          const uint32_t wa = wj[2 * T][cw], wb = wj[2 * T + 1][cw];
+          const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
+          mma_16816(lo[T], wa & 0x000F000Fu, wb & 0x000F000Fu, wa8 & 0x000F000Fu, wb8 & 0x000F000Fu, x.x, x.z);
+          mma_16816(hi[T], wa & 0x00F000F0u, wb & 0x00F000F0u, wa8 & 0x00F000F0u, wb8 & 0x00F000F0u, x.y, x.w);
+        }
+        mma_16816(one, ONES, ONES, ONES, ONES, x.x, x.z);
+        mma_16816(one, ONES, ONES, ONES, ONES, x.y, x.w);
+      }
+      // the scale and -z * scale of this lane's row (times the 2^24 of the subnormals) to the
+      // lanes that hold the row's accumulators
+      const float sc = __half2float(__ushort_as_half(st.s)) * 16777216.f;
+      const float zs = -static_cast<float>(st.z) * sc;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float scj = __shfl_sync(0xffffffffu, sc, 8 * j + g8), zsj = __shfl_sync(0xffffffffu, zs, 8 * j + g8);
+        const int T = j >> 1, e = (j & 1) * 2;
+        acc[j][0] = fmaf(fmaf(hi[T][e], 0.0625f, lo[T][e]), scj, fmaf(zsj, one[0], acc[j][0]));
+        acc[j][1] = fmaf(fmaf(hi[T][e + 1], 0.0625f, lo[T][e + 1]), scj, fmaf(zsj, one[1], acc[j][1]));
+      }
+    };
+    // Two sets of registers: the loads of one step travel while the other is multiplied.
+    for (int kb = kb_lo; kb < kb_hi; kb += 4) {
+      if (kb + 2 < kb_hi) q4m_load(st1, q + 2 * 4096, sz_row, z_off, (2 * (kb + 2)) >> gshift);
+      step(st0, aB);
+      if (kb + 2 >= kb_hi) break;
+      q += 4 * 4096;
+      if (kb + 4 < kb_hi) q4m_load(st0, q, sz_row, z_off, (2 * (kb + 4)) >> gshift);
+      step(st1, aB + 128);
+      aB += 256;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (2 * t < M) red[(warp * M + 2 * t) * 32 + 8 * j + g8] = acc[j][0];
+    if (2 * t + 1 < M) red[(warp * M + 2 * t + 1) * 32 + 8 * j + g8] = acc[j][1];
+  }
+  skptx::griddep_launch_dependents();
+  __syncthreads();
+  for (int i = tid; i < M * 32; i += nthreads) {
+    float v = red[i];                           // slice 0 of (m, row) = i
+    for (int j = 1; j < slices; ++j) v += red[j * M * 32 + i];
+    sums[i] = v;
+  }
+  __syncthreads();
+  finish_group(sums, M, 32, parts, counters, C, ldc, N, g, s, S, 0, tid, nthreads, &s_last);
 }
 
 }  // namespace
@@ -403,22 +576,40 @@ int sk_launch_gemv_f16(const sk_problem* prob, const void* A, const void* B, voi
 int sk_launch_gemv_q4(const sk_problem* prob, const void* A, const void* qblocks, const void* szblocks, void* C,
                       int gshift, int q_groups, const SkWorkspace& ws, int num_sms, int dev_sms, void* stream) {
   SkGemvPlan pl;
-  if (!sk_gemv_plan(2, prob->M, prob->N, prob->K, num_sms, &pl)) return SK_ERR_SHAPE;
-  if (pl.groups > 4 * dev_sms) return SK_ERR_LIMIT;
+  const bool mma = gshift >= 2;   // scale groups of 128 and more: the tensor-core form
+  if (!sk_gemv_plan(mma ? 2 : 3, prob->M, prob->N, prob->K, num_sms, &pl)) return SK_ERR_SHAPE;
+  if (pl.splits > 1) {   // counters and partial sums of the workspace (P = dev_sms slots)
+    if (pl.groups > 4 * dev_sms) return SK_ERR_LIMIT;
+    const size_t need = static_cast<size_t>(pl.grid) * prob->M * pl.rows * sizeof(float);
+    if (need > 2 * static_cast<size_t>(dev_sms) * SK_SLOT_BYTES) return SK_ERR_LIMIT;
+  }
   if ((prob->flags & SK_FLAG_BF16) != 0) return SK_ERR_ARG;
   const bool pdl = (prob->flags & SK_FLAG_PDL) != 0;
-  const int kblocks = prob->K / 64, kb_per_split = pl.k_per_split / 64;
-  const size_t smem = static_cast<size_t>(prob->M) * pl.k_per_split * sizeof(uint16_t);
+  const int kblocks = prob->K / 64, kb_per_split = pl.k_per_split / 64, kb_per_slice = pl.k_per_slice / 64;
   const cudaStream_t cs = static_cast<cudaStream_t>(stream);
   const uint16_t* a = static_cast<const uint16_t*>(A);
   const uint8_t* qb = static_cast<const uint8_t*>(qblocks);
   const uint8_t* sz = static_cast<const uint8_t*>(szblocks);
   uint16_t* c = static_cast<uint16_t*>(C);
   cudaError_t e = cudaSuccess;
-#define SK_GEMV_Q4(MM)                                                                                 \
-  e = sk_launch(sk_gemv_q4_kernel<MM>, pl.grid, GEMV_THREADS_Q4, smem, cs, 1, pdl, a, prob->lda, qb, sz, c, \
-                prob->ldc, prob->N, prob->K, kblocks, kb_per_split, pl.splits, gshift, q_groups,       \
-                ws.part_slots, ws.counters)
+  if (mma) {
+    e = sk_launch(sk_gemv_q4_mma_kernel, pl.grid, pl.threads, 0, cs, 1, pdl, a, prob->lda, prob->M, qb, sz, c,
+                  prob->ldc, prob->N, prob->K, kblocks, kb_per_split, kb_per_slice, pl.splits, gshift, q_groups,
+                  ws.part_slots, ws.counters);
+    if (e != cudaSuccess) return sk_set_cuda_error(e);
+    return SK_OK;
+  }
+  const size_t smem = static_cast<size_t>(pl.slices) * prob->M * pl.k_per_slice * sizeof(uint16_t);
+#define SK_GEMV_Q4(MM)                                                                                  \
+  do {                                                                                                  \
+    if (smem > 32 * 1024)                                                                               \
+      e = cudaFuncSetAttribute(sk_gemv_q4_kernel<MM>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                               SK_GEMV_Q4_SMEM_MAX);                                                    \
+    if (e == cudaSuccess)                                                                               \
+      e = sk_launch(sk_gemv_q4_kernel<MM>, pl.grid, pl.threads, smem, cs, 1, pdl, a, prob->lda, qb, sz, \
+                    c, prob->ldc, prob->N, prob->K, kblocks, kb_per_split, kb_per_slice, pl.splits,     \
+                    gshift, q_groups, ws.part_slots, ws.counters);                                      \
+  } while (0)
   switch (prob->M) {
     case 1: SK_GEMV_Q4(1); break;
     case 2: SK_GEMV_Q4(2); break;

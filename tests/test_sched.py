@@ -174,21 +174,40 @@ def test_auto_schedule_resolution(lib):
     assert (names[d["schedule"]], d["tile_m"], d["tile_n"]) == ("streamk", 128, 128)
     d = plan(8192, 28672, 8192, kind=3)
     assert names[d["schedule"]] == "hybrid" and d["tile_m"] == 256
-    # a single row of activations: the CUDA-core path, row groups of 128 x a split of K
+    # a single row of activations: the small-M path; fp16: row groups of 128 x a split of K
     d = plan(1, 4096, 4096)
     assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["tiles_n"], d["iters_per_tile"], d["tile_k"],
             d["grid"]) == ("gemv", 1, 128, 32, 16, 256, 512)
-    d = plan(1, 11008, 4096, kind=2)
-    assert (names[d["schedule"]], d["tiles_n"], d["iters_per_tile"], d["tile_k"], d["grid"]) == ("gemv", 86, 7, 640, 602)
     d = plan(2, 4096, 4096)                  # from M = 2 the tensor cores are ahead
     assert names[d["schedule"]] == "cluster"
     d = plan(1, 148 * 4 * 128 + 1, 4096)     # more row groups than the workspace has counters: tensor cores
     assert names[d["schedule"]] != "gemv"
-    # ... which an explicit request may still take up to M = 4
-    prob = L.SkProblem(M=4, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
+    # W4A16 (scale groups of 128): 32 rows per CTA over all of K, up to eight rows of activations
+    for M in (1, 8):
+        d = plan(M, 11008, 4096, kind=2)
+        assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["tiles_n"], d["iters_per_tile"], d["tile_k"],
+                d["grid"]) == ("gemv", M, 32, 344, 1, 4096, 344)
+    d = plan(9, 11008, 4096, kind=2)
+    assert names[d["schedule"]] != "gemv"
+    d = plan(4, 1024, 8192, kind=2)          # too few rows for half of the SMs: K split over 4 CTAs as well
+    assert (names[d["schedule"]], d["tiles_n"], d["iters_per_tile"], d["tile_k"], d["grid"]) == ("gemv", 32, 4, 2048, 128)
+    # scale groups of 32 or 64: the CUDA-core kernel, chosen at M = 1 and taken up to M = 4
+    g64 = 0x200
+    prob = L.SkProblem(M=1, N=11008, K=4096, schedule=L.SCHEDULES["auto"], layout=1, flags=g64)
     info = L.SkScheduleInfo()
-    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and info.grid == 602
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and names[info.schedule] == "gemv"
+    prob = L.SkProblem(M=2, N=11008, K=4096, schedule=L.SCHEDULES["auto"], layout=1, flags=g64)
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and names[info.schedule] != "gemv"
+    prob = L.SkProblem(M=4, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1, flags=g64)
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and info.grid == 344
+    prob = L.SkProblem(M=5, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1, flags=g64)
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == L.SK_ERR_SHAPE
+    # ... which an explicit request may still take up to M = 4 (fp16) or 8 (W4A16, groups of 128)
+    prob = L.SkProblem(M=4, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0 and info.grid == 516
     prob = L.SkProblem(M=5, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
+    assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_SHAPE
+    prob = L.SkProblem(M=9, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
     assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == L.SK_ERR_SHAPE
     cov = oracle.coverage(plan(300, 5000, 1000))
     assert set(cov.values()) == {1}
