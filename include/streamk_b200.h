@@ -54,13 +54,18 @@ enum { SK_SCHED_STREAMK = 0,        /* every tile is Stream-K'd                 
                                        order, so no workspace traffic and a bitwise reproducible
                                        result.  fp16 and W4A16 entry points; `fixup` is ignored.  No
                                        counterpart in the reference.                              */
-       SK_SCHED_GEMV = 6            /* M <= 4 only (fp16 / bf16 NT and W4A16 entry points): the
-                                       product runs on the CUDA cores as a stream of the weights,
-                                       row groups of 128 x a split of K whose partial sums are added
-                                       in split order by the last CTA of a group to arrive
-                                       (bitwise reproducible; `fixup`, tile_m, tile_n, group_m and
-                                       num_sms < device are ignored, N <= 512 x the SM count).
-                                       What SK_SCHED_AUTO picks at M = 1.  No counterpart in the
+       SK_SCHED_GEMV = 6            /* A few rows of activations only: the product as one stream of
+                                       the weights through small CTAs, without tensor memory,
+                                       clusters or workspace fix-ups.  fp16 / bf16 NT and W4A16 with
+                                       scale groups of 32 or 64: M <= 4, on the CUDA cores.  W4A16
+                                       with groups of 128 and more: M <= 16, register-level
+                                       tensor-core instructions on the packed nibbles.  Partial sums
+                                       meet in a fixed order (bitwise reproducible); `fixup`,
+                                       tile_m, tile_n, group_m and num_sms < device are ignored;
+                                       fp16: N <= 512 x the SM count.  What SK_SCHED_AUTO picks for
+                                       fp16 at M = 1 and for W4A16 up to M = 8 (groups of 128 and
+                                       more; up to 16 when N <= 32 x the SM count; M = 1 with
+                                       smaller groups).  No counterpart in the
                                        reference, whose kernels are tensor-core tiled at every M. */ };
 
 enum { SK_FIXUP_ATOMIC = 0,        /* fp32 red.global.add into a self-cleaning workspace

@@ -195,8 +195,10 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
     }
   }
   const int gemv_kind = sk_gemv_kind(kernel_kind, q->flags);
-  if (tiles_open && q->M <= (gemv_kind == 2 ? SK_GEMV_Q4_MAX_M : SK_GEMV_AUTO_M) &&
-      (kernel_kind == 2 || q->layout == SK_LAYOUT_NT)) {
+  // (W4A16: 9 to 16 rows cost the small-M kernel twice the instructions of 1 to 8: only where the
+  // launch is short enough to be bound by latencies, at most one 32-row CTA per SM)
+  const int gemv_m = gemv_kind != 2 ? SK_GEMV_AUTO_M : (q->N <= 32LL * num_sms ? SK_GEMV_Q4_MAX_M : 8);
+  if (tiles_open && q->M <= gemv_m && (kernel_kind == 2 || q->layout == SK_LAYOUT_NT)) {
     // Few rows of activations: the weights stream once through a kernel without the tensor-core
     // kernels' fixed costs (tensor-memory allocation, mbarrier rings, a cluster exchange or a
     // workspace fix-up).  W4A16 with scale groups of 128 and more, whose small-M kernel takes

@@ -126,7 +126,7 @@ struct alignas(64) SkPeers {
 
 // ---------------------------------------------------------------------------------------
 // Small-M path (SK_SCHED_GEMV, sk_gemv.cu): how the grid is cut.  kernel_kind 1: fp16 / bf16;
-// 2: W4A16 with scale groups of 128 and more (M <= 8); 3: W4A16 with groups of 32 or 64 (M <= 4).
+// 2: W4A16 with scale groups of 128 and more (M <= 16); 3: W4A16 with groups of 32 or 64 (M <= 4).
 //   fp16 / bf16: a row group is 128 weight rows; K is split across CTAs so that about four CTAs
 //     per SM are in flight, in units of 256 (one warp-wide 16-byte load per row), at most 2048
 //     per CTA (its activations sit in shared memory as fp32).
@@ -139,7 +139,7 @@ struct alignas(64) SkPeers {
 //     measured with kind 3: 10-40 % slower.)
 // ---------------------------------------------------------------------------------------
 constexpr int SK_GEMV_MAX_M = 4;      // what the kernels take ...
-constexpr int SK_GEMV_Q4_MAX_M = 8;   // ... W4A16 with scale groups of 128 and more
+constexpr int SK_GEMV_Q4_MAX_M = 16;  // ... W4A16 with scale groups of 128 and more
 constexpr int SK_GEMV_AUTO_M = 1;     // what SK_SCHED_AUTO sends there: fp16 and W4A16 with small groups ...
 constexpr int SK_GEMV_ROWS = 128;
 constexpr int SK_GEMV_Q4_WARPS = 16;  // per CTA, at most

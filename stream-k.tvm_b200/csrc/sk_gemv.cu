@@ -1,25 +1,31 @@
-// Small-M path (SK_SCHED_GEMV, M <= 4): C[M,N] = A[M,K] . W^T on the CUDA cores.
+// Small-M path (SK_SCHED_GEMV): C[M,N] = A[M,K] . W^T for a few rows of activations.
 //
-// With one to four rows of activations a weight is used M times, the product is a stream of the
-// weight matrix, and the tensor-core kernels spend more time on their fixed costs (tensor-memory
-// allocation, mbarrier rings, a cluster exchange or a workspace fix-up: 6-8 us per launch) than
-// the stream itself takes.  These kernels have none of that: a grid of several CTAs per SM, each
-// thread keeping eight 16-byte loads of weights in flight, fp32 FMAs, and a split of K whose
-// partial sums meet in the workspace and are added in split order by the last CTA of a row group
-// to arrive (a counter tells), so the result is bitwise reproducible like the block-reduce
-// fixup's.  The reference has no such path: its kernels are tiled for the tensor cores at every
-// M (streamk_fp16.py:143-371, streamk_fp16_ladder_block_reduce_q4.py:143-522).
+// With a few rows of activations a weight is used only a few times, the product is a stream of
+// the weight matrix, and the tensor-memory kernels spend more time on their fixed costs
+// (tensor-memory allocation, mbarrier rings, a cluster exchange or a workspace fix-up: 6-8 us per
+// launch) than the stream itself takes.  These kernels have none of that: many small CTAs, loads
+// kept in flight per thread or per warp, and partial sums that meet in shared memory (W4A16: the
+// K slices of a CTA's warps) or in the workspace (a split of K across CTAs, added in split order
+// by the last CTA of a row group to arrive: a counter tells), always in a fixed order, so the
+// result is bitwise reproducible like the block-reduce fixup's.  The reference has no such path:
+// its kernels are tiled for the tensor cores at every M (streamk_fp16.py:143-371,
+// streamk_fp16_ladder_block_reduce_q4.py:143-522).
 //
-// Work split: a row group is 128 weight rows; CTA (g, s) walks K range s of group g.
-//   fp16 / bf16 weights [N, K] row-major: a warp takes 16 rows, eight at a time; its 32 lanes read
-//     512 contiguous bytes of one row per instruction (8 K values each), the activations of the
+// Three kernels:
+//   fp16 / bf16 weights [N, K] row-major, M <= 4 (CUDA cores).  CTA (g, s) walks K range s of
+//     the 128 rows of group g; a warp takes 16 rows, eight at a time; its 32 lanes read 512
+//     contiguous bytes of one row per instruction (8 K values each), the activations of the
 //     lane's K values sit in registers for all eight rows, and the lanes' sums meet in a
 //     shuffle tree at the end.
-//   W4A16 packed image (sk_prepack_q4: [row block][K block] of [half][row][16 B]): a thread owns
-//     one weight row, reads its 2 x 16 bytes of a K block (a warp: 512 contiguous bytes each),
-//     turns the nibbles into fp32 (q - z) with one logic and one add each, multiplies with
-//     activations that every lane reads from the same shared-memory address, and applies the
-//     scale once per scale group.
+//   W4A16 packed image (sk_prepack_q4: [row block][K block] of [half][row][16 B]) with scale
+//     groups of 32 or 64, M <= 4 (CUDA cores).  A CTA takes 32 rows, a warp a slice of K, a
+//     thread one weight row: it reads its 2 x 16 bytes of a K block (a warp: 512 contiguous
+//     bytes each), turns the nibbles into fp16 pairs (q - z) with one logic and one arithmetic
+//     instruction per pair, multiplies with activations that every lane reads from the same
+//     shared-memory address (16 terms at a time in fp16, then fp32), and applies the scale once
+//     per scale group.
+//   W4A16 with scale groups of 128 and more, M <= 16 (register-level tensor-core instructions
+//     on nibbles read as fp16 subnormals; described at the kernel).
 #include "sk_common.cuh"
 
 namespace {
@@ -393,24 +399,25 @@ sk_gemv_q4_kernel(const uint16_t* __restrict__ A, int lda, const uint8_t* __rest
 // --------------------------------------------------------- W4A16, scale groups of 128 and more
 // The same split of the work (32 weight rows per CTA, one K slice per warp), with the products
 // on the tensor cores through register-level mma.sync (m16n8k16, fp32 accumulators): the eight
-// columns of the instruction hold the rows of activations, so up to eight cost what one costs.
+// columns of the instruction hold the rows of activations, so up to eight cost what one costs
+// (nine to sixteen: a second column tile, twice the instructions).
 //
-// No instruction is spent on turning nibbles into numbers: a nibble masked in place into bits
-// 0-3 (or 4-7) of an fp16 is the subnormal q * 2^-24 (or 16 q * 2^-24), which the tensor cores
-// multiply exactly; the two nibble positions get accumulators of their own, and a third set
-// takes the activations against a tile of ones (the sum that the zero-point multiplies).  Nothing
-// is staged: the activations come from global memory through L1 in the instruction's operand
-// layout as they are.  Scales and zero-points are applied to the accumulators once per step of
-// 128 along K, which is why the scale group must be a multiple of 128:
+// No arithmetic is spent on turning nibbles into numbers: a nibble masked into bits 0-3 of an
+// fp16 is the subnormal q * 2^-24, which the tensor cores multiply exactly; fp32 accumulators
+// take it from there, so the activations go in as they are, whatever their range.  A second
+// set of accumulators takes the activations against a tile of ones: the sum that the
+// zero-point multiplies.  Scales and zero-points are applied to the accumulators once per step
+// of 128 along K, which is why the scale group must be a multiple of 128:
 //   C[m][row] += s * (sum q a  -  z * sum a).
 //
-// Lane (g = lane / 4, t = lane % 4) reads the 16 bytes (32 values of K) of piece t of a step
-// (piece = K block t / 2, half t % 2) for weight rows g, g + 8, g + 16, g + 24 of the CTA's 32:
-// rows g, g + 8 are rows g, g + 8 of the first 16-row operand tile, the other two of the second.
-// A packed word holds 8 consecutive K values, the even ones in its low half: the mask
-// 0x000F000F leaves values 0, 1 of the eight as a pair, the same mask after a shift by 8 values
-// 4, 5, and these four are the lane's K slots of one instruction; 0x00F000F0 gives 2, 3 and
-// 6, 7 for the next.  The activations' 16 bytes for the same eight K values hold the pairs
+// Operand layout.  Lane (g = lane / 4, t = lane % 4) holds, of a step, the 16 bytes (32 values
+// of K) of piece t (piece = K block t / 2, half t % 2) for weight rows g, g + 8, g + 16, g + 24
+// of the CTA's 32: rows g, g + 8 are rows g, g + 8 of the first 16-row operand tile, the other
+// two of the second.  A packed word holds 8 consecutive K values, the even ones in its low
+// half: the mask 0x000F000F leaves values 0, 1 of the eight as a pair, the same mask after a
+// shift by 8 values 4, 5, and these four are the lane's K slots of one instruction; shifts by
+// 4 and 12 give 2, 3 and 6, 7 for the next.  The activations' 16 bytes for the same eight K
+// values (straight from global memory through L1, row g of A for the lane) hold the pairs
 // (0,1) (2,3) (4,5) (6,7): first and third word for the one, second and fourth for the other.
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -426,30 +433,42 @@ __device__ __forceinline__ uint4 ld_cached_v4(const void* p) {
   return v;
 }
 
-// What a lane holds of one step: its 16 bytes of four rows, and (lane = row of the CTA) that
-// row's scale and zero-point of the step's group.
-struct Q4mStep {
-  uint4 w[4];
-  uint16_t s;
-  uint8_t z;
-};
+// The weights reach the lanes through a ring of Q4M_DEPTH steps per warp in shared memory,
+// filled by asynchronous copies.  Two reasons: the bytes in flight cost no registers, and the
+// copies can be issued the way the memory pipeline likes them (lane = row: a warp-wide copy is
+// 512 contiguous bytes), whereas the instruction's operand layout, read from global memory
+// directly, makes every quarter-warp touch four different lines (measured: the L1 data pipe
+// at 70 % of its wavefront rate with HBM at 35 %).  A slot holds the step's four pieces of
+// 32 rows x 16 bytes, 544 bytes apart so that the four pieces a quarter-warp reads fall on
+// different banks.  The rows' scales and zero-points of the step's group travel with them (a
+// step ahead they would arrive a step late: every step of 128 has a group of its own).
+constexpr int Q4M_DEPTH = 4;
+constexpr int Q4M_PIECE = 544;
+constexpr int Q4M_SZ = 4 * Q4M_PIECE;        // then the 32 rows' scales (64 bytes) and zero-points (32) of the step's group
+constexpr int Q4M_SLOT = Q4M_SZ + 96;
 
-// sz_row: this lane's scale of group 0; its zero-point is z_off bytes further.
-__device__ __forceinline__ void q4m_load(Q4mStep& st, const uint8_t* q, const uint8_t* sz_row, int z_off, int blk) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) st.w[j] = ld_stream_v4(q + j * 128);
-  const uint8_t* b = sz_row + static_cast<size_t>(blk) * 384;
-  st.s = *reinterpret_cast<const uint16_t*>(b);
-  st.z = b[z_off];
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
 }
 
+// NT: column tiles of the instruction (8 rows of activations each): M <= 8 NT.
+template <int NT>
 __global__ void __launch_bounds__(GEMV_THREADS_Q4)
 sk_gemv_q4_mma_kernel(const uint16_t* __restrict__ A, int lda, int M, const uint8_t* __restrict__ qblocks,
                       const uint8_t* __restrict__ szblocks, uint16_t* __restrict__ C, int ldc, int N, int K,
                       int kblocks, int kb_per_split, int kb_per_slice, int S, int gshift, int q_groups,
                       float* parts, uint32_t* counters) {
-  __shared__ float red[SK_GEMV_Q4_MAX_M * GEMV_THREADS_Q4];   // [slice][m][row of the CTA]
-  __shared__ float sums[SK_GEMV_Q4_MAX_M * 32];
+  extern __shared__ __align__(16) uint8_t ring[];    // [warp][Q4M_DEPTH][Q4M_SLOT]
+  __shared__ float red[8 * NT * GEMV_THREADS_Q4];   // [slice][m][row of the CTA]
+  __shared__ float sums[8 * NT * 32];
   __shared__ uint32_t s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g8 = lane >> 2, t = lane & 3;
@@ -462,68 +481,115 @@ sk_gemv_q4_mma_kernel(const uint16_t* __restrict__ A, int lda, int M, const uint
   const int kb_lo = s * kb_per_split + warp * kb_per_slice;
   int kb_hi = kb_lo + kb_per_slice;
   if (kb_hi > kb_end) kb_hi = kb_end;
-  float acc[4][2];
+  float acc[NT][4][2];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) { acc[j][0] = 0.f; acc[j][1] = 0.f; }
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { acc[n][j][0] = 0.f; acc[n][j][1] = 0.f; }
   skptx::griddep_wait();
   if (kb_lo < kb_hi) {   // (K blocks come in pairs: K is a multiple of 128, and so is every slice)
-    const uint8_t* q = qblocks + (static_cast<size_t>(row0 >> 7) * kblocks + kb_lo + (t >> 1)) * 4096 +
-                       (t & 1) * 2048 + (rb0 + g8) * 16;
-    const uint8_t* sz_row = szblocks + static_cast<size_t>(row0 >> 7) * q_groups * 384 + (rb0 + lane) * 2;
-    const int z_off = 256 - (rb0 + lane);   // (the zero-point of row r is 256 + r bytes into the block, its scale 2 r)
-    // the activations this lane feeds: row g of A (column g of the operand; past M: the last row,
-    // into columns that nobody reads), piece t of the step
-    const uint16_t* aB = A + static_cast<size_t>(g8 < M ? g8 : M - 1) * lda + kb_lo * 64 + t * 32;
-    Q4mStep st0, st1;
-    q4m_load(st0, q, sz_row, z_off, (2 * kb_lo) >> gshift);
-    auto step = [&](const Q4mStep& st, const uint16_t* a) {
-      float lo[2][4], hi[2][4], one[4];
+    // copies: lane = row of the CTA, piece p of step i = K block 2 i + p / 2, half p % 2
+    const uint8_t* q = qblocks + (static_cast<size_t>(row0 >> 7) * kblocks + kb_lo) * 4096 + (rb0 + lane) * 16;
+    // (a group's block: 128 scales, then 128 zero-points; lanes 0-3 copy the CTA's 64 bytes of
+    // scales, lanes 4-5 its 32 bytes of zero-points)
+    const uint8_t* sz = szblocks + static_cast<size_t>(row0 >> 7) * q_groups * 384 +
+                        (lane < 4 ? rb0 * 2 + lane * 16 : 256 + rb0 + (lane - 4) * 16);
+    const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + warp * (Q4M_DEPTH * Q4M_SLOT);
+    const int nsteps = (kb_hi - kb_lo) >> 1;
+    auto issue = [&](int i) {   // step i of the slice into slot i % Q4M_DEPTH
+      const uint8_t* src = q + static_cast<size_t>(i) * (2 * 4096);
+      const uint32_t dst = ring_s + (i & (Q4M_DEPTH - 1)) * Q4M_SLOT + lane * 16;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { lo[0][e] = 0.f; lo[1][e] = 0.f; hi[0][e] = 0.f; hi[1][e] = 0.f; one[e] = 0.f; }
-      const uint32_t wj[4][4] = {{st.w[0].x, st.w[0].y, st.w[0].z, st.w[0].w}, {st.w[1].x, st.w[1].y, st.w[1].z, st.w[1].w},
-                                 {st.w[2].x, st.w[2].y, st.w[2].z, st.w[2].w}, {st.w[3].x, st.w[3].y, st.w[3].z, st.w[3].w}};
-      constexpr uint32_t ONES = 0x00010001u;   // 2^-24 twice
+      for (int p = 0; p < 4; ++p) cp_async_16(dst + p * Q4M_PIECE, src + p * 2048);
+      if (lane < 6)
+        cp_async_16(dst + Q4M_SZ, sz + static_cast<size_t>((2 * (kb_lo + 2 * i)) >> gshift) * 384);   // (dst: lane * 16 into the tail)
+    };
+#pragma unroll
+    for (int d = 0; d < Q4M_DEPTH; ++d) {
+      if (d < nsteps) issue(d);
+      cp_async_commit();
+    }
+    // the activations this lane feeds: rows g, 8 + g of A (column g of the operand's tiles; past
+    // M: the last row, into columns that nobody reads), piece t of the step
+    const uint16_t* aB[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      aB[n] = A + static_cast<size_t>(8 * n + g8 < M ? 8 * n + g8 : M - 1) * lda + kb_lo * 64 + t * 32;
+    const uint32_t frag_s = ring_s + t * Q4M_PIECE + g8 * 16;   // piece t, rows g + 8 j
+    for (int i = 0; i < nsteps; ++i) {
+      const uint32_t slot = (i & (Q4M_DEPTH - 1)) * Q4M_SLOT;
+      uint4 x[NT][4];   // the step's activations (L1: every CTA of the SM reads the same few KB)
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int cw = 0; cw < 4; ++cw) x[n][cw] = ld_cached_v4(aB[n] + i * 128 + cw * 8);
+      cp_async_wait<Q4M_DEPTH - 1>();   // all but the newest three groups: this lane's copies of step i have landed
+      __syncwarp();                     // ... and every other lane's
+      uint32_t wj[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = lds_v4(frag_s + slot + j * 128);
+        wj[j][0] = v.x; wj[j][1] = v.y; wj[j][2] = v.z; wj[j][3] = v.w;
+      }
+      // lane = row of the CTA: its scale and zero-point
+      uint16_t s_now;
+      uint32_t z_now;
+      asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s_now) : "r"(ring_s + slot + Q4M_SZ + lane * 2));
+      asm volatile("ld.shared.u8 %0, [%1];" : "=r"(z_now) : "r"(ring_s + slot + Q4M_SZ + 64 + lane));
+      __syncwarp();                     // the slot is read: refill it
+      if (i + Q4M_DEPTH < nsteps) issue(i + Q4M_DEPTH);
+      cp_async_commit();
+      float c[NT][2][4], one[NT][4];
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { c[n][0][e] = 0.f; c[n][1][e] = 0.f; one[n][e] = 0.f; }
+      constexpr uint32_t ONES = 0x00010001u, NIB = 0x000F000Fu;   // 2^-24 twice; the low nibble of each half
 #pragma unroll
       for (int cw = 0; cw < 4; ++cw) {
-        const uint4 x = ld_cached_v4(a + cw * 8);   // (L1: every CTA of the SM reads the same few KB)
 #pragma unroll
         for (int T = 0; T < 2; ++T) {
           const uint32_t wa = wj[2 * T][cw], wb = wj[2 * T + 1][cw];
-          const uint32_t wa8 = wa >> 8, wb8 = wb >> 8;
-          mma_16816(lo[T], wa & 0x000F000Fu, wb & 0x000F000Fu, wa8 & 0x000F000Fu, wb8 & 0x000F000Fu, x.x, x.z);
-          mma_16816(hi[T], wa & 0x00F000F0u, wb & 0x00F000F0u, wa8 & 0x00F000F0u, wb8 & 0x00F000F0u, x.y, x.w);
+          const uint32_t a0 = wa & NIB, a1 = wb & NIB, a2 = (wa >> 8) & NIB, a3 = (wb >> 8) & NIB;       // K values 0, 1, 4, 5
+          const uint32_t b0 = (wa >> 4) & NIB, b1 = (wb >> 4) & NIB, b2 = (wa >> 12) & NIB, b3 = (wb >> 12) & NIB;   // 2, 3, 6, 7
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            mma_16816(c[n][T], a0, a1, a2, a3, x[n][cw].x, x[n][cw].z);
+            mma_16816(c[n][T], b0, b1, b2, b3, x[n][cw].y, x[n][cw].w);
+          }
         }
-        mma_16816(one, ONES, ONES, ONES, ONES, x.x, x.z);
-        mma_16816(one, ONES, ONES, ONES, ONES, x.y, x.w);
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          mma_16816(one[n], ONES, ONES, ONES, ONES, x[n][cw].x, x[n][cw].z);
+          mma_16816(one[n], ONES, ONES, ONES, ONES, x[n][cw].y, x[n][cw].w);
+        }
       }
       // the scale and -z * scale of this lane's row (times the 2^24 of the subnormals) to the
       // lanes that hold the row's accumulators
-      const float sc = __half2float(__ushort_as_half(st.s)) * 16777216.f;
-      const float zs = -static_cast<float>(st.z) * sc;
+      const float sc = __half2float(__ushort_as_half(s_now)) * 16777216.f;
+      const float zs = -static_cast<float>(z_now) * sc;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float scj = __shfl_sync(0xffffffffu, sc, 8 * j + g8), zsj = __shfl_sync(0xffffffffu, zs, 8 * j + g8);
         const int T = j >> 1, e = (j & 1) * 2;
-        acc[j][0] = fmaf(fmaf(hi[T][e], 0.0625f, lo[T][e]), scj, fmaf(zsj, one[0], acc[j][0]));
-        acc[j][1] = fmaf(fmaf(hi[T][e + 1], 0.0625f, lo[T][e + 1]), scj, fmaf(zsj, one[1], acc[j][1]));
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          acc[n][j][0] = fmaf(c[n][T][e], scj, fmaf(zsj, one[n][0], acc[n][j][0]));
+          acc[n][j][1] = fmaf(c[n][T][e + 1], scj, fmaf(zsj, one[n][1], acc[n][j][1]));
+        }
       }
-    };
-    // Two sets of registers: the loads of one step travel while the other is multiplied.
-    for (int kb = kb_lo; kb < kb_hi; kb += 4) {
-      if (kb + 2 < kb_hi) q4m_load(st1, q + 2 * 4096, sz_row, z_off, (2 * (kb + 2)) >> gshift);
-      step(st0, aB);
-      if (kb + 2 >= kb_hi) break;
-      q += 4 * 4096;
-      if (kb + 4 < kb_hi) q4m_load(st0, q, sz_row, z_off, (2 * (kb + 4)) >> gshift);
-      step(st1, aB + 128);
-      aB += 256;
     }
+    cp_async_wait<0>();
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (2 * t < M) red[(warp * M + 2 * t) * 32 + 8 * j + g8] = acc[j][0];
-    if (2 * t + 1 < M) red[(warp * M + 2 * t + 1) * 32 + 8 * j + g8] = acc[j][1];
-  }
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = 8 * n + 2 * t + e;
+        if (m < M) red[(warp * M + m) * 32 + 8 * j + g8] = acc[n][j][e];
+      }
   skptx::griddep_launch_dependents();
   __syncthreads();
   for (int i = tid; i < M * 32; i += nthreads) {
@@ -593,9 +659,23 @@ int sk_launch_gemv_q4(const sk_problem* prob, const void* A, const void* qblocks
   uint16_t* c = static_cast<uint16_t*>(C);
   cudaError_t e = cudaSuccess;
   if (mma) {
-    e = sk_launch(sk_gemv_q4_mma_kernel, pl.grid, pl.threads, 0, cs, 1, pdl, a, prob->lda, prob->M, qb, sz, c,
-                  prob->ldc, prob->N, prob->K, kblocks, kb_per_split, kb_per_slice, pl.splits, gshift, q_groups,
-                  ws.part_slots, ws.counters);
+    const size_t smem = static_cast<size_t>(pl.slices) * Q4M_DEPTH * Q4M_SLOT;   // the rings of weights
+    const size_t smem_max = static_cast<size_t>(SK_GEMV_Q4_WARPS) * Q4M_DEPTH * Q4M_SLOT;
+    if (prob->M <= 8) {
+      if (smem > 24 * 1024)   // (the kernel has 17 KB of its own)
+        e = cudaFuncSetAttribute(sk_gemv_q4_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+      if (e == cudaSuccess)
+        e = sk_launch(sk_gemv_q4_mma_kernel<1>, pl.grid, pl.threads, smem, cs, 1, pdl, a, prob->lda, prob->M, qb, sz,
+                      c, prob->ldc, prob->N, prob->K, kblocks, kb_per_split, kb_per_slice, pl.splits, gshift,
+                      q_groups, ws.part_slots, ws.counters);
+    } else {
+      if (smem > 8 * 1024)   // (34 KB of its own)
+        e = cudaFuncSetAttribute(sk_gemv_q4_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+      if (e == cudaSuccess)
+        e = sk_launch(sk_gemv_q4_mma_kernel<2>, pl.grid, pl.threads, smem, cs, 1, pdl, a, prob->lda, prob->M, qb, sz,
+                      c, prob->ldc, prob->N, prob->K, kblocks, kb_per_split, kb_per_slice, pl.splits, gshift,
+                      q_groups, ws.part_slots, ws.counters);
+    }
     if (e != cudaSuccess) return sk_set_cuda_error(e);
     return SK_OK;
   }

@@ -150,7 +150,7 @@ def test_auto_schedule_resolution(lib):
     names = {v: k for k, v in L.SCHEDULES.items()}
     d = plan(16, 4096, 4096)          # 32 swapped tiles: every SM has to stream; clusters of 4
     assert (names[d["schedule"]], d["swap_ab"], d["cluster"], d["grid"]) == ("cluster", 1, 4, 128)
-    d = plan(16, 4096, 4096, kind=2)  # the W4A16 kernel alike
+    d = plan(24, 4096, 4096, kind=2)  # the W4A16 kernel alike (beyond the small-M path's 16 rows)
     assert (names[d["schedule"]], d["swap_ab"], d["cluster"]) == ("cluster", 1, 4)
     d = plan(16, 4096, 256)           # shallow K: nothing to split
     assert names[d["schedule"]] == "streamk"
@@ -187,8 +187,12 @@ def test_auto_schedule_resolution(lib):
         d = plan(M, 11008, 4096, kind=2)
         assert (names[d["schedule"]], d["tile_m"], d["tile_n"], d["tiles_n"], d["iters_per_tile"], d["tile_k"],
                 d["grid"]) == ("gemv", M, 32, 344, 1, 4096, 344)
-    d = plan(9, 11008, 4096, kind=2)
+    d = plan(9, 11008, 4096, kind=2)          # 9 to 16 rows: only up to one CTA per SM
     assert names[d["schedule"]] != "gemv"
+    d = plan(16, 4096, 4096, kind=2)
+    assert (names[d["schedule"]], d["tile_m"], d["grid"]) == ("gemv", 16, 128)
+    d = plan(17, 4096, 4096, kind=2)
+    assert names[d["schedule"]] == "cluster"
     d = plan(4, 1024, 8192, kind=2)          # too few rows for half of the SMs: K split over 4 CTAs as well
     assert (names[d["schedule"]], d["tiles_n"], d["iters_per_tile"], d["tile_k"], d["grid"]) == ("gemv", 32, 4, 2048, 128)
     # scale groups of 32 or 64: the CUDA-core kernel, chosen at M = 1 and taken up to M = 4
@@ -202,12 +206,14 @@ def test_auto_schedule_resolution(lib):
     assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0 and info.grid == 344
     prob = L.SkProblem(M=5, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1, flags=g64)
     assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == L.SK_ERR_SHAPE
-    # ... which an explicit request may still take up to M = 4 (fp16) or 8 (W4A16, groups of 128)
+    # ... which an explicit request may still take up to M = 4 (fp16) or 16 (W4A16, groups of 128)
     prob = L.SkProblem(M=4, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0 and info.grid == 516
     prob = L.SkProblem(M=5, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == L.SK_ERR_SHAPE
-    prob = L.SkProblem(M=9, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
+    prob = L.SkProblem(M=16, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
+    assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == 0
+    prob = L.SkProblem(M=17, N=11008, K=4096, schedule=L.SCHEDULES["gemv"], layout=1)
     assert lib.sk_schedule(C.byref(prob), 2, 148, C.byref(info)) == L.SK_ERR_SHAPE
     cov = oracle.coverage(plan(300, 5000, 1000))
     assert set(cov.values()) == {1}
