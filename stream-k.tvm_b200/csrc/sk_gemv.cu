@@ -466,13 +466,13 @@ sk_gemv_q4_mma_kernel(const uint16_t* __restrict__ A, int lda, int M, const uint
                       const uint8_t* __restrict__ szblocks, uint16_t* __restrict__ C, int ldc, int N, int K,
                       int kblocks, int kb_per_split, int kb_per_slice, int S, int gshift, int q_groups,
                       float* parts, uint32_t* counters) {
-  extern __shared__ __align__(16) uint8_t ring[];    // [warp][Q4M_DEPTH][Q4M_SLOT]
-  __shared__ float red[8 * NT * GEMV_THREADS_Q4];   // [slice][m][row of the CTA]
-  __shared__ float sums[8 * NT * 32];
+  extern __shared__ __align__(16) uint8_t ring[];    // [warp][Q4M_DEPTH][Q4M_SLOT], then red and sums
   __shared__ uint32_t s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g8 = lane >> 2, t = lane & 3;
   const int nthreads = blockDim.x, slices = nthreads >> 5;
+  float* red = reinterpret_cast<float*>(ring + slices * (Q4M_DEPTH * Q4M_SLOT));   // [slice][m][row of the CTA]
+  float* sums = red + slices * M * 32;                                             // [m][row]
   const int g = blockIdx.x / S, s = blockIdx.x - g * S;
   const int row0 = g * 32;                              // first weight row of the CTA
   const int rb0 = row0 & 127;                           // ... inside its 128-row block
@@ -659,17 +659,20 @@ int sk_launch_gemv_q4(const sk_problem* prob, const void* A, const void* qblocks
   uint16_t* c = static_cast<uint16_t*>(C);
   cudaError_t e = cudaSuccess;
   if (mma) {
-    const size_t smem = static_cast<size_t>(pl.slices) * Q4M_DEPTH * Q4M_SLOT;   // the rings of weights
-    const size_t smem_max = static_cast<size_t>(SK_GEMV_Q4_WARPS) * Q4M_DEPTH * Q4M_SLOT;
+    // the rings of weights, then the slices' sums [slice][M][32] and their total [M][32]
+    const size_t smem = static_cast<size_t>(pl.slices) * Q4M_DEPTH * Q4M_SLOT +
+                        static_cast<size_t>(pl.slices + 1) * prob->M * 32 * sizeof(float);
+    const size_t smem_max = static_cast<size_t>(SK_GEMV_Q4_WARPS) * Q4M_DEPTH * Q4M_SLOT +
+                            static_cast<size_t>(SK_GEMV_Q4_WARPS + 1) * SK_GEMV_Q4_MAX_M * 32 * sizeof(float);
     if (prob->M <= 8) {
-      if (smem > 24 * 1024)   // (the kernel has 17 KB of its own)
+      if (smem > 40 * 1024)
         e = cudaFuncSetAttribute(sk_gemv_q4_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
       if (e == cudaSuccess)
         e = sk_launch(sk_gemv_q4_mma_kernel<1>, pl.grid, pl.threads, smem, cs, 1, pdl, a, prob->lda, prob->M, qb, sz,
                       c, prob->ldc, prob->N, prob->K, kblocks, kb_per_split, kb_per_slice, pl.splits, gshift,
                       q_groups, ws.part_slots, ws.counters);
     } else {
-      if (smem > 8 * 1024)   // (34 KB of its own)
+      if (smem > 40 * 1024)
         e = cudaFuncSetAttribute(sk_gemv_q4_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
       if (e == cudaSuccess)
         e = sk_launch(sk_gemv_q4_mma_kernel<2>, pl.grid, pl.threads, smem, cs, 1, pdl, a, prob->lda, prob->M, qb, sz,
