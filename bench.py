@@ -583,7 +583,7 @@ def run_tune(path: str, peaks: dict) -> None:
     def candidates_q4(M, N, K):
         c = [dict(schedule="streamk"), dict(schedule="hybrid"), dict(schedule="dp"),
              dict(schedule="streamk", fixup="atomic")]
-        if M <= 4:
+        if M <= 16:
             c.append(dict(schedule="gemv"))
         # narrower tiles along M: more tiles (more CTAs streaming, cluster split-K within reach) for
         # the price of dequantising every weight once per tile column
