@@ -132,8 +132,10 @@ struct alignas(64) SkPeers {
 //     per CTA (its activations sit in shared memory as fp32).
 //   W4A16: a CTA takes 32 weight rows over all of K and cuts K into `slices` of whole steps
 //     (128 of K), one per warp, whose sums meet in shared memory: 16 warps when there is at
-//     most one CTA per SM, else 4 (kind 2) or 8 (kind 3) (measured, 11008 x 4096: kind 2 11.2 us
-//     with 4 warps, 13.7 with 8, 14.5 with 16; kind 3 13.1 / 10.4 / 11.6).  Only a matrix with too
+//     most one CTA per SM, else 8, or 4 for kind 2 with more than one row of activations
+//     (measured, kind 2, 4 / 8 / 16 warps: 1 x 11008 x 4096 11.3 / 11.3 / 13.9 us, 1 x 32000 x 4096
+//     24.9 / 21.2 / 30.8, 8 x 11008 x 4096 12.3 / 15.0 / 15.0, 4 x 14336 x 4096 13.6 / 15.5 / 18.2;
+//     kind 3, 1 x 11008 x 4096: 13.1 / 10.4 / 11.6).  Only a matrix with too
 //     few rows for half of the SMs is also split across CTAs (`splits`), in pieces of at
 //     least 512 of K.  (More rows per CTA with fewer slices each, 64 to 256 rows, were
 //     measured with kind 3: 10-40 % slower.)
@@ -155,7 +157,7 @@ inline bool sk_gemv_plan(int kernel_kind, int M, int N, int K, int num_sms, SkGe
     const long long groups = (static_cast<long long>(N) + 31) / 32;
     if (groups > 0x7fffffffLL / 64) return false;
     const int kblocks = (K + 63) / 64;
-    const int slices0 = groups <= num_sms ? SK_GEMV_Q4_WARPS : (kernel_kind == 2 ? 4 : 8);
+    const int slices0 = groups <= num_sms ? SK_GEMV_Q4_WARPS : (kernel_kind == 2 && M > 1 ? 4 : 8);
     int splits = 1;
     if (2 * groups <= num_sms) {
       splits = static_cast<int>(num_sms / groups);
