@@ -459,7 +459,111 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
   return v;
 }
 
+// One warp, 32 weight rows from row0 on, `nsteps` steps of 128 along K from K block kb_lo on:
+// acc[n][j][e] += the products of row row0 + 8 j + lane / 4 with row 8 n + 2 (lane % 4) + e of
+// the activations.  ring_s: the warp's ring (shared-memory address); on return it is free again.
 // NT: column tiles of the instruction (8 rows of activations each): M <= 8 NT.
+template <int NT>
+__device__ __forceinline__ void q4m_segment(float (&acc)[NT][4][2], const uint16_t* __restrict__ A, int lda, int M,
+                                            const uint8_t* __restrict__ qblocks, const uint8_t* __restrict__ szblocks,
+                                            int kblocks, int gshift, int q_groups, int row0, int kb_lo, int nsteps,
+                                            uint32_t ring_s, int lane) {
+  const int g8 = lane >> 2, t = lane & 3;
+  const int rb0 = row0 & 127;                           // first row inside its 128-row block
+  // copies: lane = row, piece p of step i = K block 2 i + p / 2, half p % 2
+  const uint8_t* q = qblocks + (static_cast<size_t>(row0 >> 7) * kblocks + kb_lo) * 4096 + (rb0 + lane) * 16;
+  // (a group's block: 128 scales, then 128 zero-points; lanes 0-3 copy the 32 rows' 64 bytes of
+  // scales, lanes 4-5 their 32 bytes of zero-points)
+  const uint8_t* sz = szblocks + static_cast<size_t>(row0 >> 7) * q_groups * 384 +
+                      (lane < 4 ? rb0 * 2 + lane * 16 : 256 + rb0 + (lane - 4) * 16);
+  auto issue = [&](int i) {   // step i of the segment into slot i % Q4M_DEPTH
+    const uint8_t* src = q + static_cast<size_t>(i) * (2 * 4096);
+    const uint32_t dst = ring_s + (i & (Q4M_DEPTH - 1)) * Q4M_SLOT + lane * 16;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) cp_async_16(dst + p * Q4M_PIECE, src + p * 2048);
+    if (lane < 6)
+      cp_async_16(dst + Q4M_SZ, sz + static_cast<size_t>((2 * (kb_lo + 2 * i)) >> gshift) * 384);   // (dst: lane * 16 into the tail)
+  };
+#pragma unroll
+  for (int d = 0; d < Q4M_DEPTH; ++d) {
+    if (d < nsteps) issue(d);
+    cp_async_commit();
+  }
+  // the activations this lane feeds: rows g, 8 + g of A (column g of the operand's tiles; past
+  // M: the last row, into columns that nobody reads), piece t of the step
+  const uint16_t* aB[NT];
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+    aB[n] = A + static_cast<size_t>(8 * n + g8 < M ? 8 * n + g8 : M - 1) * lda + kb_lo * 64 + t * 32;
+  const uint32_t frag_s = ring_s + t * Q4M_PIECE + g8 * 16;   // piece t, rows g + 8 j
+  for (int i = 0; i < nsteps; ++i) {
+    const uint32_t slot = (i & (Q4M_DEPTH - 1)) * Q4M_SLOT;
+    uint4 x[NT][4];   // the step's activations (L1: every CTA of the SM reads the same few KB)
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int cw = 0; cw < 4; ++cw) x[n][cw] = ld_cached_v4(aB[n] + i * 128 + cw * 8);
+    cp_async_wait<Q4M_DEPTH - 1>();   // all but the newest three groups: this lane's copies of step i have landed
+    __syncwarp();                     // ... and every other lane's
+    uint32_t wj[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v = lds_v4(frag_s + slot + j * 128);
+      wj[j][0] = v.x; wj[j][1] = v.y; wj[j][2] = v.z; wj[j][3] = v.w;
+    }
+    // lane = row: its scale and zero-point
+    uint16_t s_now;
+    uint32_t z_now;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s_now) : "r"(ring_s + slot + Q4M_SZ + lane * 2));
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(z_now) : "r"(ring_s + slot + Q4M_SZ + 64 + lane));
+    __syncwarp();                     // the slot is read: refill it
+    if (i + Q4M_DEPTH < nsteps) issue(i + Q4M_DEPTH);
+    cp_async_commit();
+    float c[NT][2][4], one[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { c[n][0][e] = 0.f; c[n][1][e] = 0.f; one[n][e] = 0.f; }
+    constexpr uint32_t ONES = 0x00010001u, NIB = 0x000F000Fu;   // 2^-24 twice; the low nibble of each half
+#pragma unroll
+    for (int cw = 0; cw < 4; ++cw) {
+#pragma unroll
+      for (int T = 0; T < 2; ++T) {
+        const uint32_t wa = wj[2 * T][cw], wb = wj[2 * T + 1][cw];
+        const uint32_t a0 = wa & NIB, a1 = wb & NIB, a2 = (wa >> 8) & NIB, a3 = (wb >> 8) & NIB;       // K values 0, 1, 4, 5
+        const uint32_t b0 = (wa >> 4) & NIB, b1 = (wb >> 4) & NIB, b2 = (wa >> 12) & NIB, b3 = (wb >> 12) & NIB;   // 2, 3, 6, 7
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          mma_16816(c[n][T], a0, a1, a2, a3, x[n][cw].x, x[n][cw].z);
+          mma_16816(c[n][T], b0, b1, b2, b3, x[n][cw].y, x[n][cw].w);
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        mma_16816(one[n], ONES, ONES, ONES, ONES, x[n][cw].x, x[n][cw].z);
+        mma_16816(one[n], ONES, ONES, ONES, ONES, x[n][cw].y, x[n][cw].w);
+      }
+    }
+    // the scale and -z * scale of this lane's row (times the 2^24 of the subnormals) to the
+    // lanes that hold the row's accumulators
+    const float sc = __half2float(__ushort_as_half(s_now)) * 16777216.f;
+    const float zs = -static_cast<float>(z_now) * sc;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float scj = __shfl_sync(0xffffffffu, sc, 8 * j + g8), zsj = __shfl_sync(0xffffffffu, zs, 8 * j + g8);
+      const int T = j >> 1, e = (j & 1) * 2;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        acc[n][j][0] = fmaf(c[n][T][e], scj, fmaf(zsj, one[n][0], acc[n][j][0]));
+        acc[n][j][1] = fmaf(c[n][T][e + 1], scj, fmaf(zsj, one[n][1], acc[n][j][1]));
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncwarp();
+}
+
+// CTA (g, s): 32 weight rows, one K slice per warp (the split of the CUDA-core W4A16 kernel).
 template <int NT>
 __global__ void __launch_bounds__(GEMV_THREADS_Q4)
 sk_gemv_q4_mma_kernel(const uint16_t* __restrict__ A, int lda, int M, const uint8_t* __restrict__ qblocks,
@@ -474,8 +578,6 @@ sk_gemv_q4_mma_kernel(const uint16_t* __restrict__ A, int lda, int M, const uint
   float* red = reinterpret_cast<float*>(ring + slices * (Q4M_DEPTH * Q4M_SLOT));   // [slice][m][row of the CTA]
   float* sums = red + slices * M * 32;                                             // [m][row]
   const int g = blockIdx.x / S, s = blockIdx.x - g * S;
-  const int row0 = g * 32;                              // first weight row of the CTA
-  const int rb0 = row0 & 127;                           // ... inside its 128-row block
   int kb_end = (s + 1) * kb_per_split;
   if (kb_end > kblocks) kb_end = kblocks;
   const int kb_lo = s * kb_per_split + warp * kb_per_slice;
@@ -487,100 +589,9 @@ sk_gemv_q4_mma_kernel(const uint16_t* __restrict__ A, int lda, int M, const uint
 #pragma unroll
     for (int j = 0; j < 4; ++j) { acc[n][j][0] = 0.f; acc[n][j][1] = 0.f; }
   skptx::griddep_wait();
-  if (kb_lo < kb_hi) {   // (K blocks come in pairs: K is a multiple of 128, and so is every slice)
-    // copies: lane = row of the CTA, piece p of step i = K block 2 i + p / 2, half p % 2
-    const uint8_t* q = qblocks + (static_cast<size_t>(row0 >> 7) * kblocks + kb_lo) * 4096 + (rb0 + lane) * 16;
-    // (a group's block: 128 scales, then 128 zero-points; lanes 0-3 copy the CTA's 64 bytes of
-    // scales, lanes 4-5 its 32 bytes of zero-points)
-    const uint8_t* sz = szblocks + static_cast<size_t>(row0 >> 7) * q_groups * 384 +
-                        (lane < 4 ? rb0 * 2 + lane * 16 : 256 + rb0 + (lane - 4) * 16);
-    const uint32_t ring_s = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + warp * (Q4M_DEPTH * Q4M_SLOT);
-    const int nsteps = (kb_hi - kb_lo) >> 1;
-    auto issue = [&](int i) {   // step i of the slice into slot i % Q4M_DEPTH
-      const uint8_t* src = q + static_cast<size_t>(i) * (2 * 4096);
-      const uint32_t dst = ring_s + (i & (Q4M_DEPTH - 1)) * Q4M_SLOT + lane * 16;
-#pragma unroll
-      for (int p = 0; p < 4; ++p) cp_async_16(dst + p * Q4M_PIECE, src + p * 2048);
-      if (lane < 6)
-        cp_async_16(dst + Q4M_SZ, sz + static_cast<size_t>((2 * (kb_lo + 2 * i)) >> gshift) * 384);   // (dst: lane * 16 into the tail)
-    };
-#pragma unroll
-    for (int d = 0; d < Q4M_DEPTH; ++d) {
-      if (d < nsteps) issue(d);
-      cp_async_commit();
-    }
-    // the activations this lane feeds: rows g, 8 + g of A (column g of the operand's tiles; past
-    // M: the last row, into columns that nobody reads), piece t of the step
-    const uint16_t* aB[NT];
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-      aB[n] = A + static_cast<size_t>(8 * n + g8 < M ? 8 * n + g8 : M - 1) * lda + kb_lo * 64 + t * 32;
-    const uint32_t frag_s = ring_s + t * Q4M_PIECE + g8 * 16;   // piece t, rows g + 8 j
-    for (int i = 0; i < nsteps; ++i) {
-      const uint32_t slot = (i & (Q4M_DEPTH - 1)) * Q4M_SLOT;
-      uint4 x[NT][4];   // the step's activations (L1: every CTA of the SM reads the same few KB)
-#pragma unroll
-      for (int n = 0; n < NT; ++n)
-#pragma unroll
-        for (int cw = 0; cw < 4; ++cw) x[n][cw] = ld_cached_v4(aB[n] + i * 128 + cw * 8);
-      cp_async_wait<Q4M_DEPTH - 1>();   // all but the newest three groups: this lane's copies of step i have landed
-      __syncwarp();                     // ... and every other lane's
-      uint32_t wj[4][4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 v = lds_v4(frag_s + slot + j * 128);
-        wj[j][0] = v.x; wj[j][1] = v.y; wj[j][2] = v.z; wj[j][3] = v.w;
-      }
-      // lane = row of the CTA: its scale and zero-point
-      uint16_t s_now;
-      uint32_t z_now;
-      asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s_now) : "r"(ring_s + slot + Q4M_SZ + lane * 2));
-      asm volatile("ld.shared.u8 %0, [%1];" : "=r"(z_now) : "r"(ring_s + slot + Q4M_SZ + 64 + lane));
-      __syncwarp();                     // the slot is read: refill it
-      if (i + Q4M_DEPTH < nsteps) issue(i + Q4M_DEPTH);
-      cp_async_commit();
-      float c[NT][2][4], one[NT][4];
-#pragma unroll
-      for (int n = 0; n < NT; ++n)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { c[n][0][e] = 0.f; c[n][1][e] = 0.f; one[n][e] = 0.f; }
-      constexpr uint32_t ONES = 0x00010001u, NIB = 0x000F000Fu;   // 2^-24 twice; the low nibble of each half
-#pragma unroll
-      for (int cw = 0; cw < 4; ++cw) {
-#pragma unroll
-        for (int T = 0; T < 2; ++T) {
-          const uint32_t wa = wj[2 * T][cw], wb = wj[2 * T + 1][cw];
-          const uint32_t a0 = wa & NIB, a1 = wb & NIB, a2 = (wa >> 8) & NIB, a3 = (wb >> 8) & NIB;       // K values 0, 1, 4, 5
-          const uint32_t b0 = (wa >> 4) & NIB, b1 = (wb >> 4) & NIB, b2 = (wa >> 12) & NIB, b3 = (wb >> 12) & NIB;   // 2, 3, 6, 7
-#pragma unroll
-          for (int n = 0; n < NT; ++n) {
-            mma_16816(c[n][T], a0, a1, a2, a3, x[n][cw].x, x[n][cw].z);
-            mma_16816(c[n][T], b0, b1, b2, b3, x[n][cw].y, x[n][cw].w);
-          }
-        }
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          mma_16816(one[n], ONES, ONES, ONES, ONES, x[n][cw].x, x[n][cw].z);
-          mma_16816(one[n], ONES, ONES, ONES, ONES, x[n][cw].y, x[n][cw].w);
-        }
-      }
-      // the scale and -z * scale of this lane's row (times the 2^24 of the subnormals) to the
-      // lanes that hold the row's accumulators
-      const float sc = __half2float(__ushort_as_half(s_now)) * 16777216.f;
-      const float zs = -static_cast<float>(z_now) * sc;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float scj = __shfl_sync(0xffffffffu, sc, 8 * j + g8), zsj = __shfl_sync(0xffffffffu, zs, 8 * j + g8);
-        const int T = j >> 1, e = (j & 1) * 2;
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          acc[n][j][0] = fmaf(c[n][T][e], scj, fmaf(zsj, one[n][0], acc[n][j][0]));
-          acc[n][j][1] = fmaf(c[n][T][e + 1], scj, fmaf(zsj, one[n][1], acc[n][j][1]));
-        }
-      }
-    }
-    cp_async_wait<0>();
-  }
+  if (kb_lo < kb_hi)   // (K blocks come in pairs: K is a multiple of 128, and so is every slice)
+    q4m_segment<NT>(acc, A, lda, M, qblocks, szblocks, kblocks, gshift, q_groups, g * 32, kb_lo, (kb_hi - kb_lo) >> 1,
+                    static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + warp * (Q4M_DEPTH * Q4M_SLOT), lane);
 #pragma unroll
   for (int n = 0; n < NT; ++n)
 #pragma unroll
