@@ -359,3 +359,33 @@ def test_tuned_table_is_consulted_first(lib):
     prob.flags = L.SK_FLAG_NO_TABLE
     assert lib.sk_schedule(C.byref(prob), 1, 148, C.byref(info)) == 0
     assert info.as_dict() == a
+
+
+def test_small_m_plans_cover_the_matrix(lib):
+    """SK_SCHED_GEMV: whatever the shape, the grid covers every weight row and all of K exactly once."""
+    from streamk_b200 import _lib as L
+    rnd = random.Random(23)
+    for _ in range(300):
+        kind = rnd.choice([1, 2])
+        flags = rnd.choice([0, 0, 0x100, 0x200, 0x300]) if kind == 2 else 0
+        small_groups = flags in (0x100, 0x200)
+        M = rnd.randint(1, 4 if (kind == 1 or small_groups) else 16)
+        N = rnd.choice([1, 31, 32, 33, 127, 128, 129, rnd.randint(1, 40000)])
+        K = 128 * rnd.randint(1, 200) if kind == 2 else 8 * rnd.randint(1, 4000)
+        prob = L.SkProblem(M=M, N=N, K=K, lda=K, ldb=K, ldc=N, layout=1, schedule=L.SCHEDULES["gemv"], flags=flags)
+        info = L.SkScheduleInfo()
+        st = lib.sk_schedule(C.byref(prob), kind, 148, C.byref(info))
+        d = info.as_dict()
+        assert st == 0, (kind, M, N, K, flags, st)
+        rows = 128 if kind == 1 else 32
+        assert d["tile_m"] == M and d["tile_n"] == rows
+        assert d["tiles_n"] == (N + rows - 1) // rows                    # row groups
+        assert d["grid"] == d["tiles_n"] * d["iters_per_tile"]           # x splits of K
+        assert d["tile_k"] * d["iters_per_tile"] >= K                    # the splits reach the end of K ...
+        assert d["tile_k"] * (d["iters_per_tile"] - 1) < K               # ... and none is empty
+        if kind == 2:
+            assert d["tile_k"] % 128 == 0                                # whole steps of the kernels
+    # beyond the kernels' rows of activations: refused, nothing planned
+    for kind, M, flags in ((1, 5, 0), (2, 17, 0), (2, 5, 0x100)):
+        prob = L.SkProblem(M=M, N=4096, K=4096, lda=4096, ldb=4096, ldc=4096, layout=1, schedule=L.SCHEDULES["gemv"], flags=flags)
+        assert lib.sk_schedule(C.byref(prob), kind, 148, C.byref(L.SkScheduleInfo())) == L.SK_ERR_SHAPE
