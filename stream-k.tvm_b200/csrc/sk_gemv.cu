@@ -129,7 +129,7 @@ __device__ __forceinline__ void finish_group(const float* sums /* shared: [M][ro
 
 // ------------------------------------------------------------------------------------- fp16
 template <int M, bool BF16>
-__global__ void __launch_bounds__(GEMV_THREADS_F16)
+__global__ void __launch_bounds__(GEMV_THREADS_F16, M == 1 ? 4 : 1)
 sk_gemv_f16_kernel(const uint16_t* __restrict__ A, int lda, const uint16_t* __restrict__ B, int ldb,
                    uint16_t* __restrict__ C, int ldc, int N, int K, int k_per_split, int S, float* parts,
                    uint32_t* counters) {
@@ -139,11 +139,23 @@ sk_gemv_f16_kernel(const uint16_t* __restrict__ A, int lda, const uint16_t* __re
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = blockIdx.x / S, s = blockIdx.x - g * S;
   const int k_lo = s * k_per_split;
-  skptx::griddep_wait();
-  stage_activations<M, BF16>(sA, A, lda, K, k_lo, k_per_split, tid, GEMV_THREADS_F16);
-  __syncthreads();
   int k_hi = k_lo + k_per_split;
   if (k_hi > K) k_hi = K;
+  uint4 w[8];
+  auto load = [&](int r0, int k) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      // (rows past N repeat the last row: loaded, never stored)
+      const int r = r0 + j < N ? r0 + j : N - 1;
+      w[j] = ld_stream_v4(B + static_cast<size_t>(r) * ldb + k);
+    }
+  };
+  skptx::griddep_wait();
+  // the first eight loads travel while the activations are staged
+  const bool first = k_lo + lane * 8 < k_hi;
+  if (first) load(g * SK_GEMV_ROWS + warp * 16, k_lo + lane * 8);
+  stage_activations<M, BF16>(sA, A, lda, K, k_lo, k_per_split, tid, GEMV_THREADS_F16);
+  __syncthreads();
 #pragma unroll 1
   for (int batch = 0; batch < 2; ++batch) {
     const int r0 = g * SK_GEMV_ROWS + warp * 16 + batch * 8;
@@ -153,13 +165,7 @@ sk_gemv_f16_kernel(const uint16_t* __restrict__ A, int lda, const uint16_t* __re
 #pragma unroll
       for (int m = 0; m < M; ++m) acc[j][m] = 0.f;
     for (int k = k_lo + lane * 8; k < k_hi; k += 256) {
-      uint4 w[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // (rows past N repeat the last row: loaded, never stored)
-        const int r = r0 + j < N ? r0 + j : N - 1;
-        w[j] = ld_stream_v4(B + static_cast<size_t>(r) * ldb + k);
-      }
+      if (batch != 0 || k != k_lo + lane * 8) load(r0, k);
       float a[M][8];
 #pragma unroll
       for (int m = 0; m < M; ++m) {
