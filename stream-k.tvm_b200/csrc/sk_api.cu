@@ -204,9 +204,9 @@ void sk_resolve_auto(sk_problem* q, int kernel_kind, int num_sms) {
     // workspace fix-up).  W4A16 with scale groups of 128 and more, whose small-M kernel takes
     // eight rows for the price of one (measured L2-cold at 4096 x 4096, 11008 x 4096,
     // 4096 x 11008: M = 1 5.9 / 11.2 / 11.3 us, M = 8 6.2 / 12.0 / 13.0, against 10.6 / 16.1 /
-    // 17.3 for the best tensor-memory kernel at either M): up to M = 8.  fp16 (10.3 against
-    // 11.1 us at 1 x 4096 x 4096, level elsewhere) and W4A16 with smaller groups (CUDA-core
-    // kernels whose time grows with M: behind from M = 2): a single row.
+    // 17.3 for the best tensor-memory kernel at either M): up to M = 8.  fp16 (9.7 / 17.3 / 17.7
+    // against 11.1 / 19.1 / 19.3 us at M = 1) and W4A16 with smaller groups (CUDA-core kernels
+    // whose time grows with M: behind from M = 2): a single row.
     SkGemvPlan pl;
     if (sk_gemv_plan(gemv_kind, q->M, q->N, q->K, num_sms, &pl)) {
       q->schedule = SK_SCHED_GEMV;
