@@ -172,3 +172,37 @@ def test_workspace_is_left_clean_for_the_other_fixups():
             C = sk.streamk_fp16_nt(A2, B2, schedule="streamk", fixup=fixup, tile_n=128)
             sk.check_status()
             assert oracle.rel_err(C, ref2) <= TOL16
+
+
+def test_w4a16_small_m_random_shapes():
+    """Random M, N, K, group size, now and then strided activations and PDL: within tolerance of the oracle,
+    finite, and the same bits on a second launch."""
+    import random
+    rnd = random.Random(7)
+    for it in range(24):
+        group = rnd.choice([128, 128, 128, 0, 32, 64])
+        M = rnd.randint(1, 16 if group in (128, 0) else 4)
+        K = 128 * rnd.randint(1, 40)
+        if group == 0 and K == 128:
+            K = 256
+        N = rnd.choice([rnd.randint(1, 300), rnd.randint(300, 6000), rnd.randint(4000, 9000)])
+        while N * K > 6_000_000:
+            N //= 2
+        g = torch.Generator().manual_seed(it)
+        A = torch.randn(M, K, generator=g).half()
+        G = K // group if group else 1
+        q = torch.randint(0, 16, (N, K), generator=g, dtype=torch.uint8)
+        z = torch.randint(0, 16, (N, G), generator=g, dtype=torch.uint8)
+        s = (0.002 + 0.018 * torch.rand(N, G, generator=g)).half()
+        ref = oracle.gemm_ref(A, oracle.dequant_ref(q, s, z, group=group if group else K), "nt")
+        P = sk.q4_prepack(oracle.pack_u4_int32(q).to(DEV), s.to(DEV), z.to(DEV), group_size=group)
+        Ad = A.to(DEV)
+        if it % 5 == 0:                                            # a view into a wider matrix
+            wide = torch.zeros(M, K + 64, dtype=torch.float16, device=DEV)
+            wide[:, :K] = Ad
+            Ad = wide[:, :K]
+        C = sk.streamk_fp16_ladder_block_reduce_q4(Ad, P, schedule="gemv", pdl=(it % 3 == 0))
+        sk.check_status()
+        assert bool(torch.isfinite(C).all()), (M, N, K, group)
+        assert oracle.rel_err(C, ref) <= TOL16, (M, N, K, group)
+        assert torch.equal(sk.streamk_fp16_ladder_block_reduce_q4(Ad, P, schedule="gemv"), C), (M, N, K, group)
